@@ -1,0 +1,759 @@
+// Memory-bound kernels (K4, K5, K13, K14 and the softmax half of K6).  Every kernel moves
+// 16-byte vectors where the layout allows it and does its arithmetic in fp32.
+#include "host_utils.h"
+#include "sm100_common.cuh"
+
+namespace ob {
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = 0.f;
+  for (int i = 0; i < nw; ++i) r += red[i];
+  return r;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = -INFINITY;
+  for (int i = 0; i < nw; ++i) r = fmaxf(r, red[i]);
+  return r;
+}
+
+// ------------------------------------------------------------------ RMSNorm (K4)
+// y = x * rsqrt(mean(x^2) + eps) * (w or 1+w).  One CTA per row, D % 8 == 0.
+template <bool kOnePlus>
+__global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                   bf16* __restrict__ y, float* __restrict__ rstd_out, int D,
+                                   float eps) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+  const int nv = D >> 3;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    uint4 q = xr[i];
+    uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = unpack_bf16(u[j]);
+      ss += f.x * f.x + f.y * f.y;
+    }
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / (float)D + eps);
+  if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * D);
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    uint4 q = xr[i], ww = wr[i], o;
+    uint32_t u[4] = {q.x, q.y, q.z, q.w}, wu[4] = {ww.x, ww.y, ww.z, ww.w}, ou[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = unpack_bf16(u[j]), g = unpack_bf16(wu[j]);
+      if (kOnePlus) { g.x += 1.f; g.y += 1.f; }
+      ou[j] = pack_bf16(f.x * rstd * g.x, f.y * rstd * g.y);
+    }
+    o.x = ou[0]; o.y = ou[1]; o.z = ou[2]; o.w = ou[3];
+    yr[i] = o;
+  }
+}
+
+// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x));  dw += sum_rows dy * x * rstd.
+// Each CTA walks rows blockIdx.x, +gridDim.x, ... and keeps its dw partial in registers
+// (D <= blockDim.x * 8 * kMaxVec); one fp32 atomic per column per CTA at the end.
+template <bool kOnePlus, int kMaxVec>
+__global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                   const bf16* __restrict__ w, const float* __restrict__ rstd_in,
+                                   bf16* __restrict__ dx, float* __restrict__ dw, int M, int D,
+                                   float eps) {
+  __shared__ float red[32];
+  const int nv = D >> 3;
+  float dwacc[kMaxVec][8];
+#pragma unroll
+  for (int a = 0; a < kMaxVec; ++a)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[a][j] = 0.f;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  for (long long row = blockIdx.x; row < M; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + row * D);
+    float rstd;
+    if (rstd_in) {
+      rstd = rstd_in[row];
+    } else {
+      float ss = 0.f;
+      for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        uint4 q = xr[i];
+        uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = unpack_bf16(u[j]);
+          ss += f.x * f.x + f.y * f.y;
+        }
+      }
+      ss = block_sum(ss, red);
+      rstd = rsqrtf(ss / (float)D + eps);
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int a = 0; a < kMaxVec; ++a) {
+      int i = threadIdx.x + a * blockDim.x;
+      if (i < nv) {
+        uint4 q = xr[i], g = gr[i], ww = wr[i];
+        uint32_t u[4] = {q.x, q.y, q.z, q.w}, gu[4] = {g.x, g.y, g.z, g.w},
+                 wu[4] = {ww.x, ww.y, ww.z, ww.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 xf = unpack_bf16(u[j]), gf = unpack_bf16(gu[j]), wf = unpack_bf16(wu[j]);
+          if (kOnePlus) { wf.x += 1.f; wf.y += 1.f; }
+          dot += gf.x * wf.x * xf.x + gf.y * wf.y * xf.y;
+          dwacc[a][2 * j] += gf.x * xf.x * rstd;
+          dwacc[a][2 * j + 1] += gf.y * xf.y * rstd;
+        }
+      }
+    }
+    dot = block_sum(dot, red);
+    const float c = dot * rstd * rstd * rstd / (float)D;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + row * D);
+#pragma unroll
+    for (int a = 0; a < kMaxVec; ++a) {
+      int i = threadIdx.x + a * blockDim.x;
+      if (i < nv) {
+        uint4 q = xr[i], g = gr[i], ww = wr[i], o;
+        uint32_t u[4] = {q.x, q.y, q.z, q.w}, gu[4] = {g.x, g.y, g.z, g.w},
+                 wu[4] = {ww.x, ww.y, ww.z, ww.w}, ou[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 xf = unpack_bf16(u[j]), gf = unpack_bf16(gu[j]), wf = unpack_bf16(wu[j]);
+          if (kOnePlus) { wf.x += 1.f; wf.y += 1.f; }
+          ou[j] = pack_bf16(gf.x * wf.x * rstd - xf.x * c, gf.y * wf.y * rstd - xf.y * c);
+        }
+        o.x = ou[0]; o.y = ou[1]; o.z = ou[2]; o.w = ou[3];
+        dxr[i] = o;
+      }
+    }
+  }
+  if (dw) {
+#pragma unroll
+    for (int a = 0; a < kMaxVec; ++a) {
+      int i = threadIdx.x + a * blockDim.x;
+      if (i < nv) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) atomicAdd(dw + i * 8 + j, dwacc[a][j]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ SwiGLU (K5)
+// gu is [M, 2F] = [gate | up];  act = silu(gate) * up.
+__global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ act, long long M,
+                                  int F) {
+  const int fv = F >> 3;
+  const long long total = M * fv;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    long long m = idx / fv;
+    int c = (int)(idx - m * fv);
+    const uint4 g = reinterpret_cast<const uint4*>(gu + m * 2 * F)[c];
+    const uint4 u = reinterpret_cast<const uint4*>(gu + m * 2 * F + F)[c];
+    uint32_t ga[4] = {g.x, g.y, g.z, g.w}, ua[4] = {u.x, u.y, u.z, u.w}, oa[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 gf = unpack_bf16(ga[j]), uf = unpack_bf16(ua[j]);
+      float a = gf.x / (1.f + __expf(-gf.x)) * uf.x;
+      float b = gf.y / (1.f + __expf(-gf.y)) * uf.y;
+      oa[j] = pack_bf16(a, b);
+    }
+    uint4 o; o.x = oa[0]; o.y = oa[1]; o.z = oa[2]; o.w = oa[3];
+    reinterpret_cast<uint4*>(act + m * F)[c] = o;
+  }
+}
+
+// dgu = [dact * up * dsilu(gate) | dact * silu(gate)]; optionally also re-emits act.
+__global__ void swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __restrict__ dact,
+                                  bf16* __restrict__ dgu, bf16* __restrict__ act_out, long long M,
+                                  int F) {
+  const int fv = F >> 3;
+  const long long total = M * fv;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    long long m = idx / fv;
+    int c = (int)(idx - m * fv);
+    const uint4 g = reinterpret_cast<const uint4*>(gu + m * 2 * F)[c];
+    const uint4 u = reinterpret_cast<const uint4*>(gu + m * 2 * F + F)[c];
+    const uint4 d = reinterpret_cast<const uint4*>(dact + m * F)[c];
+    uint32_t ga[4] = {g.x, g.y, g.z, g.w}, ua[4] = {u.x, u.y, u.z, u.w},
+             da[4] = {d.x, d.y, d.z, d.w}, dg[4], du[4], ao[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 gf = unpack_bf16(ga[j]), uf = unpack_bf16(ua[j]), df = unpack_bf16(da[j]);
+      float s0 = 1.f / (1.f + __expf(-gf.x)), s1 = 1.f / (1.f + __expf(-gf.y));
+      float si0 = gf.x * s0, si1 = gf.y * s1;
+      dg[j] = pack_bf16(df.x * uf.x * s0 * (1.f + gf.x * (1.f - s0)),
+                        df.y * uf.y * s1 * (1.f + gf.y * (1.f - s1)));
+      du[j] = pack_bf16(df.x * si0, df.y * si1);
+      ao[j] = pack_bf16(si0 * uf.x, si1 * uf.y);
+    }
+    uint4 o; o.x = dg[0]; o.y = dg[1]; o.z = dg[2]; o.w = dg[3];
+    reinterpret_cast<uint4*>(dgu + m * 2 * F)[c] = o;
+    o.x = du[0]; o.y = du[1]; o.z = du[2]; o.w = du[3];
+    reinterpret_cast<uint4*>(dgu + m * 2 * F + F)[c] = o;
+    if (act_out) {
+      o.x = ao[0]; o.y = ao[1]; o.z = ao[2]; o.w = ao[3];
+      reinterpret_cast<uint4*>(act_out + m * F)[c] = o;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ QK-RMSNorm + RoPE
+// qkv: [M, (H+2G)*K] (q heads, then k heads, then v heads).  For every q and k head:
+// per-head RMSNorm over K with weight (qw / kw, or 1+w), then rotate-half RoPE on the
+// first `rot` channels using cos/sin tables [M, rot/2] (fp32).  Outputs q_out [M,H,K],
+// k_out [M,G,K].  One warp per (row, head).
+template <bool kOnePlus>
+__global__ void qknorm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw,
+                                       const bf16* __restrict__ kw, const float* __restrict__ cosT,
+                                       const float* __restrict__ sinT, bf16* __restrict__ q_out,
+                                       bf16* __restrict__ k_out, long long M, int H, int G, int K,
+                                       int rot, float eps, int q_in_stride_heads) {
+  const int lane = threadIdx.x & 31;
+  const long long wid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int HG = H + G;
+  if (wid >= M * HG) return;
+  const long long m = wid / HG;
+  const int h = (int)(wid - m * HG);
+  const bool is_q = h < H;
+  // q heads may be interleaved with a per-head gate (q_in_stride_heads = 2 for gated attention)
+  const long long in_off = is_q ? (long long)h * K * q_in_stride_heads
+                                : (long long)H * K * q_in_stride_heads + (long long)(h - H) * K;
+  const long long row_stride = (long long)H * K * q_in_stride_heads + 2ll * G * K;
+  const bf16* src = qkv + m * row_stride + in_off;
+  const bf16* w = is_q ? qw : kw;
+  bf16* dst = is_q ? q_out + (m * H + h) * K : k_out + (m * G + (h - H)) * K;
+  float ss = 0.f;
+  for (int i = lane; i < K; i += 32) {
+    float v = __bfloat162float(src[i]);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float rstd = w ? rsqrtf(ss / (float)K + eps) : 1.f;
+  const int half = rot >> 1;
+  const float* cr = cosT + m * half;
+  const float* sr = sinT + m * half;
+  for (int i = lane; i < half; i += 32) {
+    float w1 = 1.f, w2 = 1.f;
+    if (w) {
+      w1 = __bfloat162float(w[i]) + (kOnePlus ? 1.f : 0.f);
+      w2 = __bfloat162float(w[i + half]) + (kOnePlus ? 1.f : 0.f);
+    }
+    // normalised values are rounded to bf16 before the rotation, as the module-level
+    // composition (norm then rope, both in model dtype) does
+    float x1 = __bfloat162float(__float2bfloat16(__bfloat162float(src[i]) * rstd * w1));
+    float x2 = __bfloat162float(__float2bfloat16(__bfloat162float(src[i + half]) * rstd * w2));
+    float c = cr[i], s = sr[i];
+    dst[i] = __float2bfloat16(x1 * c - x2 * s);
+    dst[i + half] = __float2bfloat16(x2 * c + x1 * s);
+  }
+  for (int i = rot + lane; i < K; i += 32) {
+    float wv = w ? __bfloat162float(w[i]) + (kOnePlus ? 1.f : 0.f) : 1.f;
+    dst[i] = __float2bfloat16(__bfloat162float(src[i]) * rstd * wv);
+  }
+}
+
+// Backward: dq_rot/dk_rot -> un-rotate -> per-head RMSNorm backward -> written into the
+// q and k slices of dqkv [M, (H+2G)*K]; dqw / dkw accumulate with fp32 atomics.
+template <bool kOnePlus>
+__global__ void qknorm_rope_bwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw,
+                                       const bf16* __restrict__ kw, const float* __restrict__ cosT,
+                                       const float* __restrict__ sinT,
+                                       const bf16* __restrict__ dq_rot,
+                                       const bf16* __restrict__ dk_rot, bf16* __restrict__ dqkv,
+                                       float* __restrict__ dqw, float* __restrict__ dkw,
+                                       long long M, int H, int G, int K, int rot, float eps,
+                                       int q_in_stride_heads, int rows_per_block) {
+  extern __shared__ float dw_sm[];  // [2][K] per-CTA partial of dqw, dkw
+  for (int i = threadIdx.x; i < 2 * K; i += blockDim.x) dw_sm[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int HG = H + G;
+  const int half = rot >> 1;
+  const long long row_stride = (long long)H * K * q_in_stride_heads + 2ll * G * K;
+  const long long m0 = (long long)blockIdx.x * rows_per_block;
+  const long long m1 = min(M, m0 + rows_per_block);
+  for (long long item = m0 * HG + warp; item < m1 * HG; item += nwarps) {
+    const long long m = item / HG;
+    const int h = (int)(item - m * HG);
+    const bool is_q = h < H;
+    const long long in_off = is_q ? (long long)h * K * q_in_stride_heads
+                                  : (long long)H * K * q_in_stride_heads + (long long)(h - H) * K;
+    const bf16* src = qkv + m * row_stride + in_off;
+    const bf16* w = is_q ? qw : kw;
+    const bf16* dsrc = is_q ? dq_rot + (m * H + h) * K : dk_rot + (m * G + (h - H)) * K;
+    bf16* ddst = dqkv + m * row_stride + in_off;
+    float* dws = dw_sm + (is_q ? 0 : K);
+    const float* cr = cosT + m * half;
+    const float* sr = sinT + m * half;
+    float ss = 0.f;
+    for (int i = lane; i < K; i += 32) {
+      float v = __bfloat162float(src[i]);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    const float rstd = w ? rsqrtf(ss / (float)K + eps) : 1.f;
+    // pass 1: gradient w.r.t. the normalised value (dn) and dot = sum dn * w * x
+    float dot = 0.f;
+    for (int i = lane; i < half; i += 32) {
+      float c = cr[i], s = sr[i];
+      float d1 = __bfloat162float(dsrc[i]), d2 = __bfloat162float(dsrc[i + half]);
+      float dn1 = d1 * c + d2 * s, dn2 = d2 * c - d1 * s;
+      float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[i + half]);
+      float w1 = 1.f, w2 = 1.f;
+      if (w) {
+        w1 = __bfloat162float(w[i]) + (kOnePlus ? 1.f : 0.f);
+        w2 = __bfloat162float(w[i + half]) + (kOnePlus ? 1.f : 0.f);
+        atomicAdd(dws + i, dn1 * x1 * rstd);
+        atomicAdd(dws + i + half, dn2 * x2 * rstd);
+      }
+      dot += dn1 * w1 * x1 + dn2 * w2 * x2;
+    }
+    for (int i = rot + lane; i < K; i += 32) {
+      float dn = __bfloat162float(dsrc[i]);
+      float xv = __bfloat162float(src[i]);
+      float wv = 1.f;
+      if (w) {
+        wv = __bfloat162float(w[i]) + (kOnePlus ? 1.f : 0.f);
+        atomicAdd(dws + i, dn * xv * rstd);
+      }
+      dot += dn * wv * xv;
+    }
+    dot = warp_sum(dot);
+    const float cc = w ? dot * rstd * rstd * rstd / (float)K : 0.f;
+    for (int i = lane; i < half; i += 32) {
+      float c = cr[i], s = sr[i];
+      float d1 = __bfloat162float(dsrc[i]), d2 = __bfloat162float(dsrc[i + half]);
+      float dn1 = d1 * c + d2 * s, dn2 = d2 * c - d1 * s;
+      float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[i + half]);
+      float w1 = 1.f, w2 = 1.f;
+      if (w) {
+        w1 = __bfloat162float(w[i]) + (kOnePlus ? 1.f : 0.f);
+        w2 = __bfloat162float(w[i + half]) + (kOnePlus ? 1.f : 0.f);
+      }
+      ddst[i] = __float2bfloat16(dn1 * w1 * rstd - x1 * cc);
+      ddst[i + half] = __float2bfloat16(dn2 * w2 * rstd - x2 * cc);
+    }
+    for (int i = rot + lane; i < K; i += 32) {
+      float dn = __bfloat162float(dsrc[i]);
+      float xv = __bfloat162float(src[i]);
+      float wv = w ? __bfloat162float(w[i]) + (kOnePlus ? 1.f : 0.f) : 1.f;
+      ddst[i] = __float2bfloat16(dn * wv * rstd - xv * cc);
+    }
+  }
+  __syncthreads();
+  if (qw && dqw)
+    for (int i = threadIdx.x; i < K; i += blockDim.x) atomicAdd(dqw + i, dw_sm[i]);
+  if (kw && dkw)
+    for (int i = threadIdx.x; i < K; i += blockDim.x) atomicAdd(dkw + i, dw_sm[K + i]);
+}
+
+// ------------------------------------------------------------------ softmax cross-entropy
+// One CTA per row of a bf16 logits chunk [R, V] (pitch ld).  Adds mask*nll to loss_sum and
+// overwrites the row with dlogits = (softmax - onehot) * mask * (*grad_scale).
+__global__ void ce_fwd_bwd_kernel(bf16* __restrict__ logits, long long ld, int V,
+                                  const int* __restrict__ targets, const float* __restrict__ mask,
+                                  const float* __restrict__ grad_scale,
+                                  float* __restrict__ loss_sum, float* __restrict__ lse_out,
+                                  int write_grad) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  bf16* lr = logits + row * ld;
+  const float mk = mask ? mask[row] : 1.f;
+  const int tgt = targets[row];
+  const int nv = V >> 3;  // V % 8 == 0
+  const uint4* lv = reinterpret_cast<const uint4*>(lr);
+  float mx = -INFINITY, sm = 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    uint4 q = lv[i];
+    uint32_t u[4] = {q.x, q.y, q.z, q.w};
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = unpack_bf16(u[j]);
+      f[2 * j] = t.x; f[2 * j + 1] = t.y;
+    }
+    float lm = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
+    if (lm > mx) {
+      sm *= __expf(mx - lm);
+      mx = lm;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sm += __expf(f[j] - mx);
+  }
+  const float gmx = block_max(mx, red);
+  sm *= (mx == -INFINITY) ? 0.f : __expf(mx - gmx);
+  const float gsum = block_sum(sm, red);
+  const float lse = gmx + logf(gsum);
+  if (threadIdx.x == 0) {
+    float tl = (tgt >= 0 && tgt < V) ? __bfloat162float(lr[tgt]) : 0.f;
+    if (mk != 0.f) atomicAdd(loss_sum, (lse - tl) * mk);
+    if (lse_out) lse_out[row] = lse;
+  }
+  if (!write_grad) return;
+  __syncthreads();
+  const float gs = mk * (grad_scale ? *grad_scale : 1.f);
+  uint4* ov = reinterpret_cast<uint4*>(lr);
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    uint4 q = lv[i], o;
+    uint32_t u[4] = {q.x, q.y, q.z, q.w}, ou[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = unpack_bf16(u[j]);
+      int c0 = i * 8 + 2 * j;
+      float p0 = __expf(t.x - lse) - (c0 == tgt ? 1.f : 0.f);
+      float p1 = __expf(t.y - lse) - (c0 + 1 == tgt ? 1.f : 0.f);
+      ou[j] = pack_bf16(p0 * gs, p1 * gs);
+    }
+    o.x = ou[0]; o.y = ou[1]; o.z = ou[2]; o.w = ou[3];
+    ov[i] = o;
+  }
+}
+
+// ------------------------------------------------------------------ embedding (K13)
+__global__ void embedding_fwd_kernel(const int* __restrict__ ids, const bf16* __restrict__ table,
+                                     bf16* __restrict__ out, long long M, int D) {
+  const int dv = D >> 3;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < M * dv;
+       idx += (long long)gridDim.x * blockDim.x) {
+    long long m = idx / dv;
+    int c = (int)(idx - m * dv);
+    reinterpret_cast<uint4*>(out + m * D)[c] =
+        reinterpret_cast<const uint4*>(table + (long long)ids[m] * D)[c];
+  }
+}
+__global__ void embedding_bwd_kernel(const int* __restrict__ ids, const bf16* __restrict__ dy,
+                                     float* __restrict__ dtable, long long M, int D, int row_lo,
+                                     int row_hi) {
+  const int dv = D >> 1;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < M * dv;
+       idx += (long long)gridDim.x * blockDim.x) {
+    long long m = idx / dv;
+    int c = (int)(idx - m * dv);
+    int id = ids[m];
+    if (id < row_lo || id >= row_hi) continue;
+    float2 f = unpack_bf16(reinterpret_cast<const uint32_t*>(dy + m * D)[c]);
+    float* d = dtable + (long long)(id - row_lo) * D + 2 * c;
+    atomicAdd(d, f.x);
+    atomicAdd(d + 1, f.y);
+  }
+}
+
+// ------------------------------------------------------------------ optimizer (K14)
+__global__ void sumsq_kernel(const float* __restrict__ g, long long n, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  const long long n4 = n >> 2;
+  const float4* g4 = reinterpret_cast<const float4*>(g);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 v = g4[i];
+    s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  if (blockIdx.x == 0)
+    for (long long i = (n4 << 2) + threadIdx.x; i < n; i += blockDim.x) s += g[i] * g[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) atomicAdd(out, s);
+}
+
+// AdamW on a flat fp32 shard.  The clip coefficient is derived on the device from the
+// already-reduced squared gradient norm so the host never synchronises:
+//   g' = g * grad_mul * min(1, max_norm / (sqrt(norm_sq) * grad_mul + 1e-6))
+// Writes the fp32 master, both moments, the bf16 compute copy, and zeroes the gradient.
+__global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                             float* __restrict__ g, bf16* __restrict__ p16, long long n, float lr,
+                             float b1, float b2, float eps, float wd, float bc1, float bc2,
+                             float grad_mul, const float* __restrict__ norm_sq, float max_norm,
+                             int zero_grad) {
+  float mul = grad_mul;
+  if (norm_sq && max_norm > 0.f) {
+    float nrm = sqrtf(*norm_sq) * grad_mul;
+    mul *= fminf(1.f, max_norm / (nrm + 1e-6f));
+  }
+  const long long n4 = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 pp = reinterpret_cast<float4*>(p)[i], mm = reinterpret_cast<float4*>(m)[i],
+           vv = reinterpret_cast<float4*>(v)[i], gg = reinterpret_cast<float4*>(g)[i];
+    float pa[4] = {pp.x, pp.y, pp.z, pp.w}, ma[4] = {mm.x, mm.y, mm.z, mm.w},
+          va[4] = {vv.x, vv.y, vv.z, vv.w}, ga[4] = {gg.x, gg.y, gg.z, gg.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float gr = ga[j] * mul;
+      ma[j] = b1 * ma[j] + (1.f - b1) * gr;
+      va[j] = b2 * va[j] + (1.f - b2) * gr * gr;
+      float mh = ma[j] / bc1, vh = va[j] / bc2;
+      pa[j] = pa[j] - lr * (mh / (sqrtf(vh) + eps) + wd * pa[j]);
+    }
+    reinterpret_cast<float4*>(p)[i] = make_float4(pa[0], pa[1], pa[2], pa[3]);
+    reinterpret_cast<float4*>(m)[i] = make_float4(ma[0], ma[1], ma[2], ma[3]);
+    reinterpret_cast<float4*>(v)[i] = make_float4(va[0], va[1], va[2], va[3]);
+    if (zero_grad) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (p16) {
+      uint2 o;
+      o.x = pack_bf16(pa[0], pa[1]);
+      o.y = pack_bf16(pa[2], pa[3]);
+      reinterpret_cast<uint2*>(p16)[i] = o;
+    }
+  }
+  if (blockIdx.x == 0) {
+    for (long long i = (n4 << 2) + threadIdx.x; i < n; i += blockDim.x) {
+      float gr = g[i] * mul;
+      float mi = b1 * m[i] + (1.f - b1) * gr;
+      float vi = b2 * v[i] + (1.f - b2) * gr * gr;
+      float pi = p[i] - lr * ((mi / bc1) / (sqrtf(vi / bc2) + eps) + wd * p[i]);
+      p[i] = pi; m[i] = mi; v[i] = vi;
+      if (zero_grad) g[i] = 0.f;
+      if (p16) p16[i] = __float2bfloat16(pi);
+    }
+  }
+}
+
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ src, bf16* __restrict__ dst,
+                                     long long n) {
+  const long long n4 = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 v = reinterpret_cast<const float4*>(src)[i];
+    uint2 o;
+    o.x = pack_bf16(v.x, v.y);
+    o.y = pack_bf16(v.z, v.w);
+    reinterpret_cast<uint2*>(dst)[i] = o;
+  }
+  if (blockIdx.x == 0)
+    for (long long i = (n4 << 2) + threadIdx.x; i < n; i += blockDim.x)
+      dst[i] = __float2bfloat16(src[i]);
+}
+
+// bf16 [R, C] -> [C, R] through a padded shared-memory tile.
+__global__ void transpose_bf16_kernel(const bf16* __restrict__ src, bf16* __restrict__ dst, int R,
+                                      int C, long long lds, long long ldd) {
+  __shared__ bf16 tile[64][66];
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  for (int i = threadIdx.y; i < 64; i += blockDim.y) {
+    int r = r0 + i;
+    for (int j = threadIdx.x; j < 64; j += blockDim.x) {
+      int c = c0 + j;
+      tile[i][j] = (r < R && c < C) ? src[(long long)r * lds + c] : __float2bfloat16(0.f);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 64; i += blockDim.y) {
+    int c = c0 + i;
+    for (int j = threadIdx.x; j < 64; j += blockDim.x) {
+      int r = r0 + j;
+      if (r < R && c < C) dst[(long long)c * ldd + r] = tile[j][i];
+    }
+  }
+}
+
+// Flush helper for benchmarks: touch a buffer larger than L2.
+__global__ void fill_u32_kernel(uint32_t* p, long long n, uint32_t v) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    p[i] = v;
+}
+
+static inline int grid_for(long long work, int threads) {
+  long long b = (work + threads - 1) / threads;
+  long long cap = (long long)num_sms() * 16;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace ob
+
+using namespace ob;
+
+extern "C" {
+
+int ob_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long M, int D,
+                   float eps, int one_plus, cudaStream_t s) {
+  if (D % 8) return 6001;
+  if (M <= 0) return 0;
+  int threads = D >= 2048 ? 256 : 128;
+  if (one_plus)
+    rmsnorm_fwd_kernel<true><<<(unsigned)M, threads, 0, s>>>((const bf16*)x, (const bf16*)w,
+                                                             (bf16*)y, rstd, D, eps);
+  else
+    rmsnorm_fwd_kernel<false><<<(unsigned)M, threads, 0, s>>>((const bf16*)x, (const bf16*)w,
+                                                              (bf16*)y, rstd, D, eps);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                   float* dw, long long M, int D, float eps, int one_plus, cudaStream_t s) {
+  if (D % 8) return 6001;
+  if (M <= 0) return 0;
+  const int threads = 256;
+  const int nv = D / 8;
+  int need = (nv + threads - 1) / threads;
+  int grid = (int)(M < (long long)num_sms() * 4 ? M : (long long)num_sms() * 4);
+#define OB_RB(OP, MV)                                                                           \
+  rmsnorm_bwd_kernel<OP, MV><<<grid, threads, 0, s>>>((const bf16*)dy, (const bf16*)x,          \
+                                                      (const bf16*)w, rstd, (bf16*)dx, dw,      \
+                                                      (int)M, D, eps)
+  if (need <= 1) { if (one_plus) OB_RB(true, 1); else OB_RB(false, 1); }
+  else if (need <= 2) { if (one_plus) OB_RB(true, 2); else OB_RB(false, 2); }
+  else if (need <= 4) { if (one_plus) OB_RB(true, 4); else OB_RB(false, 4); }
+  else return 6004;
+#undef OB_RB
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_swiglu_fwd(const void* gu, void* act, long long M, int F, cudaStream_t s) {
+  if (F % 8) return 6001;
+  if (M <= 0) return 0;
+  swiglu_fwd_kernel<<<grid_for(M * (F / 8), 256), 256, 0, s>>>((const bf16*)gu, (bf16*)act, M, F);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_swiglu_bwd(const void* gu, const void* dact, void* dgu, void* act_out, long long M, int F,
+                  cudaStream_t s) {
+  if (F % 8) return 6001;
+  if (M <= 0) return 0;
+  swiglu_bwd_kernel<<<grid_for(M * (F / 8), 256), 256, 0, s>>>(
+      (const bf16*)gu, (const bf16*)dact, (bf16*)dgu, (bf16*)act_out, M, F);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw, const float* cosT,
+                       const float* sinT, void* q_out, void* k_out, long long M, int H, int G,
+                       int K, int rot, float eps, int one_plus, int q_stride_heads,
+                       cudaStream_t s) {
+  if (M <= 0) return 0;
+  long long warps = M * (H + G);
+  int threads = 256;
+  long long blocks = (warps * 32 + threads - 1) / threads;
+  if (one_plus)
+    qknorm_rope_fwd_kernel<true><<<(unsigned)blocks, threads, 0, s>>>(
+        (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (bf16*)q_out, (bf16*)k_out,
+        M, H, G, K, rot, eps, q_stride_heads);
+  else
+    qknorm_rope_fwd_kernel<false><<<(unsigned)blocks, threads, 0, s>>>(
+        (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (bf16*)q_out, (bf16*)k_out,
+        M, H, G, K, rot, eps, q_stride_heads);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_qknorm_rope_bwd(const void* qkv, const void* qw, const void* kw, const float* cosT,
+                       const float* sinT, const void* dq_rot, const void* dk_rot, void* dqkv,
+                       float* dqw, float* dkw, long long M, int H, int G, int K, int rot,
+                       float eps, int one_plus, int q_stride_heads, cudaStream_t s) {
+  if (M <= 0) return 0;
+  const int threads = 256;
+  const int rows_per_block = 16;
+  long long blocks = (M + rows_per_block - 1) / rows_per_block;
+  size_t sm = 2 * K * sizeof(float);
+  if (one_plus)
+    qknorm_rope_bwd_kernel<true><<<(unsigned)blocks, threads, sm, s>>>(
+        (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (const bf16*)dq_rot,
+        (const bf16*)dk_rot, (bf16*)dqkv, dqw, dkw, M, H, G, K, rot, eps, q_stride_heads,
+        rows_per_block);
+  else
+    qknorm_rope_bwd_kernel<false><<<(unsigned)blocks, threads, sm, s>>>(
+        (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (const bf16*)dq_rot,
+        (const bf16*)dk_rot, (bf16*)dqkv, dqw, dkw, M, H, G, K, rot, eps, q_stride_heads,
+        rows_per_block);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_ce_fwd_bwd(void* logits, long long ld, long long R, int V, const int* targets,
+                  const float* mask, const float* grad_scale, float* loss_sum, float* lse_out,
+                  int write_grad, cudaStream_t s) {
+  if (V % 8 || ld % 8) return 6001;
+  if (R <= 0) return 0;
+  ce_fwd_bwd_kernel<<<(unsigned)R, 512, 0, s>>>((bf16*)logits, ld, V, targets, mask, grad_scale,
+                                                loss_sum, lse_out, write_grad);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_embedding_fwd(const int* ids, const void* table, void* out, long long M, int D,
+                     cudaStream_t s) {
+  if (D % 8) return 6001;
+  if (M <= 0) return 0;
+  embedding_fwd_kernel<<<grid_for(M * (D / 8), 256), 256, 0, s>>>(ids, (const bf16*)table,
+                                                                  (bf16*)out, M, D);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_embedding_bwd(const int* ids, const void* dy, float* dtable, long long M, int D, int row_lo,
+                     int row_hi, cudaStream_t s) {
+  if (D % 2) return 6001;
+  if (M <= 0) return 0;
+  embedding_bwd_kernel<<<grid_for(M * (D / 2), 256), 256, 0, s>>>(ids, (const bf16*)dy, dtable, M,
+                                                                  D, row_lo, row_hi);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_sumsq(const float* g, long long n, float* out, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if (((uintptr_t)g) & 15) return 6002;
+  sumsq_kernel<<<grid_for(n / 4 + 1, 256), 256, 0, s>>>(g, n, out);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_adamw(float* p, float* m, float* v, float* g, void* p16, long long n, float lr, float b1,
+             float b2, float eps, float wd, float bc1, float bc2, float grad_mul,
+             const float* norm_sq, float max_norm, int zero_grad, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if ((((uintptr_t)p) | ((uintptr_t)m) | ((uintptr_t)v) | ((uintptr_t)g)) & 15) return 6002;
+  if (p16 && (((uintptr_t)p16) & 7)) return 6002;
+  adamw_kernel<<<grid_for(n / 4 + 1, 256), 256, 0, s>>>(p, m, v, g, (bf16*)p16, n, lr, b1, b2, eps,
+                                                        wd, bc1, bc2, grad_mul, norm_sq, max_norm,
+                                                        zero_grad);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_cast_f32_bf16(const float* src, void* dst, long long n, cudaStream_t s) {
+  if (n <= 0) return 0;
+  if ((((uintptr_t)src) & 15) || (((uintptr_t)dst) & 7)) return 6002;
+  cast_f32_bf16_kernel<<<grid_for(n / 4 + 1, 256), 256, 0, s>>>(src, (bf16*)dst, n);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_transpose_bf16(const void* src, void* dst, int R, int C, long long lds, long long ldd,
+                      cudaStream_t s) {
+  if (R <= 0 || C <= 0) return 0;
+  dim3 grid((C + 63) / 64, (R + 63) / 64), block(32, 8);
+  transpose_bf16_kernel<<<grid, block, 0, s>>>((const bf16*)src, (bf16*)dst, R, C, lds, ldd);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_l2_flush(void* buf, long long bytes, cudaStream_t s) {
+  fill_u32_kernel<<<num_sms() * 8, 256, 0, s>>>((uint32_t*)buf, bytes / 4, 0u);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // extern "C"

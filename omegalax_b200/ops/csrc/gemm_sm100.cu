@@ -1,0 +1,559 @@
+// K1/K2: persistent, warp-specialised bf16 GEMM for sm_100a.
+//
+//   C[M,N] (+)= op(A) * op(B)^T      fp32 accumulation in TMEM
+//
+// Roles inside one CTA (192 threads): warp 0 issues TMA loads into a 4-stage ring of
+// 128-byte-swizzled shared-memory tiles, warp 1 allocates TMEM and issues tcgen05.mma
+// (one thread), warps 2..5 drain the accumulator with tcgen05.ld and run the epilogue.
+// Two accumulators of BN columns each are kept in TMEM so the epilogue of tile i
+// overlaps the main loop of tile i+1.  One CTA per SM, persistent over output tiles.
+//
+// Operand storage ("major-ness"), per operand:
+//   K-major : reduction dimension contiguous.  A is [M,K] row-major, B is [N,K] row-major.
+//   MN-major: output dimension contiguous.     A is [K,M] row-major, B is [K,N] row-major.
+// The three training GEMMs of a linear layer y = x W^T map to
+//   fprop  y  = x  W^T : A=x  (K-major),  B=W  (K-major)
+//   dgrad  dx = dy W   : A=dy (K-major),  B=W  (MN-major, reduction over W's rows)
+//   wgrad  dW = dy^T x : A=dy (MN-major), B=x  (MN-major, reduction over tokens)
+//
+// Grouped modes (mixture-of-experts):
+//   mode 1: rows of A and C are ragged per group (group_offsets, multiples of 128);
+//           B holds one matrix per group, stacked along its row dimension.
+//   mode 2: per-group weight gradient; the reduction runs over the group's rows.
+//
+// Output modes: bf16 store, fp32 store, fp32 accumulate (C += result), optional bf16
+// residual added before the store, and a peer-reduce mode in which row blocks of C are
+// owned by other GPUs and the tile is added there with vector red.global.add (used by the
+// fused GEMM -> reduce-scatter paths over NVLink peer memory).
+#include "host_utils.h"
+#include "sm100_common.cuh"
+
+namespace ob {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr int kMaxPeers = 8;
+
+struct GemmArgs {
+  int M, N, K;
+  int mode;                  // 0 plain, 1 grouped rows, 2 grouped reduction
+  int num_groups;
+  const int* group_offsets;  // [G+1] device, multiples of 128
+  int b_group_rows;          // rows per group in B's stacked 2-D view
+  int b_mn;                  // B operand major-ness (needed for the grouped row offset)
+  int num_m_blocks, num_n_blocks, total_tiles;
+  void* C;
+  long long ldc;
+  long long c_group_stride;  // mode 2: elements between consecutive groups' outputs
+  int out_mode;              // 0 bf16, 1 fp32 store, 2 fp32 accumulate, 3 fp32 peer red.add
+  const bf16* residual;
+  long long ldr;
+  // out_mode 3: rows [r*rows_per_peer, (r+1)*rows_per_peer) live on peer r at peer_ptr[r]
+  float* peer_ptr[kMaxPeers];
+  int rows_per_peer;
+  int* status;
+};
+
+struct TileInfo {
+  int a_row0;    // first row (K-major) / first column (MN-major) of the A tile
+  int b_row0;    // same for B (K-major: already offset by the group)
+  int b_k_off;   // MN-major B in grouped mode: row offset of the group's matrix
+  int c_row0;    // first output row
+  int c_col0;    // first output column
+  int rows_valid, cols_valid;
+  int k_begin, k_end;
+  long long c_off;  // extra element offset into C (mode 2)
+  bool valid;
+};
+
+__device__ __forceinline__ int find_group(const int* offs, int G, int row) {
+  int lo = 0, hi = G;  // invariant: offs[lo] <= row < offs[hi] (if row < offs[G])
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (__ldg(offs + mid) <= row) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+template <int BN>
+__device__ __forceinline__ TileInfo get_tile(const GemmArgs& p, int t) {
+  TileInfo ti;
+  ti.valid = true;
+  ti.c_off = 0;
+  ti.b_k_off = 0;
+  if (p.mode == 0) {
+    // grouped raster: 8 row blocks share a sweep over the column blocks for L2 reuse
+    const int GM = 8;
+    int per_group = GM * p.num_n_blocks;
+    int g = t / per_group;
+    int first_m = g * GM;
+    int gm = min(GM, p.num_m_blocks - first_m);
+    int r = t - g * per_group;
+    int mb = first_m + (r % gm);
+    int nb = r / gm;
+    ti.a_row0 = mb * BM;
+    ti.b_row0 = nb * BN;
+    ti.c_row0 = mb * BM;
+    ti.c_col0 = nb * BN;
+    ti.rows_valid = min(BM, p.M - ti.c_row0);
+    ti.cols_valid = min(BN, p.N - ti.c_col0);
+    ti.k_begin = 0;
+    ti.k_end = p.K;
+  } else if (p.mode == 1) {
+    int mb = t / p.num_n_blocks;
+    int nb = t - mb * p.num_n_blocks;
+    int row0 = mb * BM;
+    int total = __ldg(p.group_offsets + p.num_groups);
+    if (row0 >= total) {
+      ti.valid = false;
+      return ti;
+    }
+    int g = find_group(p.group_offsets, p.num_groups, row0);
+    ti.a_row0 = row0;
+    if (p.b_mn) {
+      ti.b_row0 = nb * BN;
+      ti.b_k_off = g * p.b_group_rows;
+    } else {
+      ti.b_row0 = g * p.b_group_rows + nb * BN;
+    }
+    ti.c_row0 = row0;
+    ti.c_col0 = nb * BN;
+    ti.rows_valid = BM;
+    ti.cols_valid = min(BN, p.N - ti.c_col0);
+    ti.k_begin = 0;
+    ti.k_end = p.K;
+  } else {
+    int per_group = p.num_m_blocks * p.num_n_blocks;
+    int g = t / per_group;
+    int r = t - g * per_group;
+    int mb = r / p.num_n_blocks;
+    int nb = r - mb * p.num_n_blocks;
+    ti.a_row0 = mb * BM;
+    ti.b_row0 = nb * BN;
+    ti.c_row0 = mb * BM;
+    ti.c_col0 = nb * BN;
+    ti.rows_valid = min(BM, p.M - ti.c_row0);
+    ti.cols_valid = min(BN, p.N - ti.c_col0);
+    ti.k_begin = __ldg(p.group_offsets + g);
+    ti.k_end = __ldg(p.group_offsets + g + 1);
+    ti.c_off = (long long)g * p.c_group_stride;
+  }
+  return ti;
+}
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOff = kStages * kStageBytes;
+  static constexpr int kTotal = kBarOff + 256 + 1024;  // barriers + alignment slack
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits.
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  using L = GemmSmem<BN>;
+  uint64_t* full_bar = (uint64_t*)(smem + L::kBarOff);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tfull_bar = empty_bar + kStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        TileInfo ti = get_tile<BN>(p, t);
+        if (!ti.valid) continue;
+        for (int k0 = ti.k_begin; k0 < ti.k_end; k0 += BK) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_EMPTY);
+          if (!ok) break;
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          if (!A_MN) {
+            tma_load_2d(sa, &tmA, &full_bar[stage], k0, ti.a_row0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * (BK * 128), &tmA, &full_bar[stage], ti.a_row0 + j * 64, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, ti.b_row0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (BK * 128), &tmB, &full_bar[stage], ti.b_row0 + j * 64,
+                          ti.b_k_off + k0);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        TileInfo ti = get_tile<BN>(p, t);
+        if (!ti.valid) continue;
+        ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status,
+                       OB_ERR_WAIT_TMEM_EMPTY);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        uint32_t accumulate = 0;
+        for (int k0 = ti.k_begin; k0 < ti.k_end; k0 += BK) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, OB_ERR_WAIT_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            uint64_t adesc = A_MN ? make_smem_desc(sa + k * 2048, BK * 128, 1024)
+                                  : make_smem_desc(sa + k * 32, 16, 1024);
+            uint64_t bdesc = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
+                                  : make_smem_desc(sb + k * 32, 16, 1024);
+            umma_ss(d_tmem, adesc, bdesc, idesc, accumulate);
+            accumulate = 1;
+          }
+          umma_commit(&empty_bar[stage]);  // stage is free once these MMAs retire
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      TileInfo ti = get_tile<BN>(p, t);
+      if (!ti.valid) continue;
+      ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      const int r = quad * 32 + lane;
+      const bool row_ok = r < ti.rows_valid;
+      const long long grow = (long long)ti.c_row0 + r;
+      const bool empty_k = ti.k_end <= ti.k_begin;  // nothing was accumulated: result is zero
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        if (!empty_k) {
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * 32, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0;
+        }
+        const int col0 = ti.c_col0 + c * 32;
+        const int ncols = min(32, ti.cols_valid - c * 32);
+        if (row_ok && ncols > 0) {
+          if (p.residual) {
+            const bf16* rp = p.residual + grow * p.ldr + col0;
+            if (ncols == 32 && ((((uintptr_t)rp) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 q = *reinterpret_cast<const uint4*>(rp + i * 8);
+                uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 f = unpack_bf16(w[j]);
+                  v[i * 8 + j * 2] = __float_as_uint(__uint_as_float(v[i * 8 + j * 2]) + f.x);
+                  v[i * 8 + j * 2 + 1] =
+                      __float_as_uint(__uint_as_float(v[i * 8 + j * 2 + 1]) + f.y);
+                }
+              }
+            } else {
+              for (int i = 0; i < ncols; ++i)
+                v[i] = __float_as_uint(__uint_as_float(v[i]) + __bfloat162float(rp[i]));
+            }
+          }
+          if (p.out_mode == 0) {
+            bf16* cp = (bf16*)p.C + ti.c_off + grow * p.ldc + col0;
+            if (ncols == 32 && ((((uintptr_t)cp) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 q;
+                q.x = pack_bf16(__uint_as_float(v[i * 8 + 0]), __uint_as_float(v[i * 8 + 1]));
+                q.y = pack_bf16(__uint_as_float(v[i * 8 + 2]), __uint_as_float(v[i * 8 + 3]));
+                q.z = pack_bf16(__uint_as_float(v[i * 8 + 4]), __uint_as_float(v[i * 8 + 5]));
+                q.w = pack_bf16(__uint_as_float(v[i * 8 + 6]), __uint_as_float(v[i * 8 + 7]));
+                *reinterpret_cast<uint4*>(cp + i * 8) = q;
+              }
+            } else {
+              for (int i = 0; i < ncols; ++i) cp[i] = __float2bfloat16(__uint_as_float(v[i]));
+            }
+          } else if (p.out_mode == 3) {
+            const int owner = (int)(grow / p.rows_per_peer);
+            const long long lrow = grow - (long long)owner * p.rows_per_peer;
+            float* cp = p.peer_ptr[owner] + lrow * p.ldc + col0;
+            if (ncols == 32 && ((((uintptr_t)cp) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + i * 4),
+                             "f"(__uint_as_float(v[i * 4 + 0])), "f"(__uint_as_float(v[i * 4 + 1])),
+                             "f"(__uint_as_float(v[i * 4 + 2])), "f"(__uint_as_float(v[i * 4 + 3]))
+                             : "memory");
+              }
+            } else {
+              for (int i = 0; i < ncols; ++i) atomicAdd(cp + i, __uint_as_float(v[i]));
+            }
+          } else {
+            float* cp = (float*)p.C + ti.c_off + grow * p.ldc + col0;
+            const bool accum = p.out_mode == 2;
+            if (ncols == 32 && ((((uintptr_t)cp) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float4 q = make_float4(__uint_as_float(v[i * 4 + 0]), __uint_as_float(v[i * 4 + 1]),
+                                       __uint_as_float(v[i * 4 + 2]), __uint_as_float(v[i * 4 + 3]));
+                if (accum) {
+                  float4 o = *reinterpret_cast<const float4*>(cp + i * 4);
+                  q.x += o.x; q.y += o.y; q.z += o.z; q.w += o.w;
+                }
+                *reinterpret_cast<float4*>(cp + i * 4) = q;
+              }
+            } else {
+              for (int i = 0; i < ncols; ++i)
+                cp[i] = __uint_as_float(v[i]) + (accum ? cp[i] : 0.f);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that may still be in flight time to land before shared memory is released
+    long long t0 = clock64();
+    while (clock64() - t0 < 2000000) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const void* A, const void* B, const GemmArgs& args, long long a_rows,
+                       long long a_cols, long long lda, long long b_rows, long long b_cols,
+                       long long ldb, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  // K-major operand: view [rows=MN extent, cols=K], box BM(BN) x 64.
+  // MN-major operand: view [rows=K extent, cols=MN], box 64 (k) x 64 (mn).
+  int e;
+  if (!A_MN) e = make_tmap_2d(&tmA, A, a_rows, a_cols, lda, BM, BK);
+  else e = make_tmap_2d(&tmA, A, a_rows, a_cols, lda, BK, 64);
+  if (e) return 2000 + e;
+  if (!B_MN) e = make_tmap_2d(&tmB, B, b_rows, b_cols, ldb, BN, BK);
+  else e = make_tmap_2d(&tmB, B, b_rows, b_cols, ldb, BK, 64);
+  if (e) return 3000 + e;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          GemmSmem<BN>::kTotal);
+    if (ce != cudaSuccess) return 4000 + (int)ce;
+    attr_set = true;
+  }
+  int grid = args.total_tiles < num_sms() ? args.total_tiles : num_sms();
+  if (grid <= 0) return 0;
+  kern<<<grid, kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(tmA, tmB, args);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // namespace ob
+
+using namespace ob;
+
+// Dispatch on operand major-ness and tile width.
+static int dispatch(int bn, int a_mn, int b_mn, const void* A, const void* B, const GemmArgs& g,
+                    long long a_rows, long long a_cols, long long lda, long long b_rows,
+                    long long b_cols, long long ldb, cudaStream_t s) {
+#define OB_CASE(BN_, AM, BMj)                                                                   \
+  if (bn == BN_ && a_mn == AM && b_mn == BMj)                                                   \
+    return launch_gemm<BN_, AM != 0, BMj != 0>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, s);
+  OB_CASE(256, 0, 0)
+  OB_CASE(256, 0, 1)
+  OB_CASE(256, 1, 1)
+  OB_CASE(256, 1, 0)
+  OB_CASE(128, 0, 0)
+  OB_CASE(128, 0, 1)
+  OB_CASE(128, 1, 1)
+  OB_CASE(128, 1, 0)
+#undef OB_CASE
+  return 5000;
+}
+
+static int pick_bn(int M, int N) {
+  // A 128x256 tile halves B traffic per flop; use 128 columns when the wide tile would
+  // leave SMs idle or waste more than a quarter of its columns.
+  long long t256 = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);
+  if (N <= 128) return 128;
+  if (N % 256 != 0 && N % 256 <= 128 && N < 1024) return 128;
+  if (t256 < 148) return 128;
+  return 256;
+}
+
+extern "C" {
+
+// Plain GEMM.  a_mn / b_mn: 0 = K-major ([M,K] / [N,K] row-major), 1 = MN-major
+// ([K,M] / [K,N] row-major).  out_mode: 0 bf16, 1 fp32, 2 fp32 accumulate.
+// residual (optional, bf16 [M,N] with pitch ldr) is added before the store.
+int ob_gemm_bf16(const void* A, const void* B, void* C, const void* residual, int M, int N, int K,
+                 long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int b_mn,
+                 int out_mode, int bn_override, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((lda & 7) || (ldb & 7)) return 6001;  // TMA needs 16-byte row pitches
+  if ((((uintptr_t)A) & 15) || (((uintptr_t)B) & 15)) return 6002;
+  int bn = bn_override ? bn_override : pick_bn(M, N);
+  GemmArgs g = {};
+  g.M = M; g.N = N; g.K = K; g.mode = 0;
+  g.num_m_blocks = (M + BM - 1) / BM;
+  g.num_n_blocks = (N + bn - 1) / bn;
+  g.total_tiles = g.num_m_blocks * g.num_n_blocks;
+  g.C = C; g.ldc = ldc; g.out_mode = out_mode;
+  g.residual = (const bf16*)residual; g.ldr = ldr;
+  g.status = status;
+  long long a_rows = a_mn ? K : M, a_cols = a_mn ? M : K;
+  long long b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;
+  return dispatch(bn, a_mn, b_mn, A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
+}
+
+// GEMM whose fp32 output rows are spread over `world` GPUs: row block r of C lives at
+// peer_ptrs[r] (rows_per_peer rows, pitch ldc) and receives the tile through
+// red.global.add.v4.f32 over NVLink.  The destination must be zeroed (or hold the running
+// sum) before any rank launches; completion is published by the caller's barrier.
+int ob_gemm_bf16_peer_reduce(const void* A, const void* B, void* const* peer_ptrs, int world,
+                             int rows_per_peer, int M, int N, int K, long long lda, long long ldb,
+                             long long ldc, int a_mn, int b_mn, int* status, cudaStream_t stream) {
+  if (world > kMaxPeers) return 6003;
+  if ((lda & 7) || (ldb & 7)) return 6001;
+  int bn = pick_bn(M, N);
+  GemmArgs g = {};
+  g.M = M; g.N = N; g.K = K; g.mode = 0;
+  g.num_m_blocks = (M + BM - 1) / BM;
+  g.num_n_blocks = (N + bn - 1) / bn;
+  g.total_tiles = g.num_m_blocks * g.num_n_blocks;
+  g.C = nullptr; g.ldc = ldc; g.out_mode = 3;
+  for (int i = 0; i < world; ++i) g.peer_ptr[i] = (float*)peer_ptrs[i];
+  g.rows_per_peer = rows_per_peer;
+  g.status = status;
+  long long a_rows = a_mn ? K : M, a_cols = a_mn ? M : K;
+  long long b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;
+  return dispatch(bn, a_mn, b_mn, A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
+}
+
+// Grouped GEMM over ragged row groups (mixture-of-experts forward and input gradient).
+//   C[rows of group g, :N] = A[rows of group g, :K] * B_g^T
+// group_offsets: device int[G+1], every entry a multiple of 128; rows beyond
+// group_offsets[G] are ignored.  max_rows bounds the row count (allocation size of A/C).
+// b_mn = 0: B is [G, N, K]; b_mn = 1: B is [G, K, N].
+int ob_gemm_bf16_grouped(const void* A, const void* B, void* C, const int* group_offsets, int G,
+                         int max_rows, int N, int K, long long lda, long long ldc, int b_mn,
+                         int out_mode, int* status, cudaStream_t stream) {
+  if (max_rows <= 0) return 0;
+  if ((lda & 7) || (max_rows % BM)) return 6001;
+  int bn = (N % 256 == 0 || N > 512) ? 256 : 128;
+  GemmArgs g = {};
+  g.M = max_rows; g.N = N; g.K = K; g.mode = 1;
+  g.num_groups = G; g.group_offsets = group_offsets;
+  g.b_group_rows = b_mn ? K : N;
+  g.b_mn = b_mn;
+  g.num_m_blocks = max_rows / BM;
+  g.num_n_blocks = (N + bn - 1) / bn;
+  g.total_tiles = g.num_m_blocks * g.num_n_blocks;
+  g.C = C; g.ldc = ldc; g.out_mode = out_mode;
+  g.status = status;
+  long long b_rows = (long long)G * (b_mn ? K : N), b_cols = b_mn ? N : K;
+  return dispatch(bn, 0, b_mn, A, B, g, max_rows, K, lda, b_rows, b_cols, b_cols, stream);
+}
+
+// Grouped weight gradient: dW_g[N, K] (+)= A[rows of g, :N]^T * B[rows of g, :K].
+// A and B are row-major token matrices (MN-major operands); C is [G, N, K].
+int ob_gemm_bf16_grouped_wgrad(const void* A, const void* B, void* C, const int* group_offsets,
+                               int G, int max_rows, int N, int K, long long lda, long long ldb,
+                               int out_mode, int* status, cudaStream_t stream) {
+  if ((lda & 7) || (ldb & 7)) return 6001;
+  int bn = (K % 256 == 0) ? 256 : 128;
+  GemmArgs g = {};
+  g.M = N; g.N = K; g.K = max_rows; g.mode = 2;
+  g.num_groups = G; g.group_offsets = group_offsets;
+  g.num_m_blocks = (N + BM - 1) / BM;
+  g.num_n_blocks = (K + bn - 1) / bn;
+  g.total_tiles = G * g.num_m_blocks * g.num_n_blocks;
+  g.C = C; g.ldc = K; g.c_group_stride = (long long)N * K; g.out_mode = out_mode;
+  g.status = status;
+  return dispatch(bn, 1, 1, A, B, g, max_rows, N, lda, max_rows, K, ldb, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,258 @@
+"""Tensor-level wrappers around the sm_100a launchers (no autograd here).
+
+All functions take CUDA bf16 tensors unless noted, launch on the current stream and
+return immediately.  ``launch_count`` counts every kernel of this library that was
+launched since the last ``reset_launch_count()``.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import lib
+
+bf16 = torch.bfloat16
+_launches = 0
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def _call(name, *args):
+    global _launches
+    _launches += 1
+    lib.call(name, *args)
+
+
+def _row_major_2d(t: torch.Tensor) -> torch.Tensor:
+    if t.dim() != 2:
+        t = t.reshape(-1, t.shape[-1])
+    if t.stride(1) != 1 or (t.stride(0) % 8) or (t.data_ptr() % 16):
+        t = t.contiguous()
+    return t
+
+
+def gemm(a, b, *, a_mn: bool = False, b_mn: bool = False, out=None, out_dtype=bf16,
+         accumulate: bool = False, residual=None, bn: int = 0):
+    """C = op(A) op(B)^T on the tcgen05 kernel.
+
+    a: [M,K] (a_mn False) or [K,M] (a_mn True); b: [N,K] (b_mn False) or [K,N] (b_mn True).
+    out: optional preallocated [M,N] (bf16 or fp32); ``accumulate`` adds into an fp32 out.
+    """
+    a = _row_major_2d(a)
+    b = _row_major_2d(b)
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"reduction mismatch {K} vs {Kb}")
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    if out.stride(1) != 1:
+        raise ValueError("out must be row-major")
+    if out.dtype == bf16:
+        mode = 0
+        if accumulate:
+            raise ValueError("accumulate needs an fp32 output")
+    elif out.dtype == torch.float32:
+        mode = 2 if accumulate else 1
+    else:
+        raise ValueError("out dtype must be bf16 or fp32")
+    res_ptr, ldr = None, 0
+    if residual is not None:
+        residual = residual.reshape(M, N)
+        if residual.stride(1) != 1:
+            residual = residual.contiguous()
+        res_ptr, ldr = residual.data_ptr(), residual.stride(0)
+    st = lib.status_tensor(a.device)
+    _call("ob_gemm_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), res_ptr, M, N, K,
+          a.stride(0), b.stride(0), out.stride(0), ldr, int(a_mn), int(b_mn), mode, bn,
+          st.data_ptr(), lib.stream_ptr())
+    return out
+
+
+def gemm_peer_reduce(a, b, peer_ptrs, rows_per_peer: int, ldc: int, *, a_mn=False, b_mn=False):
+    """GEMM whose fp32 result rows are added into buffers owned by other GPUs
+    (``peer_ptrs[r]`` holds rows [r*rows_per_peer, (r+1)*rows_per_peer))."""
+    import ctypes
+
+    a = _row_major_2d(a)
+    b = _row_major_2d(b)
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N = b.shape[1] if b_mn else b.shape[0]
+    arr = (ctypes.c_void_p * len(peer_ptrs))(*peer_ptrs)
+    st = lib.status_tensor(a.device)
+    _call("ob_gemm_bf16_peer_reduce", a.data_ptr(), b.data_ptr(), ctypes.cast(arr, ctypes.c_void_p),
+          len(peer_ptrs), rows_per_peer, M, N, K, a.stride(0), b.stride(0), ldc, int(a_mn),
+          int(b_mn), st.data_ptr(), lib.stream_ptr())
+
+
+def gemm_grouped(a, b, group_offsets, *, b_mn: bool = False, out=None, out_dtype=bf16):
+    """Ragged-row grouped GEMM.  a: [R,K] rows grouped by ``group_offsets`` (int32 [G+1],
+    multiples of 128, R % 128 == 0); b: [G,N,K] (or [G,K,N] when b_mn)."""
+    a = _row_major_2d(a)
+    G = b.shape[0]
+    R, K = a.shape
+    N = b.shape[2] if b_mn else b.shape[1]
+    b2 = b.reshape(-1, b.shape[-1])
+    if out is None:
+        out = torch.empty(R, N, dtype=out_dtype, device=a.device)
+    mode = 0 if out.dtype == bf16 else 1
+    st = lib.status_tensor(a.device)
+    _call("ob_gemm_bf16_grouped", a.data_ptr(), b2.data_ptr(), out.data_ptr(),
+          group_offsets.data_ptr(), G, R, N, K, a.stride(0), out.stride(0), int(b_mn), mode,
+          st.data_ptr(), lib.stream_ptr())
+    return out
+
+
+def gemm_grouped_wgrad(dy, x, group_offsets, out, accumulate: bool = True):
+    """out[g] (+)= dy[rows of g]^T x[rows of g]; dy [R,N], x [R,K], out fp32 [G,N,K]."""
+    dy = _row_major_2d(dy)
+    x = _row_major_2d(x)
+    G, N, K = out.shape
+    mode = (2 if accumulate else 1) if out.dtype == torch.float32 else 0
+    st = lib.status_tensor(dy.device)
+    _call("ob_gemm_bf16_grouped_wgrad", dy.data_ptr(), x.data_ptr(), out.data_ptr(),
+          group_offsets.data_ptr(), G, dy.shape[0], N, K, dy.stride(0), x.stride(0), mode,
+          st.data_ptr(), lib.stream_ptr())
+    return out
+
+
+def rmsnorm_fwd(x, w, eps, one_plus=False, want_rstd=True):
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = torch.empty_like(x2)
+    rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device) if want_rstd else None
+    _call("ob_rmsnorm_fwd", x2.data_ptr(), w.data_ptr(), y.data_ptr(), lib.ptr(rstd), x2.shape[0],
+          x2.shape[1], float(eps), int(one_plus), lib.stream_ptr())
+    return y.view(x.shape), rstd
+
+
+def rmsnorm_bwd(dy, x, w, rstd, eps, dw_out, one_plus=False):
+    x2 = x.reshape(-1, x.shape[-1])
+    dy2 = dy.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    if not dy2.is_contiguous():
+        dy2 = dy2.contiguous()
+    dx = torch.empty_like(x2)
+    _call("ob_rmsnorm_bwd", dy2.data_ptr(), x2.data_ptr(), w.data_ptr(), lib.ptr(rstd),
+          dx.data_ptr(), lib.ptr(dw_out), x2.shape[0], x2.shape[1], float(eps), int(one_plus),
+          lib.stream_ptr())
+    return dx.view(x.shape)
+
+
+def swiglu_fwd(gu):
+    g2 = gu.reshape(-1, gu.shape[-1])
+    F = g2.shape[1] // 2
+    act = torch.empty(g2.shape[0], F, dtype=gu.dtype, device=gu.device)
+    _call("ob_swiglu_fwd", g2.data_ptr(), act.data_ptr(), g2.shape[0], F, lib.stream_ptr())
+    return act.view(*gu.shape[:-1], F)
+
+
+def swiglu_bwd(gu, dact):
+    g2 = gu.reshape(-1, gu.shape[-1])
+    F = g2.shape[1] // 2
+    d2 = dact.reshape(-1, F)
+    if not d2.is_contiguous():
+        d2 = d2.contiguous()
+    dgu = torch.empty_like(g2)
+    _call("ob_swiglu_bwd", g2.data_ptr(), d2.data_ptr(), dgu.data_ptr(), None, g2.shape[0], F,
+          lib.stream_ptr())
+    return dgu.view(gu.shape)
+
+
+def qknorm_rope_fwd(qkv, qw, kw, cos, sin, H, G, K, rot, eps, one_plus=False, q_stride_heads=1):
+    M = qkv.shape[0]
+    q = torch.empty(M, H, K, dtype=qkv.dtype, device=qkv.device)
+    k = torch.empty(M, G, K, dtype=qkv.dtype, device=qkv.device)
+    _call("ob_qknorm_rope_fwd", qkv.data_ptr(), lib.ptr(qw), lib.ptr(kw), cos.data_ptr(),
+          sin.data_ptr(), q.data_ptr(), k.data_ptr(), M, H, G, K, rot, float(eps), int(one_plus),
+          q_stride_heads, lib.stream_ptr())
+    return q, k
+
+
+def qknorm_rope_bwd(qkv, qw, kw, cos, sin, dq, dk, dqkv, dqw, dkw, H, G, K, rot, eps,
+                    one_plus=False, q_stride_heads=1):
+    M = qkv.shape[0]
+    _call("ob_qknorm_rope_bwd", qkv.data_ptr(), lib.ptr(qw), lib.ptr(kw), cos.data_ptr(),
+          sin.data_ptr(), dq.data_ptr(), dk.data_ptr(), dqkv.data_ptr(), lib.ptr(dqw),
+          lib.ptr(dkw), M, H, G, K, rot, float(eps), int(one_plus), q_stride_heads,
+          lib.stream_ptr())
+
+
+def attn_fwd(q, k, v, cu_seqlens, max_seqlen, scale, causal, want_lse=True):
+    """q [N,H,K]; k,v [N,G,K] (row-strided views allowed).  Returns out [N,H,K], lse [H,N]."""
+    N, H, K = q.shape
+    G = k.shape[1]
+    for t in (q, k, v):
+        if t.stride(2) != 1 or t.stride(1) != K:
+            raise ValueError("attention operands need contiguous heads")
+    out = torch.empty(N, H, K, dtype=q.dtype, device=q.device)
+    lse = torch.empty(H, N, dtype=torch.float32, device=q.device) if want_lse else None
+    st = lib.status_tensor(q.device)
+    _call("ob_attn_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lib.ptr(lse),
+          cu_seqlens.data_ptr(), cu_seqlens.numel() - 1, int(max_seqlen), N, H, G, K, q.stride(0),
+          k.stride(0), v.stride(0), out.stride(0), float(scale), int(causal), st.data_ptr(),
+          lib.stream_ptr())
+    return out, lse
+
+
+def ce_fwd_bwd(logits, targets, mask, grad_scale, loss_sum, write_grad=True, lse_out=None):
+    R, V = logits.shape
+    _call("ob_ce_fwd_bwd", logits.data_ptr(), logits.stride(0), R, V, targets.data_ptr(),
+          lib.ptr(mask), lib.ptr(grad_scale), loss_sum.data_ptr(), lib.ptr(lse_out),
+          int(write_grad), lib.stream_ptr())
+
+
+def embedding_fwd(ids, table):
+    ids32 = ids.reshape(-1).to(torch.int32)
+    out = torch.empty(ids32.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    _call("ob_embedding_fwd", ids32.data_ptr(), table.data_ptr(), out.data_ptr(), ids32.numel(),
+          table.shape[1], lib.stream_ptr())
+    return out.view(*ids.shape, table.shape[1])
+
+
+def embedding_bwd(ids, dy, dtable_f32, row_lo=0, row_hi=None):
+    ids32 = ids.reshape(-1).to(torch.int32)
+    d2 = dy.reshape(-1, dy.shape[-1])
+    if not d2.is_contiguous():
+        d2 = d2.contiguous()
+    hi = dtable_f32.shape[0] + row_lo if row_hi is None else row_hi
+    _call("ob_embedding_bwd", ids32.data_ptr(), d2.data_ptr(), dtable_f32.data_ptr(),
+          ids32.numel(), d2.shape[1], row_lo, hi, lib.stream_ptr())
+
+
+def sumsq(g, out):
+    _call("ob_sumsq", g.data_ptr(), g.numel(), out.data_ptr(), lib.stream_ptr())
+
+
+def adamw(p, m, v, g, p16, *, lr, b1, b2, eps, wd, step, grad_mul=1.0, norm_sq=None,
+          max_norm=0.0, zero_grad=True):
+    bc1 = 1.0 - b1 ** step
+    bc2 = 1.0 - b2 ** step
+    _call("ob_adamw", p.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), lib.ptr(p16),
+          p.numel(), float(lr), float(b1), float(b2), float(eps), float(wd), float(bc1),
+          float(bc2), float(grad_mul), lib.ptr(norm_sq), float(max_norm), int(zero_grad),
+          lib.stream_ptr())
+
+
+def cast_f32_bf16(src, dst):
+    _call("ob_cast_f32_bf16", src.data_ptr(), dst.data_ptr(), src.numel(), lib.stream_ptr())
+
+
+def transpose(src):
+    R, C = src.shape
+    dst = torch.empty(C, R, dtype=src.dtype, device=src.device)
+    _call("ob_transpose_bf16", src.data_ptr(), dst.data_ptr(), R, C, src.stride(0), dst.stride(0),
+          lib.stream_ptr())
+    return dst
+
+
+def l2_flush(buf):
+    _call("ob_l2_flush", buf.data_ptr(), buf.numel() * buf.element_size(), lib.stream_ptr())

@@ -1,0 +1,130 @@
+"""ctypes binding of ``libomegalax_b200.so`` (the hand-written sm_100a kernels).
+
+The library is located next to this file.  It is loaded lazily the first time a CUDA op
+is requested; on a machine with a GPU a missing library is an error (ops never fall back
+silently to another implementation on CUDA tensors).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from pathlib import Path
+
+import torch
+
+_HERE = Path(__file__).resolve().parent
+LIB_PATH = _HERE / "libomegalax_b200.so"
+
+_lib = None
+_status = {}
+
+P = c_void_p
+I = c_int
+L = c_longlong
+F = c_float
+
+_SIGS = {
+    "ob_gemm_bf16": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P, P],
+    "ob_gemm_bf16_peer_reduce": [P, P, P, I, I, I, I, I, L, L, L, I, I, P, P],
+    "ob_gemm_bf16_grouped": [P, P, P, P, I, I, I, I, L, L, I, I, P, P],
+    "ob_gemm_bf16_grouped_wgrad": [P, P, P, P, I, I, I, I, L, L, I, P, P],
+    "ob_attn_fwd": [P, P, P, P, P, P, I, I, L, I, I, I, L, L, L, L, F, I, P, P],
+    "ob_rmsnorm_fwd": [P, P, P, P, L, I, F, I, P],
+    "ob_rmsnorm_bwd": [P, P, P, P, P, P, L, I, F, I, P],
+    "ob_swiglu_fwd": [P, P, L, I, P],
+    "ob_swiglu_bwd": [P, P, P, P, L, I, P],
+    "ob_qknorm_rope_fwd": [P, P, P, P, P, P, P, L, I, I, I, I, F, I, I, P],
+    "ob_qknorm_rope_bwd": [P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, F, I, I, P],
+    "ob_ce_fwd_bwd": [P, L, L, I, P, P, P, P, P, I, P],
+    "ob_embedding_fwd": [P, P, P, L, I, P],
+    "ob_embedding_bwd": [P, P, P, L, I, I, I, P],
+    "ob_sumsq": [P, L, P, P],
+    "ob_adamw": [P, P, P, P, P, L, F, F, F, F, F, F, F, F, P, F, I, P],
+    "ob_cast_f32_bf16": [P, P, L, P],
+    "ob_transpose_bf16": [P, P, I, I, L, L, P],
+    "ob_l2_flush": [P, L, P],
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def available() -> bool:
+    return LIB_PATH.exists()
+
+
+def load():
+    """Load the shared library (building it first when a compiler is present)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        if os.environ.get("OMEGALAX_B200_NO_BUILD") != "1":
+            from . import build as _build
+
+            _build.build()
+    if not LIB_PATH.exists():
+        raise KernelError(
+            f"{LIB_PATH} is missing: run `python -m omegalax_b200.ops.build` (needs nvcc) first"
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, sig in _SIGS.items():
+        if hasattr(lib, name):
+            fn = getattr(lib, name)
+            fn.argtypes = sig
+            fn.restype = c_int
+    _lib = lib
+    return lib
+
+
+def register(name: str, sig) -> None:
+    """Declare the signature of an additional exported launcher."""
+    _SIGS[name] = sig
+    if _lib is not None and hasattr(_lib, name):
+        fn = getattr(_lib, name)
+        fn.argtypes = sig
+        fn.restype = c_int
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def status_tensor(device) -> torch.Tensor:
+    """Per-device int32 word that kernels set when a bounded wait gives up."""
+    dev = torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
+        _status[key] = t
+    return t
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if any kernel recorded a wait timeout since the last check."""
+    for key, t in list(_status.items()):
+        if device is not None and torch.device(device).index not in (None, key):
+            continue
+        v = int(t[0].item())
+        if v != 0:
+            t.zero_()
+            raise KernelError(
+                f"kernel reported status code {v & 0xFF} from block {v >> 8} on cuda:{key} "
+                "(1 stage-full wait, 2 stage-empty wait, 3/4 accumulator waits, 5 flag wait)"
+            )
+
+
+def call(name: str, *args) -> None:
+    lib = load()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        raise KernelError(f"{name} failed with code {rc}")
+
+
+def ptr(t):
+    if t is None:
+        return None
+    return t.data_ptr()
