@@ -1,0 +1,247 @@
+"""Headline benchmark: SFT training throughput of Qwen3-8B (bf16 compute, fp32 master AdamW,
+FSDP over the N GPUs of one node), sequence length 4096, 8 sequences per GPU (global batch
+64 at N=8, weak scaling), synthetic uniform-random token ids with a 50 % prompt-masked loss.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 5 --warmup 3
+
+Prints one JSON line (rank 0).  ``value`` is total tokens/s over all GPUs for K optimizer
+steps timed with CUDA events (max over ranks) with the batches already on the device;
+``e2e`` is the same quantity through ``trainers.text.make_sft_train_step`` including the
+pinned-host -> device copy of every batch and a device -> host read of every step's loss.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "sft_train_tokens_per_sec"
+MODEL_ID = "Qwen/Qwen3-8B"
+SEQ_LEN = 4096
+SEQS_PER_GPU = 8
+
+
+def reference_arm(args) -> int:
+    """The reference is a JAX/Flax program; jax, flax, optax, orbax, grain and the tokamax fork
+    are not installable offline here, so its arm reports itself unavailable."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    why = "reference needs jax/flax/optax/orbax/grain/tokamax, none installed and no index access"
+    if os.path.isdir(os.path.join(ref_dir, "omegalax")):
+        try:
+            sys.path.insert(0, ref_dir)
+            import jax  # noqa: F401
+        except Exception as e:  # pragma: no cover - depends on the box
+            why = f"reference sources installed under baseline/_ref but its runtime is missing: {type(e).__name__}: {e}"[:300]
+        else:  # pragma: no cover
+            why = "jax is importable but the reference run harness is not enabled in this build"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.path = tempfile.NamedTemporaryFile(prefix="clocks_", suffix=".csv", delete=False).name
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path).read().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        try:
+            os.unlink(self.path)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="debug only: truncate the layer stack")
+    ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
+    ap.add_argument("--micro-seqs", type=int, default=None, help="sequences per GPU per micro-batch")
+    ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import dataclasses
+
+    import torch
+    import torch.distributed as dist
+
+    from omegalax_b200.ops import kernels as K
+    from omegalax_b200.ops import lib
+    from omegalax_b200.parallel import mesh as mesh_lib
+    from omegalax_b200.text import api as text_api
+    from omegalax_b200.trainers import text as trainer
+    from omegalax_b200.trainers.perf import PEAK_TFLOPS, training_flops_per_token
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    mesh_lib.init_distributed("nccl")
+    rank = mesh_lib.rank()
+    N = max(world, 1)
+
+    cfg = text_api.resolve_config(MODEL_ID)
+    if args.layers is not None:
+        cfg = dataclasses.replace(cfg, num_layers=args.layers)
+    micro = args.micro_seqs or (4 if N == 1 else args.seqs_per_gpu)
+    micro = min(micro, args.seqs_per_gpu)
+    accum = args.seqs_per_gpu // micro
+    T = args.seq_len
+    tcfg = trainer.TrainConfig(seed=0, batch_size=micro * N, seq_len=T, num_steps=10_000, learning_rate=1e-5,
+                               weight_decay=0.01, warmup_steps=0, lr_schedule="linear", max_grad_norm=1.0,
+                               grad_accum_steps=accum)
+    mesh = mesh_lib.ensure_mesh(tp_size=1, fsdp_size=N, dp_size=1)
+    model, cfg = trainer.init_model(cfg, 0, tp_size=1, fsdp_size=N, dp_size=1, meta=True)
+    opt = trainer.build_optimizer(model, tcfg, device=device)
+    step_fn = trainer.make_sft_train_step(cfg, pad_id=0)
+
+    # synthetic data in pinned host memory: a pool of distinct micro-batches
+    g = torch.Generator().manual_seed(1234 + rank)
+    pool = []
+    for _ in range(4):
+        tok = torch.randint(1, cfg.vocab_size, (micro, T), generator=g, dtype=torch.int32).pin_memory()
+        lm = torch.zeros(micro, T, dtype=torch.int32)
+        lm[:, T // 2:] = 1
+        pool.append({"token_ids_BT": tok, "attention_mask_BT": torch.ones(micro, T, dtype=torch.int32).pin_memory(),
+                     "loss_mask_BT": lm.pin_memory()})
+    h2d_bytes = sum(v.numel() * v.element_size() for v in pool[0].values()) * accum
+
+    def to_dev(b):
+        return {k: v.to(device, non_blocking=True) for k, v in b.items()}
+
+    def barrier():
+        if N > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one_step_e2e(i):
+        loss = None
+        for a in range(accum):
+            loss, _ = step_fn(opt, to_dev(pool[(i * accum + a) % len(pool)]))
+        return float(loss.item())  # device -> host read of the step's loss
+
+    for i in range(args.warmup):
+        one_step_e2e(i)
+    barrier()
+    lib.check_status()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
+    # ---- device-timed region: batches already on the device
+    dev_pool = [to_dev(b) for b in pool]
+    barrier()
+    K.reset_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        for a in range(accum):
+            step_fn(opt, dev_pool[(i * accum + a) % len(dev_pool)])
+    e1.record()
+    barrier()
+    launches = K.launch_count()
+    ms = e0.elapsed_time(e1)
+
+    # ---- end-to-end region
+    barrier()
+    t0 = time.perf_counter()
+    last_loss = 0.0
+    for i in range(args.steps):
+        last_loss = one_step_e2e(i)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else {}
+    lib.check_status()
+
+    t = torch.tensor([ms, e2e_s * 1000.0], device=device)
+    if N > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+    tokens_per_step = args.seqs_per_gpu * T * N
+    value = tokens_per_step * args.steps / (ms / 1000.0)
+    e2e_value = tokens_per_step * args.steps / (e2e_ms / 1000.0)
+    fpt = training_flops_per_token(cfg, T)
+    tflops_per_gpu = value / N * fpt / 1e12
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": N, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+            "config": {"model": MODEL_ID if args.layers is None else f"{MODEL_ID}[{args.layers} layers]",
+                       "global_batch": args.seqs_per_gpu * N, "seq_len": T, "parallelism": f"fsdp{N}",
+                       "micro_batch_per_gpu": micro, "grad_accum": accum, "optimizer": "AdamW fp32 master",
+                       "remat": "full", "l2": "inputs larger than L2 (16 GB of weights per step)"},
+            "tokens_per_sec_per_gpu": value / N, "tflops_per_gpu": tflops_per_gpu,
+            "mfu_of_measured_burst": tflops_per_gpu / PEAK_TFLOPS["b200_measured_burst"],
+            "mfu_of_nominal": tflops_per_gpu / PEAK_TFLOPS["b200"],
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,
+                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches, "final_loss": last_loss,
+        }
+        print(json.dumps(out), flush=True)
+    if N > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,341 @@
+"""Differentiable ops used by the models.
+
+Each op has two implementations: the hand-written sm_100a kernels (taken for CUDA bf16
+tensors) and the plain-PyTorch definition in ``reference.py`` (CPU, fp32, oracle).  On a
+CUDA bf16 tensor the kernel path is the only one; there is no silent fallback.
+
+Weight gradients: when a weight tensor carries a ``main_grad`` attribute (an fp32 buffer
+owned by the sharded train state), the backward accumulates straight into it with the
+GEMM's fp32-accumulate epilogue and returns no autograd gradient for the weight.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from . import kernels as K
+from . import reference as R
+
+bf16 = torch.bfloat16
+
+
+def use_kernels(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dtype == bf16 and os.environ.get("OMEGALAX_B200_REFERENCE_OPS") != "1"
+
+
+def _acc_main_grad(w, fn_into, fn_new):
+    """Accumulate into w.main_grad when present (returns None), else return a new grad."""
+    mg = getattr(w, "main_grad", None)
+    if mg is not None:
+        fn_into(mg)
+        return None
+    return fn_new()
+
+
+# ----------------------------------------------------------------------------- linear
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, residual):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        y = K.gemm(x2, w, residual=residual)
+        ctx.save_for_backward(x2, w)
+        ctx.shp = shp
+        ctx.has_res = residual is not None
+        ctx.w_ref = w
+        return y.view(*shp[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        w_obj = ctx.w_ref
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = K.gemm(dy2, w, b_mn=True).view(ctx.shp)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dw = _acc_main_grad(
+                w_obj,
+                lambda mg: K.gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=True),
+                lambda: K.gemm(dy2, x2, a_mn=True, b_mn=True),
+            )
+        return dx, dw, (dy if ctx.has_res else None)
+
+
+def linear(x, w, residual=None, bias=None):
+    """y = x @ w.T (+ bias) (+ residual); w is [out, in]."""
+    if use_kernels(x) and w.dtype == bf16:
+        y = _LinearFn.apply(x, w, residual if bias is None else None)
+        if bias is not None:
+            y = y + bias
+            if residual is not None:
+                y = y + residual
+        return y
+    y = torch.nn.functional.linear(x, w.to(x.dtype), None if bias is None else bias.to(x.dtype))
+    if residual is not None:
+        y = y + residual
+    return y
+
+
+# ----------------------------------------------------------------------------- rmsnorm
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps, one_plus):
+        y, rstd = K.rmsnorm_fwd(x, w, eps, one_plus)
+        ctx.save_for_backward(x, w, rstd)
+        ctx.eps, ctx.one_plus, ctx.w_ref = eps, one_plus, w
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd = ctx.saved_tensors
+        mg = getattr(ctx.w_ref, "main_grad", None)
+        if mg is not None:
+            dx = K.rmsnorm_bwd(dy, x, w, rstd, ctx.eps, mg, ctx.one_plus)
+            return dx, None, None, None
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        dx = K.rmsnorm_bwd(dy, x, w, rstd, ctx.eps, dw, ctx.one_plus)
+        return dx, dw.to(w.dtype), None, None
+
+
+def rmsnorm(x, w, eps: float, one_plus: bool = False, scale_in_dtype: bool = False):
+    if use_kernels(x) and w.dtype == bf16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192:
+        return _RMSNormFn.apply(x, w, eps, one_plus)
+    return R.rmsnorm(x, w, eps, one_plus, scale_in_dtype)
+
+
+# ----------------------------------------------------------------------------- swiglu
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        ctx.save_for_backward(gu)
+        return K.swiglu_fwd(gu)
+
+    @staticmethod
+    def backward(ctx, dact):
+        (gu,) = ctx.saved_tensors
+        return K.swiglu_bwd(gu, dact)
+
+
+def swiglu(gu):
+    """gu = [gate | up] on the last dim -> silu(gate) * up."""
+    if use_kernels(gu) and gu.shape[-1] % 16 == 0:
+        return _SwiGLUFn.apply(gu.contiguous())
+    return R.swiglu(gu)
+
+
+# ----------------------------------------------------------------------------- embedding
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table):
+        ctx.save_for_backward(ids)
+        ctx.t_ref = table
+        return K.embedding_fwd(ids, table)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        t = ctx.t_ref
+        mg = getattr(t, "main_grad", None)
+        if mg is not None:
+            K.embedding_bwd(ids, dy, mg)
+            return None, None
+        g = torch.zeros(t.shape, dtype=torch.float32, device=t.device)
+        K.embedding_bwd(ids, dy, g)
+        return None, g.to(t.dtype)
+
+
+def embedding(ids, table):
+    if table.is_cuda and table.dtype == bf16 and use_kernels(table) and table.shape[1] % 8 == 0:
+        return _EmbeddingFn.apply(ids, table)
+    return torch.nn.functional.embedding(ids.long(), table)
+
+
+# ----------------------------------------------------------------------------- qk-norm + rope
+class _QKNormRopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, qw, kw, cos, sin, H, G, Kd, rot, eps, one_plus, q_stride_heads):
+        q, k = K.qknorm_rope_fwd(qkv, qw, kw, cos, sin, H, G, Kd, rot, eps, one_plus, q_stride_heads)
+        ctx.save_for_backward(qkv, qw, kw, cos, sin)
+        ctx.cfg = (H, G, Kd, rot, eps, one_plus, q_stride_heads)
+        ctx.qw_ref, ctx.kw_ref = qw, kw
+        return q, k
+
+    @staticmethod
+    def backward(ctx, dq, dk):
+        qkv, qw, kw, cos, sin = ctx.saved_tensors
+        H, G, Kd, rot, eps, one_plus, qs = ctx.cfg
+        dqkv = torch.zeros_like(qkv) if qs != 1 else torch.empty_like(qkv)
+        if qs == 1:
+            dqkv.view(qkv.shape[0], H + 2 * G, Kd)[:, H + G:].zero_()
+        dqw = dkw = None
+        qmg = getattr(ctx.qw_ref, "main_grad", None) if qw is not None else None
+        kmg = getattr(ctx.kw_ref, "main_grad", None) if kw is not None else None
+        if qw is not None:
+            dqw_buf = qmg if qmg is not None else torch.zeros(Kd, dtype=torch.float32, device=qkv.device)
+            dkw_buf = kmg if kmg is not None else torch.zeros(Kd, dtype=torch.float32, device=qkv.device)
+        else:
+            dqw_buf = dkw_buf = None
+        K.qknorm_rope_bwd(qkv, qw, kw, cos, sin, dq.contiguous(), dk.contiguous(), dqkv, dqw_buf,
+                          dkw_buf, H, G, Kd, rot, eps, one_plus, qs)
+        if qw is not None and qmg is None:
+            dqw = dqw_buf.to(qw.dtype)
+        if kw is not None and kmg is None:
+            dkw = dkw_buf.to(kw.dtype)
+        return dqkv, dqw, dkw, None, None, None, None, None, None, None, None, None
+
+
+def qk_norm_rope(qkv, qw, kw, sin, cos, H: int, G: int, Kd: int, rot: int | None = None,
+                 eps: float = 1e-6, one_plus: bool = False, q_stride_heads: int = 1,
+                 scale_in_dtype: bool = False):
+    """Split a fused projection [M, (H*q_stride_heads + 2G) * Kd] into q, k, v; apply the
+    per-head RMSNorm (weights may be None) and rotate-half RoPE on the first ``rot`` channels.
+
+    sin/cos: fp32 [M, rot/2].  With ``q_stride_heads == 2`` every q head is followed by a
+    gate head of the same width (gated attention); the gates are returned as a 4th value.
+    Returns q [M,H,Kd], k [M,G,Kd], v [M,G,Kd] (a strided view), gate or None.
+    """
+    rot = Kd if rot is None else rot
+    M = qkv.shape[0]
+    qw_total = H * Kd * q_stride_heads
+    v = qkv[:, qw_total + G * Kd:].view(M, G, Kd)
+    gate = None
+    if q_stride_heads == 2:
+        gate = qkv[:, :qw_total].view(M, H, 2, Kd)[:, :, 1]
+    if use_kernels(qkv) and (qw is None or qw.dtype == bf16):
+        q, k = _QKNormRopeFn.apply(qkv, qw, kw, cos.contiguous(), sin.contiguous(), H, G, Kd, rot,
+                                   eps, one_plus, q_stride_heads)
+        return q, k, v, gate
+    if q_stride_heads == 2:
+        q = qkv[:, :qw_total].view(M, H, 2, Kd)[:, :, 0]
+    else:
+        q = qkv[:, :qw_total].view(M, H, Kd)
+    k = qkv[:, qw_total:qw_total + G * Kd].view(M, G, Kd)
+    if qw is not None:
+        q = R.rmsnorm(q, qw, eps, one_plus, scale_in_dtype)
+        k = R.rmsnorm(k, kw, eps, one_plus, scale_in_dtype)
+    q = R.apply_rope(q, sin, cos, rot)
+    k = R.apply_rope(k, sin, cos, rot)
+    return q, k, v, gate
+
+
+# ----------------------------------------------------------------------------- attention
+_ATTN_BWD_IMPL = {"impl": None}
+
+
+def _attn_bwd_dispatch(q, k, v, o, lse, do, cu_seqlens, max_seqlen, scale, causal):
+    """dq, dk, dv of packed-row attention."""
+    if hasattr(K, "attn_bwd") and os.environ.get("OMEGALAX_B200_ATTN_BWD", "sm100") == "sm100":
+        return K.attn_bwd(q, k, v, o, lse, do, cu_seqlens, max_seqlen, scale, causal)
+    # recompute through the PyTorch definition (reference quality; used only until the
+    # tcgen05 backward is selected)
+    with torch.enable_grad():
+        qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, k, v))
+        N, H, Kd = q.shape
+        G = k.shape[1]
+        B = cu_seqlens.numel() - 1
+        if N == B * max_seqlen:
+            out = torch.nn.functional.scaled_dot_product_attention(
+                qq.view(B, max_seqlen, H, Kd).transpose(1, 2),
+                kk.reshape(B, max_seqlen, G, Kd).transpose(1, 2),
+                vv.reshape(B, max_seqlen, G, Kd).transpose(1, 2),
+                is_causal=bool(causal), scale=scale, enable_gqa=True,
+            ).transpose(1, 2).reshape(N, H, Kd)
+        else:
+            out = R.attention_varlen(qq, kk, vv, cu_seqlens, causal=bool(causal), scale=scale)
+        return torch.autograd.grad(out, (qq, kk, vv), do)
+
+
+class _FlashAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, scale, causal):
+        o, lse = K.attn_fwd(q, k, v, cu_seqlens, max_seqlen, scale, causal)
+        ctx.save_for_backward(q, k, v, o, lse, cu_seqlens)
+        ctx.cfg = (max_seqlen, scale, causal)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse, cu = ctx.saved_tensors
+        max_seqlen, scale, causal = ctx.cfg
+        dq, dk, dv = _attn_bwd_dispatch(q, k, v, o, lse, do.contiguous(), cu, max_seqlen, scale, causal)
+        return dq, dk, dv, None, None, None, None
+
+
+def flash_attention(q, k, v, cu_seqlens, max_seqlen: int, *, scale: float, causal: bool):
+    """Packed-row attention.  q [N,H,Kd]; k, v [N,G,Kd]; cu_seqlens int32 [B+1]."""
+    if use_kernels(q) and q.shape[-1] in (64, 128):
+        return _FlashAttnFn.apply(q, k, v, cu_seqlens, int(max_seqlen), float(scale), bool(causal))
+    return R.attention_varlen(q, k, v, cu_seqlens, causal=causal, scale=scale)
+
+
+# ----------------------------------------------------------------------------- linear + CE
+class _LinearCEFn(torch.autograd.Function):
+    """loss = grad-ready fused  sum_rows mask * nll(h W^T) * scale.
+
+    The logits exist only one row-chunk at a time (bf16, chunk x V).  The gradients with
+    respect to h and W are produced in the same sweep (three GEMMs per chunk), so the
+    backward only rescales; dW goes straight into ``w.main_grad`` when it exists.
+    """
+
+    @staticmethod
+    def forward(ctx, h, w, targets, mask, scale_t, chunk):
+        M, D = h.shape
+        V = w.shape[0]
+        dev = h.device
+        loss_sum = torch.zeros(1, dtype=torch.float32, device=dev)
+        need_grad = h.requires_grad or w.requires_grad
+        mg = getattr(w, "main_grad", None)
+        dh = torch.empty_like(h) if need_grad else None
+        dw = None
+        if need_grad and w.requires_grad:
+            dw = mg if mg is not None else torch.zeros(V, D, dtype=torch.float32, device=dev)
+        t32 = targets.to(torch.int32).contiguous()
+        mk = mask.to(torch.float32).contiguous()
+        logits = torch.empty(min(chunk, M), V, dtype=bf16, device=dev)
+        for r0 in range(0, M, chunk):
+            r1 = min(M, r0 + chunk)
+            lg = logits[: r1 - r0]
+            hc = h[r0:r1]
+            K.gemm(hc, w, out=lg)
+            K.ce_fwd_bwd(lg, t32[r0:r1], mk[r0:r1], scale_t, loss_sum, write_grad=need_grad)
+            if need_grad:
+                K.gemm(lg, w, b_mn=True, out=dh[r0:r1])
+                if dw is not None:
+                    K.gemm(lg, hc, a_mn=True, b_mn=True, out=dw, accumulate=True)
+        ctx.save_for_backward(dh)
+        ctx.dw = None if (mg is not None or dw is None) else dw
+        ctx.w_dtype = w.dtype
+        return (loss_sum * scale_t).squeeze(0)
+
+    @staticmethod
+    def backward(ctx, g):
+        (dh,) = ctx.saved_tensors
+        dw = ctx.dw
+        gh = None if dh is None else (dh * g.to(dh.dtype))
+        gw = None if dw is None else (dw * g).to(ctx.w_dtype)
+        return gh, gw, None, None, None, None
+
+
+def linear_cross_entropy(h, w, targets, mask, scale, chunk: int = 4096):
+    """scale * sum_i mask_i * CE(h_i W^T, targets_i).
+
+    h [M,D], w [V,D], targets [M] int, mask [M]; ``scale`` is a float or a 1-element fp32
+    tensor (e.g. 1 / number of supervised tokens, computed on the device).  On the kernel
+    path the gradient is produced during the forward sweep and assumes this loss is
+    differentiated with an upstream gradient of one when ``w.main_grad`` is in use.
+    """
+    if not torch.is_tensor(scale):
+        scale = torch.tensor([float(scale)], dtype=torch.float32, device=h.device)
+    scale = scale.reshape(1).to(torch.float32)
+    if use_kernels(h) and w.dtype == bf16 and w.shape[0] % 8 == 0:
+        return _LinearCEFn.apply(h.contiguous(), w, targets, mask, scale, chunk)
+    total = h.new_zeros((), dtype=torch.float32)
+    for r0 in range(0, h.shape[0], chunk):
+        r1 = min(h.shape[0], r0 + chunk)
+        total = total + R.cross_entropy_sum(h[r0:r1], w, targets[r0:r1], mask[r0:r1])
+    return total * scale.squeeze(0)

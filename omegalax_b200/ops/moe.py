@@ -1,0 +1,131 @@
+"""Token-choice mixture-of-experts: routing, permutation, grouped expert MLP, combine.
+
+Only the k selected experts of every token are evaluated (the reference evaluates every
+expert for every token and then gathers, omegalax/models/qwen3/model.py:92-118; the
+selected-expert math is identical).  On CUDA bf16 the expert MLPs run on the grouped
+tcgen05 GEMM over rows permuted into per-expert segments padded to multiples of 128.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import functional as Fn
+from . import kernels as K
+from . import reference as R
+
+bf16 = torch.bfloat16
+PAD = 128
+
+
+def route(router_logits, top_k: int, renormalize: bool):
+    """fp32 softmax over experts, top-k, optional renormalisation with clip(sum, 1e-9).
+    Returns probs [M,E] fp32, weights [M,k] fp32, indices [M,k] int64."""
+    probs = torch.softmax(router_logits.float(), dim=-1)
+    w, idx = torch.topk(probs, top_k, dim=-1)
+    if renormalize:
+        w = w / w.sum(-1, keepdim=True).clamp_min(1e-9)
+    return probs, w, idx
+
+
+def load_balance_loss_qwen3(probs, idx, num_experts: int, coef: float):
+    """coef * E * sum_e (fraction of (token,slot) picks of e per token) * mean prob of e,
+    over all tokens including padding (omegalax/models/qwen3/model.py:120-124)."""
+    M = probs.shape[0]
+    counts = torch.zeros(num_experts, dtype=torch.float32, device=probs.device)
+    counts.scatter_add_(0, idx.reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=probs.device))
+    return coef * num_experts * torch.sum((counts / M) * probs.mean(0))
+
+
+def load_balance_loss_sq(probs, num_experts: int, coef: float):
+    """coef * sum_e (mean prob of e - 1/E)^2 (omegalax/models/qwen3_5/model.py:172-174)."""
+    return coef * torch.sum((probs.mean(0) - 1.0 / num_experts) ** 2)
+
+
+def build_permutation(idx, num_experts: int, pad: int = PAD):
+    """Sort (token, slot) pairs by expert into segments padded to multiples of ``pad``.
+
+    Returns
+      dest      [M*k] int64 : row of the padded buffer that pair p = token*k + slot goes to
+      offsets   [E+1] int32 : segment boundaries (multiples of pad)
+      capacity  int         : static row count of the padded buffer
+    No host synchronisation: the capacity is the worst case M*k + E*(pad-1) rounded up.
+    """
+    Mk = idx.numel()
+    flat = idx.reshape(-1)
+    counts = torch.bincount(flat, minlength=num_experts)
+    padded = (counts + pad - 1) // pad * pad
+    offsets = torch.zeros(num_experts + 1, dtype=torch.int64, device=idx.device)
+    offsets[1:] = padded.cumsum(0)
+    order = torch.argsort(flat, stable=True)
+    starts_unpadded = counts.cumsum(0) - counts
+    sorted_e = flat[order]
+    rank_in_e = torch.arange(Mk, device=idx.device) - starts_unpadded[sorted_e]
+    dest_sorted = offsets[sorted_e] + rank_in_e
+    dest = torch.empty_like(dest_sorted)
+    dest[order] = dest_sorted
+    capacity = (Mk + num_experts * (pad - 1) + pad - 1) // pad * pad
+    return dest, offsets.to(torch.int32), capacity
+
+
+class _GroupedLinearFn(torch.autograd.Function):
+    """y[rows of e] = x[rows of e] @ w[e].T for w [E,N,K]."""
+
+    @staticmethod
+    def forward(ctx, x, w, offsets):
+        y = K.gemm_grouped(x, w, offsets)
+        ctx.save_for_backward(x, w, offsets)
+        ctx.w_ref = w
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, offsets = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = K.gemm_grouped(dy, w, offsets, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(ctx.w_ref, "main_grad", None)
+            if mg is not None:
+                K.gemm_grouped_wgrad(dy, x, offsets, mg, accumulate=True)
+            else:
+                dwf = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+                K.gemm_grouped_wgrad(dy, x, offsets, dwf, accumulate=False)
+                dw = dwf.to(w.dtype)
+        return dx, dw, None
+
+
+def grouped_linear(x, w, offsets):
+    return _GroupedLinearFn.apply(x, w, offsets)
+
+
+def expert_mlp_permuted(xp, w_gate_up, w_down, offsets):
+    """SwiGLU expert MLP on rows already grouped by expert (padded layout)."""
+    gu = grouped_linear(xp, w_gate_up, offsets)
+    act = Fn.swiglu(gu)
+    return grouped_linear(act, w_down, offsets)
+
+
+def moe_mlp(x, weights, idx, w_gate_up, w_down):
+    """Routed SwiGLU experts.  x [M,D]; weights/idx [M,k]; w_gate_up [E,2F,D] with rows
+    [gate | up]; w_down [E,D,F].  Returns [M,D] = sum_k weights * expert_{idx}(x)."""
+    M, D = x.shape
+    E = w_gate_up.shape[0]
+    k = idx.shape[1]
+    if Fn.use_kernels(x) and w_gate_up.dtype == bf16 and D % 64 == 0:
+        dest, offsets, cap = build_permutation(idx, E)
+        xp = torch.zeros(cap, D, dtype=x.dtype, device=x.device)
+        src_tok = torch.arange(M, device=x.device).repeat_interleave(k)
+        xp = xp.index_copy(0, dest, x.index_select(0, src_tok))
+        yp = expert_mlp_permuted(xp, w_gate_up, w_down, offsets)
+        y = yp.index_select(0, dest).view(M, k, D)
+        return (y.float() * weights.unsqueeze(-1)).sum(1).to(x.dtype)
+    out = torch.zeros(M, D, dtype=torch.float32, device=x.device)
+    for e in range(E):
+        tok, slot = torch.nonzero(idx == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        xe = x.index_select(0, tok)
+        gu = xe @ w_gate_up[e].to(x.dtype).t()
+        ye = R.swiglu(gu) @ w_down[e].to(x.dtype).t()
+        out.index_add_(0, tok, ye.float() * weights[tok, slot].unsqueeze(-1))
+    return out.to(x.dtype)

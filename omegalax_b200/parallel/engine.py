@@ -1,0 +1,419 @@
+"""Sharded training state: fp32 master weights + AdamW moments sharded over the data ranks
+(ZeRO-3 / FSDP), bf16 compute copies gathered one unit (decoder layer) at a time, full
+rematerialisation of each unit in the backward, gradient reduce-scatter per unit, and a
+fused clip + AdamW + bf16 re-cast over the flat shard.
+
+One process drives one GPU.  With a single rank every collective degenerates to a no-op
+and the bf16 compute copy is simply the cast of the master buffer.
+
+Layout.  The model is cut into *units* (embedding, each decoder layer, final norm + head).
+Every parameter of a unit is split along dim 0 over the W shard ranks (parameters whose
+dim 0 does not divide evenly into 16-byte aligned slices stay replicated).  A rank's slice
+of all parameters of a unit is contiguous in its flat shard buffers:
+
+    master / exp_avg / exp_avg_sq / grad   fp32  [shard_numel]     (owned)
+    compute shard                          bf16  [shard_numel]     (peers read it)
+    gathered unit                          bf16  per-parameter full tensors (transient)
+
+Reference behaviour being reproduced: parameters fp32, compute bf16, optimizer state fp32
+(omegalax/trainers/optim.py:11-41), every decoder layer rematerialised
+(omegalax/models/qwen3/model.py:140-150), parameters born sharded
+(omegalax/models/sharding_runtime.py:14-26).
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from ..ops import kernels as K
+
+bf16 = torch.bfloat16
+
+
+@dataclasses.dataclass
+class ParamSlot:
+    name: str
+    param: nn.Parameter
+    shape: tuple
+    numel: int
+    sharded: bool
+    shard_numel: int      # elements this rank owns (== numel when replicated)
+    shard_off: int        # offset inside the unit's shard buffers
+    full_off: int         # offset inside the unit's gathered buffer
+    module: nn.Module = None
+    pname: str = ""
+
+
+@dataclasses.dataclass
+class Unit:
+    name: str
+    modules: list
+    slots: list
+    shard_numel: int = 0
+    full_numel: int = 0
+    shard_base: int = 0   # offset of the unit in the rank-wide flat shard buffers
+    gathered: torch.Tensor | None = None
+    full_grad: torch.Tensor | None = None
+    resident: bool = False
+
+
+def _align(n: int, a: int = 8) -> int:
+    return (n + a - 1) // a * a
+
+
+def default_units(model: nn.Module) -> list[tuple[str, list[nn.Module]]]:
+    """Embedding, each decoder layer, then everything else (final norm, head, vision...)."""
+    if hasattr(model, "train_units"):
+        return model.train_units()
+    units = []
+    claimed = set()
+    for name in ("embedder", "embed_tokens"):
+        if hasattr(model, name):
+            units.append((name, [getattr(model, name)]))
+            claimed.add(name)
+    if hasattr(model, "layers"):
+        for i, layer in enumerate(model.layers):
+            units.append((f"layers.{i}", [layer]))
+        claimed.add("layers")
+    rest = [m for n, m in model.named_children() if n not in claimed]
+    if rest:
+        units.append(("head", rest))
+    return units
+
+
+class TrainEngine:
+    def __init__(self, model: nn.Module, *, device, shard_group=None, lr: float = 1e-4,
+                 weight_decay: float = 0.01, betas=(0.9, 0.999), eps: float = 1e-8,
+                 max_grad_norm: float | None = 1.0, remat: str = "full", seed: int = 0,
+                 init_from_model: bool = False, comm: str = "auto"):
+        self.model = model
+        self.device = torch.device(device)
+        self.group = shard_group
+        self.W = dist.get_world_size(shard_group) if shard_group is not None else 1
+        self.rank = dist.get_rank(shard_group) if shard_group is not None else 0
+        self.lr, self.wd, self.betas, self.eps = lr, weight_decay, betas, eps
+        self.max_grad_norm = max_grad_norm or 0.0
+        self.remat = remat
+        self.step_count = 0
+        self.micro_steps = 0
+        self.use_cuda_kernels = self.device.type == "cuda"
+        self.compute_dtype = bf16 if self.device.type == "cuda" else torch.float32
+        self.comm_kind = comm
+        self._build_units()
+        self._allocate()
+        self._materialize(seed, init_from_model)
+        self._install()
+
+    # ------------------------------------------------------------------ construction
+    def _build_units(self):
+        self.units: list[Unit] = []
+        seen = set()
+        for uname, mods in default_units(self.model):
+            slots = []
+            shard_off = full_off = 0
+            for mi, m in enumerate(mods):
+                for pname, p in m.named_parameters():
+                    if id(p) in seen:
+                        continue
+                    seen.add(id(p))
+                    shape = tuple(p.shape)
+                    numel = p.numel()
+                    rows = shape[0] if len(shape) else 1
+                    row_numel = numel // max(rows, 1)
+                    sharded = (self.W > 1 and len(shape) >= 1 and rows % self.W == 0
+                               and ((rows // self.W) * row_numel) % 8 == 0)
+                    sn = numel // self.W if sharded else numel
+                    slots.append(ParamSlot(f"{uname}.{mi}.{pname}", p, shape, numel, sharded, sn,
+                                           shard_off, full_off, m, pname))
+                    shard_off += _align(sn)
+                    full_off += _align(numel)
+            self.units.append(Unit(uname, mods, slots, shard_off, full_off))
+        base = 0
+        for u in self.units:
+            u.shard_base = base
+            base += u.shard_numel
+        self.total_shard = base
+
+    def _allocate(self):
+        dev = self.device
+        n = self.total_shard
+        self.master = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.grad = torch.zeros(n, dtype=torch.float32, device=dev)
+        if self.compute_dtype == torch.float32 and self.W == 1:
+            self.compute_shard = self.master  # CPU/fp32 path computes on the master directly
+        else:
+            self.compute_shard = self._alloc_compute_shard(n)
+        self.norm_sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        if self.W > 1:
+            layer_like = [u for u in self.units if u.name.startswith("layers.")]
+            self._ring_numel = max((u.full_numel for u in layer_like), default=0)
+            self._ring = [torch.empty(self._ring_numel, dtype=self.compute_dtype, device=dev) for _ in range(2)]
+            self._ring_grad = torch.zeros(self._ring_numel, dtype=torch.float32, device=dev) if self._ring_numel else None
+
+    def _alloc_compute_shard(self, n):
+        return torch.zeros(n, dtype=self.compute_dtype, device=self.device)
+
+    def _unit_views(self, u: Unit, flat: torch.Tensor):
+        return flat[u.shard_base:u.shard_base + u.shard_numel]
+
+    def _materialize(self, seed: int, init_from_model: bool):
+        """Fill the master shard: either from the values the model already holds, or by
+        running each module's own initialiser on a transient fp32 copy, one unit at a time."""
+        gen_devices = [self.device] if self.device.type == "cuda" else []
+        for ui, u in enumerate(self.units):
+            on_meta = any(s.param.device.type == "meta" for s in u.slots)
+            if on_meta or not init_from_model:
+                with torch.random.fork_rng(devices=gen_devices):
+                    torch.manual_seed(seed * 100003 + ui)
+                    for m in u.modules:
+                        if on_meta:
+                            m.to_empty(device=self.device)
+                            for s in u.slots:  # to_empty replaces meta Parameters by new objects
+                                if s.module is m:
+                                    s.param = m.get_parameter(s.pname)
+                        for p in m.parameters():
+                            p.data = p.data.to(device=self.device, dtype=torch.float32)
+                        for sub in m.modules():
+                            if hasattr(sub, "reset_parameters"):
+                                sub.reset_parameters()
+            mshard = self._unit_views(u, self.master)
+            for s in u.slots:
+                src = s.param.data.detach().to(device=self.device, dtype=torch.float32).reshape(-1)
+                if s.sharded:
+                    src = src[self.rank * s.shard_numel:(self.rank + 1) * s.shard_numel]
+                mshard[s.shard_off:s.shard_off + s.shard_numel].copy_(src)
+            for s in u.slots:  # drop the transient full-precision copy
+                s.param.data = torch.empty(0, dtype=self.compute_dtype, device=self.device)
+        self._refresh_compute_shard()
+
+    def _refresh_compute_shard(self):
+        if self.compute_shard is self.master:
+            return
+        if self.use_cuda_kernels and self.compute_dtype == bf16:
+            K.cast_f32_bf16(self.master, self.compute_shard)
+        else:
+            self.compute_shard.copy_(self.master)
+
+    def _install(self):
+        """Point every parameter at its compute storage and attach ``main_grad``."""
+        for u in self.units:
+            if self.W == 1:
+                cs = self._unit_views(u, self.compute_shard)
+                gs = self._unit_views(u, self.grad)
+                for s in u.slots:
+                    s.param.data = cs[s.shard_off:s.shard_off + s.numel].view(s.shape)
+                    s.param.main_grad = gs[s.shard_off:s.shard_off + s.numel].view(s.shape)
+                u.resident = True
+            else:
+                is_layer = u.name.startswith("layers.")
+                if not is_layer:  # embedding / head stay gathered between optimizer steps
+                    u.gathered = torch.empty(u.full_numel, dtype=self.compute_dtype, device=self.device)
+                    u.full_grad = torch.zeros(u.full_numel, dtype=torch.float32, device=self.device)
+                    self._bind(u, u.gathered, u.full_grad)
+                    self._all_gather(u, u.gathered)
+                    u.resident = True
+        if hasattr(self.model, "layer_runner"):
+            self.model.layer_runner = self.run_layer
+        self._layer_units = {id(u.modules[0]): u for u in self.units if u.name.startswith("layers.")}
+
+    def _bind(self, u: Unit, full: torch.Tensor, full_grad: torch.Tensor | None):
+        for s in u.slots:
+            s.param.data = full[s.full_off:s.full_off + s.numel].view(s.shape)
+            if full_grad is not None:
+                s.param.main_grad = full_grad[s.full_off:s.full_off + s.numel].view(s.shape)
+
+    # ------------------------------------------------------------------ collectives
+    def _all_gather(self, u: Unit, full: torch.Tensor):
+        """Gather every parameter of the unit into its full tensor inside ``full``."""
+        cs = self._unit_views(u, self.compute_shard)
+        if self.W == 1:
+            return
+        stage = torch.empty(self.W * u.shard_numel, dtype=self.compute_dtype, device=self.device)
+        dist.all_gather_into_tensor(stage, cs, group=self.group)
+        st = stage.view(self.W, u.shard_numel)
+        for s in u.slots:
+            dst = full[s.full_off:s.full_off + s.numel]
+            if s.sharded:
+                dst.view(self.W, s.shard_numel).copy_(st[:, s.shard_off:s.shard_off + s.shard_numel])
+            else:
+                dst.copy_(st[self.rank, s.shard_off:s.shard_off + s.numel])
+
+    def _reduce_scatter(self, u: Unit, full_grad: torch.Tensor):
+        """Sum the unit's full fp32 gradients over ranks into this rank's grad shard."""
+        gs = self._unit_views(u, self.grad)
+        stage = torch.empty(self.W, u.shard_numel, dtype=torch.float32, device=self.device)
+        for s in u.slots:
+            src = full_grad[s.full_off:s.full_off + s.numel]
+            if s.sharded:
+                stage[:, s.shard_off:s.shard_off + s.shard_numel].copy_(src.view(self.W, s.shard_numel))
+            else:  # replicated parameter: every rank receives the full sum / W slices summed later
+                stage[:, s.shard_off:s.shard_off + s.numel].copy_(src.unsqueeze(0).expand(self.W, -1))
+        out = torch.empty(u.shard_numel, dtype=torch.float32, device=self.device)
+        dist.reduce_scatter_tensor(out, stage.view(-1), op=dist.ReduceOp.SUM, group=self.group)
+        gs.add_(out)
+        full_grad.zero_()
+
+    # ------------------------------------------------------------------ layer execution
+    def run_layer(self, layer, x, ctx):
+        u = self._layer_units[id(layer)]
+        if self.remat == "none" and self.W == 1:
+            return layer(x, ctx)
+        return _RematLayerFn.apply(x, self, u, layer, ctx)
+
+    def _acquire(self, u: Unit):
+        if u.resident:
+            return
+        idx = int(u.name.split(".")[1]) & 1
+        full = self._ring[idx]
+        self._bind(u, full, self._ring_grad)
+        self._all_gather(u, full)
+
+    def _release_grads(self, u: Unit):
+        """After a unit's backward: fold stray autograd grads, then reduce-scatter."""
+        for s in u.slots:
+            p = s.param
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(torch.float32).view(s.shape))
+                p.grad = None
+        if self.W > 1 and not u.resident:
+            self._reduce_scatter(u, self._ring_grad)
+
+    def finish_backward(self):
+        """Call once after loss.backward(): handles the units that stay resident."""
+        for u in self.units:
+            if u.name.startswith("layers.") and not (self.W == 1):
+                continue
+            for s in u.slots:
+                p = s.param
+                if p.grad is not None:
+                    p.main_grad.add_(p.grad.to(torch.float32).view(s.shape))
+                    p.grad = None
+            if self.W > 1 and u.resident:
+                self._reduce_scatter(u, u.full_grad)
+        self.micro_steps += 1
+
+    # ------------------------------------------------------------------ optimizer
+    def grad_norm_sq(self) -> torch.Tensor:
+        """Squared global gradient norm (unscaled accumulated gradients) as a device scalar."""
+        self.norm_sq.zero_()
+        if self.use_cuda_kernels:
+            K.sumsq(self.grad, self.norm_sq)
+        else:
+            self.norm_sq += (self.grad.double() ** 2).sum().float()
+        if self.W > 1:
+            self._dedup_replicated_norm()
+            dist.all_reduce(self.norm_sq, group=self.group)
+        return self.norm_sq
+
+    def _dedup_replicated_norm(self):
+        # replicated parameters hold the same summed gradient on every rank: count them once
+        for u in self.units:
+            gs = self._unit_views(u, self.grad)
+            for s in u.slots:
+                if not s.sharded and self.rank != 0:
+                    g = gs[s.shard_off:s.shard_off + s.numel]
+                    self.norm_sq -= (g * g).sum()
+
+    def optimizer_step(self, lr: float | None = None, grad_accum: int = 1) -> torch.Tensor:
+        """Clip by global norm, AdamW on the fp32 shard, re-cast the compute copy, zero grads.
+        Returns the pre-clip gradient norm (device scalar, already divided by grad_accum)."""
+        lr = self.lr if lr is None else lr
+        self.step_count += 1
+        gmul = 1.0 / grad_accum
+        nsq = self.grad_norm_sq()
+        b1, b2 = self.betas
+        if self.use_cuda_kernels:
+            p16 = None if self.compute_shard is self.master else self.compute_shard
+            K.adamw(self.master, self.exp_avg, self.exp_avg_sq, self.grad, p16, lr=lr, b1=b1, b2=b2,
+                    eps=self.eps, wd=self.wd, step=self.step_count, grad_mul=gmul, norm_sq=nsq,
+                    max_norm=self.max_grad_norm, zero_grad=True)
+        else:
+            g = self.grad * gmul
+            if self.max_grad_norm > 0:
+                nrm = torch.sqrt(nsq) * gmul
+                g = g * torch.clamp(self.max_grad_norm / (nrm + 1e-6), max=1.0)
+            self.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
+            self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
+            mh = self.exp_avg / (1 - b1 ** self.step_count)
+            vh = self.exp_avg_sq / (1 - b2 ** self.step_count)
+            self.master.sub_(lr * (mh / (vh.sqrt() + self.eps) + self.wd * self.master))
+            self.grad.zero_()
+            self._refresh_compute_shard()
+        if self.W > 1:
+            for u in self.units:
+                if u.resident:
+                    self._all_gather(u, u.gathered)
+        self.micro_steps = 0
+        return torch.sqrt(nsq) * gmul
+
+    # ------------------------------------------------------------------ state I/O
+    def named_master_shards(self):
+        """Yield (name, global shape, sharded?, fp32 shard views of master/exp_avg/exp_avg_sq)."""
+        for u in self.units:
+            ms = self._unit_views(u, self.master)
+            m1 = self._unit_views(u, self.exp_avg)
+            m2 = self._unit_views(u, self.exp_avg_sq)
+            for s in u.slots:
+                sl = slice(s.shard_off, s.shard_off + s.shard_numel)
+                yield s, ms[sl], m1[sl], m2[sl]
+
+    def load_full_param(self, slot: ParamSlot, value: torch.Tensor):
+        """Write a full fp32 parameter value into this rank's master shard."""
+        u = next(u for u in self.units if slot in u.slots)
+        ms = self._unit_views(u, self.master)
+        flat = value.detach().to(device=self.device, dtype=torch.float32).reshape(-1)
+        if slot.sharded:
+            flat = flat[self.rank * slot.shard_numel:(self.rank + 1) * slot.shard_numel]
+        ms[slot.shard_off:slot.shard_off + slot.shard_numel].copy_(flat)
+
+    def sync_compute_from_master(self):
+        self._refresh_compute_shard()
+        if self.W > 1:
+            for u in self.units:
+                if u.resident:
+                    self._all_gather(u, u.gathered)
+
+    def full_param(self, slot: ParamSlot) -> torch.Tensor:
+        """Assemble the full fp32 master value of a parameter (collective when sharded)."""
+        u = next(u for u in self.units if slot in u.slots)
+        ms = self._unit_views(u, self.master)[slot.shard_off:slot.shard_off + slot.shard_numel]
+        if self.W == 1 or not slot.sharded:
+            return ms.clone().view(slot.shape)
+        out = torch.empty(self.W * slot.shard_numel, dtype=torch.float32, device=self.device)
+        dist.all_gather_into_tensor(out, ms.contiguous(), group=self.group)
+        return out.view(slot.shape)
+
+
+class _RematLayerFn(torch.autograd.Function):
+    """Run a decoder layer without keeping its activations; recompute them in backward."""
+
+    @staticmethod
+    def forward(ctx, x, engine: TrainEngine, unit: Unit, layer, fctx):
+        engine._acquire(unit)
+        with torch.no_grad():
+            y, aux = layer(x, fctx)
+        ctx.save_for_backward(x)
+        ctx.engine, ctx.unit, ctx.layer, ctx.fctx = engine, unit, layer, fctx
+        return y, aux
+
+    @staticmethod
+    def backward(ctx, dy, daux):
+        (x,) = ctx.saved_tensors
+        engine, unit, layer, fctx = ctx.engine, ctx.unit, ctx.layer, ctx.fctx
+        engine._acquire(unit)
+        with torch.enable_grad():
+            xin = x.detach().requires_grad_(True)
+            y, aux = layer(xin, fctx)
+            outs, grads = [y], [dy]
+            if aux.requires_grad:
+                outs.append(aux)
+                grads.append(daux if daux is not None else torch.zeros_like(aux))
+            torch.autograd.backward(outs, grads)
+        engine._release_grads(unit)
+        return xin.grad, None, None, None, None

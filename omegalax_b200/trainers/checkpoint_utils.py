@@ -1,0 +1,200 @@
+"""Sharded, resumable training checkpoints.
+
+Layout under ``save_dir``::
+
+    config.json                      HF-format model config (written once at start)
+    000050/                          one directory per saved step (6 digits)
+        manifest.json                step, world size, per-parameter global shape / sharding
+        rank00000.safetensors        this rank's fp32 shards: <name>.master / .exp_avg / .exp_avg_sq
+        input_iter_00000.json        data-iterator state of this rank
+        rng_00000.pt                 torch RNG state of this rank
+
+A step directory is written under a temporary name and renamed when every rank is done, so a
+crash never leaves a half-written checkpoint; only the newest ``max_to_keep`` are kept.  The
+device->host copy happens on the caller's stream; file writing runs on a background thread.
+Restore reshards: a checkpoint written with W ranks can be read with any other shard count.
+(The reference keeps the same items -- train state incl. optimizer moments and step counters,
+rng, input iterator -- through orbax: omegalax/trainers/text.py:94-155,
+omegalax/trainers/checkpoint_utils.py:13-43.)
+"""
+from __future__ import annotations
+
+import json
+import os
+import shutil
+import threading
+from pathlib import Path
+from typing import Any, Protocol
+
+import torch
+import torch.distributed as dist
+
+
+class CheckpointableIterator(Protocol):
+    def get_state(self) -> dict: ...
+    def set_state(self, state: dict) -> None: ...
+
+
+def _barrier():
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+
+
+def _rank():
+    return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+
+
+def _world():
+    return dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+
+
+class CheckpointManager:
+    def __init__(self, save_dir: str | os.PathLike, *, save_interval_steps: int | None = None,
+                 max_to_keep: int = 2, async_write: bool = True):
+        self.dir = Path(save_dir).expanduser().resolve()
+        self.dir.mkdir(parents=True, exist_ok=True)
+        self.interval = save_interval_steps
+        self.max_to_keep = max_to_keep
+        self.async_write = async_write
+        self._thread: threading.Thread | None = None
+        self._error: BaseException | None = None
+        if _rank() == 0:
+            self.cleanup_tmp_directories()
+        _barrier()
+
+    # ---------------------------------------------------------------- discovery
+    def all_steps(self) -> list[int]:
+        out = []
+        for p in self.dir.iterdir():
+            if p.is_dir() and p.name.isdigit() and (p / "manifest.json").exists():
+                out.append(int(p.name))
+        return sorted(out)
+
+    def latest_step(self) -> int | None:
+        steps = self.all_steps()
+        return steps[-1] if steps else None
+
+    def cleanup_tmp_directories(self) -> None:
+        for p in self.dir.glob("*.tmp"):
+            shutil.rmtree(p, ignore_errors=True)
+
+    def step_dir(self, step: int) -> Path:
+        return self.dir / f"{step:06d}"
+
+    # ---------------------------------------------------------------- save
+    def save(self, step: int, engine, input_iter: CheckpointableIterator | None = None,
+             extra: dict[str, Any] | None = None) -> None:
+        """Snapshot the engine's shards on the host, then write them in the background."""
+        self.wait_until_finished()
+        r, w = _rank(), _world()
+        tensors: dict[str, torch.Tensor] = {}
+        params = []
+        for slot, master, m1, m2 in engine.named_master_shards():
+            for suffix, t in ((".master", master), (".exp_avg", m1), (".exp_avg_sq", m2)):
+                tensors[slot.name + suffix] = t.detach().to("cpu", copy=True)
+            params.append({"name": slot.name, "shape": list(slot.shape), "sharded": bool(slot.sharded),
+                           "shard_numel": int(slot.shard_numel)})
+        manifest = {"step": int(step), "world_size": w, "shard_world": int(engine.W),
+                    "optimizer_step": int(engine.step_count), "params": params, "extra": extra or {}}
+        iter_state = input_iter.get_state() if input_iter is not None else None
+        rng_state = {"cpu": torch.get_rng_state()}
+        tmp = self.dir / f"{step:06d}.tmp"
+        final = self.step_dir(step)
+        if r == 0:
+            tmp.mkdir(parents=True, exist_ok=True)
+        _barrier()
+
+        def write():
+            try:
+                from safetensors.torch import save_file
+
+                save_file(tensors, str(tmp / f"rank{r:05d}.safetensors"))
+                if iter_state is not None:
+                    (tmp / f"input_iter_{r:05d}.json").write_text(json.dumps(iter_state))
+                torch.save(rng_state, tmp / f"rng_{r:05d}.pt")
+                if r == 0:
+                    (tmp / "manifest.json").write_text(json.dumps(manifest))
+            except BaseException as e:  # surfaced by wait_until_finished
+                self._error = e
+
+        if self.async_write and w == 1:
+            self._thread = threading.Thread(target=lambda: (write(), self._finalize(tmp, final)), daemon=True)
+            self._thread.start()
+        else:
+            write()
+            _barrier()
+            if r == 0:
+                self._finalize(tmp, final)
+            _barrier()
+
+    def _finalize(self, tmp: Path, final: Path) -> None:
+        if self._error is not None:
+            return
+        if final.exists():
+            shutil.rmtree(final)
+        os.replace(tmp, final)
+        steps = self.all_steps()
+        for s in steps[:-self.max_to_keep] if self.max_to_keep else []:
+            shutil.rmtree(self.step_dir(s), ignore_errors=True)
+
+    def wait_until_finished(self) -> None:
+        if self._thread is not None:
+            self._thread.join()
+            self._thread = None
+        if self._error is not None:
+            e, self._error = self._error, None
+            raise RuntimeError("checkpoint write failed") from e
+
+    def close(self) -> None:
+        self.wait_until_finished()
+
+    # ---------------------------------------------------------------- restore
+    def restore(self, step: int | None, engine, input_iter: CheckpointableIterator | None = None) -> dict:
+        """Load master weights and moments into ``engine`` (resharding if needed), the data
+        iterator state and the RNG state.  Returns the manifest."""
+        from safetensors import safe_open
+
+        self.wait_until_finished()
+        if step is None:
+            step = self.latest_step()
+        if step is None:
+            raise ValueError("No checkpoint found to restore.")
+        d = self.step_dir(step)
+        manifest = json.loads((d / "manifest.json").read_text())
+        saved_w = manifest["shard_world"]
+        meta = {p["name"]: p for p in manifest["params"]}
+        files = [safe_open(str(d / f"rank{i:05d}.safetensors"), framework="pt") for i in range(manifest["world_size"])]
+        r = _rank()
+        for slot, master, m1, m2 in engine.named_master_shards():
+            if slot.name not in meta:
+                raise RuntimeError(f"checkpoint has no entry for parameter '{slot.name}'")
+            pm = meta[slot.name]
+            if list(slot.shape) != pm["shape"]:
+                raise RuntimeError(f"shape mismatch for '{slot.name}': {pm['shape']} vs {list(slot.shape)}")
+            for suffix, dst in ((".master", master), (".exp_avg", m1), (".exp_avg_sq", m2)):
+                key = slot.name + suffix
+                if pm["sharded"] == slot.sharded and (not slot.sharded or saved_w == engine.W):
+                    src = files[engine.rank if slot.sharded and len(files) > 1 else 0].get_tensor(key)
+                    if slot.sharded and len(files) == 1 and saved_w == 1:
+                        src = src.reshape(-1)
+                else:
+                    if pm["sharded"]:
+                        per = manifest["world_size"] // saved_w
+                        full = torch.cat([files[i * per].get_tensor(key).reshape(-1) for i in range(saved_w)])
+                    else:
+                        full = files[0].get_tensor(key).reshape(-1)
+                    if slot.sharded:
+                        src = full[engine.rank * slot.shard_numel:(engine.rank + 1) * slot.shard_numel]
+                    else:
+                        src = full
+                dst.copy_(src.reshape(-1).to(dst.device))
+        engine.step_count = int(manifest["optimizer_step"])
+        engine.sync_compute_from_master()
+        if input_iter is not None:
+            p = d / f"input_iter_{r:05d}.json"
+            if p.exists():
+                input_iter.set_state(json.loads(p.read_text()))
+        p = d / f"rng_{r:05d}.pt"
+        if p.exists():
+            torch.set_rng_state(torch.load(p, weights_only=False)["cpu"])
+        return manifest

@@ -1,0 +1,253 @@
+"""Each sm_100a kernel against a plain PyTorch fp32 evaluation of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+bf16 = torch.bfloat16
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _check(lib):
+    torch.cuda.synchronize()
+    lib.check_status()
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).abs().max() / (b.abs().max() + 1e-6))
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 384), (300, 200, 136), (1024, 1024, 1024), (128, 4096, 64), (4096, 1536, 2048)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    from omegalax_b200.ops import kernels as Kn, lib
+    torch.manual_seed(0)
+    if a_mn and M % 8:
+        pytest.skip("MN-major A needs a 16-byte aligned M pitch")
+    if b_mn and N % 8:
+        pytest.skip("MN-major B needs a 16-byte aligned N pitch")
+    a = torch.randn(M, K, device=_dev()).to(bf16)
+    b = torch.randn(N, K, device=_dev()).to(bf16)
+    ref = a.float() @ b.float().t()
+    aa = a.t().contiguous() if a_mn else a
+    bb = b.t().contiguous() if b_mn else b
+    out = Kn.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn)
+    _check(lib)
+    assert out.shape == (M, N)
+    assert _rel_err(out, ref) < 2e-2
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_epilogues(bn):
+    from omegalax_b200.ops import kernels as Kn, lib
+    torch.manual_seed(1)
+    M, N, K = 384, 640, 256
+    a = torch.randn(M, K, device=_dev()).to(bf16)
+    b = torch.randn(N, K, device=_dev()).to(bf16)
+    res = torch.randn(M, N, device=_dev()).to(bf16)
+    ref = a.float() @ b.float().t()
+    out = Kn.gemm(a, b, residual=res, bn=bn)
+    _check(lib)
+    assert _rel_err(out, ref + res.float()) < 2e-2
+    acc = torch.ones(M, N, device=_dev(), dtype=torch.float32)
+    Kn.gemm(a, b, out=acc, accumulate=True, bn=bn)
+    Kn.gemm(a, b, out=acc, accumulate=True, bn=bn)
+    _check(lib)
+    assert _rel_err(acc, 2 * ref + 1) < 1e-2
+    o32 = Kn.gemm(a, b, out_dtype=torch.float32, bn=bn)
+    _check(lib)
+    assert _rel_err(o32, ref) < 1e-2
+
+
+def test_gemm_grouped_and_wgrad():
+    from omegalax_b200.ops import kernels as Kn, lib
+    from omegalax_b200.ops import moe
+    torch.manual_seed(2)
+    E, D, F, M, k = 4, 256, 384, 500, 2
+    idx = torch.randint(0, E, (M, k), device=_dev())
+    dest, offsets, cap = moe.build_permutation(idx, E)
+    x = torch.randn(M, D, device=_dev()).to(bf16)
+    xp = torch.zeros(cap, D, device=_dev(), dtype=bf16)
+    tok = torch.arange(M, device=_dev()).repeat_interleave(k)
+    xp.index_copy_(0, dest, x[tok])
+    w = torch.randn(E, F, D, device=_dev()).to(bf16) * 0.05
+    y = Kn.gemm_grouped(xp, w, offsets)
+    _check(lib)
+    offs = offsets.tolist()
+    for e in range(E):
+        a, b = offs[e], offs[e + 1]
+        if b > a:
+            assert _rel_err(y[a:b], xp[a:b].float() @ w[e].float().t()) < 2e-2
+    # dgrad layout: B given as [E, K, N]
+    wt = w.transpose(1, 2).contiguous()
+    y2 = Kn.gemm_grouped(xp, wt, offsets, b_mn=True)
+    _check(lib)
+    assert _rel_err(y2[: offs[-1]], y[: offs[-1]]) < 2e-2
+    dy = torch.randn(cap, F, device=_dev()).to(bf16)
+    dw = torch.zeros(E, F, D, device=_dev(), dtype=torch.float32)
+    Kn.gemm_grouped_wgrad(dy, xp, offsets, dw, accumulate=True)
+    _check(lib)
+    for e in range(E):
+        a, b = offs[e], offs[e + 1]
+        ref = dy[a:b].float().t() @ xp[a:b].float()
+        assert _rel_err(dw[e], ref) < 2e-2
+
+
+@pytest.mark.parametrize("D", [64, 1024, 4096])
+@pytest.mark.parametrize("one_plus", [False, True])
+def test_rmsnorm(D, one_plus):
+    from omegalax_b200.ops import functional as Fn, reference as R, lib
+    torch.manual_seed(3)
+    x = torch.randn(70, D, device=_dev()).to(bf16).requires_grad_(True)
+    w = (torch.randn(D, device=_dev()) * 0.1 + (0 if one_plus else 1)).to(bf16).requires_grad_(True)
+    y = Fn.rmsnorm(x, w, 1e-6, one_plus)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    _check(lib)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    yr = R.rmsnorm(xr, wr, 1e-6, one_plus)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 2e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+
+
+def test_swiglu():
+    from omegalax_b200.ops import functional as Fn, reference as R, lib
+    torch.manual_seed(4)
+    gu = torch.randn(100, 512, device=_dev()).to(bf16).requires_grad_(True)
+    y = Fn.swiglu(gu)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    _check(lib)
+    gr = gu.detach().float().requires_grad_(True)
+    yr = R.swiglu(gr)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(gu.grad, gr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("Kd,rot,qs", [(128, 128, 1), (64, 64, 1), (256, 64, 2)])
+def test_qknorm_rope(Kd, rot, qs):
+    from omegalax_b200.ops import functional as Fn, reference as R, lib
+    torch.manual_seed(5)
+    M, H, G = 96, 4, 2
+    qkv = torch.randn(M, (H * qs + 2 * G) * Kd, device=_dev()).to(bf16).requires_grad_(True)
+    qw = (1 + 0.1 * torch.randn(Kd, device=_dev())).to(bf16).requires_grad_(True)
+    kw = (1 + 0.1 * torch.randn(Kd, device=_dev())).to(bf16).requires_grad_(True)
+    sin, cos = R.rope_tables(torch.arange(M, device=_dev()), rot, 1e6)
+    q, k, v, gate = Fn.qk_norm_rope(qkv, qw, kw, sin, cos, H, G, Kd, rot=rot, q_stride_heads=qs)
+    dq, dk = torch.randn_like(q), torch.randn_like(k)
+    torch.autograd.backward([q, k], [dq, dk])
+    _check(lib)
+    import os
+    os.environ["OMEGALAX_B200_REFERENCE_OPS"] = "1"
+    try:
+        qkv_r = qkv.detach().float().requires_grad_(True)
+        qw_r, kw_r = qw.detach().float().requires_grad_(True), kw.detach().float().requires_grad_(True)
+        qr, kr, vr, _ = Fn.qk_norm_rope(qkv_r, qw_r, kw_r, sin, cos, H, G, Kd, rot=rot, q_stride_heads=qs)
+        torch.autograd.backward([qr, kr], [dq.float(), dk.float()])
+    finally:
+        del os.environ["OMEGALAX_B200_REFERENCE_OPS"]
+    assert _rel_err(q, qr) < 2e-2 and _rel_err(k, kr) < 2e-2
+    assert _rel_err(qkv.grad, qkv_r.grad) < 3e-2
+    assert _rel_err(qw.grad, qw_r.grad) < 3e-2 and _rel_err(kw.grad, kw_r.grad) < 3e-2
+
+
+@pytest.mark.parametrize("HD", [128, 64])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("T", [128, 384, 1000])
+def test_attention_forward(HD, causal, T):
+    from omegalax_b200.ops import kernels as Kn, reference as R, lib
+    torch.manual_seed(6)
+    B, H, G = 2, 4, 2
+    q = torch.randn(B * T, H, HD, device=_dev()).to(bf16)
+    k = torch.randn(B * T, G, HD, device=_dev()).to(bf16)
+    v = torch.randn(B * T, G, HD, device=_dev()).to(bf16)
+    cu = torch.arange(B + 1, device=_dev(), dtype=torch.int32) * T
+    scale = HD ** -0.5
+    o, lse = Kn.attn_fwd(q, k, v, cu, T, scale, causal)
+    _check(lib)
+    ref = R.attention(q.view(B, T, H, HD).float(), k.view(B, T, G, HD).float(), v.view(B, T, G, HD).float(),
+                      causal=causal, scale=scale).reshape(B * T, H, HD)
+    assert _rel_err(o, ref) < 2e-2
+
+
+def test_attention_varlen_strided_v():
+    from omegalax_b200.ops import kernels as Kn, reference as R, lib
+    torch.manual_seed(7)
+    H, G, HD = 4, 2, 128
+    lens = [200, 456, 77]
+    N = sum(lens)
+    qkv = torch.randn(N, (H + 2 * G) * HD, device=_dev()).to(bf16)
+    q = qkv[:, : H * HD].reshape(N, H, HD).contiguous()
+    k = qkv[:, H * HD:(H + G) * HD].reshape(N, G, HD).contiguous()
+    v = qkv[:, (H + G) * HD:].view(N, G, HD)
+    cu = torch.tensor([0, 200, 656, 733], device=_dev(), dtype=torch.int32)
+    o, _ = Kn.attn_fwd(q, k, v, cu, max(lens), HD ** -0.5, True)
+    _check(lib)
+    ref = R.attention_varlen(q.float(), k.float(), v.float(), cu, causal=True, scale=HD ** -0.5)
+    assert _rel_err(o, ref) < 2e-2
+
+
+def test_linear_cross_entropy():
+    from omegalax_b200.ops import functional as Fn, lib
+    torch.manual_seed(8)
+    M, D, V = 300, 256, 2048
+    h = (torch.randn(M, D, device=_dev()) * 0.5).to(bf16).requires_grad_(True)
+    w = (torch.randn(V, D, device=_dev()) * 0.05).to(bf16).requires_grad_(True)
+    tgt = torch.randint(0, V, (M,), device=_dev())
+    mask = (torch.rand(M, device=_dev()) > 0.5).float()
+    scale = 1.0 / mask.sum()
+    loss = Fn.linear_cross_entropy(h, w, tgt, mask, scale, chunk=128)
+    loss.backward()
+    _check(lib)
+    hr = h.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    lr = Fn.linear_cross_entropy(hr, wr, tgt, mask, scale, chunk=128)
+    lr.backward()
+    assert abs(float(loss) - float(lr)) < 2e-2 * abs(float(lr))
+    assert _rel_err(h.grad, hr.grad) < 3e-2
+    assert _rel_err(w.grad, wr.grad) < 3e-2
+
+
+def test_embedding_and_optimizer_kernels():
+    from omegalax_b200.ops import kernels as Kn, lib
+    torch.manual_seed(9)
+    V, D, M = 512, 128, 300
+    table = torch.randn(V, D, device=_dev()).to(bf16)
+    ids = torch.randint(0, V, (M,), device=_dev())
+    out = Kn.embedding_fwd(ids, table)
+    assert torch.equal(out, table[ids])
+    dy = torch.randn(M, D, device=_dev()).to(bf16)
+    dt = torch.zeros(V, D, device=_dev())
+    Kn.embedding_bwd(ids, dy, dt)
+    ref = torch.zeros(V, D, device=_dev()).index_add_(0, ids, dy.float())
+    _check(lib)
+    assert _rel_err(dt, ref) < 1e-5
+    n = 100003
+    p = torch.randn(n, device=_dev()); m = torch.zeros(n, device=_dev()); v = torch.zeros(n, device=_dev())
+    g = torch.randn(n, device=_dev()); p16 = torch.empty(n, device=_dev(), dtype=bf16)
+    nsq = torch.zeros(1, device=_dev())
+    Kn.sumsq(g, nsq)
+    _check(lib)
+    assert abs(float(nsq) - float((g.double() ** 2).sum())) < 1e-3 * float(nsq)
+    p0, g0 = p.clone(), g.clone()
+    Kn.adamw(p, m, v, g, p16, lr=1e-2, b1=0.9, b2=0.999, eps=1e-8, wd=0.01, step=1, grad_mul=0.5,
+             norm_sq=nsq, max_norm=1.0)
+    _check(lib)
+    mul = 0.5 * min(1.0, 1.0 / (math.sqrt(float(nsq)) * 0.5 + 1e-6))
+    gg = g0 * mul
+    mr = 0.1 * gg
+    vr = 0.001 * gg * gg
+    pr = p0 - 1e-2 * ((mr / 0.1) / ((vr / 0.001).sqrt() + 1e-8) + 0.01 * p0)
+    assert _rel_err(p, pr) < 1e-5
+    assert float(g.abs().max()) == 0.0
+    assert _rel_err(p16, pr) < 1e-2
