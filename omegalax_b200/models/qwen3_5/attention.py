@@ -1,0 +1,53 @@
+"""Gated full attention of Qwen3.5 (reference: omegalax/models/qwen3_5/attention.py).
+
+The query projection emits, per head, [q | gate]; q and k get a (1+w) RMSNorm over the head
+dimension and partial interleaved MRoPE; causal attention; the output is multiplied by
+sigmoid(gate) before the output projection.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from ...ops import functional as Fn
+from ...ops import reference as R
+from ..qwen3.model import Linear
+from .norms import RMSNorm
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg, device=None, dtype=None):
+        super().__init__()
+        H, G, Kd, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.hidden_size
+        self.H, self.G, self.Kd = H, G, Kd
+        self.rot = int(Kd * cfg.partial_rotary_factor)
+        kw = dict(device=device, dtype=dtype)
+        # fused rows: [per head (q | gate)] then k heads then v heads
+        self.qkv_proj = Linear(D, (2 * H + 2 * G) * Kd, bias=cfg.attention_bias, **kw)
+        self.o_proj = Linear(H * Kd, D, bias=cfg.attention_bias, **kw)
+        self.q_norm = RMSNorm(Kd, cfg.rms_norm_eps, **kw)
+        self.k_norm = RMSNorm(Kd, cfg.rms_norm_eps, **kw)
+        self.eps = cfg.rms_norm_eps
+        self.scale = Kd ** -0.5
+
+    def forward(self, x, ctx, residual=None):
+        M = x.shape[0]
+        B, T = ctx.B, ctx.T
+        qkv = self.qkv_proj(x)
+        q, k, v, gate = Fn.qk_norm_rope(qkv, self.q_norm.weight, self.k_norm.weight, ctx.sin, ctx.cos,
+                                        self.H, self.G, self.Kd, rot=self.rot, eps=self.eps, one_plus=True,
+                                        q_stride_heads=2)
+        if Fn.use_kernels(q) and self.Kd in (64, 128):
+            o = Fn.flash_attention(q, k, v, ctx.cu_seqlens, T, scale=self.scale, causal=True)
+        elif q.is_cuda:
+            o = torch.nn.functional.scaled_dot_product_attention(
+                q.view(B, T, self.H, self.Kd).transpose(1, 2), k.reshape(B, T, self.G, self.Kd).transpose(1, 2),
+                v.reshape(B, T, self.G, self.Kd).transpose(1, 2), is_causal=True, scale=self.scale,
+                enable_gqa=True).transpose(1, 2).reshape(M, self.H, self.Kd)
+        else:
+            ks = None if ctx.k_start is None else ctx.k_start[:, None].expand(B, T)
+            o = R.attention(q.reshape(B, T, self.H, self.Kd), k.reshape(B, T, self.G, self.Kd),
+                            v.reshape(B, T, self.G, self.Kd), causal=True, scale=self.scale,
+                            k_start=ks).reshape(M, self.H, self.Kd)
+        o = o * torch.sigmoid(gate.to(o.dtype))
+        return self.o_proj(o.reshape(M, self.H * self.Kd), residual=residual)

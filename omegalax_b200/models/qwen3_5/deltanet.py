@@ -1,0 +1,105 @@
+"""GatedDeltaNet linear-attention block (reference: omegalax/models/qwen3_5/deltanet.py).
+
+    mixed = in_proj_qkv(x); z = in_proj_z(x); b = in_proj_b(x); a = in_proj_a(x)
+    mixed = silu(causal_depthwise_conv1d(mixed, k=4))
+    q, k, v = split(mixed);  beta = sigmoid(b);  g = -exp(A_log) * softplus(a + dt_bias)   (fp32)
+    q, k heads repeated to the number of value heads; chunked gated delta rule in fp32
+    out = out_proj(RMSNormGated(core, z))
+
+Padded tokens are zeroed before the projections.  Tensor-parallel note: the fused
+``in_proj_qkv`` output is ordered [all q | all k | all v]; a head-sharded layout therefore
+has to permute the columns per rank so that every rank holds whole (q, k, v) head groups --
+``tp_column_permutation`` returns that permutation.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from ...ops import functional as Fn
+from ...ops import reference as R
+from ..qwen3.model import Linear
+from .norms import RMSNormGated
+
+
+def _l2norm(x, eps: float = 1e-6):
+    return R.l2norm(x, eps)
+
+
+def _causal_depthwise_conv1d(x_BCT, w_CK):
+    return R.causal_conv1d(x_BCT, w_CK, activation_silu=False)
+
+
+chunk_gated_delta_rule = R.chunk_gated_delta_rule
+
+
+def tp_column_permutation(num_k_heads: int, num_v_heads: int, head_k: int, head_v: int, tp: int) -> torch.Tensor:
+    """Column order of in_proj_qkv such that a contiguous 1/tp slice holds, for that rank's
+    key heads, [q | k | v of the matching value heads]."""
+    key_dim, rep = num_k_heads * head_k, num_v_heads // num_k_heads
+    q_cols = torch.arange(key_dim).view(num_k_heads, head_k)
+    k_cols = q_cols + key_dim
+    v_cols = (torch.arange(num_v_heads * head_v) + 2 * key_dim).view(num_k_heads, rep * head_v)
+    per = num_k_heads // tp
+    out = []
+    for r in range(tp):
+        sl = slice(r * per, (r + 1) * per)
+        out += [q_cols[sl].reshape(-1), k_cols[sl].reshape(-1), v_cols[sl].reshape(-1)]
+    return torch.cat(out)
+
+
+class GatedDeltaNet(nn.Module):
+    def __init__(self, cfg, device=None, dtype=None):
+        super().__init__()
+        D = cfg.hidden_size
+        self.nk, self.nv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+        self.ak, self.av = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        self.key_dim, self.value_dim = self.nk * self.ak, self.nv * self.av
+        self.conv_dim = 2 * self.key_dim + self.value_dim
+        self.conv_k = cfg.linear_conv_kernel_dim
+        kw = dict(device=device, dtype=dtype)
+        self.in_proj_qkv = Linear(D, self.conv_dim, **kw)
+        self.in_proj_z = Linear(D, self.value_dim, **kw)
+        self.in_proj_b = Linear(D, self.nv, **kw)
+        self.in_proj_a = Linear(D, self.nv, **kw)
+        self.conv_weight = nn.Parameter(torch.empty(self.conv_dim, self.conv_k, **kw))
+        self.dt_bias = nn.Parameter(torch.ones(self.nv, **kw))
+        self.A_log = nn.Parameter(torch.empty(self.nv, **kw))
+        self.norm = RMSNormGated(self.av, cfg.rms_norm_eps, **kw)
+        self.out_proj = Linear(self.value_dim, D, **kw)
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        if self.conv_weight.device.type == "meta":
+            return
+        with torch.no_grad():
+            nn.init.normal_(self.conv_weight, std=1.0 / math.sqrt(self.conv_k))
+            self.dt_bias.fill_(1.0)
+            self.A_log.copy_(torch.log(torch.empty(self.nv).uniform_(0, 16).clamp_min(1e-4)))
+
+    def forward(self, x, ctx, residual=None):
+        """x [M, D] packed rows of a [B, T] batch; ctx.segment_ids marks real tokens."""
+        B, T = ctx.B, ctx.T
+        mask = (ctx.segment_ids != 0).reshape(-1, 1).to(x.dtype)
+        x = x * mask
+        mixed = self.in_proj_qkv(x).view(B, T, self.conv_dim)
+        z = self.in_proj_z(x)
+        b = self.in_proj_b(x)
+        a = self.in_proj_a(x)
+        mixed = Fn.causal_conv1d_silu(mixed, self.conv_weight)
+        q, k, v = torch.split(mixed, [self.key_dim, self.key_dim, self.value_dim], dim=-1)
+        q = q.reshape(B, T, self.nk, self.ak)
+        k = k.reshape(B, T, self.nk, self.ak)
+        v = v.reshape(B, T, self.nv, self.av)
+        beta = torch.sigmoid(b.float()).view(B, T, self.nv)
+        g = (-torch.exp(self.A_log.float()) * F.softplus(a.float() + self.dt_bias.float())).view(B, T, self.nv)
+        rep = self.nv // self.nk
+        if rep > 1:
+            q = q.repeat_interleave(rep, dim=2)
+            k = k.repeat_interleave(rep, dim=2)
+        core = Fn.gated_delta_rule(q, k, v, g, beta)               # [B,T,nv,av], input dtype
+        core = self.norm(core.reshape(-1, self.av), z.reshape(-1, self.av))
+        return self.out_proj(core.reshape(B * T, self.value_dim), residual=residual)

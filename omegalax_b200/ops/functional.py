@@ -229,7 +229,7 @@ _ATTN_BWD_IMPL = {"impl": None}
 
 def _attn_bwd_dispatch(q, k, v, o, lse, do, cu_seqlens, max_seqlen, scale, causal):
     """dq, dk, dv of packed-row attention."""
-    if hasattr(K, "attn_bwd") and os.environ.get("OMEGALAX_B200_ATTN_BWD", "sm100") == "sm100":
+    if q.shape[-1] == 128 and os.environ.get("OMEGALAX_B200_ATTN_BWD", "sm100") == "sm100":
         return K.attn_bwd(q, k, v, o, lse, do, cu_seqlens, max_seqlen, scale, causal)
     # recompute through the PyTorch definition (reference quality; used only until the
     # tcgen05 backward is selected)
@@ -339,3 +339,17 @@ def linear_cross_entropy(h, w, targets, mask, scale, chunk: int = 4096):
         r1 = min(h.shape[0], r0 + chunk)
         total = total + R.cross_entropy_sum(h[r0:r1], w, targets[r0:r1], mask[r0:r1])
     return total * scale.squeeze(0)
+
+
+# ----------------------------------------------------------------------------- GatedDeltaNet ops
+def causal_conv1d_silu(x_BTC, w_CK):
+    """Depthwise causal conv over time (left pad K-1) followed by SiLU.  x [B,T,C], w [C,K]."""
+    if use_kernels(x_BTC) and hasattr(K, "causal_conv1d_fwd"):
+        return _CausalConv1dFn.apply(x_BTC.contiguous(), w_CK)
+    y = R.causal_conv1d(x_BTC.transpose(1, 2), w_CK, activation_silu=True)
+    return y.transpose(1, 2)
+
+
+def gated_delta_rule(q, k, v, g, beta, chunk: int = 64):
+    """Chunked gated delta rule (fp32 inside); q,k [B,T,H,A], v [B,T,H,U], g/beta [B,T,H]."""
+    return R.chunk_gated_delta_rule(q, k, v, g, beta, chunk=chunk)

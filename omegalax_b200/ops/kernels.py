@@ -203,6 +203,35 @@ def attn_fwd(q, k, v, cu_seqlens, max_seqlen, scale, causal, want_lse=True):
     return out, lse
 
 
+_attn_scratch: dict = {}
+
+
+def attn_bwd(q, k, v, o, lse, do, cu_seqlens, max_seqlen, scale, causal, dk_out=None, dv_out=None):
+    """Gradients of ``attn_fwd`` (head_dim 128).  Returns dq [N,H,K], dk, dv [N,G,K].
+    ``dk_out`` / ``dv_out`` may be row-strided views (e.g. slices of a fused dqkv buffer).
+    The fp32 dq accumulation buffer and the delta vector are cached per shape and reused."""
+    N, H, Kd = q.shape
+    G = k.shape[1]
+    dq = torch.empty(N, H, Kd, dtype=q.dtype, device=q.device)
+    dk = dk_out if dk_out is not None else torch.empty(N, G, Kd, dtype=q.dtype, device=q.device)
+    dv = dv_out if dv_out is not None else torch.empty(N, G, Kd, dtype=q.dtype, device=q.device)
+    key = (q.device.index, N, H, Kd)
+    scratch = _attn_scratch.get(key)
+    if scratch is None:
+        _attn_scratch.clear()
+        scratch = (torch.empty(N * H * Kd, dtype=torch.float32, device=q.device),
+                   torch.empty(H * N, dtype=torch.float32, device=q.device))
+        _attn_scratch[key] = scratch
+    dq_acc, delta = scratch
+    st = lib.status_tensor(q.device)
+    _call("ob_attn_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(),
+          lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+          dv.data_ptr(), cu_seqlens.data_ptr(), cu_seqlens.numel() - 1, int(max_seqlen), N, H, G, Kd,
+          q.stride(0), k.stride(0), v.stride(0), o.stride(0), do.stride(0), dk.stride(0), dv.stride(0),
+          float(scale), int(causal), st.data_ptr(), lib.stream_ptr())
+    return dq, dk, dv
+
+
 def ce_fwd_bwd(logits, targets, mask, grad_scale, loss_sum, write_grad=True, lse_out=None):
     R, V = logits.shape
     _call("ob_ce_fwd_bwd", logits.data_ptr(), logits.stride(0), R, V, targets.data_ptr(),

@@ -251,3 +251,27 @@ def test_embedding_and_optimizer_kernels():
     assert _rel_err(p, pr) < 1e-5
     assert float(g.abs().max()) == 0.0
     assert _rel_err(p16, pr) < 1e-2
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("T,B", [(256, 2), (1000, 2), (77, 3)])
+def test_attention_backward(causal, T, B):
+    from omegalax_b200.ops import kernels as Kn, reference as R, lib
+    torch.manual_seed(10)
+    H, G, HD = 4, 2, 128
+    N = B * T
+    q = torch.randn(N, H, HD, device=_dev()).to(bf16)
+    k = torch.randn(N, G, HD, device=_dev()).to(bf16)
+    v = torch.randn(N, G, HD, device=_dev()).to(bf16)
+    do = torch.randn(N, H, HD, device=_dev()).to(bf16)
+    cu = torch.arange(B + 1, device=_dev(), dtype=torch.int32) * T
+    scale = HD ** -0.5
+    o, lse = Kn.attn_fwd(q, k, v, cu, T, scale, causal)
+    dq, dk, dv = Kn.attn_bwd(q, k, v, o, lse, do, cu, T, scale, causal)
+    _check(lib)
+    qr, kr, vr = (t.float().view(B, T, -1, HD).requires_grad_(True) for t in (q, k, v))
+    ref = R.attention(qr, kr, vr, causal=causal, scale=scale)
+    ref.backward(do.float().view(B, T, H, HD))
+    assert _rel_err(dq, qr.grad.reshape(N, H, HD)) < 3e-2
+    assert _rel_err(dk, kr.grad.reshape(N, G, HD)) < 3e-2
+    assert _rel_err(dv, vr.grad.reshape(N, G, HD)) < 3e-2
