@@ -134,9 +134,11 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
             log_every: int = 1, resume: bool = False, pad_id: int = 0, peak_tflops: float | None = None,
             tp_size: int | None = None, fsdp_size: int | None = None, dp_size: int | None = None,
             profile_dir=None, profile_steps: tuple[int, int] = (3, 8), wandb_run=None, val_data_iter=None,
-            val_every: int | None = None, val_steps: int = 10, device=None, log_file=None):
+            val_every: int | None = None, val_steps: int = 10, device=None, log_file=None, _family=None,
+            pretrained_loader=None):
     """SFT from a checkpointable iterator of batch dicts (numpy / CPU tensors, this rank's
     rows).  Returns (optimizer, last logged metrics)."""
+    fam = _family or _TEXT_FAMILY
     save_path = Path(save_dir).expanduser().resolve() if save_dir is not None else None
     if resume:
         if save_path is None:
@@ -146,13 +148,13 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
         probe = checkpoint_utils.CheckpointManager(save_path)
         if probe.latest_step() is None:
             raise ValueError(f"resume=True but no checkpoints found under: {save_path}")
-        model_cfg = text_api.resolve_config(str(save_path))
+        model_cfg = fam.api.resolve_config(str(save_path))
         startup_log(f"resolved model config from checkpoint {str(save_path)!r}")
     else:
-        model_cfg = text_api.resolve_config(model_id_or_cfg)
+        model_cfg = fam.api.resolve_config(model_id_or_cfg)
         startup_log("resolved model config")
     mesh = mesh_lib.ensure_mesh(tp_size=tp_size, fsdp_size=fsdp_size, dp_size=dp_size)
-    model_cfg = text_api.align_config_to_mesh(model_cfg, mesh)
+    model_cfg = fam.api.align_config_to_mesh(model_cfg, mesh)
     mult = mesh_lib.required_batch_multiple(mesh)
     if train_cfg.batch_size % mult != 0:
         raise ValueError(f"Global batch size {train_cfg.batch_size} must be divisible by the mesh batch multiple {mult}.")
@@ -161,13 +163,16 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
     torch.manual_seed(train_cfg.seed)
 
     with mesh_lib.mesh_rules(mesh):
-        model, model_cfg = init_model(model_cfg, train_cfg.seed, tp_size=tp_size, fsdp_size=fsdp_size,
-                                      dp_size=dp_size, meta=True)
+        model, model_cfg = fam.api.init_model(model_cfg, train_cfg.seed, tp_size=tp_size, fsdp_size=fsdp_size,
+                                              dp_size=dp_size, meta=True)
         startup_log("initialized model (meta)")
         optimizer = build_optimizer(model, train_cfg, device=device)
+        if pretrained_loader is not None and not resume:
+            pretrained_loader(optimizer, model_cfg)
+            startup_log("loaded pretrained weights")
     startup_log("built optimizer / materialised shards")
-    sft_step = make_sft_train_step(model_cfg, pad_id=pad_id)
-    eval_step = make_sft_eval_step(model_cfg, pad_id=pad_id) if val_data_iter is not None else None
+    sft_step = fam.make_train_step(model_cfg, pad_id=pad_id)
+    eval_step = fam.make_eval_step(model_cfg, pad_id=pad_id) if val_data_iter is not None else None
 
     accum = train_cfg.grad_accum_steps
     use_cuda = torch.device(device).type == "cuda"
@@ -215,8 +220,9 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
         acc_time = datetime.timedelta(0)
         for _ in range(accum):
             batch = next(data_iter)
-            acc_flops += per_device_flops_per_step(model_cfg, train_cfg.seq_len, train_cfg.batch_size)
-            batch = text_api.shard_batch_dict(batch, model_cfg, mesh, device)
+            acc_flops += per_device_flops_per_step(model_cfg, train_cfg.seq_len, train_cfg.batch_size,
+                                                   batch.get("image_grid_thw"))
+            batch = fam.api.shard_batch_dict(batch, model_cfg, mesh, device)
             _, metrics = sft_step(optimizer, batch)
             acc_time += timer.step()
             acc_loss = acc_loss + metrics["loss"]
@@ -234,7 +240,7 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
         if eval_step is not None and val_every and step % val_every == 0:
             tot = sup = 0.0
             for _ in range(val_steps):
-                vb = text_api.shard_batch_dict(next(val_data_iter), model_cfg, mesh, device)
+                vb = fam.api.shard_batch_dict(next(val_data_iter), model_cfg, mesh, device)
                 vl, vs = eval_step(optimizer.model, vb, optimizer.group)
                 tot += float(vl)
                 sup += float(vs)
@@ -257,6 +263,16 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
 
         lib.check_status()
     return optimizer, last_metrics
+
+
+@dataclasses.dataclass
+class _Family:
+    api: object
+    make_train_step: object
+    make_eval_step: object
+
+
+_TEXT_FAMILY = _Family(text_api, make_sft_train_step, make_sft_eval_step)
 
 
 def _start_profiler(profile_dir):
