@@ -50,6 +50,8 @@ class Linear(nn.Module):
     def reset_parameters(self):
         if self.weight.device.type != "meta":
             nn.init.normal_(self.weight, std=1.0 / math.sqrt(self.weight.shape[1]))
+            if self.bias is not None:
+                nn.init.zeros_(self.bias)
 
     def forward(self, x, residual=None):
         return Fn.linear(x, self.weight, residual=residual, bias=self.bias)

@@ -135,9 +135,10 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
             tp_size: int | None = None, fsdp_size: int | None = None, dp_size: int | None = None,
             profile_dir=None, profile_steps: tuple[int, int] = (3, 8), wandb_run=None, val_data_iter=None,
             val_every: int | None = None, val_steps: int = 10, device=None, log_file=None, _family=None,
-            pretrained_loader=None):
+            pretrained_loader=None, stop_after_step: int | None = None):
     """SFT from a checkpointable iterator of batch dicts (numpy / CPU tensors, this rank's
-    rows).  Returns (optimizer, last logged metrics)."""
+    rows).  Returns (optimizer, last logged metrics).  ``stop_after_step`` ends this invocation
+    early (after the usual final checkpoint) while keeping the schedule of ``num_steps``."""
     fam = _family or _TEXT_FAMILY
     save_path = Path(save_dir).expanduser().resolve() if save_dir is not None else None
     if resume:
@@ -211,7 +212,8 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
     prof = None
     p0, p1 = profile_steps
     startup_log("entering training loop")
-    for step_idx in range(start_step, train_cfg.num_steps):
+    end_step = train_cfg.num_steps if stop_after_step is None else min(train_cfg.num_steps, stop_after_step)
+    for step_idx in range(start_step, end_step):
         step = step_idx + 1
         if profile_dir is not None and step_idx == p0 and prof is None:
             prof = _start_profiler(profile_dir)

@@ -1,0 +1,53 @@
+"""Worker functions for multi-process CPU tests (gloo).  Launched by torch.multiprocessing."""
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def _init(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+
+def fsdp_train(rank, world, port, model_id, steps, out_path, ckpt_dir=None, resume=False):
+    """Train `steps` optimizer steps with FSDP over `world` CPU ranks on a fixed global batch;
+    rank 0 stores the loss curve and the gathered fp32 parameters."""
+    _init(rank, world, port)
+    from omegalax_b200.parallel import mesh as mesh_lib
+    from omegalax_b200.trainers import checkpoint_utils
+    from omegalax_b200.trainers import text as trainer
+
+    mesh_lib.set_default_mesh(None)
+    mesh_lib.ensure_mesh(tp_size=1, fsdp_size=world, dp_size=1)
+    tcfg = trainer.TrainConfig(seed=0, batch_size=4, seq_len=32, num_steps=100, learning_rate=1e-2, max_grad_norm=1.0)
+    model, cfg = trainer.init_model(model_id, 0, tp_size=1, fsdp_size=world, dp_size=1, meta=True)
+    opt = trainer.build_optimizer(model, tcfg, device=torch.device("cpu"))
+    step = trainer.make_sft_train_step(cfg)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(1, cfg.vocab_size, (4, 32), generator=g, dtype=torch.int32)
+    lm = torch.ones(4, 32, dtype=torch.int32)
+    lm[:, :8] = 0
+    lm[1, 20:] = 0  # uneven supervised counts across ranks
+    per = 4 // world
+    batch = {"token_ids_BT": tok[rank * per:(rank + 1) * per], "attention_mask_BT": torch.ones(per, 32, dtype=torch.int32),
+             "loss_mask_BT": lm[rank * per:(rank + 1) * per]}
+    mgr = checkpoint_utils.CheckpointManager(ckpt_dir, async_write=False) if ckpt_dir else None
+    if resume:
+        mgr.restore(None, opt)
+    losses = []
+    for i in range(steps):
+        loss, m = step(opt, batch)
+        losses.append(float(loss))
+    if mgr is not None and not resume:
+        mgr.save(steps, opt)
+        mgr.close()
+    names = {id(p): n for n, p in model.named_parameters()}
+    full = {}
+    for u in opt.units:
+        for s in u.slots:
+            full[names[id(s.param)]] = opt.full_param(s).clone()
+    if rank == 0:
+        torch.save({"losses": losses, "params": full, "grad_norm": float(opt.last_grad_norm)}, out_path)
+    dist.barrier()
+    dist.destroy_process_group()

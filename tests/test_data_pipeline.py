@@ -1,0 +1,124 @@
+"""Dataset compile / chunk index / iterator: blocking, packing across payload blocks,
+checkpoint-restore of the iterator, per-rank sharding, deterministic shuffle."""
+import json
+
+import numpy as np
+import pytest
+
+from omegalax_b200.data import pipeline as P
+from omegalax_b200.data import recordio as rio
+from omegalax_b200.data.collator_qwen3 import TextSFTCollator
+from omegalax_b200.data.qwen3_encoding import make_message_length_fn
+from omegalax_b200.data.stub_tokenizer import StubTokenizer
+
+
+def _write_jsonl(path, sessions=23):
+    with open(path, "w") as f:
+        for s in range(sessions):
+            msgs = [{"role": "user" if i % 2 == 0 else "assistant", "content": f"msg {i} of {s} " * (1 + (i + s) % 3)}
+                    for i in range(2 + s % 6)]
+            f.write(json.dumps({"messages": msgs, "source": f"s{s}"}) + "\n")
+
+
+@pytest.fixture()
+def dataset(tmp_path):
+    jl = tmp_path / "train.jsonl"
+    _write_jsonl(jl)
+    P.compile_jsonl_to_records(jl, tmp_path / "payload", messages_per_record=2, records_per_shard=7)
+    tok = StubTokenizer()
+    P.build_chunk_index(tmp_path / "payload", tmp_path / "index", make_message_length_fn(tok), max_length=96,
+                        records_per_shard=11)
+    return tmp_path, tok
+
+
+@pytest.mark.parametrize("native", [True, False])
+def test_record_file_roundtrip(tmp_path, native):
+    p = tmp_path / "x.olrf"
+    with rio.RecordWriter(p, native=native) as w:
+        for i in range(50):
+            w.write(bytes([i % 251]) * (i * 3))
+    for rn in (True, False):
+        r = rio.RecordReader(p, native=rn)
+        assert len(r) == 50 and r[49] == bytes([49]) * 147 and r[0] == b""
+        assert r.read_many([5, 1, 49]) == [r[5], r[1], r[49]]
+    raw = bytearray(p.read_bytes())
+    raw[20] ^= 0xFF  # corrupt a payload byte: the checksum must catch it
+    p.write_bytes(bytes(raw))
+    with pytest.raises(OSError):
+        rio.RecordReader(p, native=native)[1]
+
+
+def test_payload_blocks_and_metadata(dataset):
+    d, _ = dataset
+    meta = P.load_metadata(d / "payload")
+    assert meta["num_sessions"] == 23 and meta["messages_per_record"] == 2 and meta["num_shards"] > 1
+    src = P.open_source(d / "payload")
+    blocks = [json.loads(src[i]) for i in range(len(src))]
+    assert all(len(b["messages"]) <= 2 for b in blocks)
+    b0 = [b for b in blocks if b["session_id"].endswith("000000005")]
+    assert [b["block_idx"] for b in b0] == list(range(len(b0)))
+    assert b0[0]["session_meta"] == {"source": "s5"}
+
+
+def test_chunks_never_cross_sessions_and_respect_max_length(dataset):
+    d, tok = dataset
+    meta = P.load_metadata(d / "index")
+    assert meta["kind"] == "chunk_index" and meta["max_length"] == 96
+    src = P.open_source(d / "index")
+    resolver = P.ChunkResolver(meta["payload_path"])
+    fn = make_message_length_fn(tok)
+    total_msgs = 0
+    for i in range(len(src)):
+        desc = json.loads(src[i])
+        ex = resolver(desc)
+        assert desc["measured_length"] <= 96
+        assert sum(fn(m)["length"] for m in ex["messages"]) == desc["measured_length"]
+        assert len(ex["messages"]) == desc["num_messages"]
+        total_msgs += desc["num_messages"]
+    assert total_msgs == sum(2 + s % 6 for s in range(23))
+    assert (d / "index" / "token_stats.json").exists()
+
+
+def test_single_message_longer_than_max_length_is_an_error(tmp_path):
+    jl = tmp_path / "a.jsonl"
+    jl.write_text(json.dumps({"messages": [{"role": "user", "content": "x" * 500}]}) + "\n")
+    P.compile_jsonl_to_records(jl, tmp_path / "p")
+    with pytest.raises(ValueError):
+        P.build_chunk_index(tmp_path / "p", tmp_path / "i", make_message_length_fn(StubTokenizer()), max_length=64)
+
+
+def test_iterator_checkpoint_restore_yields_same_next_batch(dataset):
+    d, tok = dataset
+    col = TextSFTCollator(tok, 96)
+    mk = lambda: P.make_data_iterator(d / "index", batch_size=3, collator=col, seed=7, num_epochs=3, dp_index=0, dp_size=1)  # noqa: E731
+    it = mk()
+    for _ in range(4):
+        next(it)
+    state = json.loads(json.dumps(it.get_state()))
+    want = [next(it) for _ in range(3)]
+    it2 = mk()
+    it2.set_state(state)
+    got = [next(it2) for _ in range(3)]
+    for a, b in zip(want, got):
+        assert all(np.array_equal(a[k], b[k]) for k in a)
+
+
+def test_ranks_see_disjoint_records_and_shuffle_is_deterministic(dataset):
+    d, _ = dataset
+    ident = lambda rows: [r["_omegalax_session_id"] + str(r["_omegalax_measured_length"]) + str(r["messages"][0]) for r in rows]  # noqa: E731
+    seen = []
+    for r in range(2):
+        it = P.make_data_iterator(d / "index", batch_size=2, collator=ident, seed=5, num_epochs=1, dp_index=r, dp_size=2,
+                                  prefetch=0)
+        seen.append([x for b in it for x in b])
+    assert not (set(seen[0]) & set(seen[1]))
+    again = P.make_data_iterator(d / "index", batch_size=2, collator=ident, seed=5, num_epochs=1, dp_index=0, dp_size=2)
+    assert [x for b in again for x in b] == seen[0]
+    other = P.make_data_iterator(d / "index", batch_size=2, collator=ident, seed=6, num_epochs=1, dp_index=0, dp_size=2)
+    assert [x for b in other for x in b] != seen[0]
+
+
+def test_required_epochs():
+    assert P.required_epochs_for_batches(100, 8, 10, dp_size=2) == 2
+    with pytest.raises(ValueError):
+        P.required_epochs_for_batches(3, 8, 1)

@@ -1,0 +1,85 @@
+"""FLOP accounting, step metrics, timers, LR schedules, batch-size helpers."""
+import datetime
+
+import pytest
+
+from omegalax_b200.models.qwen3.config import make_config
+from omegalax_b200.models.qwen3_5.config import make_config as make_q35
+from omegalax_b200.models.qwen3_vl.config import make_vl_config
+from omegalax_b200.parallel import mesh as mesh_lib
+from omegalax_b200.trainers import perf
+from omegalax_b200.trainers.lr_schedule import build_lr_schedule
+
+
+def test_qwen3_8b_flops_per_token():
+    cfg = make_config("Qwen/Qwen3-8B")
+    f = perf.training_flops_per_token(cfg, 4096)
+    assert 48.5e9 < f < 49.5e9  # 49.03 GFLOP per token at T=4096
+    assert perf.training_flops_per_token(cfg, 8192) > f
+
+
+def test_moe_counts_only_routed_experts():
+    cfg = make_config("Qwen/Qwen3-30B-A3B-Instruct-2507")
+    f = perf.training_flops_per_token(cfg, 4096)
+    assert 22.5e9 < f < 23.6e9
+
+
+def test_qwen3_5_and_vl():
+    q = make_q35("qwen3.5-397b-a17b-8layer")
+    f = perf.training_flops_per_token(q, 8192)
+    assert 18.5e9 < f < 20e9
+    vl = make_vl_config("qwen3-vl-smoke")
+    one = perf.qwen3_vl_vision_training_flops(vl, [[1, 4, 4]])
+    two = perf.qwen3_vl_vision_training_flops(vl, [[1, 4, 4], [1, 4, 4]])
+    assert two == 2 * one  # block-diagonal attention: linear in the number of images
+    assert perf.qwen3_vl_vision_training_flops(vl, None) == 0
+    with pytest.raises(ValueError):
+        perf.qwen3_vl_vision_training_flops(vl, [[1, 2]])
+
+
+def test_step_metrics_and_peak_resolution():
+    m = perf.step_metrics(2e15, datetime.timedelta(seconds=2), 1000, 1000.0)
+    assert m["tflops_per_device"] == pytest.approx(1000.0) and m["mfu"] == pytest.approx(1.0)
+    assert m["global_tokens_per_sec"] == pytest.approx(500.0)
+    assert perf.step_metrics(1.0, datetime.timedelta(0), 10, None)["mfu"] == 0.0
+    assert perf.resolve_peak_tflops("h100_sxm") == 989.0 and perf.resolve_peak_tflops("b200") == 2250.0
+    assert perf.resolve_peak_tflops("123.5") == 123.5 and perf.resolve_peak_tflops(None) is None
+    with pytest.raises(ValueError):
+        perf.resolve_peak_tflops("nope")
+
+
+def test_step_timer_warmup():
+    t = perf.StepTimer(warmup=2)
+    assert t.step() == datetime.timedelta(0) and t.step() == datetime.timedelta(0)
+    assert t.step() >= datetime.timedelta(0)
+
+
+def test_log_requires_loss_and_grad_norm():
+    with pytest.raises(KeyError):
+        perf.maybe_log_step_metrics(1, {"loss": 1.0}, datetime.timedelta(seconds=1), is_primary_process=True, log_every=1,
+                                    per_device_flops=1.0, global_tokens_per_step=1, peak_tflops=None)
+    out = perf.maybe_log_step_metrics(2, {"loss": 1.0, "grad_norm": 2.0}, datetime.timedelta(seconds=1),
+                                      is_primary_process=True, log_every=2, per_device_flops=1e12,
+                                      global_tokens_per_step=10, peak_tflops=10.0, batch_size=4)
+    assert out["total_samples"] == 8 and out["mfu"] == pytest.approx(0.1)
+    assert perf.maybe_log_step_metrics(3, {"loss": 1.0, "grad_norm": 2.0}, datetime.timedelta(seconds=1),
+                                       is_primary_process=True, log_every=2, per_device_flops=1.0,
+                                       global_tokens_per_step=1, peak_tflops=None) is None
+
+
+def test_lr_schedules():
+    lin = build_lr_schedule("linear", 1.0, 100, warmup_steps=10)
+    assert lin(0) == 0.0 and lin(5) == pytest.approx(0.5) and lin(10) == 1.0 and lin(99) == 1.0
+    cos = build_lr_schedule("cosine", 1.0, 110, warmup_steps=10, end_factor=0.1)
+    assert cos(10) == pytest.approx(1.0) and cos(110) == pytest.approx(0.1) and 0.1 < cos(60) < 1.0
+    wsd = build_lr_schedule("wsd", 1.0, 110, warmup_steps=10, end_factor=0.0, stable_fraction=0.8)
+    assert wsd(50) == 1.0 and wsd(89) == 1.0 and wsd(100) == pytest.approx(0.5) and wsd(110) == pytest.approx(0.0)
+    with pytest.raises(ValueError):
+        build_lr_schedule("step", 1.0, 10)
+
+
+def test_process_local_batch_size():
+    mesh_lib.set_default_mesh(None)
+    assert mesh_lib.process_local_batch_size(16, dp_size=4) == 4
+    with pytest.raises(ValueError):
+        mesh_lib.process_local_batch_size(10, dp_size=4)
