@@ -1,0 +1,160 @@
+// NVLink peer-memory substrate: allocation + CUDA IPC handle exchange helpers, a bounded
+// device-side barrier over peer flags, and the pull all-gather used by the sharded engine.
+//
+// Every GPU allocates the same buffers ("symmetric heap"); handles are exchanged once through
+// the host process group and each rank maps all peers' buffers.  Kernels then read and write
+// peer memory with ordinary ld/st/red instructions over NVLink; nothing here uses cluster
+// multicast loads.  All waits on peer flags are bounded and report through the status word.
+#include "host_utils.h"
+#include "sm100_common.cuh"
+
+namespace ob {
+
+constexpr int kMaxRanks = 8;
+
+struct PeerPtrs {
+  void* p[kMaxRanks];
+};
+
+// ---------------------------------------------------------------- barrier
+// flags layout on every rank: uint32 slots[kMaxRanks]; rank r writes its epoch into slot r of
+// every peer, then waits until all slots of its own array have reached the epoch.
+__global__ void symm_barrier_kernel(PeerPtrs flags, int world, int rank, uint32_t epoch,
+                                    long long budget_cycles, int* status) {
+  const int t = threadIdx.x;
+  if (t < world) {
+    uint32_t* dst = reinterpret_cast<uint32_t*>(flags.p[t]) + rank;
+    __threadfence_system();
+    st_release_sys(dst, epoch);
+  }
+  if (t < world) {
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(flags.p[rank]) + t;
+    flag_wait_ge<true>(mine, epoch, budget_cycles, status, OB_ERR_WAIT_FLAG);
+  }
+}
+
+// ---------------------------------------------------------------- pull all-gather
+// Copy segments: for segment s, `elems16` 16-byte units from peer `src_rank` at byte offset
+// `src_off` (inside that peer's shard buffer) to the local buffer at `dst_off`.
+struct CopySeg {
+  long long src_off, dst_off, bytes;
+  int src_rank, pad;
+};
+
+__global__ void allgather_pull_kernel(PeerPtrs shard, uint8_t* __restrict__ dst,
+                                      const CopySeg* __restrict__ segs, int nsegs) {
+  // grid.y walks segments, grid.x * blockDim.x threads stride over the 16-byte units of one
+  for (int s = blockIdx.y; s < nsegs; s += gridDim.y) {
+    const CopySeg sg = segs[s];
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(shard.p[sg.src_rank]) + sg.src_off);
+    uint4* d = reinterpret_cast<uint4*>(dst + sg.dst_off);
+    const long long n = sg.bytes >> 4;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    // four independent 16-byte loads in flight per thread to cover the NVLink latency
+    for (; i + 3 * stride < n; i += 4 * stride) {
+      uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], e = src[i + 3 * stride];
+      d[i] = a; d[i + stride] = b; d[i + 2 * stride] = c; d[i + 3 * stride] = e;
+    }
+    for (; i < n; i += stride) d[i] = src[i];
+  }
+}
+
+// ---------------------------------------------------------------- pull reduce-scatter
+// out[i] += sum over ranks r != self of peer_full[r][my_off + i]  (fp32); used for parameters
+// whose gradient cannot go through the GEMM peer-reduce epilogue (norm weights, embeddings).
+__global__ void reduce_scatter_pull_kernel(PeerPtrs full, float* __restrict__ out, long long src_off_elems,
+                                           long long n, int world, int rank, int include_self) {
+  const long long n4 = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = reinterpret_cast<float4*>(out)[i];
+    for (int r = 0; r < world; ++r) {
+      if (r == rank && !include_self) continue;
+      float4 v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(full.p[r]) + src_off_elems)[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    reinterpret_cast<float4*>(out)[i] = acc;
+  }
+  if (blockIdx.x == 0) {
+    for (long long i = (n4 << 2) + threadIdx.x; i < n; i += blockDim.x) {
+      float a = out[i];
+      for (int r = 0; r < world; ++r) {
+        if (r == rank && !include_self) continue;
+        a += (reinterpret_cast<const float*>(full.p[r]) + src_off_elems)[i];
+      }
+      out[i] = a;
+    }
+  }
+}
+
+}  // namespace ob
+
+using namespace ob;
+
+extern "C" {
+
+// ---- allocation / IPC (host side)
+int ob_symm_alloc(void** out, long long bytes) {
+  cudaError_t e = cudaMalloc(out, (size_t)bytes);
+  if (e != cudaSuccess) return 1000 + (int)e;
+  e = cudaMemset(*out, 0, (size_t)bytes);
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
+}
+int ob_symm_free(void* p) { return cudaFree(p) == cudaSuccess ? 0 : 1; }
+int ob_ipc_get_handle(void* p, void* handle64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) return 1000 + (int)e;
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+int ob_ipc_open_handle(const void* handle64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
+}
+int ob_ipc_close_handle(void* p) { return cudaIpcCloseMemHandle(p) == cudaSuccess ? 0 : 1; }
+int ob_ipc_handle_size() { return (int)sizeof(cudaIpcMemHandle_t); }
+
+// ---- device barrier over peer flags (bounded wait of ~budget_ms)
+int ob_symm_barrier(void* const* flag_ptrs, int world, int rank, unsigned epoch, int budget_ms, int* status,
+                    cudaStream_t stream) {
+  if (world > kMaxRanks) return 6003;
+  PeerPtrs f = {};
+  for (int i = 0; i < world; ++i) f.p[i] = flag_ptrs[i];
+  long long cycles = (long long)budget_ms * 2000000ll;
+  symm_barrier_kernel<<<1, 32, 0, stream>>>(f, world, rank, epoch, cycles, status);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+// ---- pull all-gather: segs is a device array of CopySeg (6 x int64 words each)
+int ob_allgather_pull(void* const* shard_ptrs, int world, void* dst, const void* segs, int nsegs,
+                      cudaStream_t stream) {
+  if (world > kMaxRanks) return 6003;
+  if (nsegs <= 0) return 0;
+  PeerPtrs s = {};
+  for (int i = 0; i < world; ++i) s.p[i] = shard_ptrs[i];
+  dim3 grid(num_sms() * 2 / (nsegs < 8 ? nsegs : 8) + 1, nsegs < 8 ? nsegs : 8);
+  allgather_pull_kernel<<<grid, 256, 0, stream>>>(s, (uint8_t*)dst, (const CopySeg*)segs, nsegs);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_reduce_scatter_pull(void* const* full_ptrs, int world, int rank, float* out, long long src_off_elems,
+                           long long n, int include_self, cudaStream_t stream) {
+  if (world > kMaxRanks) return 6003;
+  if (n <= 0) return 0;
+  PeerPtrs f = {};
+  for (int i = 0; i < world; ++i) f.p[i] = full_ptrs[i];
+  long long blocks = (n / 4 + 255) / 256;
+  long long cap = (long long)num_sms() * 4;
+  reduce_scatter_pull_kernel<<<(unsigned)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks)), 256, 0, stream>>>(
+      f, out, src_off_elems, n, world, rank, include_self);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // extern "C"

@@ -57,7 +57,10 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = K.gemm(dy2, w, b_mn=True).view(ctx.shp)
         dw = None
-        if ctx.needs_input_grad[1]:
+        pg = getattr(w_obj, "peer_grad", None)
+        if ctx.needs_input_grad[1] and pg is not None:
+            K.gemm_peer_reduce(dy2, x2, pg[0], pg[1], pg[2], a_mn=True, b_mn=True)
+        elif ctx.needs_input_grad[1]:
             dw = _acc_main_grad(
                 w_obj,
                 lambda mg: K.gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=True),
@@ -290,9 +293,10 @@ class _LinearCEFn(torch.autograd.Function):
         loss_sum = torch.zeros(1, dtype=torch.float32, device=dev)
         need_grad = h.requires_grad or w.requires_grad
         mg = getattr(w, "main_grad", None)
+        pg = getattr(w, "peer_grad", None)
         dh = torch.empty_like(h) if need_grad else None
         dw = None
-        if need_grad and w.requires_grad:
+        if need_grad and w.requires_grad and pg is None:
             dw = mg if mg is not None else torch.zeros(V, D, dtype=torch.float32, device=dev)
         t32 = targets.to(torch.int32).contiguous()
         mk = mask.to(torch.float32).contiguous()
@@ -305,7 +309,9 @@ class _LinearCEFn(torch.autograd.Function):
             K.ce_fwd_bwd(lg, t32[r0:r1], mk[r0:r1], scale_t, loss_sum, write_grad=need_grad)
             if need_grad:
                 K.gemm(lg, w, b_mn=True, out=dh[r0:r1])
-                if dw is not None:
+                if pg is not None:
+                    K.gemm_peer_reduce(lg, hc, pg[0], pg[1], pg[2], a_mn=True, b_mn=True)
+                elif dw is not None:
                     K.gemm(lg, hc, a_mn=True, b_mn=True, out=dw, accumulate=True)
         ctx.save_for_backward(dh)
         ctx.dw = None if (mg is not None or dw is None) else dw

@@ -46,6 +46,7 @@ class ParamSlot:
     full_off: int         # offset inside the unit's gathered buffer
     module: nn.Module = None
     pname: str = ""
+    peer: bool = False     # gradient goes through the GEMM peer-reduce epilogue
 
 
 @dataclasses.dataclass
@@ -102,7 +103,9 @@ class TrainEngine:
         self.micro_steps = 0
         self.use_cuda_kernels = self.device.type == "cuda"
         self.compute_dtype = bf16 if self.device.type == "cuda" else torch.float32
-        self.comm_kind = comm
+        if comm == "auto":
+            comm = "p2p" if (self.device.type == "cuda" and self.W > 1) else "nccl"
+        self.comm_kind = comm if self.W > 1 else "none"
         self._build_units()
         self._allocate()
         self._materialize(seed, init_from_model)
@@ -144,7 +147,16 @@ class TrainEngine:
         self.master = torch.zeros(n, dtype=torch.float32, device=dev)
         self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
-        self.grad = torch.zeros(n, dtype=torch.float32, device=dev)
+        if self.comm_kind == "p2p":
+            from . import symm
+
+            self._symm = symm
+            self._grad_buf = symm.SymmetricBuffer(n * 4, self.group)
+            self.grad = self._grad_buf.view(torch.float32, n)
+            self._barrier = symm.DeviceBarrier(self.group)
+            self._comm_stream = torch.cuda.Stream(device=dev)
+        else:
+            self.grad = torch.zeros(n, dtype=torch.float32, device=dev)
         if self.compute_dtype == torch.float32 and self.W == 1:
             self.compute_shard = self.master  # CPU/fp32 path computes on the master directly
         else:
@@ -157,6 +169,10 @@ class TrainEngine:
             self._ring_grad = torch.zeros(self._ring_numel, dtype=torch.float32, device=dev) if self._ring_numel else None
 
     def _alloc_compute_shard(self, n):
+        if self.comm_kind == "p2p":
+            esz = 2 if self.compute_dtype == bf16 else 4
+            self._shard_buf = self._symm.SymmetricBuffer(n * esz, self.group)
+            return self._shard_buf.view(self.compute_dtype, n)
         return torch.zeros(n, dtype=self.compute_dtype, device=self.device)
 
     def _unit_views(self, u: Unit, flat: torch.Tensor):
@@ -202,6 +218,12 @@ class TrainEngine:
 
     def _install(self):
         """Point every parameter at its compute storage and attach ``main_grad``."""
+        self._weights_version = 0
+        self._ring_owner = [None, None]
+        self._ring_event = [None, None]
+        self._seg_tables = {}
+        if self.comm_kind == "p2p":
+            self._barrier()  # every rank has written its compute shard
         for u in self.units:
             if self.W == 1:
                 cs = self._unit_views(u, self.compute_shard)
@@ -211,6 +233,8 @@ class TrainEngine:
                     s.param.main_grad = gs[s.shard_off:s.shard_off + s.numel].view(s.shape)
                 u.resident = True
             else:
+                if self.comm_kind == "p2p":
+                    self._mark_peer_slots(u)
                 is_layer = u.name.startswith("layers.")
                 if not is_layer:  # embedding / head stay gathered between optimizer steps
                     u.gathered = torch.empty(u.full_numel, dtype=self.compute_dtype, device=self.device)
@@ -221,6 +245,7 @@ class TrainEngine:
         if hasattr(self.model, "layer_runner"):
             self.model.layer_runner = self.run_layer
         self._layer_units = {id(u.modules[0]): u for u in self.units if u.name.startswith("layers.")}
+        self._layer_by_index = {int(u.name.split(".")[1]): u for u in self.units if u.name.startswith("layers.")}
 
     def _bind(self, u: Unit, full: torch.Tensor, full_grad: torch.Tensor | None):
         for s in u.slots:
@@ -228,11 +253,43 @@ class TrainEngine:
             if full_grad is not None:
                 s.param.main_grad = full_grad[s.full_off:s.full_off + s.numel].view(s.shape)
 
+    def _mark_peer_slots(self, u: Unit):
+        """Weights of Linear modules take their gradient through the GEMM epilogue that adds
+        each row block straight into the owning rank's fp32 gradient shard over NVLink."""
+        for s in u.slots:
+            if not (s.sharded and len(s.shape) == 2 and s.pname.endswith("weight")):
+                continue
+            owner = s.module.get_submodule(s.pname.rsplit(".", 1)[0]) if "." in s.pname else s.module
+            if type(owner).__name__ != "Linear":
+                continue
+            s.peer = True
+            off_bytes = (u.shard_base + s.shard_off) * 4
+            s.param.peer_grad = (self._grad_buf.peer_ptr_list(off_bytes), s.shape[0] // self.W, s.shape[1])
+
+    def _seg_table(self, u: Unit):
+        tab = self._seg_tables.get(u.name)
+        if tab is None:
+            esz = 2 if self.compute_dtype == bf16 else 4
+            segs = []
+            for s in u.slots:
+                src = (u.shard_base + s.shard_off) * esz
+                if s.sharded:
+                    for r in range(self.W):
+                        segs.append((r, src, (s.full_off + r * s.shard_numel) * esz, s.shard_numel * esz))
+                else:
+                    segs.append((self.rank, src, s.full_off * esz, _align(s.numel) * esz))
+            tab = self._symm.make_copy_segments(segs, self.device)
+            self._seg_tables[u.name] = tab
+        return tab
+
     # ------------------------------------------------------------------ collectives
     def _all_gather(self, u: Unit, full: torch.Tensor):
         """Gather every parameter of the unit into its full tensor inside ``full``."""
         cs = self._unit_views(u, self.compute_shard)
         if self.W == 1:
+            return
+        if self.comm_kind == "p2p":
+            self._symm.allgather_pull(self._shard_buf, full, self._seg_table(u))
             return
         stage = torch.empty(self.W * u.shard_numel, dtype=self.compute_dtype, device=self.device)
         dist.all_gather_into_tensor(stage, cs, group=self.group)
@@ -247,17 +304,25 @@ class TrainEngine:
     def _reduce_scatter(self, u: Unit, full_grad: torch.Tensor):
         """Sum the unit's full fp32 gradients over ranks into this rank's grad shard."""
         gs = self._unit_views(u, self.grad)
-        stage = torch.empty(self.W, u.shard_numel, dtype=torch.float32, device=self.device)
-        for s in u.slots:
+        slots = [s for s in u.slots if not s.peer]
+        if not slots:
+            return
+        offs, tot = [], 0
+        for s in slots:
+            offs.append(tot)
+            tot += _align(s.shard_numel)
+        stage = torch.zeros(self.W, tot, dtype=torch.float32, device=self.device)
+        for s, o in zip(slots, offs):
             src = full_grad[s.full_off:s.full_off + s.numel]
             if s.sharded:
-                stage[:, s.shard_off:s.shard_off + s.shard_numel].copy_(src.view(self.W, s.shard_numel))
-            else:  # replicated parameter: every rank receives the full sum / W slices summed later
-                stage[:, s.shard_off:s.shard_off + s.numel].copy_(src.unsqueeze(0).expand(self.W, -1))
-        out = torch.empty(u.shard_numel, dtype=torch.float32, device=self.device)
+                stage[:, o:o + s.shard_numel].copy_(src.view(self.W, s.shard_numel))
+            else:  # replicated parameter: every rank receives the full sum
+                stage[:, o:o + s.numel].copy_(src.unsqueeze(0).expand(self.W, -1))
+        out = torch.empty(tot, dtype=torch.float32, device=self.device)
         dist.reduce_scatter_tensor(out, stage.view(-1), op=dist.ReduceOp.SUM, group=self.group)
-        gs.add_(out)
-        full_grad.zero_()
+        for s, o in zip(slots, offs):
+            gs[s.shard_off:s.shard_off + s.shard_numel].add_(out[o:o + s.shard_numel])
+            full_grad[s.full_off:s.full_off + s.numel].zero_()
 
     # ------------------------------------------------------------------ layer execution
     def run_layer(self, layer, x, ctx):
@@ -266,13 +331,36 @@ class TrainEngine:
             return layer(x, ctx)
         return _RematLayerFn.apply(x, self, u, layer, ctx)
 
-    def _acquire(self, u: Unit):
+    def _acquire(self, u: Unit, direction: int = 1):
+        """Make the unit's gathered parameters current.  With peer-memory transport the gather
+        of the neighbouring layer (next in forward, previous in backward) is issued on the
+        communication stream into the other ring slot so it overlaps this layer's math."""
         if u.resident:
             return
-        idx = int(u.name.split(".")[1]) & 1
-        full = self._ring[idx]
-        self._bind(u, full, self._ring_grad)
-        self._all_gather(u, full)
+        li = int(u.name.split(".")[1])
+        idx = li & 1
+        self._bind(u, self._ring[idx], self._ring_grad)
+        if self.comm_kind != "p2p":
+            self._all_gather(u, self._ring[idx])
+            return
+        if self._ring_owner[idx] != (u.name, self._weights_version):
+            self._issue_gather(u, idx)
+        torch.cuda.current_stream().wait_event(self._ring_event[idx])
+        nb = self._layer_by_index.get(li + direction)
+        if nb is not None and self._ring_owner[(li + direction) & 1] != (nb.name, self._weights_version):
+            self._issue_gather(nb, (li + direction) & 1)
+
+    def _issue_gather(self, u: Unit, idx: int):
+        cur = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(cur)  # the previous user of this ring slot has been enqueued before this point
+        with torch.cuda.stream(self._comm_stream):
+            self._comm_stream.wait_event(ready)
+            self._symm.allgather_pull(self._shard_buf, self._ring[idx], self._seg_table(u))
+            ev = torch.cuda.Event()
+            ev.record(self._comm_stream)
+        self._ring_event[idx] = ev
+        self._ring_owner[idx] = (u.name, self._weights_version)
 
     def _release_grads(self, u: Unit):
         """After a unit's backward: fold stray autograd grads, then reduce-scatter."""
@@ -296,6 +384,8 @@ class TrainEngine:
                     p.grad = None
             if self.W > 1 and u.resident:
                 self._reduce_scatter(u, u.full_grad)
+        if self.comm_kind == "p2p":
+            self._barrier()  # every peer's gradient contributions to this shard have landed
         self.micro_steps += 1
 
     # ------------------------------------------------------------------ optimizer
@@ -346,6 +436,9 @@ class TrainEngine:
             self.grad.zero_()
             self._refresh_compute_shard()
         if self.W > 1:
+            self._weights_version += 1
+            if self.comm_kind == "p2p":
+                self._barrier()  # all compute shards hold the new weights before anyone pulls
             for u in self.units:
                 if u.resident:
                     self._all_gather(u, u.gathered)
@@ -395,7 +488,7 @@ class _RematLayerFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, engine: TrainEngine, unit: Unit, layer, fctx):
-        engine._acquire(unit)
+        engine._acquire(unit, +1)
         with torch.no_grad():
             y, aux = layer(x, fctx)
         ctx.save_for_backward(x)
@@ -406,7 +499,7 @@ class _RematLayerFn(torch.autograd.Function):
     def backward(ctx, dy, daux):
         (x,) = ctx.saved_tensors
         engine, unit, layer, fctx = ctx.engine, ctx.unit, ctx.layer, ctx.fctx
-        engine._acquire(unit)
+        engine._acquire(unit, -1)
         with torch.enable_grad():
             xin = x.detach().requires_grad_(True)
             y, aux = layer(xin, fctx)

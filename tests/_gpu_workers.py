@@ -1,0 +1,89 @@
+"""Worker functions for multi-GPU tests (NCCL bootstrap, one process per GPU)."""
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def _init(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+
+
+def symm_primitives(rank, world, port, out_path):
+    _init(rank, world, port)
+    from omegalax_b200.ops import kernels as K, lib
+    from omegalax_b200.parallel import symm
+
+    dev = torch.device("cuda", rank)
+    res = {}
+    n = 1 << 20
+    shard = symm.SymmetricBuffer(n * 2)
+    mine = shard.view(torch.bfloat16, n)
+    mine.copy_((torch.arange(n, device=dev) % 251 + rank * 1000).to(torch.bfloat16))
+    bar = symm.DeviceBarrier()
+    bar()
+    full = torch.zeros(world * n, dtype=torch.bfloat16, device=dev)
+    tab = symm.make_copy_segments([(r, 0, r * n * 2, n * 2) for r in range(world)], dev)
+    symm.allgather_pull(shard, full, tab)
+    torch.cuda.synchronize()
+    want = torch.cat([(torch.arange(n, device=dev) % 251 + r * 1000).to(torch.bfloat16) for r in range(world)])
+    res["allgather_ok"] = bool(torch.equal(full, want))
+    # GEMM whose fp32 output rows are reduced into the owning rank's buffer
+    M, N, Kd = 512, 256 * world, 384
+    torch.manual_seed(1 + rank)
+    a = torch.randn(M, Kd, device=dev).to(torch.bfloat16)     # this rank's activations
+    dy = torch.randn(M, N, device=dev).to(torch.bfloat16)
+    gbuf = symm.SymmetricBuffer((N // world) * Kd * 4)
+    bar()
+    K.gemm_peer_reduce(dy, a, gbuf.peer_ptr_list(0), N // world, Kd, a_mn=True, b_mn=True)
+    bar()
+    torch.cuda.synchronize()
+    got = gbuf.view(torch.float32, (N // world) * Kd).view(N // world, Kd)
+    ref_local = dy.float().t() @ a.float()                        # [N, Kd] contribution of this rank
+    dist.all_reduce(ref_local)
+    ref = ref_local[rank * (N // world):(rank + 1) * (N // world)]
+    res["peer_reduce_err"] = float((got - ref).abs().max() / ref.abs().max())
+    lib.check_status()
+    if rank == 0:
+        torch.save(res, out_path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def fsdp_train_gpu(rank, world, port, comm, steps, out_path):
+    _init(rank, world, port)
+    import dataclasses
+
+    from omegalax_b200.ops import lib
+    from omegalax_b200.parallel import mesh as mesh_lib
+    from omegalax_b200.text import api as text_api
+    from omegalax_b200.trainers import text as trainer
+    from omegalax_b200.trainers.optim import MixedPrecisionOptimizer
+
+    mesh_lib.set_default_mesh(None)
+    mesh = mesh_lib.ensure_mesh(tp_size=1, fsdp_size=world, dp_size=1)
+    cfg = dataclasses.replace(text_api.resolve_config("Qwen/Qwen3-8B"), num_layers=3, emb_dim=512, mlp_dim=1024,
+                              num_heads=4, num_kv_heads=2, vocab_size=4096)
+    tcfg = trainer.TrainConfig(seed=0, batch_size=4, seq_len=256, num_steps=100, learning_rate=1e-3, max_grad_norm=1.0)
+    model, cfg = trainer.init_model(cfg, 0, tp_size=1, fsdp_size=world, dp_size=1, meta=True)
+    group = mesh.group("shard")
+    opt = MixedPrecisionOptimizer(model, device=torch.device("cuda", rank), shard_group=group, lr=1e-3,
+                                  weight_decay=0.01, max_grad_norm=1.0, seed=0, comm=comm)
+    step = trainer.make_sft_train_step(cfg)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(1, cfg.vocab_size, (4, 256), generator=g, dtype=torch.int32)
+    per = 4 // world
+    sl = slice(rank * per, (rank + 1) * per)
+    batch = {"token_ids_BT": tok[sl].cuda(), "attention_mask_BT": torch.ones(per, 256, dtype=torch.int32).cuda(),
+             "loss_mask_BT": torch.ones(per, 256, dtype=torch.int32).cuda()}
+    losses = [float(step(opt, batch)[0]) for _ in range(steps)]
+    torch.cuda.synchronize()
+    lib.check_status()
+    if rank == 0:
+        torch.save({"losses": losses, "grad_norm": float(opt.last_grad_norm)}, out_path)
+    if world > 1:
+        dist.barrier()
+    dist.destroy_process_group()
