@@ -485,3 +485,56 @@ int ob_attn_bwd(const void* q, const void* k, const void* v, const void* out, co
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant (see attention_noalloc.h).  The work buffers of ob_attn_bwd live in
+// this fixed device array: [0, 16 MiB) the fp32 dQ accumulator, then 128 KiB for delta.
+#include "attention_noalloc.h"
+
+namespace {
+constexpr size_t kNoAllocDqBytes = (size_t)OB_ATTN_NOALLOC_MAX_ROW_HEADS * 128 * sizeof(float);
+constexpr size_t kNoAllocDeltaBytes = (size_t)OB_ATTN_NOALLOC_MAX_ROW_HEADS * sizeof(float);
+static __device__ __align__(256) unsigned char g_attn_noalloc_scratch[kNoAllocDqBytes + kNoAllocDeltaBytes];
+
+// In host code the array's name is only a handle for the runtime, not a device address; the
+// address is resolved once per device (with that device current) and cached here.
+unsigned char* noalloc_scratch_for_current_device(int* err) {
+  static unsigned char* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    *err = 6101;
+    return nullptr;
+  }
+  if (!cached[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_attn_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      *err = 6101;
+      return nullptr;
+    }
+    cached[dev] = (unsigned char*)p;
+  }
+  *err = 0;
+  return cached[dev];
+}
+}  // namespace
+
+extern "C" int ob_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                   const float* lse, void* dq, void* dk, void* dv, const int* cu_seqlens, int B,
+                                   int max_seqlen, long long total_rows, int H, int G, int HD,
+                                   long long q_row_stride, long long k_row_stride, long long v_row_stride,
+                                   long long o_row_stride, long long do_row_stride, long long dk_row_stride,
+                                   long long dv_row_stride, float scale, int causal, int* status,
+                                   cudaStream_t stream) {
+  if (B <= 0 || total_rows <= 0) return 0;
+  if (total_rows * (long long)H > OB_ATTN_NOALLOC_MAX_ROW_HEADS) return 6100;  // beyond the built-in scratch
+  int err = 0;
+  unsigned char* base = noalloc_scratch_for_current_device(&err);
+  if (!base) return err;
+  float* dq_acc = reinterpret_cast<float*>(base);
+  float* delta = reinterpret_cast<float*>(base + kNoAllocDqBytes);
+  // ob_attn_bwd zeroes dq_acc itself (cudaMemsetAsync on `stream`) and overwrites delta fully.
+  return ob_attn_bwd(q, k, v, out, dout, lse, delta, dq_acc, dq, dk, dv, cu_seqlens, B, max_seqlen, total_rows, H,
+                     G, HD, q_row_stride, k_row_stride, v_row_stride, o_row_stride, do_row_stride, dk_row_stride,
+                     dv_row_stride, scale, causal, status, stream);
+}
