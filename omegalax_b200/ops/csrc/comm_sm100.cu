@@ -158,3 +158,127 @@ int ob_reduce_scatter_pull(void* const* full_ptrs, int world, int rank, float* o
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Expert-parallel token exchange over peer memory (dispatch / combine).
+//
+// push: for every (token, slot) pair p, the token's row is written into the receive buffer of
+//       the GPU that owns the chosen expert, at the row the routing plan assigned to it (the
+//       router permutation is folded into the destination address).  An optional per-pair
+//       scale implements the backward of the weighted combine.
+// pull: every token gathers its k expert outputs from the owners' buffers and forms the
+//       weighted sum in fp32 (weighted un-permute); optionally also the per-pair dot product
+//       with an upstream gradient (gradient of the routing weights).
+// One warp per pair (push) or per token (pull); rows are moved as 16-byte vectors.
+namespace ob {
+
+__global__ void ep_push_kernel(PeerPtrs dst, const bf16* __restrict__ src, const int* __restrict__ src_row,
+                               const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
+                               const float* __restrict__ scale, long long P, int D) {
+  const long long p = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (p >= P) return;
+  const uint4* s = reinterpret_cast<const uint4*>(src + (long long)src_row[p] * D);
+  uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst.p[dst_rank[p]]) + (long long)dst_row[p] * D);
+  const int nv = D >> 3;
+  if (scale == nullptr) {
+    for (int i = lane; i < nv; i += 32) d[i] = s[i];
+  } else {
+    const float sc = scale[p];
+    for (int i = lane; i < nv; i += 32) {
+      uint4 q = s[i];
+      uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = unpack_bf16(u[j]);
+        u[j] = pack_bf16(f.x * sc, f.y * sc);
+      }
+      d[i] = make_uint4(u[0], u[1], u[2], u[3]);
+    }
+  }
+}
+
+__global__ void ep_pull_kernel(PeerPtrs src, bf16* __restrict__ out, const int* __restrict__ src_rank,
+                               const int* __restrict__ src_row, const float* __restrict__ w,
+                               const bf16* __restrict__ g, float* __restrict__ dot_out, long long M, int k, int D) {
+  const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= M) return;
+  const int nv = D >> 3;
+  for (int c0 = 0; c0 < nv; c0 += 32) {
+    const int i = c0 + lane;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float gv[8];
+    if (g != nullptr && i < nv) {
+      uint4 q = reinterpret_cast<const uint4*>(g + t * D)[i];
+      uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = unpack_bf16(u[j]);
+        gv[2 * j] = f.x; gv[2 * j + 1] = f.y;
+      }
+    }
+    for (int j = 0; j < k; ++j) {
+      const long long p = t * k + j;
+      float dot = 0.f;
+      if (i < nv) {
+        const uint4 q = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(src.p[src_rank[p]]) +
+                                                       (long long)src_row[p] * D)[i];
+        const float wj = w ? w[p] : 1.f;
+        uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float2 f = unpack_bf16(u[e]);
+          acc[2 * e] += wj * f.x;
+          acc[2 * e + 1] += wj * f.y;
+          if (g != nullptr) dot += gv[2 * e] * f.x + gv[2 * e + 1] * f.y;
+        }
+      }
+      if (g != nullptr) {
+        dot = warp_sum(dot);
+        if (lane == 0) {
+          if (c0 == 0) dot_out[p] = dot; else dot_out[p] += dot;
+        }
+      }
+    }
+    if (out != nullptr && i < nv) {
+      uint4 o;
+      o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+      o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+      reinterpret_cast<uint4*>(out + t * D)[i] = o;
+    }
+  }
+}
+
+}  // namespace ob
+
+extern "C" {
+
+int ob_ep_push(void* const* dst_ptrs, int world, const void* src, const int* src_row, const int* dst_rank,
+               const int* dst_row, const float* scale, long long P, int D, cudaStream_t stream) {
+  if (world > kMaxRanks) return 6003;
+  if (D % 8) return 6001;
+  if (P <= 0) return 0;
+  PeerPtrs d = {};
+  for (int i = 0; i < world; ++i) d.p[i] = dst_ptrs[i];
+  long long blocks = (P * 32 + 255) / 256;
+  ep_push_kernel<<<(unsigned)blocks, 256, 0, stream>>>(d, (const bf16*)src, src_row, dst_rank, dst_row, scale, P, D);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_ep_pull(void* const* src_ptrs, int world, void* out, const int* src_rank, const int* src_row,
+               const float* w, const void* g, float* dot_out, long long M, int k, int D, cudaStream_t stream) {
+  if (world > kMaxRanks) return 6003;
+  if (D % 8) return 6001;
+  if (M <= 0) return 0;
+  PeerPtrs s = {};
+  for (int i = 0; i < world; ++i) s.p[i] = src_ptrs[i];
+  long long blocks = (M * 32 + 255) / 256;
+  ep_pull_kernel<<<(unsigned)blocks, 256, 0, stream>>>(s, (bf16*)out, src_rank, src_row, w, (const bf16*)g, dot_out,
+                                                       M, k, D);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // extern "C"

@@ -47,6 +47,7 @@ class ParamSlot:
     module: nn.Module = None
     pname: str = ""
     peer: bool = False     # gradient goes through the GEMM peer-reduce epilogue
+    ep: bool = False       # expert-parallel: never gathered, this rank computes with its own slice
 
 
 @dataclasses.dataclass
@@ -90,7 +91,8 @@ class TrainEngine:
     def __init__(self, model: nn.Module, *, device, shard_group=None, lr: float = 1e-4,
                  weight_decay: float = 0.01, betas=(0.9, 0.999), eps: float = 1e-8,
                  max_grad_norm: float | None = 1.0, remat: str = "full", seed: int = 0,
-                 init_from_model: bool = False, comm: str = "auto"):
+                 init_from_model: bool = False, comm: str = "auto", expert_parallel: bool = True,
+                 ep_capacity_factor: float = 2.0):
         self.model = model
         self.device = torch.device(device)
         self.group = shard_group
@@ -106,6 +108,9 @@ class TrainEngine:
         if comm == "auto":
             comm = "p2p" if (self.device.type == "cuda" and self.W > 1) else "nccl"
         self.comm_kind = comm if self.W > 1 else "none"
+        self.expert_parallel = bool(expert_parallel) and self.comm_kind == "p2p"
+        self.ep_capacity_factor = ep_capacity_factor
+        self._ep = None
         self._build_units()
         self._allocate()
         self._materialize(seed, init_from_model)
@@ -249,6 +254,12 @@ class TrainEngine:
 
     def _bind(self, u: Unit, full: torch.Tensor, full_grad: torch.Tensor | None):
         for s in u.slots:
+            if s.ep:  # this rank's experts only, straight from the shard buffers
+                shp = (s.shape[0] // self.W, *s.shape[1:])
+                cs, gs = self._unit_views(u, self.compute_shard), self._unit_views(u, self.grad)
+                s.param.data = cs[s.shard_off:s.shard_off + s.shard_numel].view(shp)
+                s.param.main_grad = gs[s.shard_off:s.shard_off + s.shard_numel].view(shp)
+                continue
             s.param.data = full[s.full_off:s.full_off + s.numel].view(s.shape)
             if full_grad is not None:
                 s.param.main_grad = full_grad[s.full_off:s.full_off + s.numel].view(s.shape)
@@ -257,6 +268,11 @@ class TrainEngine:
         """Weights of Linear modules take their gradient through the GEMM epilogue that adds
         each row block straight into the owning rank's fp32 gradient shard over NVLink."""
         for s in u.slots:
+            if self.expert_parallel and s.sharded and s.pname.rsplit(".", 1)[-1] in ("experts_gate_up", "experts_down"):
+                s.ep = s.peer = True
+                owner = s.module.get_submodule(s.pname.rsplit(".", 1)[0]) if "." in s.pname else s.module
+                owner.ep = _LazyEP(self, owner)
+                continue
             if not (s.sharded and len(s.shape) == 2 and s.pname.endswith("weight")):
                 continue
             owner = s.module.get_submodule(s.pname.rsplit(".", 1)[0]) if "." in s.pname else s.module
@@ -272,6 +288,8 @@ class TrainEngine:
             esz = 2 if self.compute_dtype == bf16 else 4
             segs = []
             for s in u.slots:
+                if s.ep:
+                    continue
                 src = (u.shard_base + s.shard_off) * esz
                 if s.sharded:
                     for r in range(self.W):
@@ -481,6 +499,24 @@ class TrainEngine:
         out = torch.empty(self.W * slot.shard_numel, dtype=torch.float32, device=self.device)
         dist.all_gather_into_tensor(out, ms.contiguous(), group=self.group)
         return out.view(slot.shape)
+
+
+class _LazyEP:
+    """Creates the shared expert-parallel exchange (symmetric receive buffers) on first use,
+    when the number of tokens per rank is known."""
+
+    def __init__(self, engine: "TrainEngine", module):
+        self.engine, self.module = engine, module
+
+    def moe_mlp(self, x, w, idx, gate_up_local, down_local):
+        eng = self.engine
+        if eng._ep is None or eng._ep.max_tokens < x.shape[0]:
+            from .ep import ExpertParallel
+
+            eng._ep = ExpertParallel(eng.group, self.module.E, x.shape[1], x.shape[0], idx.shape[1],
+                                     capacity_factor=eng.ep_capacity_factor, dtype=x.dtype)
+            eng._ep.max_tokens = x.shape[0]
+        return eng._ep.moe_mlp(x, w, idx, gate_up_local, down_local)
 
 
 class _RematLayerFn(torch.autograd.Function):

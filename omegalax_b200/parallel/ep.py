@@ -1,0 +1,181 @@
+"""Expert parallelism: experts are sharded over the data ranks and tokens travel to them.
+
+Rank r owns experts [r*E/W, (r+1)*E/W).  One MoE layer runs as
+
+    plan      counts per (rank, expert) are all-gathered (E ints per rank); every rank derives
+              the same row layout of every receive buffer: per local expert, the senders'
+              segments in rank order, each expert padded to a multiple of 128 rows
+    dispatch  each (token, slot) row is written straight into the owner's receive buffer at
+              its final row -- router permutation and all-to-all in one kernel (peer stores)
+    experts   grouped tcgen05 GEMMs + SwiGLU on the local receive buffer
+    combine   every token pulls its k expert outputs from the owners (peer loads) and forms the
+              weighted sum in fp32 -- all-to-all and weighted un-permute in one kernel
+
+The backward uses the same two kernels with the roles swapped (a scaled push for the combine,
+a pull for the dispatch, plus a pull that returns the per-pair dot products for the routing
+weight gradient).  Cross-GPU ordering uses the bounded device barrier.  The reference has no
+expert parallelism (it evaluates every expert for every token: omegalax/models/qwen3/model.py:92-104).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ..ops import lib
+from ..ops import moe as moe_ops
+from . import symm
+
+PAD = 128
+
+
+def _register():
+    P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    lib.register("ob_ep_push", [P, I, P, P, P, P, P, L, I, P])
+    lib.register("ob_ep_pull", [P, I, P, P, P, P, P, P, L, I, I, P])
+
+
+_register()
+
+
+class Plan:
+    """Row assignment of one MoE layer call (device tensors, no host sync)."""
+    __slots__ = ("dst_rank", "dst_row", "src_tok", "offsets_local", "M", "k", "overflow")
+
+
+def build_plan(idx, E: int, W: int, rank: int, group, capacity: int) -> Plan:
+    """idx [M,k] global expert ids -> destination (rank, row) of every pair and the local
+    group offsets of this rank's receive buffer."""
+    M, k = idx.shape
+    dev = idx.device
+    El = E // W
+    flat = idx.reshape(-1)
+    counts = torch.bincount(flat, minlength=E).to(torch.int32)             # my pairs per global expert
+    allc = torch.empty(W, E, dtype=torch.int32, device=dev)
+    if W > 1:
+        dist.all_gather_into_tensor(allc.view(-1), counts, group=group)
+    else:
+        allc[0] = counts
+    allc = allc.to(torch.int64)
+    tot = allc.sum(0)                                                      # rows per global expert
+    padded = (tot + PAD - 1) // PAD * PAD
+    pe = padded.view(W, El)
+    base_e = (pe.cumsum(1) - pe).reshape(-1)                               # start of expert inside its owner's buffer
+    before_me = allc[:rank].sum(0) if rank > 0 else torch.zeros(E, dtype=torch.int64, device=dev)
+    # rank of every pair among my pairs of the same expert (stable sort)
+    order = torch.argsort(flat, stable=True)
+    starts = counts.to(torch.int64).cumsum(0) - counts.to(torch.int64)
+    sorted_e = flat[order]
+    r_in_e = torch.arange(flat.numel(), device=dev) - starts[sorted_e]
+    row_sorted = base_e[sorted_e] + before_me[sorted_e] + r_in_e
+    dst_row = torch.empty_like(row_sorted)
+    dst_row[order] = row_sorted
+    p = Plan()
+    p.dst_rank = (flat // El).to(torch.int32)
+    p.dst_row = dst_row.to(torch.int32)
+    p.src_tok = torch.arange(M, device=dev, dtype=torch.int32).repeat_interleave(k)
+    mine = pe[rank]
+    offs = torch.zeros(El + 1, dtype=torch.int64, device=dev)
+    offs[1:] = mine.cumsum(0)
+    p.offsets_local = offs.to(torch.int32)
+    p.M, p.k = M, k
+    p.overflow = (pe.sum(1).max() > capacity)                             # checked lazily by the caller
+    return p
+
+
+class ExpertParallel:
+    def __init__(self, group, num_experts: int, hidden: int, max_tokens: int, top_k: int, *,
+                 capacity_factor: float = 2.0, dtype=torch.bfloat16):
+        self.group = group
+        self.W = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        if num_experts % self.W:
+            raise ValueError(f"{num_experts} experts do not divide over {self.W} ranks")
+        self.E, self.D, self.El = num_experts, hidden, num_experts // self.W
+        cap = int(capacity_factor * max_tokens * top_k) + self.El * (PAD - 1)
+        self.capacity = (cap + PAD - 1) // PAD * PAD
+        nbytes = self.capacity * hidden * 2
+        # receive buffers: token rows in, expert outputs, and their two gradient counterparts
+        self.buf_in = symm.SymmetricBuffer(nbytes, group)
+        self.buf_out = symm.SymmetricBuffer(nbytes, group)
+        self.buf_gout = symm.SymmetricBuffer(nbytes, group)
+        self.buf_gin = symm.SymmetricBuffer(nbytes, group)
+        self.barrier = symm.DeviceBarrier(group)
+        self.dtype = dtype
+        self.overflow_flag = torch.zeros(1, dtype=torch.bool, device="cuda")
+
+    def local(self, buf: symm.SymmetricBuffer) -> torch.Tensor:
+        return buf.view(self.dtype, self.capacity * self.D).view(self.capacity, self.D)
+
+    def push(self, buf, src, plan: Plan, scale=None):
+        lib.call("ob_ep_push", buf.ptr_table(), self.W, src.data_ptr(), plan.src_tok.data_ptr(),
+                 plan.dst_rank.data_ptr(), plan.dst_row.data_ptr(), lib.ptr(scale), plan.M * plan.k, self.D,
+                 lib.stream_ptr())
+
+    def pull(self, buf, plan: Plan, weights=None, out=True, grad=None):
+        o = torch.empty(plan.M, self.D, dtype=self.dtype, device="cuda") if out else None
+        dots = torch.empty(plan.M * plan.k, dtype=torch.float32, device="cuda") if grad is not None else None
+        lib.call("ob_ep_pull", buf.ptr_table(), self.W, lib.ptr(o), plan.dst_rank.data_ptr(), plan.dst_row.data_ptr(),
+                 lib.ptr(weights), lib.ptr(grad), lib.ptr(dots), plan.M, plan.k, self.D, lib.stream_ptr())
+        return o, dots
+
+    def check(self):
+        if bool(self.overflow_flag.item()):
+            raise RuntimeError("expert-parallel receive buffer overflow: raise capacity_factor")
+
+    def moe_mlp(self, x, weights, idx, w_gate_up_local, w_down_local):
+        """x [M,D] local tokens; weights/idx [M,k]; expert weights are this rank's E/W experts."""
+        plan = build_plan(idx, self.E, self.W, self.rank, self.group, self.capacity)
+        self.overflow_flag |= plan.overflow
+        xp = _Dispatch.apply(x.contiguous(), self, plan)
+        yp = moe_ops.expert_mlp_permuted(xp, w_gate_up_local, w_down_local, plan.offsets_local)
+        return _Combine.apply(yp, weights.contiguous().float(), self, plan)
+
+
+class _Dispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, ep: ExpertParallel, plan: Plan):
+        ep.local(ep.buf_in).zero_()           # padding rows must be zero for the grouped GEMMs
+        ep.barrier()                          # every rank has cleared its buffer before peers write
+        ep.push(ep.buf_in, x, plan)
+        ep.barrier()                          # all rows have landed
+        ctx.ep, ctx.plan = ep, plan
+        return ep.local(ep.buf_in).clone()
+
+    @staticmethod
+    def backward(ctx, d_xp):
+        ep, plan = ctx.ep, ctx.plan
+        ep.local(ep.buf_gin).copy_(d_xp)
+        ep.barrier()
+        dx, _ = ep.pull(ep.buf_gin, plan, weights=None)
+        ep.barrier()                          # peers are done reading before the buffer is reused
+        return dx, None, None
+
+
+class _Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, yp, weights, ep: ExpertParallel, plan: Plan):
+        ep.local(ep.buf_out).copy_(yp)
+        ep.barrier()
+        y, _ = ep.pull(ep.buf_out, plan, weights=weights.reshape(-1))
+        ep.barrier()
+        ctx.ep, ctx.plan = ep, plan
+        ctx.save_for_backward(weights, yp)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        ep, plan = ctx.ep, ctx.plan
+        weights, yp = ctx.saved_tensors
+        dy = dy.contiguous()
+        # gradient of the routing weights: <dy[token], expert output row>
+        ep.local(ep.buf_out).copy_(yp)
+        ep.local(ep.buf_gout).zero_()
+        ep.barrier()
+        _, dots = ep.pull(ep.buf_out, plan, weights=None, out=False, grad=dy)
+        # gradient of the expert outputs: weight * dy[token], pushed to the owners
+        ep.push(ep.buf_gout, dy, plan, scale=weights.reshape(-1))
+        ep.barrier()
+        d_yp = ep.local(ep.buf_gout).clone()
+        return d_yp, dots.view_as(weights), None, None

@@ -87,3 +87,41 @@ def fsdp_train_gpu(rank, world, port, comm, steps, out_path):
     if world > 1:
         dist.barrier()
     dist.destroy_process_group()
+
+
+def ep_train_gpu(rank, world, port, steps, out_path):
+    """Qwen3-MoE with experts sharded over the ranks (expert parallel) vs the same run on one GPU."""
+    _init(rank, world, port)
+    import dataclasses
+
+    from omegalax_b200.ops import lib
+    from omegalax_b200.parallel import mesh as mesh_lib
+    from omegalax_b200.text import api as text_api
+    from omegalax_b200.trainers import text as trainer
+    from omegalax_b200.trainers.optim import MixedPrecisionOptimizer
+
+    mesh_lib.set_default_mesh(None)
+    mesh = mesh_lib.ensure_mesh(tp_size=1, fsdp_size=world, dp_size=1)
+    cfg = dataclasses.replace(text_api.resolve_config("Qwen/Qwen3-30B-A3B-Instruct-2507"), num_layers=2, emb_dim=256,
+                              mlp_dim=512, moe_intermediate_size=128, num_experts=8, num_experts_per_tok=2,
+                              num_heads=2, num_kv_heads=1, vocab_size=2048)
+    model, cfg = trainer.init_model(cfg, 0, tp_size=1, fsdp_size=world, dp_size=1, meta=True)
+    opt = MixedPrecisionOptimizer(model, device=torch.device("cuda", rank), shard_group=mesh.group("shard"), lr=1e-3,
+                                  weight_decay=0.01, max_grad_norm=1.0, seed=0)
+    step = trainer.make_sft_train_step(cfg)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(1, cfg.vocab_size, (4, 256), generator=g, dtype=torch.int32)
+    per = 4 // world
+    sl = slice(rank * per, (rank + 1) * per)
+    batch = {"token_ids_BT": tok[sl].cuda(), "attention_mask_BT": torch.ones(per, 256, dtype=torch.int32).cuda(),
+             "loss_mask_BT": torch.ones(per, 256, dtype=torch.int32).cuda()}
+    losses = [float(step(opt, batch)[0]) for _ in range(steps)]
+    torch.cuda.synchronize()
+    lib.check_status()
+    if opt._ep is not None:
+        opt._ep.check()
+    if rank == 0:
+        torch.save({"losses": losses, "used_ep": opt._ep is not None}, out_path)
+    if world > 1:
+        dist.barrier()
+    dist.destroy_process_group()
