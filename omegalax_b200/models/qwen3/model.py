@@ -16,6 +16,7 @@ from torch import nn
 from ...ops import functional as Fn
 from ...ops import moe as moe_ops
 from ...ops import reference as R
+from ...parallel import tp as tp_lib
 from .cache import LayerCache
 from .config import Qwen3Config
 from .norms import RMSNorm
@@ -45,6 +46,7 @@ class Linear(nn.Module):
         super().__init__()
         self.weight = nn.Parameter(torch.empty(out_dim, in_dim, device=device, dtype=dtype))
         self.bias = nn.Parameter(torch.zeros(out_dim, device=device, dtype=dtype)) if bias else None
+        self.tp_sharded = False  # True when this rank holds only its tensor-parallel slice
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -72,18 +74,25 @@ class ForwardCtx:
 
 
 class Attention(nn.Module):
-    def __init__(self, cfg: Qwen3Config, device=None, dtype=None):
+    def __init__(self, cfg: Qwen3Config, device=None, dtype=None, tp_size: int = 1):
         super().__init__()
-        H, G, Kd, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.emb_dim
-        self.H, self.G, self.Kd = H, G, Kd
+        if cfg.num_heads % tp_size or cfg.num_kv_heads % tp_size:
+            raise ValueError(f"heads ({cfg.num_heads} q / {cfg.num_kv_heads} kv) do not divide over tp_size={tp_size}")
+        H, G, Kd, D = cfg.num_heads // tp_size, cfg.num_kv_heads // tp_size, cfg.head_dim, cfg.emb_dim
+        self.H, self.G, self.Kd = H, G, Kd   # heads held by this tensor-parallel rank
+        self.tp_size = tp_size
         self.qkv_proj = Linear(D, (H + 2 * G) * Kd, device=device, dtype=dtype)
         self.o_proj = Linear(H * Kd, D, device=device, dtype=dtype)
         self.q_norm = RMSNorm(Kd, cfg.norm_eps, device=device, dtype=dtype)
         self.k_norm = RMSNorm(Kd, cfg.norm_eps, device=device, dtype=dtype)
         self.eps = cfg.norm_eps
         self.scale = Kd ** -0.5
+        self.qkv_proj.tp_sharded = self.o_proj.tp_sharded = tp_size > 1
 
     def forward(self, x, ctx: ForwardCtx, residual=None, cache: LayerCache | None = None):
+        tp = tp_lib.current() if self.tp_size > 1 else None
+        if tp is not None:
+            x = tp_lib.all_gather_rows(x, tp)      # sequence-parallel rows -> all rows
         M = x.shape[0]
         qkv = self.qkv_proj(x)
         q, k, v, _ = Fn.qk_norm_rope(qkv, self.q_norm.weight, self.k_norm.weight, ctx.sin, ctx.cos,
@@ -99,7 +108,10 @@ class Attention(nn.Module):
                                 k_start=ks).reshape(M, self.H, self.Kd)
         else:
             o = self._decode(q, k, v, ctx, cache)
-        return self.o_proj(o.reshape(M, self.H * self.Kd), residual=residual)
+        o = o.reshape(M, self.H * self.Kd)
+        if tp is not None:
+            return tp_lib.row_parallel_linear(o, self.o_proj.weight, residual, tp)
+        return self.o_proj(o, residual=residual)
 
     def _decode(self, q, k, v, ctx: ForwardCtx, cache: LayerCache):
         """Append this call's K/V at the cursor and attend over the whole cache with the mask
@@ -128,12 +140,21 @@ class Attention(nn.Module):
 class MLP(nn.Module):
     """SwiGLU feed-forward: down(silu(gate(x)) * up(x)) with gate and up fused row-wise."""
 
-    def __init__(self, dim: int, hidden: int, device=None, dtype=None):
+    def __init__(self, dim: int, hidden: int, device=None, dtype=None, tp_size: int = 1):
         super().__init__()
-        self.gate_up_proj = Linear(dim, 2 * hidden, device=device, dtype=dtype)
+        if hidden % tp_size:
+            raise ValueError(f"mlp width {hidden} does not divide over tp_size={tp_size}")
+        hidden //= tp_size
+        self.tp_size = tp_size
+        self.gate_up_proj = Linear(dim, 2 * hidden, device=device, dtype=dtype)   # this rank's [gate | up]
         self.down_proj = Linear(hidden, dim, device=device, dtype=dtype)
+        self.gate_up_proj.tp_sharded = self.down_proj.tp_sharded = tp_size > 1
 
     def forward(self, x, residual=None):
+        tp = tp_lib.current() if self.tp_size > 1 else None
+        if tp is not None:
+            h = Fn.swiglu(tp_lib.column_parallel_linear(x, self.gate_up_proj.weight, tp))
+            return tp_lib.row_parallel_linear(h, self.down_proj.weight, residual, tp)
         return self.down_proj(Fn.swiglu(self.gate_up_proj(x)), residual=residual)
 
 
@@ -170,16 +191,16 @@ class MoEFeedForward(nn.Module):
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: Qwen3Config, layer_idx: int, device=None, dtype=None):
+    def __init__(self, cfg: Qwen3Config, layer_idx: int, device=None, dtype=None, tp_size: int = 1):
         super().__init__()
         self.input_norm = RMSNorm(cfg.emb_dim, cfg.norm_eps, device=device, dtype=dtype)
-        self.attn = Attention(cfg, device=device, dtype=dtype)
+        self.attn = Attention(cfg, device=device, dtype=dtype, tp_size=tp_size)
         self.post_norm = RMSNorm(cfg.emb_dim, cfg.norm_eps, device=device, dtype=dtype)
         self.is_moe = cfg.is_moe_layer(layer_idx)
         if self.is_moe:
             self.mlp = MoEFeedForward(cfg, device=device, dtype=dtype)
         else:
-            self.mlp = MLP(cfg.emb_dim, cfg.mlp_dim, device=device, dtype=dtype)
+            self.mlp = MLP(cfg.emb_dim, cfg.mlp_dim, device=device, dtype=dtype, tp_size=tp_size)
 
     def forward(self, x, ctx: ForwardCtx, cache: LayerCache | None = None):
         x = self.attn(self.input_norm(x), ctx, residual=x, cache=cache)
@@ -195,12 +216,13 @@ class Qwen3(nn.Module):
     """Returns the final hidden states (before lm_head) and the summed auxiliary loss; the
     lm_head is a separate projection applied by callers (loss, decode)."""
 
-    def __init__(self, cfg: Qwen3Config, device=None, dtype=None):
+    def __init__(self, cfg: Qwen3Config, device=None, dtype=None, tp_size: int = 1):
         super().__init__()
         self.cfg = cfg
+        self.tp_size = tp_size
         dtype = dtype or torch.float32
         self.embedder = Embedding(cfg.vocab_size, cfg.emb_dim, device=device, dtype=dtype)
-        self.layers = nn.ModuleList(DecoderLayer(cfg, i, device=device, dtype=dtype)
+        self.layers = nn.ModuleList(DecoderLayer(cfg, i, device=device, dtype=dtype, tp_size=tp_size)
                                     for i in range(cfg.num_layers))
         self.final_norm = RMSNorm(cfg.emb_dim, cfg.norm_eps, device=device, dtype=dtype)
         self.lm_head = Linear(cfg.emb_dim, cfg.vocab_size, device=device, dtype=dtype)
@@ -225,7 +247,11 @@ class Qwen3(nn.Module):
     def embed(self, token_ids):
         return Fn.embedding(token_ids.reshape(-1), self.embedder.weight)
 
-    def forward(self, token_ids, segment_ids, cache=None, num_right_pads: int = 0):
+    def forward(self, token_ids, segment_ids, cache=None, num_right_pads: int = 0, return_local_rows: bool = False):
+        """With tensor parallelism the activations between blocks are sequence-parallel: this rank
+        carries rows [r*M/tp, (r+1)*M/tp) of the flattened [B*T] token rows.  By default the final
+        hidden states are gathered back to [B,T,D]; ``return_local_rows`` returns this rank's
+        rows [M/tp, D] instead (the trainer computes the loss on them)."""
         B, T = token_ids.shape
         if cache is None:
             ctx = self.make_ctx(token_ids, segment_ids)
@@ -245,6 +271,12 @@ class Qwen3(nn.Module):
             ctx = self.make_ctx(token_ids, segment_ids, position_offset=cur, start_ind=first.start_ind)
             ctx.extra["kv_valid"] = valid
         x = self.embed(token_ids)
+        tp = tp_lib.current() if self.tp_size > 1 else None
+        if tp is not None:
+            if (B * T) % tp.size or cache is not None:
+                raise ValueError("tensor parallelism needs B*T divisible by tp_size and no decode cache")
+            m = B * T // tp.size
+            x = x[tp.rank * m:(tp.rank + 1) * m]
         aux_total = torch.zeros((), dtype=torch.float32, device=x.device)
         for i, layer in enumerate(self.layers):
             lc = None if cache is None else cache[i]
@@ -254,4 +286,8 @@ class Qwen3(nn.Module):
                 x, aux = layer(x, ctx, lc)
             aux_total = aux_total + aux
         x = self.final_norm(x)
+        if tp is not None:
+            if return_local_rows:
+                return x, aux_total
+            x = tp_lib.all_gather_rows(x, tp)
         return x.view(B, T, -1), aux_total

@@ -16,11 +16,19 @@ _ATTN_BACKEND = {"text": "sm100"}
 
 
 def init_model_sharded(model_cls, cfg, seed: int, mesh, *, meta: bool = True, device=None, dtype=None):
+    import inspect
+
     torch.manual_seed(int(seed))
+    kw = {}
+    tp = getattr(mesh, "tp", 1) if mesh is not None else 1
+    if tp > 1:
+        if "tp_size" not in inspect.signature(model_cls.__init__).parameters:
+            raise NotImplementedError(f"{model_cls.__name__} has no tensor-parallel layout (tp_size={tp})")
+        kw["tp_size"] = tp
     if meta:
         with torch.device("meta"):
-            return model_cls(cfg, dtype=dtype or torch.float32)
-    return model_cls(cfg, device=device, dtype=dtype or torch.float32)
+            return model_cls(cfg, dtype=dtype or torch.float32, **kw)
+    return model_cls(cfg, device=device, dtype=dtype or torch.float32, **kw)
 
 
 def set_attn_backend(model, backend: str) -> None:

@@ -48,6 +48,7 @@ class ParamSlot:
     pname: str = ""
     peer: bool = False     # gradient goes through the GEMM peer-reduce epilogue
     ep: bool = False       # expert-parallel: never gathered, this rank computes with its own slice
+    tp_sharded: bool = False   # differs between tensor-parallel ranks (no gradient all-reduce over tp)
 
 
 @dataclasses.dataclass
@@ -92,7 +93,7 @@ class TrainEngine:
                  weight_decay: float = 0.01, betas=(0.9, 0.999), eps: float = 1e-8,
                  max_grad_norm: float | None = 1.0, remat: str = "full", seed: int = 0,
                  init_from_model: bool = False, comm: str = "auto", expert_parallel: bool = True,
-                 ep_capacity_factor: float = 2.0):
+                 ep_capacity_factor: float = 2.0, tp_group=None):
         self.model = model
         self.device = torch.device(device)
         self.group = shard_group
@@ -103,6 +104,9 @@ class TrainEngine:
         self.remat = remat
         self.step_count = 0
         self.micro_steps = 0
+        self.tp_group = tp_group
+        self.TP = dist.get_world_size(tp_group) if tp_group is not None else 1
+        self.tp_rank = dist.get_rank(tp_group) if tp_group is not None else 0
         self.use_cuda_kernels = self.device.type == "cuda"
         self.compute_dtype = bf16 if self.device.type == "cuda" else torch.float32
         if comm == "auto":
@@ -135,8 +139,10 @@ class TrainEngine:
                     sharded = (self.W > 1 and len(shape) >= 1 and rows % self.W == 0
                                and ((rows // self.W) * row_numel) % 8 == 0)
                     sn = numel // self.W if sharded else numel
-                    slots.append(ParamSlot(f"{uname}.{mi}.{pname}", p, shape, numel, sharded, sn,
-                                           shard_off, full_off, m, pname))
+                    slot = ParamSlot(f"{uname}.{mi}.{pname}", p, shape, numel, sharded, sn, shard_off, full_off, m, pname)
+                    owner = m.get_submodule(pname.rsplit(".", 1)[0]) if "." in pname else m
+                    slot.tp_sharded = bool(getattr(owner, "tp_sharded", False))
+                    slots.append(slot)
                     shard_off += _align(sn)
                     full_off += _align(numel)
             self.units.append(Unit(uname, mods, slots, shard_off, full_off))
@@ -202,6 +208,8 @@ class TrainEngine:
                             p.data = p.data.to(device=self.device, dtype=torch.float32)
                         for sub in m.modules():
                             if hasattr(sub, "reset_parameters"):
+                                if getattr(sub, "tp_sharded", False):  # distinct slice per tensor-parallel rank
+                                    torch.manual_seed(seed * 100003 + ui + 7919 * (self.tp_rank + 1))
                                 sub.reset_parameters()
             mshard = self._unit_views(u, self.master)
             for s in u.slots:
@@ -406,10 +414,35 @@ class TrainEngine:
             self._barrier()  # every peer's gradient contributions to this shard have landed
         self.micro_steps += 1
 
+    def _tp_sync_grads(self):
+        """Parameters replicated over the tensor-parallel group (norms, embeddings, router, head)
+        see only this rank's sequence shard: their gradient shards are summed over tp."""
+        for u in self.units:
+            gs = self._unit_views(u, self.grad)
+            for s in u.slots:
+                if not s.tp_sharded:
+                    dist.all_reduce(gs[s.shard_off:s.shard_off + s.shard_numel], group=self.tp_group)
+
     # ------------------------------------------------------------------ optimizer
     def grad_norm_sq(self) -> torch.Tensor:
         """Squared global gradient norm (unscaled accumulated gradients) as a device scalar."""
         self.norm_sq.zero_()
+        if self.TP > 1:
+            # tp-sharded slices add up over tp ranks, replicated parameters count once
+            rep = torch.zeros(1, dtype=torch.float32, device=self.device)
+            shd = torch.zeros(1, dtype=torch.float32, device=self.device)
+            for u in self.units:
+                gs = self._unit_views(u, self.grad)
+                for s in u.slots:
+                    if not s.sharded and self.W > 1 and self.rank != 0:
+                        continue
+                    g = gs[s.shard_off:s.shard_off + s.shard_numel]
+                    (shd if s.tp_sharded else rep).add_((g.double() ** 2).sum().float())
+            dist.all_reduce(shd, group=self.tp_group)
+            self.norm_sq += rep + shd
+            if self.W > 1:
+                dist.all_reduce(self.norm_sq, group=self.group)
+            return self.norm_sq
         if self.use_cuda_kernels:
             K.sumsq(self.grad, self.norm_sq)
         else:
@@ -434,6 +467,8 @@ class TrainEngine:
         lr = self.lr if lr is None else lr
         self.step_count += 1
         gmul = 1.0 / grad_accum
+        if self.TP > 1:
+            self._tp_sync_grads()
         nsq = self.grad_norm_sq()
         b1, b2 = self.betas
         if self.use_cuda_kernels:

@@ -1,0 +1,214 @@
+"""Tensor parallelism with sequence-parallel activations (Megatron style).
+
+Between blocks every tp rank holds M/tp rows of the activations.  A column-parallel
+projection (QKV, gate/up) first all-gathers the rows, a row-parallel projection (o, down)
+ends in a reduce-scatter over rows:
+
+    column:  y_local_cols[M, N/tp] = all_gather_rows(x[M/tp, D]) @ W_r^T
+    row:     y[M/tp, D]            = reduce_scatter_rows(x_local_cols[M, F/tp] @ W_r^T) + residual
+
+Transports.  "p2p" (CUDA, bf16): the gather is the pull kernel over NVLink peer pointers into a
+local staging buffer that the tcgen05 GEMM then reads; the row-parallel GEMM uses the
+peer-reduce epilogue, i.e. every output tile is added (fp32) directly into the owning rank's
+rows over NVLink -- GEMM and reduce-scatter are one kernel.  "dist": torch.distributed
+collectives (NCCL baseline, gloo on CPU ranks).  The reference shards heads / mlp over a "tp"
+mesh axis and lets the compiler insert all-reduces (omegalax/models/shard_config.py:12-24); it
+has no sequence parallelism.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as Fn
+from ..ops import kernels as K
+
+_ACTIVE: "TPContext | None" = None
+
+
+def current() -> "TPContext | None":
+    return _ACTIVE
+
+
+def set_current(ctx: "TPContext | None") -> None:
+    global _ACTIVE
+    _ACTIVE = ctx
+
+
+class TPContext:
+    def __init__(self, group, transport: str = "auto"):
+        self.group = group
+        self.size = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        if transport == "auto":
+            transport = "p2p" if (torch.cuda.is_available() and self.size > 1
+                                  and dist.get_backend(group) == "nccl") else "dist"
+        self.transport = transport
+        self._gather_buf = None
+        self._rs_buf = None
+        self._barrier = None
+
+    # ---- peer-memory resources (allocated on first use, sized by the largest request)
+    def _symm(self):
+        from . import symm
+
+        return symm
+
+    def gather_buffer(self, rows_local: int, cols: int, dtype):
+        n = rows_local * cols * 2
+        if self._gather_buf is None or self._gather_buf.nbytes < n:
+            self._gather_buf = self._symm().SymmetricBuffer(n, self.group)
+            if self._barrier is None:
+                self._barrier = self._symm().DeviceBarrier(self.group)
+        return self._gather_buf
+
+    def rs_buffer(self, rows_local: int, cols: int):
+        n = rows_local * cols * 4
+        if self._rs_buf is None or self._rs_buf.nbytes < n:
+            self._rs_buf = self._symm().SymmetricBuffer(n, self.group)
+            if self._barrier is None:
+                self._barrier = self._symm().DeviceBarrier(self.group)
+        return self._rs_buf
+
+
+# ----------------------------------------------------------------------------- collectives
+def _ag_rows(x, tp: TPContext):
+    m, D = x.shape
+    out = torch.empty(m * tp.size, D, dtype=x.dtype, device=x.device)
+    if tp.transport == "p2p" and x.dtype == torch.bfloat16:
+        symm = tp._symm()
+        buf = tp.gather_buffer(m, D, x.dtype)
+        buf.view(x.dtype, m * D).copy_(x.reshape(-1))
+        tp._barrier()
+        tab = symm.make_copy_segments([(r, 0, r * m * D * 2, m * D * 2) for r in range(tp.size)], x.device)
+        symm.allgather_pull(buf, out, tab)
+        tp._barrier()  # peers have finished reading before the staging buffer is reused
+    else:
+        dist.all_gather_into_tensor(out, x.contiguous(), group=tp.group)
+    return out
+
+
+def _rs_rows(y, tp: TPContext):
+    M, D = y.shape
+    m = M // tp.size
+    out = torch.empty(m, D, dtype=y.dtype, device=y.device)
+    dist.reduce_scatter_tensor(out, y.contiguous(), op=dist.ReduceOp.SUM, group=tp.group)
+    return out
+
+
+class _AllGatherRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _ag_rows(x, tp)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _rs_rows(g, ctx.tp), None
+
+
+class _ReduceScatterRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, tp):
+        ctx.tp = tp
+        return _rs_rows(y, tp)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _ag_rows(g.contiguous(), ctx.tp), None
+
+
+def all_gather_rows(x, tp: TPContext | None):
+    if tp is None or tp.size == 1:
+        return x
+    return _AllGatherRows.apply(x, tp)
+
+
+def reduce_scatter_rows(y, tp: TPContext | None):
+    if tp is None or tp.size == 1:
+        return y
+    return _ReduceScatterRows.apply(y, tp)
+
+
+# ----------------------------------------------------------------------------- fused row-parallel
+class _RowParallelLinearFn(torch.autograd.Function):
+    """y[M/tp, N] = reduce_scatter_rows(x[M, K/tp] @ w[N, K/tp]^T) (+ residual), with the
+    reduce-scatter performed by the GEMM epilogue over NVLink peer memory."""
+
+    @staticmethod
+    def forward(ctx, x, w, residual, tp: TPContext):
+        M, N = x.shape[0], w.shape[0]
+        m = M // tp.size
+        buf = tp.rs_buffer(m, N)
+        acc = buf.view(torch.float32, m * N)
+        acc.zero_()
+        tp._barrier()                                   # every owner has cleared its rows
+        K.gemm_peer_reduce(x, w, buf.peer_ptr_list(0), m, N)
+        tp._barrier()                                   # all contributions have landed
+        y = acc.view(m, N).to(x.dtype)
+        if residual is not None:
+            y = y + residual
+        ctx.save_for_backward(x, w)
+        ctx.tp, ctx.w_ref, ctx.has_res = tp, w, residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        tp = ctx.tp
+        gfull = _ag_rows(g.contiguous(), tp)            # [M, N]
+        dx = K.gemm(gfull, w, b_mn=True)
+        mg = getattr(ctx.w_ref, "main_grad", None)
+        pg = getattr(ctx.w_ref, "peer_grad", None)
+        dw = None
+        if pg is not None:
+            K.gemm_peer_reduce(gfull, x, pg[0], pg[1], pg[2], a_mn=True, b_mn=True)
+        elif mg is not None:
+            K.gemm(gfull, x, a_mn=True, b_mn=True, out=mg, accumulate=True)
+        else:
+            dw = K.gemm(gfull, x, a_mn=True, b_mn=True)
+        return dx, dw, (g if ctx.has_res else None), None
+
+
+def column_parallel_linear(x_local, w_local, tp: TPContext | None):
+    """all-gather rows -> projection with this rank's output columns."""
+    return Fn.linear(all_gather_rows(x_local, tp), w_local)
+
+
+def row_parallel_linear(x_cols, w_local, residual_local, tp: TPContext | None):
+    """projection over this rank's input columns -> reduce-scatter over rows (+ residual)."""
+    if tp is None or tp.size == 1:
+        return Fn.linear(x_cols, w_local, residual=residual_local)
+    if tp.transport == "p2p" and Fn.use_kernels(x_cols) and w_local.dtype == torch.bfloat16 \
+            and (x_cols.shape[0] // tp.size) % 1 == 0:
+        return _RowParallelLinearFn.apply(x_cols.contiguous(), w_local, residual_local, tp)
+    y = reduce_scatter_rows(Fn.linear(x_cols, w_local), tp)
+    return y if residual_local is None else y + residual_local
+
+
+# ----------------------------------------------------------------------------- weight slicing
+def slice_rows(t, tp: int, rank: int):
+    n = t.shape[0] // tp
+    return t[rank * n:(rank + 1) * n]
+
+
+def slice_cols(t, tp: int, rank: int):
+    n = t.shape[1] // tp
+    return t[:, rank * n:(rank + 1) * n]
+
+
+def qkv_rows_for_rank(H: int, G: int, Kd: int, tp: int, rank: int, q_mult: int = 1) -> torch.Tensor:
+    """Row indices of a fused [q | k | v] projection that belong to one tp rank: its query
+    heads, its kv heads (keys) and its kv heads (values)."""
+    Hl, Gl = H // tp, G // tp
+    q = torch.arange(rank * Hl * Kd * q_mult, (rank + 1) * Hl * Kd * q_mult)
+    k0 = H * Kd * q_mult
+    k = torch.arange(k0 + rank * Gl * Kd, k0 + (rank + 1) * Gl * Kd)
+    v0 = k0 + G * Kd
+    v = torch.arange(v0 + rank * Gl * Kd, v0 + (rank + 1) * Gl * Kd)
+    return torch.cat([q, k, v])
+
+
+def gate_up_rows_for_rank(F: int, tp: int, rank: int) -> torch.Tensor:
+    Fl = F // tp
+    return torch.cat([torch.arange(rank * Fl, (rank + 1) * Fl), torch.arange(F + rank * Fl, F + (rank + 1) * Fl)])

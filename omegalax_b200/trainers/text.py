@@ -73,19 +73,41 @@ def build_optimizer(model, train_cfg: TrainConfig, *, device=None, init_from_mod
     sched = build_lr_schedule(train_cfg.lr_schedule, train_cfg.learning_rate, train_cfg.num_steps,
                               train_cfg.warmup_steps, train_cfg.lr_end_factor, train_cfg.lr_stable_fraction)
     group = mesh.group("shard") if mesh is not None else None
+    tp_group = mesh.group("tp") if mesh is not None and mesh.tp > 1 else None
+    if tp_group is not None:
+        from ..parallel import tp as tp_lib
+
+        tp_lib.set_current(tp_lib.TPContext(tp_group))
     if init_from_model is None:
         init_from_model = not any(p.device.type == "meta" for p in model.parameters())
     return MixedPrecisionOptimizer(
         model, device=device, shard_group=group, lr=train_cfg.learning_rate, weight_decay=train_cfg.weight_decay,
         max_grad_norm=train_cfg.max_grad_norm, remat=train_cfg.remat_policy, seed=train_cfg.seed,
-        init_from_model=init_from_model, lr_schedule=sched, grad_accum_steps=train_cfg.grad_accum_steps)
+        init_from_model=init_from_model, lr_schedule=sched, grad_accum_steps=train_cfg.grad_accum_steps,
+        tp_group=tp_group)
 
 
 def _loss_and_count(model, cfg, batch, pad_id: int, group):
     tok = batch["token_ids_BT"]
     mask = batch["loss_mask_BT"]
-    hidden, aux = text_api.forward(model, tok, pad_id, cfg)
     count = supervised_count(mask, group)
+    if getattr(model, "tp_size", 1) > 1:
+        # sequence-parallel rows: this tp rank scores its own slice of the (shifted) token rows
+        from ..ops import functional as Fn
+        from ..parallel import tp as tp_lib
+
+        tp = tp_lib.current()
+        seg = (tok != pad_id).to(torch.int32)
+        rows, aux = model(tok, seg, None, 0, return_local_rows=True)
+        B, T = tok.shape
+        m = B * T // tp.size
+        tgt = torch.roll(tok, -1, dims=1).reshape(-1)
+        msk = torch.roll(mask, -1, dims=1).to(torch.float32)
+        msk[:, -1] = 0
+        sl = slice(tp.rank * m, (tp.rank + 1) * m)
+        ce = Fn.linear_cross_entropy(rows, model.lm_head.weight, tgt[sl], msk.reshape(-1)[sl], 1.0 / count.clamp_min(1.0))
+        return ce, aux / tp.size, count
+    hidden, aux = text_api.forward(model, tok, pad_id, cfg)
     ce = chunked_cross_entropy_loss(hidden, model.lm_head.weight, tok, mask, num_tiles=_NUM_LOSS_TILES, count=count)
     return ce, aux, count
 
@@ -106,6 +128,9 @@ def make_sft_train_step(cfg, pad_id: int = 0):
         if optimizer.W > 1:
             loss_d = loss_d.clone()
             dist.all_reduce(loss_d, group=group)
+        if optimizer.TP > 1:
+            loss_d = loss_d.clone()
+            dist.all_reduce(loss_d, group=optimizer.tp_group)
         metrics = {"loss": loss_d, "supervised_tokens": count.squeeze(0),
                    "grad_norm": gnorm if gnorm is not None else torch.zeros((), device=loss_d.device)}
         return loss_d, metrics

@@ -51,3 +51,50 @@ def fsdp_train(rank, world, port, model_id, steps, out_path, ckpt_dir=None, resu
         torch.save({"losses": losses, "params": full, "grad_norm": float(opt.last_grad_norm)}, out_path)
     dist.barrier()
     dist.destroy_process_group()
+
+
+def tp_train(rank, world, port, tp, steps, out_path):
+    """Same weights, same batch: tensor-parallel (tp) x fsdp (world/tp) run on CPU ranks."""
+    _init(rank, world, port)
+    import dataclasses
+
+    from omegalax_b200.models.qwen3.config import make_config
+    from omegalax_b200.models.qwen3.model import Qwen3
+    from omegalax_b200.models.qwen3.tp_layout import tp_slice
+    from omegalax_b200.parallel import mesh as mesh_lib
+    from omegalax_b200.parallel import tp as tp_lib
+    from omegalax_b200.trainers import text as trainer
+
+    mesh_lib.set_default_mesh(None)
+    tp_lib.set_current(None)
+    mesh = mesh_lib.ensure_mesh(tp_size=tp, fsdp_size=world // tp, dp_size=1)
+    cfg = dataclasses.replace(make_config("qwen3-smoke"), num_kv_heads=2)
+    torch.manual_seed(0)
+    full = Qwen3(cfg, dtype=torch.float32)                       # identical on every rank
+    tcfg = trainer.TrainConfig(seed=0, batch_size=2 * (world // tp), seq_len=32, num_steps=100, learning_rate=1e-2,
+                               max_grad_norm=1.0)
+    model, cfg2 = trainer.init_model(cfg, 0, tp_size=tp, fsdp_size=world // tp, dp_size=1, meta=True)
+    opt = trainer.build_optimizer(model, tcfg, device=torch.device("cpu"))
+    src = dict(full.named_parameters())
+    names = {id(p): n for n, p in model.named_parameters()}
+    tpr = mesh.coords()["tp"]
+    for u in opt.units:
+        for s in u.slots:
+            n = names[id(s.param)]
+            opt.load_full_param(s, tp_slice(n, src[n].detach(), cfg, tp, tpr))
+    opt.sync_compute_from_master()
+    step = trainer.make_sft_train_step(cfg2)
+    g = torch.Generator().manual_seed(0)
+    nb = 2 * (world // tp)
+    tok = torch.randint(1, cfg.vocab_size, (nb, 32), generator=g, dtype=torch.int32)
+    lm = torch.ones(nb, 32, dtype=torch.int32)
+    lm[:, :5] = 0
+    di = mesh_lib.data_parallel_index()
+    sl = slice(di * 2, di * 2 + 2)
+    batch = {"token_ids_BT": tok[sl], "attention_mask_BT": torch.ones(2, 32, dtype=torch.int32), "loss_mask_BT": lm[sl]}
+    losses = [float(step(opt, batch)[0]) for _ in range(steps)]
+    if rank == 0:
+        torch.save({"losses": losses, "grad_norm": float(opt.last_grad_norm)}, out_path)
+    dist.barrier()
+    tp_lib.set_current(None)
+    dist.destroy_process_group()

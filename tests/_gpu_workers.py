@@ -125,3 +125,50 @@ def ep_train_gpu(rank, world, port, steps, out_path):
     if world > 1:
         dist.barrier()
     dist.destroy_process_group()
+
+
+def tp_train_gpu(rank, world, port, tp, steps, out_path):
+    """Tensor parallel (sequence-parallel activations, peer-memory transport) vs one GPU, same weights."""
+    _init(rank, world, port)
+    import dataclasses
+
+    from omegalax_b200.models.qwen3.model import Qwen3
+    from omegalax_b200.models.qwen3.tp_layout import tp_slice
+    from omegalax_b200.ops import lib
+    from omegalax_b200.parallel import mesh as mesh_lib
+    from omegalax_b200.parallel import tp as tp_lib
+    from omegalax_b200.text import api as text_api
+    from omegalax_b200.trainers import text as trainer
+
+    mesh_lib.set_default_mesh(None)
+    tp_lib.set_current(None)
+    mesh = mesh_lib.ensure_mesh(tp_size=tp, fsdp_size=world // tp, dp_size=1)
+    cfg = dataclasses.replace(text_api.resolve_config("Qwen/Qwen3-8B"), num_layers=2, emb_dim=512, mlp_dim=1024,
+                              num_heads=4, num_kv_heads=2, vocab_size=4096)
+    torch.manual_seed(0)
+    full = Qwen3(cfg, dtype=torch.float32)
+    tcfg = trainer.TrainConfig(seed=0, batch_size=2, seq_len=256, num_steps=100, learning_rate=1e-3, max_grad_norm=1.0)
+    model, cfg2 = trainer.init_model(cfg, 0, tp_size=tp, fsdp_size=world // tp, dp_size=1, meta=True)
+    opt = trainer.build_optimizer(model, tcfg, device=torch.device("cuda", rank))
+    src = dict(full.named_parameters())
+    names = {id(p): n for n, p in model.named_parameters()}
+    tpr = mesh.coords()["tp"]
+    for u in opt.units:
+        for s in u.slots:
+            n = names[id(s.param)]
+            opt.load_full_param(s, tp_slice(n, src[n].detach(), cfg, tp, tpr))
+    opt.sync_compute_from_master()
+    step = trainer.make_sft_train_step(cfg2)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(1, cfg.vocab_size, (2, 256), generator=g, dtype=torch.int32).cuda()
+    batch = {"token_ids_BT": tok, "attention_mask_BT": torch.ones_like(tok), "loss_mask_BT": torch.ones_like(tok)}
+    losses = [float(step(opt, batch)[0]) for _ in range(steps)]
+    torch.cuda.synchronize()
+    lib.check_status()
+    ctx = tp_lib.current()
+    if rank == 0:
+        torch.save({"losses": losses, "transport": ctx.transport if ctx else "none"}, out_path)
+    if world > 1:
+        dist.barrier()
+    tp_lib.set_current(None)
+    dist.destroy_process_group()

@@ -78,3 +78,15 @@ def test_expert_parallel_two_gpus_matches_one(tmp_path):
     assert b["used_ep"] and not a["used_ep"]
     assert b["losses"][-1] < b["losses"][0]
     assert a["losses"] == pytest.approx(b["losses"], rel=3e-2, abs=3e-2)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_two_gpus_matches_one(tmp_path):
+    from tests import _gpu_workers as W
+
+    mp.spawn(W.tp_train_gpu, args=(1, _port(), 1, 4, str(tmp_path / "one.pt")), nprocs=1, join=True)
+    mp.spawn(W.tp_train_gpu, args=(2, _port(), 2, 4, str(tmp_path / "two.pt")), nprocs=2, join=True)
+    a, b = torch.load(tmp_path / "one.pt"), torch.load(tmp_path / "two.pt")
+    assert b["transport"] == "p2p"
+    assert b["losses"][-1] < b["losses"][0]
+    assert a["losses"] == pytest.approx(b["losses"], rel=3e-2, abs=3e-2)
