@@ -109,6 +109,7 @@ def main() -> int:
     ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--micro-seqs", type=int, default=None, help="sequences per GPU per micro-batch")
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
+    ap.add_argument("--remat", default=None, help="full | selective | save:<tags> (default depends on N)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -139,13 +140,16 @@ def main() -> int:
     cfg = text_api.resolve_config(MODEL_ID)
     if args.layers is not None:
         cfg = dataclasses.replace(cfg, num_layers=args.layers)
-    micro = args.micro_seqs or (4 if N == 1 else args.seqs_per_gpu)
+    micro = args.micro_seqs or (4 if N <= 2 else args.seqs_per_gpu)  # keeps the kept activations inside 180 GB
     micro = min(micro, args.seqs_per_gpu)
     accum = args.seqs_per_gpu // micro
     T = args.seq_len
+    # One GPU holds all fp32 state (148 GB): only the small attention-side tensors are kept from the
+    # first forward.  With the state sharded there is room to keep the wide MLP activation too.
+    remat = args.remat or ("save:qkv,attn" if N == 1 else "selective")
     tcfg = trainer.TrainConfig(seed=0, batch_size=micro * N, seq_len=T, num_steps=10_000, learning_rate=1e-5,
                                weight_decay=0.01, warmup_steps=0, lr_schedule="linear", max_grad_norm=1.0,
-                               grad_accum_steps=accum)
+                               grad_accum_steps=accum, remat_policy=remat)
     mesh = mesh_lib.ensure_mesh(tp_size=1, fsdp_size=N, dp_size=1)
     model, cfg = trainer.init_model(cfg, 0, tp_size=1, fsdp_size=N, dp_size=1, meta=True)
     opt = trainer.build_optimizer(model, tcfg, device=device)
@@ -227,7 +231,7 @@ def main() -> int:
             "config": {"model": MODEL_ID if args.layers is None else f"{MODEL_ID}[{args.layers} layers]",
                        "global_batch": args.seqs_per_gpu * N, "seq_len": T, "parallelism": f"fsdp{N}",
                        "micro_batch_per_gpu": micro, "grad_accum": accum, "optimizer": "AdamW fp32 master",
-                       "remat": "full", "l2": "inputs larger than L2 (16 GB of weights per step)"},
+                       "remat": remat, "l2": "inputs larger than L2 (16 GB of weights per step)"},
             "tokens_per_sec_per_gpu": value / N, "tflops_per_gpu": tflops_per_gpu,
             "mfu_of_measured_burst": tflops_per_gpu / PEAK_TFLOPS["b200_measured_burst"],
             "mfu_of_nominal": tflops_per_gpu / PEAK_TFLOPS["b200"],
@@ -235,6 +239,7 @@ def main() -> int:
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": launches, "final_loss": last_loss,
+            "peak_mem_gb": torch.cuda.max_memory_allocated(device) / 1e9,
         }
         print(json.dumps(out), flush=True)
     if N > 1:

@@ -55,8 +55,8 @@ class Linear(nn.Module):
             if self.bias is not None:
                 nn.init.zeros_(self.bias)
 
-    def forward(self, x, residual=None):
-        return Fn.linear(x, self.weight, residual=residual, bias=self.bias)
+    def forward(self, x, residual=None, tag=None):
+        return Fn.linear(x, self.weight, residual=residual, bias=self.bias, tag=tag)
 
 
 @dataclasses.dataclass
@@ -94,13 +94,13 @@ class Attention(nn.Module):
         if tp is not None:
             x = tp_lib.all_gather_rows(x, tp)      # sequence-parallel rows -> all rows
         M = x.shape[0]
-        qkv = self.qkv_proj(x)
+        qkv = self.qkv_proj(x, tag="qkv")
         q, k, v, _ = Fn.qk_norm_rope(qkv, self.q_norm.weight, self.k_norm.weight, ctx.sin, ctx.cos,
                                      self.H, self.G, self.Kd, eps=self.eps)
         B, T = ctx.B, ctx.T
         if cache is None:
             if Fn.use_kernels(q):
-                o = Fn.flash_attention(q, k, v, ctx.cu_seqlens, T, scale=self.scale, causal=True)
+                o = Fn.flash_attention(q, k, v, ctx.cu_seqlens, T, scale=self.scale, causal=True, tag="attn")
             else:
                 ks = None if ctx.k_start is None else ctx.k_start[:, None].expand(B, T)
                 o = R.attention(q.reshape(B, T, self.H, self.Kd), k.reshape(B, T, self.G, self.Kd),
@@ -155,7 +155,7 @@ class MLP(nn.Module):
         if tp is not None:
             h = Fn.swiglu(tp_lib.column_parallel_linear(x, self.gate_up_proj.weight, tp))
             return tp_lib.row_parallel_linear(h, self.down_proj.weight, residual, tp)
-        return self.down_proj(Fn.swiglu(self.gate_up_proj(x)), residual=residual)
+        return self.down_proj(Fn.swiglu(self.gate_up_proj(x, tag="gate_up")), residual=residual)
 
 
 class MoEFeedForward(nn.Module):

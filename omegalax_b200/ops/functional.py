@@ -20,6 +20,60 @@ from . import reference as R
 bf16 = torch.bfloat16
 
 
+class _Stash:
+    """Selective rematerialisation: tagged op outputs recorded during the no-grad forward of a
+    layer are replayed (instead of recomputed) when the layer is re-run for its backward."""
+
+    def __init__(self, tags):
+        self.tags = frozenset(tags)
+        self.items: dict = {}
+        self.mode = "off"      # "record" | "replay" | "off"
+        self.counter: dict = {}
+
+    def key(self, tag):
+        i = self.counter.get(tag, 0)
+        self.counter[tag] = i + 1
+        return (tag, i)
+
+
+_ACTIVE_STASH: "_Stash | None" = None
+
+
+class stash_scope:
+    def __init__(self, stash, mode):
+        self.stash, self.mode = stash, mode
+
+    def __enter__(self):
+        global _ACTIVE_STASH
+        self.prev = _ACTIVE_STASH
+        if self.stash is not None:
+            self.stash.mode = self.mode
+            self.stash.counter = {}
+        _ACTIVE_STASH = self.stash
+        return self.stash
+
+    def __exit__(self, *a):
+        global _ACTIVE_STASH
+        if self.stash is not None:
+            self.stash.mode = "off"
+        _ACTIVE_STASH = self.prev
+
+
+def _stash_lookup(tag):
+    """(key, stored value or None) for a tagged call under the active stash."""
+    st = _ACTIVE_STASH
+    if st is None or tag is None or tag not in st.tags or st.mode == "off":
+        return None, None
+    k = st.key(tag)
+    return k, (st.items.get(k) if st.mode == "replay" else None)
+
+
+def _stash_store(key, value):
+    st = _ACTIVE_STASH
+    if st is not None and key is not None and st.mode == "record":
+        st.items[key] = value
+
+
 def use_kernels(t: torch.Tensor) -> bool:
     return t.is_cuda and t.dtype == bf16 and os.environ.get("OMEGALAX_B200_REFERENCE_OPS") != "1"
 
@@ -36,10 +90,10 @@ def _acc_main_grad(w, fn_into, fn_new):
 # ----------------------------------------------------------------------------- linear
 class _LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, residual):
+    def forward(ctx, x, w, residual, y_pre=None):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
-        y = K.gemm(x2, w, residual=residual)
+        y = y_pre if y_pre is not None else K.gemm(x2, w, residual=residual)
         ctx.save_for_backward(x2, w)
         ctx.shp = shp
         ctx.has_res = residual is not None
@@ -66,13 +120,16 @@ class _LinearFn(torch.autograd.Function):
                 lambda mg: K.gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=True),
                 lambda: K.gemm(dy2, x2, a_mn=True, b_mn=True),
             )
-        return dx, dw, (dy if ctx.has_res else None)
+        return dx, dw, (dy if ctx.has_res else None), None
 
 
-def linear(x, w, residual=None, bias=None):
+def linear(x, w, residual=None, bias=None, tag=None):
     """y = x @ w.T (+ bias) (+ residual); w is [out, in]."""
     if use_kernels(x) and w.dtype == bf16:
-        y = _LinearFn.apply(x, w, residual if bias is None else None)
+        key, pre = _stash_lookup(tag if bias is None else None)
+        y = _LinearFn.apply(x, w, residual if bias is None else None,
+                            None if pre is None else pre.view(-1, w.shape[0]))
+        _stash_store(key, y)
         if bias is not None:
             y = y + bias
             if residual is not None:
@@ -255,24 +312,31 @@ def _attn_bwd_dispatch(q, k, v, o, lse, do, cu_seqlens, max_seqlen, scale, causa
 
 class _FlashAttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, scale, causal):
-        o, lse = K.attn_fwd(q, k, v, cu_seqlens, max_seqlen, scale, causal)
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, scale, causal, pre=None):
+        if pre is not None:
+            o, lse = pre
+        else:
+            o, lse = K.attn_fwd(q, k, v, cu_seqlens, max_seqlen, scale, causal)
         ctx.save_for_backward(q, k, v, o, lse, cu_seqlens)
         ctx.cfg = (max_seqlen, scale, causal)
-        return o
+        ctx.mark_non_differentiable(lse)
+        return o, lse
 
     @staticmethod
-    def backward(ctx, do):
+    def backward(ctx, do, _dlse):
         q, k, v, o, lse, cu = ctx.saved_tensors
         max_seqlen, scale, causal = ctx.cfg
         dq, dk, dv = _attn_bwd_dispatch(q, k, v, o, lse, do.contiguous(), cu, max_seqlen, scale, causal)
-        return dq, dk, dv, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None
 
 
-def flash_attention(q, k, v, cu_seqlens, max_seqlen: int, *, scale: float, causal: bool):
+def flash_attention(q, k, v, cu_seqlens, max_seqlen: int, *, scale: float, causal: bool, tag=None):
     """Packed-row attention.  q [N,H,Kd]; k, v [N,G,Kd]; cu_seqlens int32 [B+1]."""
     if use_kernels(q) and q.shape[-1] in (64, 128):
-        return _FlashAttnFn.apply(q, k, v, cu_seqlens, int(max_seqlen), float(scale), bool(causal))
+        key, pre = _stash_lookup(tag)
+        o, lse = _FlashAttnFn.apply(q, k, v, cu_seqlens, int(max_seqlen), float(scale), bool(causal), pre)
+        _stash_store(key, (o, lse))
+        return o
     return R.attention_varlen(q, k, v, cu_seqlens, causal=causal, scale=scale)
 
 

@@ -29,6 +29,7 @@ import torch
 import torch.distributed as dist
 from torch import nn
 
+from ..ops import functional as Fn
 from ..ops import kernels as K
 
 bf16 = torch.bfloat16
@@ -102,6 +103,14 @@ class TrainEngine:
         self.lr, self.wd, self.betas, self.eps = lr, weight_decay, betas, eps
         self.max_grad_norm = max_grad_norm or 0.0
         self.remat = remat
+        # remat policies: "full" recomputes the whole layer; "selective" (or "save:tag,tag") keeps the
+        # tagged GEMM / attention outputs from the first forward; "none" keeps everything (single rank)
+        if remat == "selective":
+            self.remat_tags = ("qkv", "attn", "gate_up")
+        elif remat.startswith("save:"):
+            self.remat_tags = tuple(t for t in remat[5:].split(",") if t)
+        else:
+            self.remat_tags = ()
         self.step_count = 0
         self.micro_steps = 0
         self.tp_group = tp_group
@@ -560,8 +569,10 @@ class _RematLayerFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, engine: TrainEngine, unit: Unit, layer, fctx):
         engine._acquire(unit, +1)
-        with torch.no_grad():
+        stash = Fn._Stash(engine.remat_tags) if engine.remat_tags else None
+        with torch.no_grad(), Fn.stash_scope(stash, "record"):
             y, aux = layer(x, fctx)
+        ctx.stash = stash
         ctx.save_for_backward(x)
         ctx.engine, ctx.unit, ctx.layer, ctx.fctx = engine, unit, layer, fctx
         return y, aux
@@ -571,9 +582,11 @@ class _RematLayerFn(torch.autograd.Function):
         (x,) = ctx.saved_tensors
         engine, unit, layer, fctx = ctx.engine, ctx.unit, ctx.layer, ctx.fctx
         engine._acquire(unit, -1)
-        with torch.enable_grad():
+        with torch.enable_grad(), Fn.stash_scope(ctx.stash, "replay"):
             xin = x.detach().requires_grad_(True)
             y, aux = layer(xin, fctx)
+        ctx.stash = None
+        with torch.enable_grad():
             outs, grads = [y], [dy]
             if aux.requires_grad:
                 outs.append(aux)

@@ -53,7 +53,7 @@ def common_train_flags(p: Flags, *, batch_size: int, workers: int, worker_buffer
     p.define("fsdp_size", 1)
     p.define("dp_size", 1)
     p.define("ep_size", 1, "expert-parallel size (experts sharded over the data ranks)")
-    p.define("remat_policy", "full", choices=["full", "none"])
+    p.define("remat_policy", "full", "full | selective | save:<tag,tag> (tags: qkv, attn, gate_up) | none")
     p.define("save_dir", None, type=str)
     p.define("jax_cache_dir", None, "accepted for command-line compatibility; unused", type=str)
     p.define("save_every", 50)
