@@ -244,6 +244,65 @@ class Qwen3(nn.Module):
         return ForwardCtx(B=B, T=T, sin=sin, cos=cos, cu_seqlens=cu, segment_ids=segment_ids,
                           k_start=k_start, positions=positions)
 
+    @torch.no_grad()
+    def decode_paged(self, token_ids, segment_ids, cache):
+        """Prefill or one decode step against a ``PagedKVCache`` (CUDA bf16).  Only real tokens
+        are processed and stored; returns the final hidden state of every sequence's last new
+        token, [B, D] (zeros for sequences without a new token)."""
+        from ...ops import kernels as K
+
+        cfg = self.cfg
+        B, T = token_ids.shape
+        dev = token_ids.device
+        real = segment_ids != 0
+        counts = real.sum(-1)
+        new_tokens = [int(c) for c in counts.tolist()]
+        cache.reserve(new_tokens)
+        seq_of = torch.arange(B, device=dev)[:, None].expand(B, T)[real].to(torch.int32)
+        rank_in = (real.cumsum(-1) - 1)[real]
+        start = cache.seq_lens[seq_of.long()]
+        slot = (start + rank_in).to(torch.int32)
+        ids = token_ids[real]
+        x = self.embed(ids)
+        N = x.shape[0]
+        single = max(new_tokens) <= 1
+        if not single and any(cache.seq_lens_host[b] > 0 and new_tokens[b] > 0 for b in range(B)):
+            raise NotImplementedError("multi-token calls are only supported on an empty cache (prefill)")
+        cu = torch.zeros(B + 1, dtype=torch.int32, device=dev)
+        cu[1:] = counts.cumsum(0)
+        sin, cos = R.rope_tables(slot, cfg.head_dim, cfg.rope_theta)
+        lens_after = (cache.seq_lens + counts.to(torch.int32)).contiguous()
+        rows = cache.flat_rows(seq_of, slot)
+        last = (cu[1:] - 1).long().clamp_min(0)
+        for li, layer in enumerate(self.layers):
+            a = layer.attn
+            h = layer.input_norm(x)
+            qkv = a.qkv_proj(h)
+            if single:
+                q = K.decode_append(qkv, a.q_norm.weight, a.k_norm.weight, slot, seq_of, slot, cache.block_table,
+                                    cache.page_size, cache.k_pages[li], cache.v_pages[li], a.H, a.G, a.Kd, a.Kd,
+                                    cfg.rope_theta, a.eps)
+                # every sequence contributes exactly one row in this mode
+                qb = torch.zeros(B, a.H, a.Kd, dtype=q.dtype, device=dev)
+                qb[seq_of.long()] = q
+                ob = K.decode_attn(qb, cache.k_pages[li], cache.v_pages[li], cache.block_table, lens_after,
+                                   cache.page_size, a.scale)
+                o = ob[seq_of.long()]
+            else:
+                q, k, v, _ = Fn.qk_norm_rope(qkv, a.q_norm.weight, a.k_norm.weight, sin, cos, a.H, a.G, a.Kd, eps=a.eps)
+                o = Fn.flash_attention(q, k, v, cu, T, scale=a.scale, causal=True)
+                cache.k_pages[li].view(-1, a.G, a.Kd).index_copy_(0, rows, k)
+                cache.v_pages[li].view(-1, a.G, a.Kd).index_copy_(0, rows, v.contiguous())
+            x = a.o_proj(o.reshape(N, a.H * a.Kd), residual=x)
+            hh = layer.post_norm(x)
+            x = layer.mlp(hh, residual=x)[0] if layer.is_moe else layer.mlp(hh, residual=x)
+        cache.advance(new_tokens)
+        x = self.final_norm(x)
+        out = torch.zeros(B, x.shape[1], dtype=x.dtype, device=dev)
+        has = counts > 0
+        out[has] = x[last[has]]
+        return out
+
     def embed(self, token_ids):
         return Fn.embedding(token_ids.reshape(-1), self.embedder.weight)
 

@@ -285,3 +285,37 @@ def transpose(src):
 
 def l2_flush(buf):
     _call("ob_l2_flush", buf.data_ptr(), buf.numel() * buf.element_size(), lib.stream_ptr())
+
+
+def decode_append(qkv, qw, kw, positions, seq_of_token, slot_of_token, block_table, page_size, k_pages, v_pages,
+                  H, G, HD, rot, theta, eps, one_plus=False):
+    """Per-head RMSNorm + RoPE of the new tokens' q and k; k/v go to their page slots.  Returns q."""
+    n = qkv.shape[0]
+    q = torch.empty(n, H, HD, dtype=qkv.dtype, device=qkv.device)
+    _call("ob_decode_append", qkv.data_ptr(), lib.ptr(qw), lib.ptr(kw), positions.data_ptr(),
+          seq_of_token.data_ptr(), slot_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+          page_size, q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), n, H, G, HD, rot, float(theta),
+          float(eps), int(one_plus), lib.stream_ptr())
+    return q
+
+
+_decode_scratch: dict = {}
+
+
+def decode_attn(q, k_pages, v_pages, block_table, seq_lens, page_size, scale, splits=None):
+    """q [B,H,HD] attends over each sequence's pages; returns [B,H,HD]."""
+    B, H, HD = q.shape
+    G = k_pages.shape[2]
+    if splits is None:
+        splits = max(1, min(16, (148 * 2) // max(B * G, 1)))
+    key = (q.device.index, B, H, HD, splits)
+    sc = _decode_scratch.get(key)
+    if sc is None:
+        sc = (torch.empty(B * H * splits * HD, dtype=torch.float32, device=q.device),
+              torch.empty(B * H * splits * 2, dtype=torch.float32, device=q.device))
+        _decode_scratch[key] = sc
+    out = torch.empty_like(q)
+    _call("ob_decode_attn", q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+          seq_lens.data_ptr(), B, H, G, HD, block_table.shape[1], page_size, splits, float(scale),
+          sc[0].data_ptr(), sc[1].data_ptr(), out.data_ptr(), lib.stream_ptr())
+    return out

@@ -17,6 +17,7 @@ from ..models import sharding_runtime as _rt
 from ..models.qwen3 import registry as qwen3_registry
 from ..models.qwen3.cache import Cache, init_cache
 from ..models.qwen3.model import Qwen3
+from ..models.qwen3.paged_cache import PagedKVCache
 from ..models.qwen3.utils import count_right_pads
 from ..models.hf_io import load_hf_config_from_source
 from ..models.shard_config import shard_config_for_mesh
@@ -112,6 +113,10 @@ def decode(model, cache: Cache, token_ids_BT, pad_id: int, cfg):
     if not isinstance(model, Qwen3):
         raise NotImplementedError("decode is only implemented for Qwen3 text models.")
     segment_ids = (token_ids_BT != pad_id).to(torch.int32)
+    if isinstance(cache, PagedKVCache):
+        hidden = model.decode_paged(token_ids_BT, segment_ids, cache)
+        with torch.no_grad():
+            return model.lm_head(hidden), cache, torch.zeros((), device=hidden.device)
     nrp = count_right_pads(token_ids_BT, pad_id)
     with torch.no_grad():
         hidden, aux = model(token_ids_BT, segment_ids, cache, nrp)
@@ -120,7 +125,15 @@ def decode(model, cache: Cache, token_ids_BT, pad_id: int, cfg):
     return logits, cache, aux
 
 
-def make_cache(cfg, batch_size: int, token_len: int, generate_steps: int, dtype=torch.bfloat16, device=None):
+def make_cache(cfg, batch_size: int, token_len: int, generate_steps: int, dtype=torch.bfloat16, device=None,
+               paged: bool | None = None, page_size: int = 64):
+    """KV cache for ``decode``.  On CUDA with bf16 (head_dim 128) the paged cache + decode kernels
+    are used by default; otherwise the contiguous power-of-two cache of the reference."""
     if not isinstance(cfg, ModelConfig):
         raise NotImplementedError("Cache is only available for Qwen3 text models.")
+    if paged is None:
+        paged = (device is not None and torch.device(device).type == "cuda" and dtype == torch.bfloat16
+                 and cfg.head_dim == 128 and (cfg.num_heads // cfg.num_kv_heads) in (1, 2, 4, 8))
+    if paged:
+        return PagedKVCache(cfg, batch_size, token_len + generate_steps, page_size=page_size, dtype=dtype, device=device)
     return init_cache(cfg, batch_size, token_len, generate_steps, dtype, device)
