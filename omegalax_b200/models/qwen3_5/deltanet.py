@@ -96,10 +96,7 @@ class GatedDeltaNet(nn.Module):
         v = v.reshape(B, T, self.nv, self.av)
         beta = torch.sigmoid(b.float()).view(B, T, self.nv)
         g = (-torch.exp(self.A_log.float()) * F.softplus(a.float() + self.dt_bias.float())).view(B, T, self.nv)
-        rep = self.nv // self.nk
-        if rep > 1:
-            q = q.repeat_interleave(rep, dim=2)
-            k = k.repeat_interleave(rep, dim=2)
-        core = Fn.gated_delta_rule(q, k, v, g, beta)               # [B,T,nv,av], input dtype
+        core = Fn.gated_delta_rule(q, k, v, g, beta)               # key heads are shared by nv/nk value heads
+
         core = self.norm(core.reshape(-1, self.av), z.reshape(-1, self.av))
         return self.out_proj(core.reshape(B * T, self.value_dim), residual=residual)

@@ -13,6 +13,7 @@ from __future__ import annotations
 import os
 
 import torch
+import torch.nn.functional as F
 
 from . import kernels as K
 from . import reference as R
@@ -412,14 +413,73 @@ def linear_cross_entropy(h, w, targets, mask, scale, chunk: int = 4096):
 
 
 # ----------------------------------------------------------------------------- GatedDeltaNet ops
+class _CausalConv1dFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        ctx.w_ref = w
+        return K.causal_conv1d_fwd(x, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        mg = getattr(ctx.w_ref, "main_grad", None)
+        dwf = mg if mg is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        dx = K.causal_conv1d_bwd(x, w, dy.contiguous(), dwf)
+        return dx, (None if mg is not None else dwf.to(w.dtype))
+
+
 def causal_conv1d_silu(x_BTC, w_CK):
     """Depthwise causal conv over time (left pad K-1) followed by SiLU.  x [B,T,C], w [C,K]."""
-    if use_kernels(x_BTC) and hasattr(K, "causal_conv1d_fwd"):
-        return _CausalConv1dFn.apply(x_BTC.contiguous(), w_CK)
+    if use_kernels(x_BTC) and w_CK.dtype == bf16 and w_CK.shape[1] == 4 and x_BTC.shape[-1] % 8 == 0:
+        return _CausalConv1dFn.apply(x_BTC.contiguous(), w_CK.contiguous())
     y = R.causal_conv1d(x_BTC.transpose(1, 2), w_CK, activation_silu=True)
     return y.transpose(1, 2)
 
 
-def gated_delta_rule(q, k, v, g, beta, chunk: int = 64):
-    """Chunked gated delta rule (fp32 inside); q,k [B,T,H,A], v [B,T,H,U], g/beta [B,T,H]."""
-    return R.chunk_gated_delta_rule(q, k, v, g, beta, chunk=chunk)
+class _GatedDeltaRuleFn(torch.autograd.Function):
+    """fp32 tensors, T a multiple of 64; q,k already normalised / scaled."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, s0, want_final):
+        save = any(ctx.needs_input_grad[:6])
+        o, n_out, states, s_final = K.gdn_fwd(q, k, v, g, beta, s0=s0, save=save, want_final=want_final)
+        if save:
+            ctx.save_for_backward(q, k, v, g, beta, n_out, states)
+        ctx.has_s0 = s0 is not None
+        if want_final:
+            return o, s_final
+        return o, None
+
+    @staticmethod
+    def backward(ctx, d_o, d_sf):
+        q, k, v, g, beta, n_out, states = ctx.saved_tensors
+        dq, dk, dv, dg, dbeta, ds0 = K.gdn_bwd(q, k, v, g, beta, n_out, states, d_o.contiguous(),
+                                               d_sfinal=None if d_sf is None else d_sf.contiguous(),
+                                               want_ds0=ctx.has_s0)
+        return dq, dk, dv, dg, dbeta, ds0, None
+
+
+def gated_delta_rule(q, k, v, g, beta, chunk: int = 64, initial_state=None, output_final_state=False):
+    """Chunked gated delta rule (fp32 inside); q,k [B,T,Hk,A] with Hk dividing H, v [B,T,H,U],
+    g/beta [B,T,H].  Key heads are shared by groups of H/Hk value heads."""
+    H, Hk = v.shape[2], q.shape[2]
+    if use_kernels(v) and q.shape[-1] == 128 and v.shape[-1] % 64 == 0 and chunk == 64:
+        dt, T, A = v.dtype, q.shape[1], q.shape[-1]
+        qf = R.l2norm(q.float()) * (A ** -0.5)
+        kf = R.l2norm(k.float())
+        vf, gf, bf_ = v.float(), g.float(), beta.float()
+        pad = (-T) % 64
+        if pad:
+            qf, kf, vf = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (qf, kf, vf))
+            gf, bf_ = (F.pad(t, (0, 0, 0, pad)) for t in (gf, bf_))
+        s0 = None if initial_state is None else initial_state.float().contiguous()
+        o, sf = _GatedDeltaRuleFn.apply(qf.contiguous(), kf.contiguous(), vf.contiguous(), gf.contiguous(),
+                                        bf_.contiguous(), s0, output_final_state)
+        o = o[:, :T].to(dt)
+        return (o, sf) if output_final_state else o
+    if Hk != H:
+        q = q.repeat_interleave(H // Hk, dim=2)
+        k = k.repeat_interleave(H // Hk, dim=2)
+    return R.chunk_gated_delta_rule(q, k, v, g, beta, chunk=chunk, initial_state=initial_state,
+                                    output_final_state=output_final_state)

@@ -319,3 +319,44 @@ def decode_attn(q, k_pages, v_pages, block_table, seq_lens, page_size, scale, sp
           seq_lens.data_ptr(), B, H, G, HD, block_table.shape[1], page_size, splits, float(scale),
           sc[0].data_ptr(), sc[1].data_ptr(), out.data_ptr(), lib.stream_ptr())
     return out
+
+
+def causal_conv1d_fwd(x_BTC, w_CK):
+    B, T, C = x_BTC.shape
+    y = torch.empty_like(x_BTC)
+    _call("ob_conv1d_silu_fwd", x_BTC.data_ptr(), w_CK.data_ptr(), y.data_ptr(), B, T, C, w_CK.shape[1], lib.stream_ptr())
+    return y
+
+
+def causal_conv1d_bwd(x_BTC, w_CK, dy, dw_f32):
+    B, T, C = x_BTC.shape
+    dx = torch.empty_like(x_BTC)
+    _call("ob_conv1d_silu_bwd", x_BTC.data_ptr(), w_CK.data_ptr(), dy.data_ptr(), dx.data_ptr(), lib.ptr(dw_f32), B, T, C,
+          w_CK.shape[1], lib.stream_ptr())
+    return dx
+
+
+def gdn_fwd(q, k, v, g, beta, s0=None, save=True, want_final=False):
+    """Chunked gated delta rule, fp32.  q,k [B,T,Hk,128]; v [B,T,H,U]; g,beta [B,T,H]; T % 64 == 0."""
+    B, T, Hk, A = q.shape
+    H, U = v.shape[2], v.shape[3]
+    o = torch.empty_like(v)
+    n_out = torch.empty_like(v) if save else None
+    states = torch.empty(B, H, T // 64, A, U, dtype=torch.float32, device=v.device) if save else None
+    s_final = torch.empty(B, H, A, U, dtype=torch.float32, device=v.device) if want_final else None
+    _call("ob_gdn_fwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), lib.ptr(s0),
+          o.data_ptr(), lib.ptr(n_out), lib.ptr(states), lib.ptr(s_final), B, T, H, Hk, A, U, lib.stream_ptr())
+    return o, n_out, states, s_final
+
+
+def gdn_bwd(q, k, v, g, beta, n_out, states, d_o, d_sfinal=None, want_ds0=False):
+    B, T, Hk, A = q.shape
+    H, U = v.shape[2], v.shape[3]
+    dq, dk = torch.zeros_like(q), torch.zeros_like(k)
+    dv = torch.empty_like(v)
+    dg, dbeta = torch.zeros_like(g), torch.zeros_like(beta)
+    ds0 = torch.empty(B, H, A, U, dtype=torch.float32, device=v.device) if want_ds0 else None
+    _call("ob_gdn_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), n_out.data_ptr(),
+          states.data_ptr(), d_o.data_ptr(), lib.ptr(d_sfinal), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+          dg.data_ptr(), dbeta.data_ptr(), lib.ptr(ds0), B, T, H, Hk, A, U, lib.stream_ptr())
+    return dq, dk, dv, dg, dbeta, ds0

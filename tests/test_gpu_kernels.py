@@ -314,3 +314,58 @@ def test_paged_decode_matches_full_forward():
         logits, cache, _ = text_api.decode(model, cache, nxt, 0, cfg)
     _check(lib)
     mesh_lib.set_default_mesh(None)
+
+
+def test_causal_conv1d_silu():
+    from omegalax_b200.ops import functional as Fn, reference as R, lib
+    torch.manual_seed(11)
+    B, T, C = 2, 100, 64
+    x = torch.randn(B, T, C, device=_dev()).to(bf16).requires_grad_(True)
+    w = (torch.randn(C, 4, device=_dev()) * 0.5).to(bf16).requires_grad_(True)
+    y = Fn.causal_conv1d_silu(x, w)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    _check(lib)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    yr = R.causal_conv1d(xr.transpose(1, 2), wr, activation_silu=True).transpose(1, 2)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 2e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("U,Hk,H,T,with_state", [(128, 2, 4, 200, False), (64, 1, 2, 128, True)])
+def test_gated_delta_rule_fwd_bwd(U, Hk, H, T, with_state):
+    from omegalax_b200.ops import functional as Fn, reference as R, lib
+    torch.manual_seed(5)
+    B, A = 2, 128
+    dev = _dev()
+    q = torch.randn(B, T, Hk, A, device=dev, requires_grad=True)
+    k = torch.randn(B, T, Hk, A, device=dev, requires_grad=True)
+    v = torch.randn(B, T, H, U, device=dev, requires_grad=True)
+    g = (-torch.rand(B, T, H, device=dev) * 0.3).requires_grad_(True)
+    beta = torch.sigmoid(torch.randn(B, T, H, device=dev)).requires_grad_(True)
+    s0 = (torch.randn(B, H, A, U, device=dev) * 0.1).requires_grad_(True) if with_state else None
+    out = Fn.gated_delta_rule(q, k, v, g, beta, initial_state=s0, output_final_state=with_state)
+    o, sf = out if with_state else (out, None)
+    do = torch.randn_like(o)
+    dsf = torch.randn_like(sf) * 0.1 if with_state else None
+    loss = (o * do).sum() + ((sf * dsf).sum() if with_state else 0.0)
+    loss.backward()
+    _check(lib)
+    leaves = [q, k, v, g, beta] + ([s0] if with_state else [])
+    got = [t.grad.clone() for t in leaves]
+    for t in leaves:
+        t.grad = None
+    rep = H // Hk
+    ref = R.chunk_gated_delta_rule(q.repeat_interleave(rep, 2), k.repeat_interleave(rep, 2), v, g, beta,
+                                   initial_state=s0, output_final_state=with_state)
+    ro, rsf = ref if with_state else (ref, None)
+    rl = (ro * do).sum() + ((rsf * dsf).sum() if with_state else 0.0)
+    rl.backward()
+    assert _rel_err(o, ro) < 1e-4
+    if with_state:
+        assert _rel_err(sf, rsf) < 1e-4
+    for name, a, t in zip(["q", "k", "v", "g", "beta", "s0"], got, leaves):
+        assert _rel_err(a, t.grad) < 2e-3, name
