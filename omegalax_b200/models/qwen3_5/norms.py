@@ -39,7 +39,7 @@ class RMSNormGated(nn.Module):
                 self.weight.fill_(1.0)
 
     def forward(self, x, gate):
-        return R.rmsnorm_gated(x, self.weight, gate, self.eps)
+        return Fn.rmsnorm_gated(x, self.weight, gate, self.eps)
 
 
 class LayerNorm(nn.Module):
@@ -58,4 +58,4 @@ class LayerNorm(nn.Module):
                 self.bias.zero_()
 
     def forward(self, x):
-        return R.layernorm(x, self.weight, self.bias, self.eps)
+        return Fn.layernorm(x, self.weight, self.bias, self.eps)

@@ -169,6 +169,59 @@ def rmsnorm(x, w, eps: float, one_plus: bool = False, scale_in_dtype: bool = Fal
     return R.rmsnorm(x, w, eps, one_plus, scale_in_dtype)
 
 
+class _GatedRMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, z, eps):
+        y, rstd = K.gated_rmsnorm_fwd(x, z, w, eps)
+        ctx.save_for_backward(x, w, z, rstd)
+        ctx.eps, ctx.w_ref = eps, w
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, z, rstd = ctx.saved_tensors
+        mg = getattr(ctx.w_ref, "main_grad", None)
+        dwf = mg if mg is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        dx, dz = K.gated_rmsnorm_bwd(dy.contiguous(), x, z, w, rstd, ctx.eps, dwf)
+        return dx, (None if mg is not None else dwf.to(w.dtype)), dz, None
+
+
+def rmsnorm_gated(x, w, z, eps: float):
+    """weight * norm(x) in the input dtype, times silu(z) in fp32; x, z [M, D]."""
+    if use_kernels(x) and w.dtype == bf16 and x.dim() == 2 and x.shape[-1] in (128, 256):
+        return _GatedRMSNormFn.apply(x.contiguous(), w, z.contiguous(), eps)
+    return R.rmsnorm_gated(x, w, z, eps)
+
+
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        y, mean, rstd = K.layernorm_fwd(x, w, b, eps)
+        ctx.save_for_backward(x, w, mean, rstd)
+        ctx.w_ref, ctx.b_ref = w, b
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, mean, rstd = ctx.saved_tensors
+        mgw, mgb = getattr(ctx.w_ref, "main_grad", None), getattr(ctx.b_ref, "main_grad", None)
+        fused = mgw is not None and mgb is not None
+        dwf = mgw if fused else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        dbf = mgb if fused else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        dx = K.layernorm_bwd(dy.contiguous(), x, w, mean, rstd, dwf, dbf)
+        if fused:
+            return dx, None, None, None
+        return dx, dwf.to(w.dtype), dbf.to(w.dtype), None
+
+
+def layernorm(x, w, b, eps: float):
+    """LayerNorm with bias over the last dim, fp32 statistics."""
+    D = x.shape[-1]
+    if use_kernels(x) and w.dtype == bf16 and b.dtype == bf16 and D % 8 == 0 and D <= 2048:
+        return _LayerNormFn.apply(x.reshape(-1, D).contiguous(), w, b, eps).view(x.shape)
+    return R.layernorm(x, w, b, eps)
+
+
 # ----------------------------------------------------------------------------- swiglu
 class _SwiGLUFn(torch.autograd.Function):
     @staticmethod

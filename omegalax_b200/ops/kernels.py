@@ -360,3 +360,72 @@ def gdn_bwd(q, k, v, g, beta, n_out, states, d_o, d_sfinal=None, want_ds0=False)
           states.data_ptr(), d_o.data_ptr(), lib.ptr(d_sfinal), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
           dg.data_ptr(), dbeta.data_ptr(), lib.ptr(ds0), B, T, H, Hk, A, U, lib.stream_ptr())
     return dq, dk, dv, dg, dbeta, ds0
+
+
+def gated_rmsnorm_fwd(x, z, w, eps):
+    M, D = x.shape
+    y = torch.empty_like(x)
+    rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+    _call("ob_gated_rmsnorm_fwd", x.data_ptr(), z.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), M, D,
+          float(eps), lib.stream_ptr())
+    return y, rstd
+
+
+def gated_rmsnorm_bwd(dy, x, z, w, rstd, eps, dw_f32):
+    M, D = x.shape
+    dx, dz = torch.empty_like(x), torch.empty_like(z)
+    _call("ob_gated_rmsnorm_bwd", dy.data_ptr(), x.data_ptr(), z.data_ptr(), w.data_ptr(), lib.ptr(rstd), dx.data_ptr(),
+          dz.data_ptr(), dw_f32.data_ptr(), M, D, float(eps), lib.stream_ptr())
+    return dx, dz
+
+
+def layernorm_fwd(x, w, b, eps):
+    M, D = x.shape
+    y = torch.empty_like(x)
+    mean = torch.empty(M, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+    _call("ob_layernorm_fwd", x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+          M, D, float(eps), lib.stream_ptr())
+    return y, mean, rstd
+
+
+def layernorm_bwd(dy, x, w, mean, rstd, dw_f32, db_f32):
+    M, D = x.shape
+    dx = torch.empty_like(x)
+    _call("ob_layernorm_bwd", dy.data_ptr(), x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+          dw_f32.data_ptr(), db_f32.data_ptr(), M, D, lib.stream_ptr())
+    return dx
+
+
+def router_topk(logits, k, renorm, counts=None):
+    """logits [M,E] bf16 -> probs [M,E] fp32, weights [M,k] fp32, idx [M,k] int32; counts [E] int32 += picks."""
+    M, E = logits.shape
+    probs = torch.empty(M, E, dtype=torch.float32, device=logits.device)
+    w = torch.empty(M, k, dtype=torch.float32, device=logits.device)
+    idx = torch.empty(M, k, dtype=torch.int32, device=logits.device)
+    _call("ob_router_topk", logits.data_ptr(), probs.data_ptr(), w.data_ptr(), idx.data_ptr(), lib.ptr(counts), M, E, k,
+          int(renorm), lib.stream_ptr())
+    return probs, w, idx
+
+
+def router_topk_bwd(probs, w, idx, dw, dprobs, renorm):
+    M, E = probs.shape
+    dlogits = torch.empty(M, E, dtype=bf16, device=probs.device)
+    _call("ob_router_topk_bwd", probs.data_ptr(), w.data_ptr(), idx.data_ptr(), dw.data_ptr(), lib.ptr(dprobs),
+          dlogits.data_ptr(), M, E, idx.shape[1], int(renorm), lib.stream_ptr())
+    return dlogits
+
+
+def moe_plan(idx32, E, pad=128, counts=None):
+    """idx [M,k] int32 -> offsets [E+1] int32 (segments padded to ``pad``), dest [M*k] int32.
+    ``counts`` [E] int32 may carry the histogram already (from the router)."""
+    have = counts is not None
+    if not have:
+        counts = torch.empty(E, dtype=torch.int32, device=idx32.device)
+    Pn = idx32.numel()
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=idx32.device)
+    cursor = torch.empty(E, dtype=torch.int32, device=idx32.device)
+    dest = torch.empty(Pn, dtype=torch.int32, device=idx32.device)
+    _call("ob_moe_plan", idx32.data_ptr(), counts.data_ptr(), offsets.data_ptr(), cursor.data_ptr(), dest.data_ptr(), Pn,
+          E, pad, int(not have), lib.stream_ptr())
+    return offsets, dest

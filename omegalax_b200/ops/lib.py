@@ -33,6 +33,13 @@ _SIGS = {
     "ob_attn_bwd": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, L, I, I, I, L, L, L, L, L, L, L, F, I, P, P],
     "ob_decode_append": [P, P, P, P, P, P, P, I, I, P, P, P, L, I, I, I, I, F, F, I, P],
     "ob_decode_attn": [P, P, P, P, P, I, I, I, I, I, I, I, F, P, P, P, P],
+    "ob_gated_rmsnorm_fwd": [P, P, P, P, P, L, I, F, P],
+    "ob_gated_rmsnorm_bwd": [P, P, P, P, P, P, P, P, L, I, F, P],
+    "ob_layernorm_fwd": [P, P, P, P, P, P, L, I, F, P],
+    "ob_layernorm_bwd": [P, P, P, P, P, P, P, P, L, I, P],
+    "ob_router_topk": [P, P, P, P, P, L, I, I, I, P],
+    "ob_router_topk_bwd": [P, P, P, P, P, P, L, I, I, I, P],
+    "ob_moe_plan": [P, P, P, P, P, L, I, I, I, P],
     "ob_gdn_fwd": [P] * 10 + [I] * 6 + [P],
     "ob_gdn_bwd": [P] * 15 + [I] * 6 + [P],
     "ob_conv1d_silu_fwd": [P, P, P, I, I, I, I, P],

@@ -17,9 +17,35 @@ bf16 = torch.bfloat16
 PAD = 128
 
 
+class _RouteFn(torch.autograd.Function):
+    """Router kernel: softmax + top-k + renormalisation in one pass, analytic backward."""
+
+    @staticmethod
+    def forward(ctx, logits, top_k, renormalize):
+        probs, w, idx32 = K.router_topk(logits, top_k, renormalize)
+        ctx.save_for_backward(probs, w, idx32)
+        ctx.renorm = renormalize
+        ctx.set_materialize_grads(False)
+        idx = idx32.to(torch.int64)
+        ctx.mark_non_differentiable(idx)
+        return probs, w, idx
+
+    @staticmethod
+    def backward(ctx, dprobs, dw, _didx):
+        probs, w, idx32 = ctx.saved_tensors
+        if dw is None:
+            dw = torch.zeros_like(w)
+        dp = None if dprobs is None else dprobs.contiguous().float()
+        return K.router_topk_bwd(probs, w, idx32, dw.contiguous().float(), dp, ctx.renorm), None, None
+
+
 def route(router_logits, top_k: int, renormalize: bool):
     """fp32 softmax over experts, top-k, optional renormalisation with clip(sum, 1e-9).
     Returns probs [M,E] fp32, weights [M,k] fp32, indices [M,k] int64."""
+    E = router_logits.shape[-1]
+    if Fn.use_kernels(router_logits) and router_logits.dtype == bf16 and router_logits.dim() == 2 \
+            and E % 32 == 0 and E <= 512 and top_k <= 16:
+        return _RouteFn.apply(router_logits.contiguous(), top_k, bool(renormalize))
     probs = torch.softmax(router_logits.float(), dim=-1)
     w, idx = torch.topk(probs, top_k, dim=-1)
     if renormalize:
@@ -105,6 +131,67 @@ def expert_mlp_permuted(xp, w_gate_up, w_down, offsets):
     return grouped_linear(act, w_down, offsets)
 
 
+# ---- row movement on one GPU: the dispatch / combine kernels of the expert-parallel path with a
+# single "rank" whose buffer is a local tensor
+def _ptr1(t):
+    import ctypes
+
+    return (ctypes.c_void_p * 1)(t.data_ptr())
+
+
+def _push_rows(buf, src, src_tok, rank0, dst_row, scale):
+    from . import lib
+
+    lib.call("ob_ep_push", _ptr1(buf), 1, src.data_ptr(), src_tok.data_ptr(), rank0.data_ptr(), dst_row.data_ptr(),
+             lib.ptr(scale), dst_row.numel(), src.shape[1], lib.stream_ptr())
+
+
+def _pull_rows(buf, rank0, src_row, M, k, weights=None, want_out=True, grad=None):
+    from . import lib
+
+    D = buf.shape[1]
+    out = torch.empty(M, D, dtype=buf.dtype, device=buf.device) if want_out else None
+    dots = torch.empty(M * k, dtype=torch.float32, device=buf.device) if grad is not None else None
+    lib.call("ob_ep_pull", _ptr1(buf), 1, lib.ptr(out), rank0.data_ptr(), src_row.data_ptr(), lib.ptr(weights),
+             lib.ptr(grad), lib.ptr(dots), M, k, D, lib.stream_ptr())
+    return out, dots
+
+
+class _LocalDispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, dest, src_tok, rank0, cap, k):
+        xp = torch.zeros(cap, x.shape[1], dtype=x.dtype, device=x.device)   # padding rows stay zero
+        _push_rows(xp, x, src_tok, rank0, dest, None)
+        ctx.save_for_backward(dest, rank0)
+        ctx.M, ctx.k = x.shape[0], k
+        return xp
+
+    @staticmethod
+    def backward(ctx, d_xp):
+        dest, rank0 = ctx.saved_tensors
+        dx, _ = _pull_rows(d_xp.contiguous(), rank0, dest, ctx.M, ctx.k)
+        return dx, None, None, None, None, None
+
+
+class _LocalCombine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, yp, weights, dest, src_tok, rank0):
+        M, k = weights.shape
+        y, _ = _pull_rows(yp, rank0, dest, M, k, weights=weights.reshape(-1))
+        ctx.save_for_backward(yp, weights, dest, src_tok, rank0)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        yp, weights, dest, src_tok, rank0 = ctx.saved_tensors
+        M, k = weights.shape
+        dy = dy.contiguous()
+        _, dots = _pull_rows(yp, rank0, dest, M, k, want_out=False, grad=dy)
+        d_yp = torch.zeros_like(yp)
+        _push_rows(d_yp, dy, src_tok, rank0, dest, weights.reshape(-1))
+        return d_yp, dots.view(M, k), None, None, None
+
+
 def moe_mlp(x, weights, idx, w_gate_up, w_down):
     """Routed SwiGLU experts.  x [M,D]; weights/idx [M,k]; w_gate_up [E,2F,D] with rows
     [gate | up]; w_down [E,D,F].  Returns [M,D] = sum_k weights * expert_{idx}(x)."""
@@ -112,13 +199,13 @@ def moe_mlp(x, weights, idx, w_gate_up, w_down):
     E = w_gate_up.shape[0]
     k = idx.shape[1]
     if Fn.use_kernels(x) and w_gate_up.dtype == bf16 and D % 64 == 0:
-        dest, offsets, cap = build_permutation(idx, E)
-        xp = torch.zeros(cap, D, dtype=x.dtype, device=x.device)
-        src_tok = torch.arange(M, device=x.device).repeat_interleave(k)
-        xp = xp.index_copy(0, dest, x.index_select(0, src_tok))
+        offsets, dest = K.moe_plan(idx.to(torch.int32).contiguous(), E, PAD)
+        cap = (M * k + E * (PAD - 1) + PAD - 1) // PAD * PAD
+        src_tok = torch.arange(M, device=x.device, dtype=torch.int32).repeat_interleave(k)
+        rank0 = torch.zeros(M * k, dtype=torch.int32, device=x.device)
+        xp = _LocalDispatch.apply(x.contiguous(), dest, src_tok, rank0, cap, k)
         yp = expert_mlp_permuted(xp, w_gate_up, w_down, offsets)
-        y = yp.index_select(0, dest).view(M, k, D)
-        return (y.float() * weights.unsqueeze(-1)).sum(1).to(x.dtype)
+        return _LocalCombine.apply(yp, weights.contiguous().float(), dest, src_tok, rank0)
     out = torch.zeros(M, D, dtype=torch.float32, device=x.device)
     for e in range(E):
         tok, slot = torch.nonzero(idx == e, as_tuple=True)
