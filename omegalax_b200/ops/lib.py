@@ -33,6 +33,8 @@ _SIGS = {
     "ob_attn_bwd": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, L, I, I, I, L, L, L, L, L, L, L, F, I, P, P],
     "ob_decode_append": [P, P, P, P, P, P, P, I, I, P, P, P, L, I, I, I, I, F, F, I, P],
     "ob_decode_attn": [P, P, P, P, P, I, I, I, I, I, I, I, F, P, P, P, P],
+    "ob_ep_push": [P, I, P, P, P, P, P, L, I, P],
+    "ob_ep_pull": [P, I, P, P, P, P, P, P, L, I, I, P],
     "ob_gated_rmsnorm_fwd": [P, P, P, P, P, L, I, F, P],
     "ob_gated_rmsnorm_bwd": [P, P, P, P, P, P, P, P, L, I, F, P],
     "ob_layernorm_fwd": [P, P, P, P, P, P, L, I, F, P],

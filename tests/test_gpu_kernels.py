@@ -369,3 +369,94 @@ def test_gated_delta_rule_fwd_bwd(U, Hk, H, T, with_state):
         assert _rel_err(sf, rsf) < 1e-4
     for name, a, t in zip(["q", "k", "v", "g", "beta", "s0"], got, leaves):
         assert _rel_err(a, t.grad) < 2e-3, name
+
+
+def test_gated_rmsnorm_and_layernorm():
+    from omegalax_b200.ops import functional as Fn, reference as R, lib
+    torch.manual_seed(3)
+    dev = _dev()
+    M, D = 1000, 128
+    x = torch.randn(M, D, device=dev).to(bf16).requires_grad_(True)
+    z = torch.randn(M, D, device=dev).to(bf16).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(D, device=dev)).to(bf16).requires_grad_(True)
+    y = Fn.rmsnorm_gated(x, w, z, 1e-6)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    _check(lib)
+    xr, zr, wr = (t.detach().float().requires_grad_(True) for t in (x, z, w))
+    yr = R.rmsnorm_gated(xr, wr, zr, 1e-6)
+    yr.backward(dy.float())
+    assert _rel_err(y, yr) < 2e-2
+    for a, b in ((x.grad, xr.grad), (z.grad, zr.grad), (w.grad, wr.grad)):
+        assert _rel_err(a, b) < 3e-2
+    for D in (1024, 1152):
+        x = torch.randn(300, D, device=dev).to(bf16).requires_grad_(True)
+        w = (1 + 0.1 * torch.randn(D, device=dev)).to(bf16).requires_grad_(True)
+        b = (0.1 * torch.randn(D, device=dev)).to(bf16).requires_grad_(True)
+        y = Fn.layernorm(x, w, b, 1e-6)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        _check(lib)
+        xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+        yr = R.layernorm(xr, wr, br, 1e-6)
+        yr.backward(dy.float())
+        assert _rel_err(y, yr) < 2e-2
+        for a, c in ((x.grad, xr.grad), (w.grad, wr.grad), (b.grad, br.grad)):
+            assert _rel_err(a, c) < 3e-2
+
+
+@pytest.mark.parametrize("E,k,renorm", [(128, 8, True), (512, 10, True), (64, 4, False)])
+def test_router_kernel(E, k, renorm):
+    from omegalax_b200.ops import moe as moe_ops, lib
+    torch.manual_seed(9)
+    dev = _dev()
+    M = 777
+    logits = (torch.randn(M, E, device=dev) * 2).to(bf16).requires_grad_(True)
+    probs, w, idx = moe_ops.route(logits, k, renorm)
+    gp = torch.randn_like(probs) * 0.1
+    gw = torch.randn_like(w)
+    (probs * gp).sum().add((w * gw).sum()).backward()
+    _check(lib)
+    lr = logits.detach().float().requires_grad_(True)
+    pr = torch.softmax(lr, -1)
+    _, ir = torch.topk(pr, k, dim=-1)
+    wr = pr.gather(-1, idx)          # same pick order as the kernel (bf16 logits produce exact ties)
+    if renorm:
+        wr = wr / wr.sum(-1, keepdim=True).clamp_min(1e-9)
+    (pr * gp).sum().add((wr * gw).sum()).backward()
+    tie_free = (torch.sort(idx, -1).values == torch.sort(ir, -1).values).all(-1)
+    assert tie_free.float().mean() > 0.98
+    assert _rel_err(probs, pr) < 1e-5
+    assert _rel_err(w, wr) < 1e-5
+    assert _rel_err(logits.grad, lr.grad) < 2e-2
+
+
+def test_moe_mlp_kernel_path_matches_dense_loop():
+    from omegalax_b200.ops import moe as moe_ops, lib
+    torch.manual_seed(21)
+    dev = _dev()
+    M, D, F_, E, k = 300, 128, 64, 8, 2
+    x = torch.randn(M, D, device=dev).to(bf16).requires_grad_(True)
+    wg = (torch.randn(E, 2 * F_, D, device=dev) * D ** -0.5).to(bf16).requires_grad_(True)
+    wd = (torch.randn(E, D, F_, device=dev) * F_ ** -0.5).to(bf16).requires_grad_(True)
+    logits = torch.randn(M, E, device=dev)
+    wts, idx = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+    wts = wts.clone().requires_grad_(True)
+    y = moe_ops.moe_mlp(x, wts, idx, wg, wd)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    _check(lib)
+    xr, wgr, wdr, wtr = (t.detach().float().requires_grad_(True) for t in (x, wg, wd, wts))
+    out = torch.zeros(M, D, device=dev)
+    for e in range(E):
+        tok, slot = torch.nonzero(idx == e, as_tuple=True)
+        gu = xr[tok] @ wgr[e].t()
+        g, u = gu.chunk(2, -1)
+        ye = (torch.nn.functional.silu(g) * u) @ wdr[e].t()
+        out = out.index_add(0, tok, ye * wtr[tok, slot].unsqueeze(-1))
+    out.backward(dy.float())
+    assert _rel_err(y, out) < 3e-2
+    assert _rel_err(x.grad, xr.grad) < 4e-2
+    assert _rel_err(wts.grad, wtr.grad) < 4e-2
+    assert _rel_err(wg.grad, wgr.grad) < 4e-2
+    assert _rel_err(wd.grad, wdr.grad) < 4e-2
