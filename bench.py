@@ -31,6 +31,13 @@ METRIC = "sft_train_tokens_per_sec"
 MODEL_ID = "Qwen/Qwen3-8B"
 SEQ_LEN = 4096
 SEQS_PER_GPU = 8
+# --model: the headline config (default) and the other text configs that are benchmarked at 8 GPUs.
+# (model id, sequence length, sequences per GPU, parallelism label at N > 1)
+MODELS = {
+    "qwen3-8b": (MODEL_ID, SEQ_LEN, SEQS_PER_GPU, "fsdp"),
+    "qwen3-30b-a3b": ("Qwen/Qwen3-30B-A3B-Instruct-2507", 4096, 4, "ep+fsdp"),
+    "qwen3.5-8l": ("qwen3.5-397b-a17b-8layer", 8192, 2, "ep+fsdp"),
+}
 
 
 def reference_arm(args) -> int:
@@ -105,10 +112,11 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="qwen3-8b", choices=sorted(MODELS))
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncate the layer stack")
-    ap.add_argument("--seqs-per-gpu", type=int, default=SEQS_PER_GPU)
+    ap.add_argument("--seqs-per-gpu", type=int, default=None)
     ap.add_argument("--micro-seqs", type=int, default=None, help="sequences per GPU per micro-batch")
-    ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
+    ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--remat", default=None, help="full | selective | save:<tags> (default depends on N)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -137,9 +145,15 @@ def main() -> int:
     rank = mesh_lib.rank()
     N = max(world, 1)
 
-    cfg = text_api.resolve_config(MODEL_ID)
+    model_id, def_T, def_seqs, par = MODELS[args.model]
+    args.seqs_per_gpu = args.seqs_per_gpu or def_seqs
+    args.seq_len = args.seq_len or def_T
+    cfg = text_api.resolve_config(model_id)
     if args.layers is not None:
-        cfg = dataclasses.replace(cfg, num_layers=args.layers)
+        if hasattr(cfg, "num_layers"):
+            cfg = dataclasses.replace(cfg, num_layers=args.layers)
+        else:
+            cfg = dataclasses.replace(cfg, num_hidden_layers=args.layers, layer_types=cfg.layer_types[:args.layers])
     micro = args.micro_seqs or (4 if N <= 2 else args.seqs_per_gpu)  # keeps the kept activations inside 180 GB
     micro = min(micro, args.seqs_per_gpu)
     accum = args.seqs_per_gpu // micro
@@ -147,6 +161,8 @@ def main() -> int:
     # One GPU holds all fp32 state (148 GB): only the small attention-side tensors are kept from the
     # first forward.  With the state sharded there is room to keep the wide MLP activation too.
     remat = args.remat or ("save:qkv,attn" if N == 1 else "selective")
+    if args.model != "qwen3-8b" and args.remat is None:
+        remat = "full"
     tcfg = trainer.TrainConfig(seed=0, batch_size=micro * N, seq_len=T, num_steps=10_000, learning_rate=1e-5,
                                weight_decay=0.01, warmup_steps=0, lr_schedule="linear", max_grad_norm=1.0,
                                grad_accum_steps=accum, remat_policy=remat)
@@ -228,8 +244,9 @@ def main() -> int:
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": N, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-            "config": {"model": MODEL_ID if args.layers is None else f"{MODEL_ID}[{args.layers} layers]",
-                       "global_batch": args.seqs_per_gpu * N, "seq_len": T, "parallelism": f"fsdp{N}",
+            "config": {"model": model_id if args.layers is None else f"{model_id}[{args.layers} layers]",
+                       "global_batch": args.seqs_per_gpu * N, "seq_len": T,
+                       "parallelism": f"fsdp{N}" if par == "fsdp" else f"ep{N}+fsdp{N}",
                        "micro_batch_per_gpu": micro, "grad_accum": accum, "optimizer": "AdamW fp32 master",
                        "remat": remat, "l2": "inputs larger than L2 (16 GB of weights per step)"},
             "tokens_per_sec_per_gpu": value / N, "tflops_per_gpu": tflops_per_gpu,

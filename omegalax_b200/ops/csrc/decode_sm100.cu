@@ -74,17 +74,20 @@ __global__ void decode_append_kernel(const bf16* __restrict__ qkv, const bf16* _
   }
 }
 
-// grid (B, G, splits); 128 threads = 4 warps; warp w walks keys w, w+4, ... of the split.
-// HD = 128: each lane owns 4 consecutive channels.  R <= 8 query heads per kv head.
+// grid (B, G, splits); 128 threads = 8 half-warps; half-warp w walks keys w, w+8, ... of the split.
+// HD = 128: each lane owns 8 consecutive channels (one 16-byte load per K and V row).
+// R <= 8 query heads per kv head share every row that is read.
 template <int HD, int R>
 __global__ void __launch_bounds__(128)
 decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                    const int* __restrict__ block_table, const int* __restrict__ seq_lens, int max_blocks,
                    int page_size, int G, int splits, float scale, float* __restrict__ part_o,
                    float* __restrict__ part_ml) {
-  constexpr int C = HD / 32;  // channels per lane
+  static_assert(HD == 128, "one half-warp covers a 128-channel row");
+  constexpr int C = 8;    // channels per lane
+  constexpr int NW = 8;   // half-warps per CTA
   const int b = blockIdx.x, g = blockIdx.y, sp = blockIdx.z;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = threadIdx.x >> 4, hl = threadIdx.x & 15;
   const int H = G * R;
   const int S = seq_lens[b];
   const int per = (S + splits - 1) / splits;
@@ -92,9 +95,13 @@ decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
   float qv[R][C];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const bf16* qp = q + ((long long)b * H + g * R + r) * HD + lane * C;
+    const uint4 u = *reinterpret_cast<const uint4*>(q + ((long long)b * H + g * R + r) * HD + hl * C);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-    for (int c = 0; c < C; ++c) qv[r][c] = __bfloat162float(qp[c]) * scale;
+    for (int c = 0; c < 4; ++c) {
+      const float2 t = unpack_bf16(w[c]);
+      qv[r][2 * c] = t.x * scale; qv[r][2 * c + 1] = t.y * scale;
+    }
   }
   float m[R], l[R], o[R][C];
 #pragma unroll
@@ -103,52 +110,57 @@ decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
 #pragma unroll
     for (int c = 0; c < C; ++c) o[r][c] = 0.f;
   }
-  for (int s = k_lo + warp; s < k_hi; s += 4) {
-    const int page = block_table[(long long)b * max_blocks + s / page_size];
-    const long long row = (((long long)page * page_size + s % page_size) * G + g) * HD + lane * C;
+  for (int s0 = k_lo; s0 < k_hi; s0 += NW) {   // uniform trip count: the shuffles below need all lanes
+    const int s = s0 + sub;
+    const bool ok = s < k_hi;
     float kv[C], vv[C];
-    if (C == 4) {
-      uint2 ku = *reinterpret_cast<const uint2*>(k_pages + row);
-      uint2 vu = *reinterpret_cast<const uint2*>(v_pages + row);
-      float2 a = unpack_bf16(ku.x), b2 = unpack_bf16(ku.y), c2 = unpack_bf16(vu.x), d = unpack_bf16(vu.y);
-      kv[0] = a.x; kv[1] = a.y; kv[2] = b2.x; kv[3] = b2.y;
-      vv[0] = c2.x; vv[1] = c2.y; vv[2] = d.x; vv[3] = d.y;
-    } else {
 #pragma unroll
-      for (int c = 0; c < C; ++c) {
-        kv[c] = __bfloat162float(k_pages[row + c]);
-        vv[c] = __bfloat162float(v_pages[row + c]);
+    for (int c = 0; c < C; ++c) { kv[c] = 0.f; vv[c] = 0.f; }
+    if (ok) {
+      const int page = block_table[(long long)b * max_blocks + s / page_size];
+      const long long row = (((long long)page * page_size + s % page_size) * G + g) * HD + hl * C;
+      const uint4 ku = *reinterpret_cast<const uint4*>(k_pages + row);
+      const uint4 vu = *reinterpret_cast<const uint4*>(v_pages + row);
+      const uint32_t kw[4] = {ku.x, ku.y, ku.z, ku.w}, vw[4] = {vu.x, vu.y, vu.z, vu.w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float2 a = unpack_bf16(kw[c]), d = unpack_bf16(vw[c]);
+        kv[2 * c] = a.x; kv[2 * c + 1] = a.y;
+        vv[2 * c] = d.x; vv[2 * c + 1] = d.y;
       }
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       float d = 0.f;
 #pragma unroll
-      for (int c = 0; c < C; ++c) d += qv[r][c] * kv[c];
-      d = warp_sum(d);
-      const float mn = fmaxf(m[r], d);
-      const float a = __expf(m[r] - mn), p = __expf(d - mn);
-      l[r] = l[r] * a + p;
+      for (int c = 0; c < C; ++c) d = fmaf(qv[r][c], kv[c], d);
 #pragma unroll
-      for (int c = 0; c < C; ++c) o[r][c] = o[r][c] * a + p * vv[c];
-      m[r] = mn;
+      for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
+      if (ok) {
+        const float mn = fmaxf(m[r], d);
+        const float a = __expf(m[r] - mn), p = __expf(d - mn);
+        l[r] = l[r] * a + p;
+#pragma unroll
+        for (int c = 0; c < C; ++c) o[r][c] = o[r][c] * a + p * vv[c];
+        m[r] = mn;
+      }
     }
   }
-  // merge the four warps through shared memory
-  __shared__ float sm_m[4][R], sm_l[4][R], sm_o[4][R][HD];
+  // merge the eight half-warps through shared memory
+  __shared__ float sm_m[NW][R], sm_l[NW][R], sm_o[NW][R][HD];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    if (lane == 0) { sm_m[warp][r] = m[r]; sm_l[warp][r] = l[r]; }
+    if (hl == 0) { sm_m[sub][r] = m[r]; sm_l[sub][r] = l[r]; }
 #pragma unroll
-    for (int c = 0; c < C; ++c) sm_o[warp][r][lane * C + c] = o[r][c];
+    for (int c = 0; c < C; ++c) sm_o[sub][r][hl * C + c] = o[r][c];
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < R * HD; idx += 128) {
     const int r = idx / HD, c = idx - r * HD;
     float mm = -INFINITY;
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_m[w][r]);
+    for (int w = 0; w < NW; ++w) mm = fmaxf(mm, sm_m[w][r]);
     float ll = 0.f, oo = 0.f;
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < NW; ++w) {
       const float a = (sm_m[w][r] == -INFINITY) ? 0.f : __expf(sm_m[w][r] - mm);
       ll += sm_l[w][r] * a;
       oo += sm_o[w][r][c] * a;

@@ -126,6 +126,13 @@ class _LinearFn(torch.autograd.Function):
 
 def linear(x, w, residual=None, bias=None, tag=None):
     """y = x @ w.T (+ bias) (+ residual); w is [out, in]."""
+    if use_kernels(x) and w.dtype == bf16 and w.shape[0] % 8:
+        # narrow heads (a 1-row gate, a handful of per-head scalars): the GEMM tiles need rows in
+        # multiples of 8, so run on a zero-padded weight and drop the padding columns
+        n = w.shape[0]
+        y = linear(x, F.pad(w, (0, 0, 0, 8 - n % 8)), None, None if bias is None else F.pad(bias, (0, 8 - n % 8)))
+        y = y[..., :n]
+        return y if residual is None else y + residual
     if use_kernels(x) and w.dtype == bf16:
         key, pre = _stash_lookup(tag if bias is None else None)
         y = _LinearFn.apply(x, w, residual if bias is None else None,

@@ -307,7 +307,10 @@ def decode_attn(q, k_pages, v_pages, block_table, seq_lens, page_size, scale, sp
     B, H, HD = q.shape
     G = k_pages.shape[2]
     if splits is None:
-        splits = max(1, min(16, (148 * 2) // max(B * G, 1)))
+        # the per-key work is latency bound, so fill every SM with ~16 small CTAs, but keep at
+        # least 128 keys of cache capacity per split
+        cap = block_table.shape[1] * page_size
+        splits = max(1, min(32, -(-(148 * 16) // max(B * G, 1)), cap // 128))
     key = (q.device.index, B, H, HD, splits)
     sc = _decode_scratch.get(key)
     if sc is None:

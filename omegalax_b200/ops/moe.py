@@ -47,7 +47,10 @@ def route(router_logits, top_k: int, renormalize: bool):
             and E % 32 == 0 and E <= 512 and top_k <= 16:
         return _RouteFn.apply(router_logits.contiguous(), top_k, bool(renormalize))
     probs = torch.softmax(router_logits.float(), dim=-1)
-    w, idx = torch.topk(probs, top_k, dim=-1)
+    # stable sort: equal probabilities (frequent with bf16 logits) go to the lower expert id, the
+    # same rule as the router kernel
+    w, idx = torch.sort(probs, dim=-1, descending=True, stable=True)
+    w, idx = w[..., :top_k], idx[..., :top_k]
     if renormalize:
         w = w / w.sum(-1, keepdim=True).clamp_min(1e-9)
     return probs, w, idx

@@ -290,7 +290,7 @@ class TrainEngine:
                 owner = s.module.get_submodule(s.pname.rsplit(".", 1)[0]) if "." in s.pname else s.module
                 owner.ep = _LazyEP(self, owner)
                 continue
-            if not (s.sharded and len(s.shape) == 2 and s.pname.endswith("weight")):
+            if not (s.sharded and len(s.shape) == 2 and s.pname.endswith("weight") and s.shape[0] % 8 == 0):
                 continue
             owner = s.module.get_submodule(s.pname.rsplit(".", 1)[0]) if "." in s.pname else s.module
             if type(owner).__name__ != "Linear":

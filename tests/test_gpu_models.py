@@ -1,0 +1,136 @@
+"""Whole-model checks on a GPU: every family runs forward + backward in bf16 once through the
+CUDA kernels and once through the plain PyTorch definitions of the same ops (on the same
+device, same weights); logits and a sample of gradients must agree to bf16 accuracy, and a few
+optimizer steps through the training engine must reduce the loss."""
+import dataclasses
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+bf16 = torch.bfloat16
+
+
+def _dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    return torch.device("cuda", 0)
+
+
+@pytest.fixture(autouse=True)
+def _mesh():
+    from omegalax_b200.parallel import mesh as mesh_lib
+
+    mesh_lib.set_default_mesh(None)
+    yield
+    mesh_lib.set_default_mesh(None)
+    os.environ.pop("OMEGALAX_B200_REFERENCE_OPS", None)
+
+
+def _configs():
+    from omegalax_b200.models.qwen3_5.config import make_config as q35
+    from omegalax_b200.text import api as text_api
+
+    dense = dataclasses.replace(text_api.resolve_config("Qwen/Qwen3-8B"), num_layers=2, emb_dim=256, mlp_dim=512,
+                                num_heads=4, num_kv_heads=2, vocab_size=2048)
+    moe = dataclasses.replace(text_api.resolve_config("Qwen/Qwen3-30B-A3B-Instruct-2507"), num_layers=2, emb_dim=256,
+                              num_heads=4, num_kv_heads=2, vocab_size=2048, num_experts=32, num_experts_per_tok=4,
+                              moe_intermediate_size=128)
+    t = q35("qwen3.5-smoke").text_config
+    hybrid = dataclasses.replace(t, hidden_size=256, vocab_size=2048, num_attention_heads=4, num_key_value_heads=2,
+                                 head_dim=128, linear_key_head_dim=128, linear_value_head_dim=128,
+                                 linear_num_key_heads=2, linear_num_value_heads=4, num_experts=32,
+                                 num_experts_per_tok=4, moe_intermediate_size=128,
+                                 shared_expert_intermediate_size=128, mrope_section=(8, 4, 4))
+    return {"qwen3-dense": dense, "qwen3-moe": moe, "qwen3.5-hybrid-moe": hybrid}
+
+
+def _run(model, cfg, tok, reference: bool):
+    from omegalax_b200.text import api as text_api
+
+    if reference:
+        os.environ["OMEGALAX_B200_REFERENCE_OPS"] = "1"
+    else:
+        os.environ.pop("OMEGALAX_B200_REFERENCE_OPS", None)
+    for p in model.parameters():
+        p.grad = None
+    hidden, aux = text_api.forward(model, tok, 0, cfg)
+    logits = model.lm_head(hidden)
+    loss = torch.nn.functional.cross_entropy(logits.float().view(-1, logits.shape[-1]), tok.view(-1).long())
+    if aux is not None:
+        loss = loss + aux.float().sum()
+    loss.backward()
+    grads = {n: p.grad.detach().float().clone() for n, p in model.named_parameters() if p.grad is not None}
+    return logits.detach().float(), grads
+
+
+@pytest.mark.parametrize("name", ["qwen3-dense", "qwen3-moe", "qwen3.5-hybrid-moe"])
+def test_kernels_match_reference_ops(name, monkeypatch):
+    from omegalax_b200.ops import lib
+    from omegalax_b200.text import api as text_api
+
+    dev = _dev()
+    cfg = _configs()[name]
+    torch.manual_seed(0)
+    model, cfg = text_api.init_model(cfg, 0, tp_size=1, fsdp_size=1, dp_size=1)
+    model = model.to(dev).to(bf16)
+    tok = torch.randint(1, cfg.vocab_size, (2, 192), device=dev, dtype=torch.int32)
+    # The two passes see router logits that differ in the last bf16 bit, which is enough to send a
+    # token to a different expert when two probabilities are close.  The kernel pass records its
+    # expert choices and the reference pass replays them, so both evaluate the same function.
+    from omegalax_b200.ops import moe as moe_ops
+
+    picks, orig_route = [], moe_ops.route
+
+    def recording(logits, k, renorm):
+        probs, w, idx = orig_route(logits, k, renorm)
+        picks.append(idx)
+        return probs, w, idx
+
+    def replaying(logits, k, renorm):
+        idx = picks.pop(0)
+        probs = torch.softmax(logits.float(), dim=-1)
+        w = probs.gather(-1, idx)
+        if renorm:
+            w = w / w.sum(-1, keepdim=True).clamp_min(1e-9)
+        return probs, w, idx
+
+    monkeypatch.setattr(moe_ops, "route", recording)
+    lk, gk = _run(model, cfg, tok, reference=False)
+    lib.check_status()
+    monkeypatch.setattr(moe_ops, "route", replaying)
+    lr, gr = _run(model, cfg, tok, reference=True)
+    monkeypatch.setattr(moe_ops, "route", orig_route)
+    err = (lk - lr).abs()
+    assert err.max() < 0.5 * max(1.0, float(lr.abs().max()) / 8), float(err.max())
+    assert err.median() < 0.02
+    assert (lk.argmax(-1) == lr.argmax(-1)).float().mean() > 0.9
+    assert set(gk) == set(gr)
+    bad = []
+    for n in gk:
+        denom = gr[n].norm() + 1e-6
+        rel = float((gk[n] - gr[n]).norm() / denom)
+        if rel > 0.15 and float(denom) > 1e-4:
+            bad.append((n, rel))
+    assert not bad, bad[:8]
+
+
+@pytest.mark.parametrize("name", ["qwen3-moe", "qwen3.5-hybrid-moe"])
+def test_training_engine_reduces_loss(name):
+    from omegalax_b200.ops import lib
+    from omegalax_b200.trainers import text as trainer
+
+    dev = _dev()
+    cfg = _configs()[name]
+    tcfg = trainer.TrainConfig(batch_size=2, seq_len=192, num_steps=8, learning_rate=2e-3, max_grad_norm=1.0)
+    model, cfg = trainer.init_model(cfg, 0, tp_size=1, fsdp_size=1, dp_size=1, meta=True)
+    opt = trainer.build_optimizer(model, tcfg, device=dev)
+    step = trainer.make_sft_train_step(cfg)
+    tok = torch.randint(1, cfg.vocab_size, (2, 192), device=dev, dtype=torch.int32)
+    batch = {"token_ids_BT": tok, "attention_mask_BT": torch.ones_like(tok), "loss_mask_BT": torch.ones_like(tok)}
+    losses = [float(step(opt, batch)[0]) for _ in range(6)]
+    lib.check_status()
+    assert all(l == l for l in losses), losses
+    assert losses[-1] < losses[0] - 0.05, losses
