@@ -114,6 +114,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="qwen3-8b", choices=sorted(MODELS))
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncate the layer stack")
+    ap.add_argument("--experts", type=int, default=None, help="debug only: shrink the expert count")
     ap.add_argument("--seqs-per-gpu", type=int, default=None)
     ap.add_argument("--micro-seqs", type=int, default=None, help="sequences per GPU per micro-batch")
     ap.add_argument("--seq-len", type=int, default=None)
@@ -154,6 +155,8 @@ def main() -> int:
             cfg = dataclasses.replace(cfg, num_layers=args.layers)
         else:
             cfg = dataclasses.replace(cfg, num_hidden_layers=args.layers, layer_types=cfg.layer_types[:args.layers])
+    if args.experts is not None:
+        cfg = dataclasses.replace(cfg, num_experts=args.experts)
     micro = args.micro_seqs or (4 if N <= 2 else args.seqs_per_gpu)  # keeps the kept activations inside 180 GB
     micro = min(micro, args.seqs_per_gpu)
     accum = args.seqs_per_gpu // micro
@@ -244,7 +247,8 @@ def main() -> int:
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": N, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-            "config": {"model": model_id if args.layers is None else f"{model_id}[{args.layers} layers]",
+            "config": {"model": model_id if args.layers is None and args.experts is None
+                       else f"{model_id}[layers={args.layers or 'all'}, experts={args.experts or 'all'}]",
                        "global_batch": args.seqs_per_gpu * N, "seq_len": T,
                        "parallelism": f"fsdp{N}" if par == "fsdp" else f"ep{N}+fsdp{N}",
                        "micro_batch_per_gpu": micro, "grad_accum": accum, "optimizer": "AdamW fp32 master",

@@ -130,7 +130,7 @@ int ob_symm_barrier(void* const* flag_ptrs, int world, int rank, unsigned epoch,
   return 0;
 }
 
-// ---- pull all-gather: segs is a device array of CopySeg (6 x int64 words each)
+// ---- pull all-gather: segs is a device array of CopySeg (4 x int64 words each)
 int ob_allgather_pull(void* const* shard_ptrs, int world, void* dst, const void* segs, int nsegs,
                       cudaStream_t stream) {
   if (world > kMaxRanks) return 6003;
@@ -178,6 +178,7 @@ __global__ void ep_push_kernel(PeerPtrs dst, const bf16* __restrict__ src, const
   const long long p = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (p >= P) return;
+  if (dst_row[p] < 0) return;   // dropped pair (receive buffer overflow)
   const uint4* s = reinterpret_cast<const uint4*>(src + (long long)src_row[p] * D);
   uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst.p[dst_rank[p]]) + (long long)dst_row[p] * D);
   const int nv = D >> 3;
@@ -221,7 +222,7 @@ __global__ void ep_pull_kernel(PeerPtrs src, bf16* __restrict__ out, const int* 
     for (int j = 0; j < k; ++j) {
       const long long p = t * k + j;
       float dot = 0.f;
-      if (i < nv) {
+      if (i < nv && src_row[p] >= 0) {
         const uint4 q = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(src.p[src_rank[p]]) +
                                                        (long long)src_row[p] * D)[i];
         const float wj = w ? w[p] : 1.f;

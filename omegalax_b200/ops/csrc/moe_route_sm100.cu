@@ -164,6 +164,53 @@ __global__ void moe_dest_kernel(const int* __restrict__ idx, const int* __restri
   dest[p] = offsets[e] + atomicAdd(cursor + e, 1);
 }
 
+// Expert-parallel plan.  allc [W][E] holds every rank's pick counts.  For expert e owned by rank
+// e / El: start[e] = (first row of e inside its owner's receive buffer) + (rows that lower ranks
+// send to e); offsets_local [El+1] are the padded segment boundaries of this rank's own experts;
+// overflow is set when any owner would need more than `capacity` rows.  One CTA, E <= 1024.
+__global__ void ep_plan_kernel(const int* __restrict__ allc, int* __restrict__ start, int* __restrict__ cursor,
+                               int* __restrict__ offsets_local, int* __restrict__ overflow, int W, int E, int El,
+                               int rank, int pad, int capacity) {
+  __shared__ int sh[1024];
+  const int t = threadIdx.x;
+  int tot = 0, before = 0;
+  if (t < E)
+    for (int r = 0; r < W; ++r) {
+      const int c = allc[r * E + t];
+      if (r < rank) before += c;
+      tot += c;
+    }
+  const int padded = (t < E) ? (tot + pad - 1) / pad * pad : 0;
+  sh[t] = padded;
+  __syncthreads();
+  for (int o = 1; o < 1024; o <<= 1) {
+    const int add = (t >= o) ? sh[t - o] : 0;
+    __syncthreads();
+    sh[t] += add;
+    __syncthreads();
+  }
+  if (t < E) {
+    const int owner_first = (t / El) * El;
+    const int s0 = owner_first > 0 ? sh[owner_first - 1] : 0;
+    start[t] = sh[t] - padded - s0 + before;
+    cursor[t] = 0;
+    if (t / El == rank) offsets_local[t - owner_first + 1] = sh[t] - s0;
+    if (t % El == El - 1 && sh[t] - s0 > capacity) atomicExch(overflow, 1);
+  }
+  if (t == 0) offsets_local[0] = 0;
+}
+
+__global__ void ep_dest_kernel(const int* __restrict__ idx, const int* __restrict__ start, int* __restrict__ cursor,
+                               int* __restrict__ dst_rank, int* __restrict__ dst_row, long long P, int El,
+                               int capacity) {
+  const long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (p >= P) return;
+  const int e = idx[p];
+  dst_rank[p] = e / El;
+  const int row = start[e] + atomicAdd(cursor + e, 1);
+  dst_row[p] = row < capacity ? row : -1;   // beyond the receive buffer: dropped (the overflow flag is set)
+}
+
 }  // namespace ob
 
 using namespace ob;
@@ -205,6 +252,30 @@ int ob_moe_plan(const int* idx, int* counts, int* offsets, int* cursor, int* des
   OB_CHECK_LAUNCH();
   if (P > 0) {
     moe_dest_kernel<<<(unsigned)((P + 255) / 256), 256, 0, s>>>(idx, offsets, cursor, dest, P);
+    OB_CHECK_LAUNCH();
+  }
+  return 0;
+}
+
+// counts[E] = histogram of idx (zeroed here first)
+int ob_moe_count(const int* idx, int* counts, long long P, int E, cudaStream_t s) {
+  cudaMemsetAsync(counts, 0, sizeof(int) * E, s);
+  if (P > 0) {
+    moe_count_kernel<<<(unsigned)((P + 255) / 256), 256, 0, s>>>(idx, counts, P);
+    OB_CHECK_LAUNCH();
+  }
+  return 0;
+}
+
+// scratch: 2*E ints (start, cursor).  overflow is a sticky device flag.
+int ob_ep_plan(const int* idx, const int* allc, int* scratch, int* offsets_local, int* dst_rank, int* dst_row,
+               int* overflow, long long P, int W, int E, int rank, int pad, int capacity, cudaStream_t s) {
+  if (E > 1024 || E <= 0 || W <= 0 || E % W) return 6001;
+  const int El = E / W;
+  ep_plan_kernel<<<1, 1024, 0, s>>>(allc, scratch, scratch + E, offsets_local, overflow, W, E, El, rank, pad, capacity);
+  OB_CHECK_LAUNCH();
+  if (P > 0) {
+    ep_dest_kernel<<<(unsigned)((P + 255) / 256), 256, 0, s>>>(idx, scratch, scratch + E, dst_rank, dst_row, P, El, capacity);
     OB_CHECK_LAUNCH();
   }
   return 0;

@@ -41,6 +41,8 @@ _SIGS = {
     "ob_layernorm_bwd": [P, P, P, P, P, P, P, P, L, I, P],
     "ob_router_topk": [P, P, P, P, P, L, I, I, I, P],
     "ob_router_topk_bwd": [P, P, P, P, P, P, L, I, I, I, P],
+    "ob_moe_count": [P, P, L, I, P],
+    "ob_ep_plan": [P, P, P, P, P, P, P, L, I, I, I, I, I, P],
     "ob_moe_plan": [P, P, P, P, P, L, I, I, I, P],
     "ob_gdn_fwd": [P] * 10 + [I] * 6 + [P],
     "ob_gdn_bwd": [P] * 15 + [I] * 6 + [P],

@@ -100,8 +100,8 @@ class _GroupedLinearFn(torch.autograd.Function):
     """y[rows of e] = x[rows of e] @ w[e].T for w [E,N,K]."""
 
     @staticmethod
-    def forward(ctx, x, w, offsets):
-        y = K.gemm_grouped(x, w, offsets)
+    def forward(ctx, x, w, offsets, out=None):
+        y = K.gemm_grouped(x, w, offsets, out=out)
         ctx.save_for_backward(x, w, offsets)
         ctx.w_ref = w
         return y
@@ -120,18 +120,19 @@ class _GroupedLinearFn(torch.autograd.Function):
                 dwf = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
                 K.gemm_grouped_wgrad(dy, x, offsets, dwf, accumulate=False)
                 dw = dwf.to(w.dtype)
-        return dx, dw, None
+        return dx, dw, None, None
 
 
-def grouped_linear(x, w, offsets):
-    return _GroupedLinearFn.apply(x, w, offsets)
+def grouped_linear(x, w, offsets, out=None):
+    return _GroupedLinearFn.apply(x, w, offsets, out)
 
 
-def expert_mlp_permuted(xp, w_gate_up, w_down, offsets):
-    """SwiGLU expert MLP on rows already grouped by expert (padded layout)."""
+def expert_mlp_permuted(xp, w_gate_up, w_down, offsets, out=None):
+    """SwiGLU expert MLP on rows already grouped by expert (padded layout).  ``out`` may name
+    the buffer that receives the result (e.g. the exchange buffer the combine step reads)."""
     gu = grouped_linear(xp, w_gate_up, offsets)
     act = Fn.swiglu(gu)
-    return grouped_linear(act, w_down, offsets)
+    return grouped_linear(act, w_down, offsets, out)
 
 
 # ---- row movement on one GPU: the dispatch / combine kernels of the expert-parallel path with a

@@ -151,9 +151,14 @@ class TrainEngine:
                     slot = ParamSlot(f"{uname}.{mi}.{pname}", p, shape, numel, sharded, sn, shard_off, full_off, m, pname)
                     owner = m.get_submodule(pname.rsplit(".", 1)[0]) if "." in pname else m
                     slot.tp_sharded = bool(getattr(owner, "tp_sharded", False))
+                    # expert tensors under expert parallelism are never gathered: they take no room
+                    # in the gathered-layer buffers
+                    slot.ep = bool(self.expert_parallel and sharded
+                                   and pname.rsplit(".", 1)[-1] in ("experts_gate_up", "experts_down"))
                     slots.append(slot)
                     shard_off += _align(sn)
-                    full_off += _align(numel)
+                    if not slot.ep:
+                        full_off += _align(numel)
             self.units.append(Unit(uname, mods, slots, shard_off, full_off))
         base = 0
         for u in self.units:
@@ -558,7 +563,8 @@ class _LazyEP:
             from .ep import ExpertParallel
 
             eng._ep = ExpertParallel(eng.group, self.module.E, x.shape[1], x.shape[0], idx.shape[1],
-                                     capacity_factor=eng.ep_capacity_factor, dtype=x.dtype)
+                                     capacity_factor=eng.ep_capacity_factor, dtype=x.dtype,
+                                     reuse_buffers=(eng.remat == "full"))
             eng._ep.max_tokens = x.shape[0]
         return eng._ep.moe_mlp(x, w, idx, gate_up_local, down_local)
 

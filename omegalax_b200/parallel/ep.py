@@ -84,9 +84,35 @@ def build_plan(idx, E: int, W: int, rank: int, group, capacity: int) -> Plan:
     return p
 
 
+def build_plan_device(idx, E: int, W: int, rank: int, group, capacity: int, overflow_flag, src_tok) -> Plan:
+    """Same plan as ``build_plan`` from three kernel launches and one count all-gather.  Rows of
+    one sender inside an expert segment are assigned by an atomic cursor, so their order (not
+    their set) can differ from run to run."""
+    M, k = idx.shape
+    dev = idx.device
+    idx32 = idx.reshape(-1).to(torch.int32)
+    allc = torch.empty(W, E, dtype=torch.int32, device=dev)
+    mine = allc[rank]
+    lib.call("ob_moe_count", idx32.data_ptr(), mine.data_ptr(), idx32.numel(), E, lib.stream_ptr())
+    if W > 1:
+        dist.all_gather_into_tensor(allc.view(-1), mine.clone(), group=group)
+    p = Plan()
+    scratch = torch.empty(2 * E, dtype=torch.int32, device=dev)
+    p.offsets_local = torch.empty(E // W + 1, dtype=torch.int32, device=dev)
+    p.dst_rank = torch.empty(M * k, dtype=torch.int32, device=dev)
+    p.dst_row = torch.empty(M * k, dtype=torch.int32, device=dev)
+    lib.call("ob_ep_plan", idx32.data_ptr(), allc.data_ptr(), scratch.data_ptr(), p.offsets_local.data_ptr(),
+             p.dst_rank.data_ptr(), p.dst_row.data_ptr(), overflow_flag.data_ptr(), M * k, W, E, rank, PAD, capacity,
+             lib.stream_ptr())
+    p.src_tok = src_tok
+    p.M, p.k = M, k
+    p.overflow = None
+    return p
+
+
 class ExpertParallel:
     def __init__(self, group, num_experts: int, hidden: int, max_tokens: int, top_k: int, *,
-                 capacity_factor: float = 2.0, dtype=torch.bfloat16):
+                 capacity_factor: float = 2.0, dtype=torch.bfloat16, reuse_buffers: bool = False):
         self.group = group
         self.W = dist.get_world_size(group) if group is not None else 1
         self.rank = dist.get_rank(group) if group is not None else 0
@@ -103,7 +129,17 @@ class ExpertParallel:
         self.buf_gin = symm.SymmetricBuffer(nbytes, group)
         self.barrier = symm.DeviceBarrier(group)
         self.dtype = dtype
-        self.overflow_flag = torch.zeros(1, dtype=torch.bool, device="cuda")
+        self.overflow_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self._src_tok = {}
+        # With layer-by-layer rematerialisation a layer's exchange buffers are consumed before the
+        # next layer touches them, so the expert MLP can read and write them in place.  The
+        # buffers start zeroed and only ever hold finite activations afterwards: padding rows may
+        # then carry stale values, which is harmless because the gradient of the expert output is
+        # always zero on padding rows (so no weight gradient sees them).
+        self.reuse_buffers = reuse_buffers
+        for b in (self.buf_in, self.buf_out, self.buf_gout, self.buf_gin):
+            self.local(b).zero_()
+        self.barrier()
 
     def local(self, buf: symm.SymmetricBuffer) -> torch.Tensor:
         return buf.view(self.dtype, self.capacity * self.D).view(self.capacity, self.D)
@@ -126,22 +162,28 @@ class ExpertParallel:
 
     def moe_mlp(self, x, weights, idx, w_gate_up_local, w_down_local):
         """x [M,D] local tokens; weights/idx [M,k]; expert weights are this rank's E/W experts."""
-        plan = build_plan(idx, self.E, self.W, self.rank, self.group, self.capacity)
-        self.overflow_flag |= plan.overflow
+        key = tuple(idx.shape)
+        st = self._src_tok.get(key)
+        if st is None:
+            st = torch.arange(idx.shape[0], device=idx.device, dtype=torch.int32).repeat_interleave(idx.shape[1])
+            self._src_tok[key] = st
+        plan = build_plan_device(idx, self.E, self.W, self.rank, self.group, self.capacity, self.overflow_flag, st)
         xp = _Dispatch.apply(x.contiguous(), self, plan)
-        yp = moe_ops.expert_mlp_permuted(xp, w_gate_up_local, w_down_local, plan.offsets_local)
+        out = self.local(self.buf_out) if self.reuse_buffers else None
+        yp = moe_ops.expert_mlp_permuted(xp, w_gate_up_local, w_down_local, plan.offsets_local, out)
         return _Combine.apply(yp, weights.contiguous().float(), self, plan)
 
 
 class _Dispatch(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, ep: ExpertParallel, plan: Plan):
-        ep.local(ep.buf_in).zero_()           # padding rows must be zero for the grouped GEMMs
-        ep.barrier()                          # every rank has cleared its buffer before peers write
+        if not ep.reuse_buffers:
+            ep.local(ep.buf_in).zero_()       # padding rows start from zero
+        ep.barrier()                          # every rank is done with the previous contents
         ep.push(ep.buf_in, x, plan)
         ep.barrier()                          # all rows have landed
         ctx.ep, ctx.plan = ep, plan
-        return ep.local(ep.buf_in).clone()
+        return ep.local(ep.buf_in) if ep.reuse_buffers else ep.local(ep.buf_in).clone()
 
     @staticmethod
     def backward(ctx, d_xp):
@@ -156,7 +198,9 @@ class _Dispatch(torch.autograd.Function):
 class _Combine(torch.autograd.Function):
     @staticmethod
     def forward(ctx, yp, weights, ep: ExpertParallel, plan: Plan):
-        ep.local(ep.buf_out).copy_(yp)
+        ctx.in_place = yp.data_ptr() == ep.local(ep.buf_out).data_ptr()
+        if not ctx.in_place:
+            ep.local(ep.buf_out).copy_(yp)
         ep.barrier()
         y, _ = ep.pull(ep.buf_out, plan, weights=weights.reshape(-1))
         ep.barrier()
@@ -170,12 +214,13 @@ class _Combine(torch.autograd.Function):
         weights, yp = ctx.saved_tensors
         dy = dy.contiguous()
         # gradient of the routing weights: <dy[token], expert output row>
-        ep.local(ep.buf_out).copy_(yp)
-        ep.local(ep.buf_gout).zero_()
+        if not ctx.in_place:                  # in place: the recomputation has just rewritten it
+            ep.local(ep.buf_out).copy_(yp)
+        ep.local(ep.buf_gout).zero_()         # padding rows of the output gradient must be zero
         ep.barrier()
         _, dots = ep.pull(ep.buf_out, plan, weights=None, out=False, grad=dy)
         # gradient of the expert outputs: weight * dy[token], pushed to the owners
         ep.push(ep.buf_gout, dy, plan, scale=weights.reshape(-1))
         ep.barrier()
-        d_yp = ep.local(ep.buf_gout).clone()
-        return d_yp, dots.view_as(weights), None, None
+        # consumed by the expert MLP's backward before any other layer writes this buffer
+        return ep.local(ep.buf_gout), dots.view_as(weights), None, None
