@@ -25,6 +25,13 @@
 // residual added before the store, and a peer-reduce mode in which row blocks of C are
 // owned by other GPUs and the tile is added there with vector red.global.add (used by the
 // fused GEMM -> reduce-scatter paths over NVLink peer memory).
+//
+// Gather mode (all-gather -> GEMM in one launch): one K-major operand is spread over the GPUs in
+// equal row chunks.  The first few CTAs of the grid do not compute: one thread of each streams
+// its share of every chunk from the owner's memory (bulk copies, peer memory included) through a
+// ring of shared-memory buffers into this GPU's full operand and bumps a per-chunk counter.  The
+// TMA producer of a computing CTA waits (bounded) for the counter of the chunk its tile reads;
+// tiles are visited own chunk first, then in the order the chunks arrive.
 #include "host_utils.h"
 #include "sm100_common.cuh"
 
@@ -53,6 +60,14 @@ struct GemmArgs {
   // out_mode 3: rows [r*rows_per_peer, (r+1)*rows_per_peer) live on peer r at peer_ptr[r]
   float* peer_ptr[kMaxPeers];
   int rows_per_peer;
+  // gather mode: ag_side 1 = rows of A, 2 = rows of B are assembled inside this launch
+  int ag_side, ag_world, ag_rank, ag_copy_ctas;
+  int ag_rows_per_rank;            // multiple of the tile extent on that side
+  const void* ag_src[kMaxPeers];   // every rank's chunk (contiguous rows)
+  void* ag_dst;                    // this GPU's full operand (what the tensor map covers)
+  long long ag_chunk_bytes;
+  uint32_t* ag_flags;              // [world] counters, only ever incremented
+  uint32_t ag_target;              // value a chunk's counter has when the chunk is complete
   int* status;
 };
 
@@ -86,13 +101,30 @@ __device__ __forceinline__ TileInfo get_tile(const GemmArgs& p, int t) {
   if (p.mode == 0) {
     // grouped raster: 8 row blocks share a sweep over the column blocks for L2 reuse
     const int GM = 8;
-    int per_group = GM * p.num_n_blocks;
-    int g = t / per_group;
-    int first_m = g * GM;
-    int gm = min(GM, p.num_m_blocks - first_m);
-    int r = t - g * per_group;
-    int mb = first_m + (r % gm);
-    int nb = r / gm;
+    int mb, nb;
+    if (p.ag_side != 2) {
+      int per_group = GM * p.num_n_blocks;
+      int g = t / per_group;
+      int first_m = g * GM;
+      int gm = min(GM, p.num_m_blocks - first_m);
+      int r = t - g * per_group;
+      mb = first_m + (r % gm);
+      nb = r / gm;
+      if (p.ag_side == 1) {  // own chunk of A first, then the chunks in arrival order
+        mb += p.ag_rank * (p.ag_rows_per_rank / BM);
+        if (mb >= p.num_m_blocks) mb -= p.num_m_blocks;
+      }
+    } else {  // B is gathered: sweep the row blocks for 8 column blocks of one chunk at a time
+      int per_group = GM * p.num_m_blocks;
+      int g = t / per_group;
+      int first_n = g * GM;
+      int gn = min(GM, p.num_n_blocks - first_n);
+      int r = t - g * per_group;
+      nb = first_n + (r % gn);
+      mb = r / gn;
+      nb += p.ag_rank * (p.ag_rows_per_rank / BN);
+      if (nb >= p.num_n_blocks) nb -= p.num_n_blocks;
+    }
     ti.a_row0 = mb * BM;
     ti.b_row0 = nb * BN;
     ti.c_row0 = mb * BM;
@@ -152,10 +184,63 @@ struct GemmSmem {
   static constexpr int kTotal = kBarOff + 256 + 1024;  // barriers + alignment slack
 };
 
+// Gather-mode copy role (one thread): chunk by chunk, own chunk first, this CTA's share of every
+// chunk travels owner -> shared-memory ring -> local full operand in 32 KB bulk copies.
+__device__ __forceinline__ void ag_copy_role(const GemmArgs& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag) {
+  constexpr int kPiece = 32768;
+  constexpr int kRing = 6;      // ring slots
+  constexpr int kLoads = 4;     // loads in flight; the other two slots may still be draining to memory
+  for (int i = 0; i < kRing; ++i) mbar_init(&bars[i], 1);
+  *abort_flag = 0;
+  mbar_fence_init();
+  const int W = p.ag_world, C = p.ag_copy_ctas, cta = blockIdx.x;
+  const long long per = ((p.ag_chunk_bytes + C - 1) / C + 15) & ~15ll;
+  const long long lo = (long long)cta * per;
+  const long long hi = lo + per < p.ag_chunk_bytes ? lo + per : p.ag_chunk_bytes;
+  const long long npc = hi > lo ? (hi - lo + kPiece - 1) / kPiece : 0;
+  if (npc == 0) {
+    for (int r = 0; r < W; ++r) red_release_gpu_add(p.ag_flags + r, 1);
+    return;
+  }
+  const long long total = npc * W;
+  long long head = 0, tail = 0;
+  bool ok = true;
+  while (tail < total && ok) {
+    while (head < total && head - tail < kLoads) {
+      // slot head % kRing was last read by store head - kRing; stores 0 .. tail-1 are committed, so at
+      // most tail-1 - (head-kRing) >= kRing - kLoads of the newest ones may still be pending
+      if (head >= kRing) tma_store_wait_read<kRing - kLoads>();
+      const int r = (p.ag_rank + 1 + (int)(head / npc)) % W;   // own chunk last: nobody waits for it
+      const long long off = lo + (head % npc) * kPiece;
+      const uint32_t n = (uint32_t)(hi - off < kPiece ? hi - off : kPiece);
+      const int slot = (int)(head % kRing);
+      mbar_expect_tx(&bars[slot], n);
+      bulk_g2s(smem + slot * kPiece, (const char*)p.ag_src[r] + off, n, &bars[slot]);
+      ++head;
+    }
+    const int slot = (int)(tail % kRing);
+    ok = mbar_wait(&bars[slot], (uint32_t)((tail / kRing) & 1), abort_flag, p.status, OB_ERR_WAIT_MISC);
+    if (!ok) break;
+    const int r = (p.ag_rank + 1 + (int)(tail / npc)) % W;
+    const long long pi = tail % npc;
+    const long long off = lo + pi * kPiece;
+    const uint32_t n = (uint32_t)(hi - off < kPiece ? hi - off : kPiece);
+    bulk_s2g((char*)p.ag_dst + (long long)r * p.ag_chunk_bytes + off, smem + slot * kPiece, n);
+    tma_store_commit();
+    if (pi == npc - 1) {  // this CTA's share of chunk r is in place
+      tma_store_wait_all<0>();
+      __threadfence();
+      red_release_gpu_add(p.ag_flags + r, 1);
+    }
+    ++tail;
+  }
+  tma_store_wait_all<0>();
+}
+
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmArgs p) {
+                 const __grid_constant__ CUtensorMap tmL, const GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits.
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -169,6 +254,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+
+  const int ncopy = p.ag_side ? p.ag_copy_ctas : 0;
+  if ((int)blockIdx.x < ncopy) {  // gather mode: this CTA only moves data
+    if (threadIdx.x == 0) ag_copy_role(p, smem, full_bar, abort_flag);
+    return;
+  }
+  const int cta0 = (int)blockIdx.x - ncopy;
+  const int cta_step = (int)gridDim.x - ncopy;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
@@ -196,12 +289,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
+      if (p.ag_side) tma_prefetch_desc(&tmL);
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t ag_seen = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      for (int t = cta0; t < p.total_tiles && ok; t += cta_step) {
         TileInfo ti = get_tile<BN>(p, t);
         if (!ti.valid) continue;
+        bool ag_local = false;   // tile of this GPU's own chunk: read it where it already is
+        int ag_row = 0;
+        if (p.ag_side) {  // the chunk this tile reads must have arrived
+          const int row0 = p.ag_side == 1 ? ti.a_row0 : ti.b_row0;
+          const int ch = row0 / p.ag_rows_per_rank;
+          ag_local = ch == p.ag_rank;
+          ag_row = row0 - ch * p.ag_rows_per_rank;
+          if (!ag_local && !((ag_seen >> ch) & 1u)) {
+            ok = flag_wait_ge<false>(p.ag_flags + ch, p.ag_target, OB_WAIT_CYCLES, p.status, OB_ERR_WAIT_FLAG);
+            if (!ok) {
+              *abort_flag = 1;
+              break;
+            }
+            fence_proxy_async_all();  // written through the generic / bulk path, read by TMA next
+            ag_seen |= 1u << ch;
+          }
+        }
         for (int k0 = ti.k_begin; k0 < ti.k_end; k0 += BK) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_EMPTY);
           if (!ok) break;
@@ -209,14 +321,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sb = sa + L::kABytes;
           mbar_expect_tx(&full_bar[stage], L::kStageBytes);
           if (!A_MN) {
-            tma_load_2d(sa, &tmA, &full_bar[stage], k0, ti.a_row0);
+            if (ag_local && p.ag_side == 1) tma_load_2d(sa, &tmL, &full_bar[stage], k0, ag_row);
+            else tma_load_2d(sa, &tmA, &full_bar[stage], k0, ti.a_row0);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
               tma_load_2d(sa + j * (BK * 128), &tmA, &full_bar[stage], ti.a_row0 + j * 64, k0);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &tmB, &full_bar[stage], k0, ti.b_row0);
+            if (ag_local && p.ag_side == 2) tma_load_2d(sb, &tmL, &full_bar[stage], k0, ag_row);
+            else tma_load_2d(sb, &tmB, &full_bar[stage], k0, ti.b_row0);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
@@ -239,7 +353,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      for (int t = cta0; t < p.total_tiles && ok; t += cta_step) {
         TileInfo ti = get_tile<BN>(p, t);
         if (!ti.valid) continue;
         ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status,
@@ -283,7 +397,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+    for (int t = cta0; t < p.total_tiles && ok; t += cta_step) {
       TileInfo ti = get_tile<BN>(p, t);
       if (!ti.valid) continue;
       ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL);
@@ -416,6 +530,12 @@ static int launch_gemm(const void* A, const void* B, const GemmArgs& args, long 
   if (!B_MN) e = make_tmap_2d(&tmB, B, b_rows, b_cols, ldb, BN, BK);
   else e = make_tmap_2d(&tmB, B, b_rows, b_cols, ldb, BK, 64);
   if (e) return 3000 + e;
+  CUtensorMap tmL = tmA;  // gather mode: this GPU's own chunk of the gathered operand, in place
+  if (args.ag_side) {
+    e = make_tmap_2d(&tmL, args.ag_src[args.ag_rank], args.ag_rows_per_rank, args.K, args.K,
+                     args.ag_side == 1 ? BM : BN, BK);
+    if (e) return 3500 + e;
+  }
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -426,7 +546,13 @@ static int launch_gemm(const void* A, const void* B, const GemmArgs& args, long 
   }
   int grid = args.total_tiles < num_sms() ? args.total_tiles : num_sms();
   if (grid <= 0) return 0;
-  kern<<<grid, kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(tmA, tmB, args);
+  if (args.ag_side) {  // copy CTAs come first in the grid; every CTA is resident from the start
+    int compute = num_sms() - args.ag_copy_ctas;
+    if (compute > args.total_tiles) compute = args.total_tiles;
+    if (compute <= 0) return 6006;
+    grid = compute + args.ag_copy_ctas;
+  }
+  kern<<<grid, kGemmThreads, GemmSmem<BN>::kTotal, stream>>>(tmA, tmB, tmL, args);
   OB_CHECK_LAUNCH();
   return 0;
 }
@@ -554,6 +680,42 @@ int ob_gemm_bf16_grouped_wgrad(const void* A, const void* B, void* C, const int*
   g.C = C; g.ldc = K; g.c_group_stride = (long long)N * K; g.out_mode = out_mode;
   g.status = status;
   return dispatch(bn, 1, 1, A, B, g, max_rows, N, lda, max_rows, K, ldb, stream);
+}
+
+// All-gather -> GEMM in one launch.  Both operands K-major: C[M,N] = A[M,K] B[N,K]^T (+ residual).
+// side 1: A's rows are spread over `world` GPUs (rows_per_rank each, contiguous [rows, K] chunks at
+// src_ptrs[r]); side 2: B's rows.  The gathered operand is assembled in `full` (this GPU's memory,
+// [rows_per_rank * world, K] contiguous), which stays valid after the launch.  flags: `world`
+// device counters owned by the caller that only grow; target = their common value before this
+// call + copy_ctas.  Peers' chunks must be complete before any rank launches (caller's barrier).
+int ob_gemm_bf16_ag(const void* other, void* full, void* const* src_ptrs, void* C, const void* residual, int M, int N,
+                    int K, long long ldc, long long ldr, int out_mode, int side, int world, int rank,
+                    int rows_per_rank, unsigned* flags, unsigned target, int copy_ctas, int* status,
+                    cudaStream_t stream) {
+  if (world > kMaxPeers || world <= 0 || copy_ctas <= 0 || copy_ctas > 32) return 6003;
+  if (side != 1 && side != 2) return 6005;
+  if (K & 7) return 6001;
+  int bn = 256;
+  if (side == 2 && rows_per_rank % 256) bn = 128;
+  if (side == 1 ? (rows_per_rank % BM) : (rows_per_rank % bn)) return 6007;
+  if ((long long)rows_per_rank * world != (side == 1 ? M : N)) return 6007;
+  GemmArgs g = {};
+  g.M = M; g.N = N; g.K = K; g.mode = 0;
+  g.num_m_blocks = (M + BM - 1) / BM;
+  g.num_n_blocks = (N + bn - 1) / bn;
+  g.total_tiles = g.num_m_blocks * g.num_n_blocks;
+  g.C = C; g.ldc = ldc; g.out_mode = out_mode;
+  g.residual = (const bf16*)residual; g.ldr = ldr;
+  g.ag_side = side; g.ag_world = world; g.ag_rank = rank; g.ag_copy_ctas = copy_ctas;
+  g.ag_rows_per_rank = rows_per_rank;
+  for (int i = 0; i < world; ++i) g.ag_src[i] = src_ptrs[i];
+  g.ag_dst = full;
+  g.ag_chunk_bytes = (long long)rows_per_rank * K * 2;
+  g.ag_flags = flags; g.ag_target = target;
+  g.status = status;
+  const void* A = side == 1 ? full : other;
+  const void* B = side == 2 ? full : other;
+  return dispatch(bn, 0, 0, A, B, g, M, K, K, N, K, K, stream);
 }
 
 }  // extern "C"

@@ -91,6 +91,42 @@ def gemm_peer_reduce(a, b, peer_ptrs, rows_per_peer: int, ldc: int, *, a_mn=Fals
           int(b_mn), st.data_ptr(), lib.stream_ptr())
 
 
+def ag_copy_ctas(M: int, N: int, Kd: int, total_bytes: float) -> int:
+    """Copy CTAs for the gather mode.  The tiles walk the chunks in arrival order starting with this
+    GPU's own chunk (read in place), so the chunks must arrive at the rate the tiles consume them:
+    the whole operand within ~80 % of the GEMM's duration, at ~45 GB/s per copy thread (128 KB in
+    flight)."""
+    t_gemm = 2.0 * M * N * Kd / 1.1e15
+    need = total_bytes / max(0.8 * t_gemm, 1e-6) / 45e9
+    return int(min(16, max(2, -(-need // 1))))
+
+
+def gemm_ag(other, full, src_ptrs, *, side: int, rank: int, rows_per_rank: int, flags, target: int,
+            copy_ctas: int = 8, residual=None, out=None):
+    """All-gather -> GEMM in one launch: y = A @ B^T with both operands [rows, K] row-major.
+    side 1: A = ``full`` [rows_per_rank * W, K] is assembled from the ranks' row chunks at
+    ``src_ptrs`` while the tiles run; side 2: B likewise.  ``other`` is the operand that is
+    already complete.  ``flags`` (uint32 [W]) only grow: ``target`` is their value after this call."""
+    import ctypes
+
+    W = len(src_ptrs)
+    Kd = full.shape[1]
+    if side == 1:
+        M, N = full.shape[0], other.shape[0]
+    else:
+        M, N = other.shape[0], full.shape[0]
+    other = _row_major_2d(other)
+    assert other.stride(0) == Kd and full.is_contiguous()
+    if out is None:
+        out = torch.empty(M, N, dtype=bf16, device=full.device)
+    arr = (ctypes.c_void_p * W)(*src_ptrs)
+    st = lib.status_tensor(full.device)
+    _call("ob_gemm_bf16_ag", other.data_ptr(), full.data_ptr(), ctypes.cast(arr, ctypes.c_void_p), out.data_ptr(),
+          lib.ptr(residual), M, N, Kd, out.stride(0), residual.stride(0) if residual is not None else 0, 0, side, W,
+          rank, rows_per_rank, flags.data_ptr(), int(target) & 0xFFFFFFFF, copy_ctas, st.data_ptr(), lib.stream_ptr())
+    return out
+
+
 def gemm_grouped(a, b, group_offsets, *, b_mn: bool = False, out=None, out_dtype=bf16):
     """Ragged-row grouped GEMM.  a: [R,K] rows grouped by ``group_offsets`` (int32 [G+1],
     multiples of 128, R % 128 == 0); b: [G,N,K] (or [G,K,N] when b_mn)."""

@@ -19,6 +19,8 @@ LIB_PATH = _HERE / "libomegalax_b200.so"
 _lib = None
 _status = {}
 
+from ctypes import c_uint
+
 P = c_void_p
 I = c_int
 L = c_longlong
@@ -26,6 +28,7 @@ F = c_float
 
 _SIGS = {
     "ob_gemm_bf16": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P, P],
+    "ob_gemm_bf16_ag": [P, P, P, P, P, I, I, I, L, L, I, I, I, I, I, P, c_uint, I, P, P],
     "ob_gemm_bf16_peer_reduce": [P, P, P, I, I, I, I, I, L, L, L, I, I, P, P],
     "ob_gemm_bf16_grouped": [P, P, P, P, I, I, I, I, L, L, I, I, P, P],
     "ob_gemm_bf16_grouped_wgrad": [P, P, P, P, I, I, I, I, L, L, I, P, P],

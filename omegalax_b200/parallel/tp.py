@@ -47,6 +47,10 @@ class TPContext:
         self._gather_buf = None
         self._rs_buf = None
         self._barrier = None
+        self._ag_bufs = [None, None]   # alternating staging buffers of the fused gather + GEMM
+        self._ag_calls = 0
+        self._ag_flags = None
+        self._ag_count = 0             # value of the chunk counters after the calls issued so far
 
     # ---- peer-memory resources (allocated on first use, sized by the largest request)
     def _symm(self):
@@ -61,6 +65,21 @@ class TPContext:
             if self._barrier is None:
                 self._barrier = self._symm().DeviceBarrier(self.group)
         return self._gather_buf
+
+    def ag_stage(self, nbytes: int):
+        """Staging buffer for this call of the fused gather + GEMM, the per-chunk counters and the
+        value they reach when this call's chunks are complete.  Two buffers alternate: a buffer is
+        rewritten two calls later, and the barrier of the call in between proves that every peer
+        has finished reading it."""
+        i = self._ag_calls & 1
+        if self._ag_bufs[i] is None or self._ag_bufs[i].nbytes < nbytes:
+            self._ag_bufs[i] = self._symm().SymmetricBuffer(nbytes, self.group)
+        if self._barrier is None:
+            self._barrier = self._symm().DeviceBarrier(self.group)
+        if self._ag_flags is None:
+            self._ag_flags = torch.zeros(self.size, dtype=torch.int32, device="cuda")
+        self._ag_calls += 1
+        return self._ag_bufs[i], self._ag_flags
 
     def rs_buffer(self, rows_local: int, cols: int):
         n = rows_local * cols * 4
@@ -170,8 +189,58 @@ class _RowParallelLinearFn(torch.autograd.Function):
         return dx, dw, (g if ctx.has_res else None), None
 
 
+class _ColumnParallelLinearFn(torch.autograd.Function):
+    """y[M, N/tp] = all_gather_rows(x[M/tp, K]) @ w[N/tp, K]^T with the gather running inside the
+    GEMM launch (copy CTAs stream the peers' row chunks in while the tiles of the chunks that
+    have arrived are computed).  Backward: the input gradient GEMM reduce-scatters in its epilogue."""
+
+    @staticmethod
+    def forward(ctx, x, w, tp: TPContext):
+        m, Kd = x.shape
+        stage, flags = tp.ag_stage(m * Kd * 2)
+        stage.view(x.dtype, m * Kd).copy_(x.reshape(-1))
+        tp._barrier()                                   # every rank's chunk is in its staging buffer
+        full = torch.empty(m * tp.size, Kd, dtype=x.dtype, device=x.device)
+        ctas = K.ag_copy_ctas(m * tp.size, w.shape[0], Kd, tp.size * m * Kd * 2.0)
+        tp._ag_count += ctas
+        y = K.gemm_ag(w, full, stage.peer_ptr_list(0), side=1, rank=tp.rank, rows_per_rank=m, flags=flags,
+                      target=tp._ag_count, copy_ctas=ctas)
+        ctx.save_for_backward(full, w)
+        ctx.tp, ctx.w_ref = tp, w
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        full, w = ctx.saved_tensors
+        tp = ctx.tp
+        dy = dy.contiguous()
+        M, Kd = full.shape
+        m = M // tp.size
+        buf = tp.rs_buffer(m, Kd)
+        acc = buf.view(torch.float32, m * Kd)
+        acc.zero_()
+        tp._barrier()
+        K.gemm_peer_reduce(dy, w, buf.peer_ptr_list(0), m, Kd, b_mn=True)   # dx rows land on their owners
+        tp._barrier()
+        dx = acc.view(m, Kd).to(dy.dtype)
+        mg = getattr(ctx.w_ref, "main_grad", None)
+        pg = getattr(ctx.w_ref, "peer_grad", None)
+        dw = None
+        if pg is not None:
+            K.gemm_peer_reduce(dy, full, pg[0], pg[1], pg[2], a_mn=True, b_mn=True)
+        elif mg is not None:
+            K.gemm(dy, full, a_mn=True, b_mn=True, out=mg, accumulate=True)
+        else:
+            dw = K.gemm(dy, full, a_mn=True, b_mn=True)
+        return dx, dw, None
+
+
 def column_parallel_linear(x_local, w_local, tp: TPContext | None):
     """all-gather rows -> projection with this rank's output columns."""
+    if tp is not None and tp.size > 1 and tp.transport == "p2p" and Fn.use_kernels(x_local) \
+            and w_local.dtype == torch.bfloat16 and x_local.dim() == 2 and x_local.shape[0] % 128 == 0 \
+            and x_local.shape[1] % 8 == 0 and w_local.shape[0] % 8 == 0:
+        return _ColumnParallelLinearFn.apply(x_local.contiguous(), w_local, tp)
     return Fn.linear(all_gather_rows(x_local, tp), w_local)
 
 

@@ -460,3 +460,28 @@ def test_moe_mlp_kernel_path_matches_dense_loop():
     assert _rel_err(wts.grad, wtr.grad) < 4e-2
     assert _rel_err(wg.grad, wgr.grad) < 4e-2
     assert _rel_err(wd.grad, wdr.grad) < 4e-2
+
+
+@pytest.mark.parametrize("side", [1, 2])
+def test_gemm_with_in_kernel_all_gather(side):
+    """Gather mode on one GPU: the 'ranks' are four buffers of this GPU, so the copy CTAs, the
+    per-chunk counters and the chunk-ordered tile walk are exercised without a second device."""
+    from omegalax_b200.ops import kernels as K, lib
+    torch.manual_seed(17)
+    dev = _dev()
+    W, Kd, rank = 4, 512, 1
+    rows = 256
+    flags = torch.zeros(W, dtype=torch.int32, device=dev)
+    for call in range(2):
+        chunks = [torch.randn(rows, Kd, device=dev).to(bf16) for _ in range(W)]
+        full = torch.zeros(rows * W, Kd, dtype=bf16, device=dev)
+        other = torch.randn(384 if side == 1 else 300, Kd, device=dev).to(bf16)
+        y = K.gemm_ag(other, full, [c.data_ptr() for c in chunks], side=side, rank=rank, rows_per_rank=rows,
+                      flags=flags, target=8 * (call + 1), copy_ctas=8)
+        torch.cuda.synchronize()
+        _check(lib)
+        want_full = torch.cat(chunks)
+        assert torch.equal(full, want_full)
+        ref = want_full.float() @ other.float().t() if side == 1 else other.float() @ want_full.float().t()
+        assert _rel_err(y, ref) < 1e-2
+        assert flags.tolist() == [8 * (call + 1)] * W
