@@ -94,7 +94,12 @@ class _LinearFn(torch.autograd.Function):
     def forward(ctx, x, w, residual, y_pre=None):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
-        y = y_pre if y_pre is not None else K.gemm(x2, w, residual=residual)
+        y = y_pre
+        ag = getattr(w, "ag_spec", None)
+        if y is None and ag is not None:   # sharded weight that is gathered inside this GEMM's launch
+            y = ag.run(x2.contiguous(), w, residual)
+        if y is None:
+            y = K.gemm(x2, w, residual=residual)
         ctx.save_for_backward(x2, w)
         ctx.shp = shp
         ctx.has_res = residual is not None

@@ -49,6 +49,7 @@ class ParamSlot:
     pname: str = ""
     peer: bool = False     # gradient goes through the GEMM peer-reduce epilogue
     ep: bool = False       # expert-parallel: never gathered, this rank computes with its own slice
+    fused_ag: bool = False  # gathered inside its forward GEMM launch, not by the prefetch
     tp_sharded: bool = False   # differs between tensor-parallel ranks (no gradient all-reduce over tp)
 
 
@@ -94,7 +95,7 @@ class TrainEngine:
                  weight_decay: float = 0.01, betas=(0.9, 0.999), eps: float = 1e-8,
                  max_grad_norm: float | None = 1.0, remat: str = "full", seed: int = 0,
                  init_from_model: bool = False, comm: str = "auto", expert_parallel: bool = True,
-                 ep_capacity_factor: float = 2.0, tp_group=None):
+                 ep_capacity_factor: float = 2.0, tp_group=None, fused_gather: bool = True):
         self.model = model
         self.device = torch.device(device)
         self.group = shard_group
@@ -122,6 +123,13 @@ class TrainEngine:
             comm = "p2p" if (self.device.type == "cuda" and self.W > 1) else "nccl"
         self.comm_kind = comm if self.W > 1 else "none"
         self.expert_parallel = bool(expert_parallel) and self.comm_kind == "p2p"
+        # The weight of a layer's first projection is gathered inside that projection's GEMM launch
+        # instead of by the prefetch.  Every backward must re-run the forward GEMM for this to hold
+        # the weight when the gradient GEMMs need it, hence only with full rematerialisation.
+        self.fused_gather = bool(fused_gather) and self.comm_kind == "p2p" and remat == "full" and self.TP == 1
+        self._fused_done = [None, None]
+        self._ag_count = 0
+        self._ag_flags = None
         self.ep_capacity_factor = ep_capacity_factor
         self._ep = None
         self._build_units()
@@ -303,6 +311,10 @@ class TrainEngine:
             s.peer = True
             off_bytes = (u.shard_base + s.shard_off) * 4
             s.param.peer_grad = (self._grad_buf.peer_ptr_list(off_bytes), s.shape[0] // self.W, s.shape[1])
+            if (self.fused_gather and u.name.startswith("layers.") and s.pname.endswith("qkv_proj.weight")
+                    and (s.shape[0] // self.W) % 128 == 0 and s.shape[1] % 8 == 0 and self.compute_dtype == bf16):
+                s.fused_ag = True
+                s.param.ag_spec = _FusedGather(self, u, s)
 
     def _seg_table(self, u: Unit):
         tab = self._seg_tables.get(u.name)
@@ -310,7 +322,7 @@ class TrainEngine:
             esz = 2 if self.compute_dtype == bf16 else 4
             segs = []
             for s in u.slots:
-                if s.ep:
+                if s.ep or s.fused_ag:
                     continue
                 src = (u.shard_base + s.shard_off) * esz
                 if s.sharded:
@@ -401,6 +413,7 @@ class TrainEngine:
             ev.record(self._comm_stream)
         self._ring_event[idx] = ev
         self._ring_owner[idx] = (u.name, self._weights_version)
+        self._fused_done[idx] = None   # the slot's in-GEMM gathered weight belongs to the previous owner
 
     def _release_grads(self, u: Unit):
         """After a unit's backward: fold stray autograd grads, then reduce-scatter."""
@@ -548,6 +561,34 @@ class TrainEngine:
         out = torch.empty(self.W * slot.shard_numel, dtype=torch.float32, device=self.device)
         dist.all_gather_into_tensor(out, ms.contiguous(), group=self.group)
         return out.view(slot.shape)
+
+
+class _FusedGather:
+    """Attached to a weight that is gathered inside its forward GEMM (``Fn.linear`` looks for
+    ``weight.ag_spec``).  ``run`` returns None when the gathered copy in the ring slot is current,
+    in which case the caller uses the plain GEMM."""
+
+    def __init__(self, engine: "TrainEngine", unit: Unit, slot: ParamSlot):
+        self.engine, self.unit, self.slot = engine, unit, slot
+        off = (unit.shard_base + slot.shard_off) * 2
+        self.src_ptrs = engine._shard_buf.peer_ptr_list(off)
+        self.flags = None
+
+    def run(self, x2, w, residual):
+        eng, s = self.engine, self.slot
+        idx = int(self.unit.name.split(".")[1]) & 1
+        key = (self.unit.name, eng._weights_version)
+        if eng._fused_done[idx] == key or w.shape != s.shape:
+            return None
+        if eng._ag_flags is None:
+            eng._ag_flags = torch.zeros(eng.W, dtype=torch.int32, device=eng.device)
+        rows = s.shape[0] // eng.W
+        ctas = K.ag_copy_ctas(x2.shape[0], s.shape[0], s.shape[1], s.numel * 2.0)
+        eng._ag_count += ctas
+        y = K.gemm_ag(x2, w, self.src_ptrs, side=2, rank=eng.rank, rows_per_rank=rows, flags=eng._ag_flags,
+                      target=eng._ag_count, copy_ctas=ctas, residual=residual)
+        eng._fused_done[idx] = key
+        return y
 
 
 class _LazyEP:

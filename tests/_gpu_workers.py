@@ -83,7 +83,8 @@ def fsdp_train_gpu(rank, world, port, comm, steps, out_path):
     torch.cuda.synchronize()
     lib.check_status()
     if rank == 0:
-        torch.save({"losses": losses, "grad_norm": float(opt.last_grad_norm)}, out_path)
+        torch.save({"losses": losses, "grad_norm": float(opt.last_grad_norm),
+                    "fused_gather_ctas": int(getattr(opt, "_ag_count", 0))}, out_path)
     if world > 1:
         dist.barrier()
     dist.destroy_process_group()
