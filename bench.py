@@ -37,7 +37,54 @@ MODELS = {
     "qwen3-8b": (MODEL_ID, SEQ_LEN, SEQS_PER_GPU, "fsdp"),
     "qwen3-30b-a3b": ("Qwen/Qwen3-30B-A3B-Instruct-2507", 4096, 4, "ep+fsdp"),
     "qwen3.5-8l": ("qwen3.5-397b-a17b-8layer", 8192, 2, "ep+fsdp"),
+    # Qwen3-VL-2B: one 448x448 image (784 patches -> 196 tokens) + text ids per sample, 4 samples per GPU
+    "qwen3-vl-2b": ("Qwen/Qwen3-VL-2B-Instruct", 1220, 4, "fsdp"),
 }
+
+
+def qwen3_vl_2b_config():
+    """Dimensions of the published Qwen3-VL-2B-Instruct config.json (no hub access here)."""
+    import torch
+
+    from omegalax_b200.models.qwen3_vl.config import Qwen3VLConfig, Qwen3VLVisionConfig
+
+    vis = Qwen3VLVisionConfig(hidden_size=1024, intermediate_size=4096, num_heads=16, patch_size=16,
+                              temporal_patch_size=2, in_channels=3, spatial_merge_size=2, out_hidden_size=2048,
+                              depth=24, hidden_act="gelu_pytorch_tanh", num_position_embeddings=2304,
+                              deepstack_visual_indexes=(5, 11, 17))
+    return Qwen3VLConfig(num_layers=28, vocab_size=151936, emb_dim=2048, mlp_dim=6144, num_heads=16, head_dim=128,
+                         num_kv_heads=8, rope_theta=5e6, norm_eps=1e-6, tie_word_embeddings=True,
+                         mrope_section=(24, 20, 20), vision=vis, image_token_id=151655, video_token_id=151656,
+                         vision_start_token_id=151652, dtype=torch.bfloat16)
+
+
+def vlm_batches(cfg, micro: int, T: int, n: int, seed: int):
+    """Synthetic VLM micro-batches in pinned host memory: per sample <vision_start>, 196 image
+    placeholders (one 448x448 image, grid [1,28,28]), then random text ids; pixels ~ N(0,1)."""
+    import numpy as np
+    import torch
+
+    from omegalax_b200.models.qwen3_vl.model import get_rope_index
+
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    n_img = 196
+    for _ in range(n):
+        tok = torch.randint(1, 151000, (micro, T), generator=g, dtype=torch.int32)
+        tok[:, 0] = cfg.vision_start_token_id
+        tok[:, 1:1 + n_img] = cfg.image_token_id
+        grid = np.tile(np.array([[1, 28, 28]], dtype=np.int64), (micro, 1))
+        pos, _ = get_rope_index(tok.numpy(), grid, None, None, 2, cfg.image_token_id, cfg.video_token_id,
+                                cfg.vision_start_token_id)
+        lm = torch.zeros(micro, T, dtype=torch.int32)
+        lm[:, T // 2:] = 1
+        b = {"token_ids_BT": tok, "attention_mask_BT": torch.ones(micro, T, dtype=torch.int32), "loss_mask_BT": lm,
+             "pixel_values": torch.randn(784 * micro, 3 * 2 * 16 * 16, generator=g),
+             "image_grid_thw": torch.from_numpy(grid).to(torch.int32),
+             "vision_cu_seqlens": torch.arange(micro + 1, dtype=torch.int32) * 784,
+             "position_ids_ZBT": torch.from_numpy(pos).to(torch.int32)}
+        out.append({k: v.pin_memory() for k, v in b.items()})
+    return out
 
 
 def reference_arm(args) -> int:
@@ -149,7 +196,8 @@ def main() -> int:
     model_id, def_T, def_seqs, par = MODELS[args.model]
     args.seqs_per_gpu = args.seqs_per_gpu or def_seqs
     args.seq_len = args.seq_len or def_T
-    cfg = text_api.resolve_config(model_id)
+    is_vlm = args.model == "qwen3-vl-2b"
+    cfg = qwen3_vl_2b_config() if is_vlm else text_api.resolve_config(model_id)
     if args.layers is not None:
         if hasattr(cfg, "num_layers"):
             cfg = dataclasses.replace(cfg, num_layers=args.layers)
@@ -170,14 +218,21 @@ def main() -> int:
                                weight_decay=0.01, warmup_steps=0, lr_schedule="linear", max_grad_norm=1.0,
                                grad_accum_steps=accum, remat_policy=remat)
     mesh = mesh_lib.ensure_mesh(tp_size=1, fsdp_size=N, dp_size=1)
-    model, cfg = trainer.init_model(cfg, 0, tp_size=1, fsdp_size=N, dp_size=1, meta=True)
-    opt = trainer.build_optimizer(model, tcfg, device=device)
-    step_fn = trainer.make_sft_train_step(cfg, pad_id=0)
+    if is_vlm:
+        from omegalax_b200.trainers import vlm as vlm_trainer
+
+        model, cfg = vlm_trainer.init_model(cfg, 0, tp_size=1, fsdp_size=N, dp_size=1, meta=True)
+        opt = trainer.build_optimizer(model, tcfg, device=device)
+        step_fn = vlm_trainer.make_sft_train_step(cfg, pad_id=0)
+    else:
+        model, cfg = trainer.init_model(cfg, 0, tp_size=1, fsdp_size=N, dp_size=1, meta=True)
+        opt = trainer.build_optimizer(model, tcfg, device=device)
+        step_fn = trainer.make_sft_train_step(cfg, pad_id=0)
 
     # synthetic data in pinned host memory: a pool of distinct micro-batches
     g = torch.Generator().manual_seed(1234 + rank)
-    pool = []
-    for _ in range(4):
+    pool = vlm_batches(cfg, micro, T, 4, 1234 + rank) if is_vlm else []
+    for _ in range(0 if is_vlm else 4):
         tok = torch.randint(1, cfg.vocab_size, (micro, T), generator=g, dtype=torch.int32).pin_memory()
         lm = torch.zeros(micro, T, dtype=torch.int32)
         lm[:, T // 2:] = 1
@@ -241,6 +296,10 @@ def main() -> int:
     value = tokens_per_step * args.steps / (ms / 1000.0)
     e2e_value = tokens_per_step * args.steps / (e2e_ms / 1000.0)
     fpt = training_flops_per_token(cfg, T)
+    if is_vlm:  # add the vision tower (per-image FLOPs spread over the sample's tokens)
+        from omegalax_b200.trainers.perf import qwen3_vl_vision_training_flops
+
+        fpt += qwen3_vl_vision_training_flops(cfg, [(1, 28, 28)]) / T
     tflops_per_gpu = value / N * fpt / 1e12
     if rank == 0:
         out = {
@@ -252,7 +311,7 @@ def main() -> int:
                        "global_batch": args.seqs_per_gpu * N, "seq_len": T,
                        "parallelism": f"fsdp{N}" if par == "fsdp" else f"ep{N}+fsdp{N}",
                        "micro_batch_per_gpu": micro, "grad_accum": accum, "optimizer": "AdamW fp32 master",
-                       "remat": remat, "l2": "inputs larger than L2 (16 GB of weights per step)"},
+                       "remat": remat, "l2": "inputs larger than L2 (weights and activations of one step far exceed 126 MB)"},
             "tokens_per_sec_per_gpu": value / N, "tflops_per_gpu": tflops_per_gpu,
             "mfu_of_measured_burst": tflops_per_gpu / PEAK_TFLOPS["b200_measured_burst"],
             "mfu_of_nominal": tflops_per_gpu / PEAK_TFLOPS["b200"],
