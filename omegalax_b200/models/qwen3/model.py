@@ -111,7 +111,7 @@ class Attention(nn.Module):
         o = o.reshape(M, self.H * self.Kd)
         if tp is not None:
             return tp_lib.row_parallel_linear(o, self.o_proj.weight, residual, tp)
-        return self.o_proj(o, residual=residual)
+        return self.o_proj(o, residual=residual, tag="o")
 
     def _decode(self, q, k, v, ctx: ForwardCtx, cache: LayerCache):
         """Append this call's K/V at the cursor and attend over the whole cache with the mask
@@ -155,7 +155,7 @@ class MLP(nn.Module):
         if tp is not None:
             h = Fn.swiglu(tp_lib.column_parallel_linear(x, self.gate_up_proj.weight, tp))
             return tp_lib.row_parallel_linear(h, self.down_proj.weight, residual, tp)
-        return self.down_proj(Fn.swiglu(self.gate_up_proj(x, tag="gate_up")), residual=residual)
+        return self.down_proj(Fn.swiglu(self.gate_up_proj(x, tag="gate_up")), residual=residual, tag="down")
 
 
 class MoEFeedForward(nn.Module):

@@ -26,7 +26,11 @@ class _Stash:
     layer are replayed (instead of recomputed) when the layer is re-run for its backward."""
 
     def __init__(self, tags):
-        self.tags = frozenset(tags)
+        # a tag written "name!" marks an op whose output value nothing in the layer's backward
+        # needs (the layer's last projection): it is neither stored nor recomputed, the replay
+        # gets an uninitialised tensor of the right shape
+        self.skip = frozenset(t[:-1] for t in tags if t.endswith("!"))
+        self.tags = frozenset(t.rstrip("!") for t in tags)
         self.items: dict = {}
         self.mode = "off"      # "record" | "replay" | "off"
         self.counter: dict = {}
@@ -66,12 +70,17 @@ def _stash_lookup(tag):
     if st is None or tag is None or tag not in st.tags or st.mode == "off":
         return None, None
     k = st.key(tag)
+    if tag in st.skip:
+        return k, (_SKIP if st.mode == "replay" else None)
     return k, (st.items.get(k) if st.mode == "replay" else None)
+
+
+_SKIP = object()
 
 
 def _stash_store(key, value):
     st = _ACTIVE_STASH
-    if st is not None and key is not None and st.mode == "record":
+    if st is not None and key is not None and st.mode == "record" and key[0] not in st.skip:
         st.items[key] = value
 
 
@@ -140,6 +149,8 @@ def linear(x, w, residual=None, bias=None, tag=None):
         return y if residual is None else y + residual
     if use_kernels(x) and w.dtype == bf16:
         key, pre = _stash_lookup(tag if bias is None else None)
+        if pre is _SKIP:
+            pre = torch.empty(x.numel() // x.shape[-1], w.shape[0], dtype=x.dtype, device=x.device)
         y = _LinearFn.apply(x, w, residual if bias is None else None,
                             None if pre is None else pre.view(-1, w.shape[0]))
         _stash_store(key, y)

@@ -106,10 +106,14 @@ class TrainEngine:
         self.remat = remat
         # remat policies: "full" recomputes the whole layer; "selective" (or "save:tag,tag") keeps the
         # tagged GEMM / attention outputs from the first forward; "none" keeps everything (single rank)
+        # "down!": the output of a dense layer's last projection is the layer output, which nothing
+        # in that layer's backward reads, so the re-run never computes it
         if remat == "selective":
-            self.remat_tags = ("qkv", "attn", "gate_up")
+            self.remat_tags = ("qkv", "attn", "o", "gate_up", "down!")
         elif remat.startswith("save:"):
-            self.remat_tags = tuple(t for t in remat[5:].split(",") if t)
+            self.remat_tags = tuple(t for t in remat[5:].split(",") if t) + ("down!",)
+        elif remat == "full":
+            self.remat_tags = ("down!",)
         else:
             self.remat_tags = ()
         self.step_count = 0

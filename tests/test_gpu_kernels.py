@@ -485,3 +485,56 @@ def test_gemm_with_in_kernel_all_gather(side):
         ref = want_full.float() @ other.float().t() if side == 1 else other.float() @ want_full.float().t()
         assert _rel_err(y, ref) < 1e-2
         assert flags.tolist() == [8 * (call + 1)] * W
+
+
+def test_gated_delta_rule_strong_decay_against_fp64_recurrence():
+    """Decay rates as large as a freshly initialised model produces (|g| up to ~20 per token).
+    Ground truth is the token-by-token recurrence in float64; the kernel must be about as close
+    to it as the fp32 chunked PyTorch definition is."""
+    from omegalax_b200.ops import functional as Fn, reference as R, lib
+    torch.manual_seed(13)
+    dev = _dev()
+    B, T, Hk, H, A, U = 1, 128, 1, 2, 128, 64
+
+    def leaves(dtype):
+        torch.manual_seed(13)
+        q = torch.randn(B, T, Hk, A, device=dev)
+        k = torch.randn(B, T, Hk, A, device=dev)
+        v = torch.randn(B, T, H, U, device=dev)
+        g = -torch.rand(B, T, H, device=dev) * 20.0
+        g[:, ::3] *= 0.01                      # a mix of nearly no decay and very strong decay
+        beta = torch.sigmoid(torch.randn(B, T, H, device=dev))
+        return [t.to(dtype).requires_grad_(True) for t in (q, k, v, g, beta)]
+
+    do = torch.randn(B, T, H, U, device=dev)
+    # float64 recurrence
+    q, k, v, g, beta = leaves(torch.float64)
+    qn = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * A ** -0.5
+    kn = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    qn, kn = qn.repeat_interleave(H // Hk, 2), kn.repeat_interleave(H // Hk, 2)
+    S = torch.zeros(B, H, A, U, dtype=torch.float64, device=dev)
+    outs = []
+    for t in range(T):
+        S = S * torch.exp(g[:, t])[..., None, None]
+        kv = torch.einsum("bha,bhau->bhu", kn[:, t], S)
+        delta = (v[:, t] - kv) * beta[:, t][..., None]
+        S = S + torch.einsum("bha,bhu->bhau", kn[:, t], delta)
+        outs.append(torch.einsum("bha,bhau->bhu", qn[:, t], S))
+    o64 = torch.stack(outs, 1)
+    (o64 * do.double()).sum().backward()
+    truth = [o64.detach()] + [t.grad.clone() for t in (q, k, v, g, beta)]
+
+    def run(fn):
+        ls = leaves(torch.float32)
+        o = fn(*ls)
+        (o * do).sum().backward()
+        return [o.detach()] + [t.grad.clone() for t in ls]
+
+    kern = run(lambda q, k, v, g, b: Fn.gated_delta_rule(q, k, v, g, b))
+    _check(lib)
+    ref = run(lambda q, k, v, g, b: R.chunk_gated_delta_rule(q.repeat_interleave(H // Hk, 2),
+                                                             k.repeat_interleave(H // Hk, 2), v, g, b))
+    for name, t64, tk, tr in zip(["o", "dq", "dk", "dv", "dg", "dbeta"], truth, kern, ref):
+        ek = float((tk.double() - t64).norm() / (t64.norm() + 1e-30))
+        er = float((tr.double() - t64).norm() / (t64.norm() + 1e-30))
+        assert ek < max(5e-4, 5 * er), (name, ek, er)
