@@ -43,19 +43,10 @@ MODELS = {
 
 
 def qwen3_vl_2b_config():
-    """Dimensions of the published Qwen3-VL-2B-Instruct config.json (no hub access here)."""
-    import torch
+    """Architecture of the published Qwen3-VL-2B-Instruct config.json (built-in preset: no hub access here)."""
+    from omegalax_b200.models.qwen3_vl.config import make_vl_config
 
-    from omegalax_b200.models.qwen3_vl.config import Qwen3VLConfig, Qwen3VLVisionConfig
-
-    vis = Qwen3VLVisionConfig(hidden_size=1024, intermediate_size=4096, num_heads=16, patch_size=16,
-                              temporal_patch_size=2, in_channels=3, spatial_merge_size=2, out_hidden_size=2048,
-                              depth=24, hidden_act="gelu_pytorch_tanh", num_position_embeddings=2304,
-                              deepstack_visual_indexes=(5, 11, 17))
-    return Qwen3VLConfig(num_layers=28, vocab_size=151936, emb_dim=2048, mlp_dim=6144, num_heads=16, head_dim=128,
-                         num_kv_heads=8, rope_theta=5e6, norm_eps=1e-6, tie_word_embeddings=True,
-                         mrope_section=(24, 20, 20), vision=vis, image_token_id=151655, video_token_id=151656,
-                         vision_start_token_id=151652, dtype=torch.bfloat16)
+    return make_vl_config("Qwen/Qwen3-VL-2B-Instruct")
 
 
 def vlm_batches(cfg, micro: int, T: int, n: int, seed: int):

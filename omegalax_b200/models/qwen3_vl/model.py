@@ -8,6 +8,7 @@ import numpy as np
 import torch
 from torch import nn
 
+from ...ops import functional as Fn
 from ...ops import reference as R
 from ..qwen3.model import DecoderLayer, Embedding, ForwardCtx, Linear
 from ..qwen3.norms import RMSNorm
@@ -137,8 +138,7 @@ class Qwen3VL(nn.Module):
             feats, deep = self.visual(pixel_values.to(x.dtype), image_grid_thw, vision_cu_seqlens.to(torch.int32))
             is_img = token_ids.reshape(-1) == self.cfg.image_token_id
             vis_pos = torch.nonzero(is_img, as_tuple=False).squeeze(-1)[: feats.shape[0]]
-            x = x * (~is_img).unsqueeze(-1).to(x.dtype)
-            x = x.index_add(0, vis_pos, feats[: vis_pos.numel()].to(x.dtype))
+            x = Fn.scatter_rows(x, vis_pos, feats[: vis_pos.numel()].to(x.dtype), replace=True)
         if position_ids_ZBT is None:
             pos = (attention_mask.cumsum(-1) - 1).clamp_min(0) * (attention_mask != 0)
             position_ids_ZBT = pos[None].expand(3, B, T)
@@ -157,5 +157,5 @@ class Qwen3VL(nn.Module):
                 x, aux = layer(x, ctx)
             aux_total = aux_total + aux
             if vis_pos is not None and i < len(deep):  # DeepStack: add tapped vision features
-                x = x.index_add(0, vis_pos, deep[i][: vis_pos.numel()].to(x.dtype))
+                x = Fn.scatter_rows(x, vis_pos, deep[i][: vis_pos.numel()].to(x.dtype))
         return self.final_norm(x).view(B, T, -1), aux_total

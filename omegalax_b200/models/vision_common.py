@@ -63,7 +63,7 @@ class VisionMLP(nn.Module):
 
     def forward(self, x):
         h = self.linear_fc1(x)
-        h = R.gelu_tanh(h) if self.act in ("gelu_pytorch_tanh", "gelu_tanh") else F.gelu(h)
+        h = Fn.gelu_tanh(h) if self.act in ("gelu_pytorch_tanh", "gelu_tanh") else F.gelu(h)
         return self.linear_fc2(h)
 
 
@@ -153,12 +153,14 @@ class VisionTower(nn.Module):
             h0, w0 = hi.floor().long(), wi.floor().long()
             h1, w1 = (h0 + 1).clamp(max=side - 1), (w0 + 1).clamp(max=side - 1)
             dh, dw = (hi - h0).to(table.dtype), (wi - w0).to(table.dtype)
-            def gather(hh, ww):
-                return table[(hh[:, None] * side + ww[None, :]).reshape(-1)]
-            pe = (gather(h0, w0) * ((1 - dh)[:, None] * (1 - dw)[None, :]).reshape(-1, 1)
-                  + gather(h0, w1) * ((1 - dh)[:, None] * dw[None, :]).reshape(-1, 1)
-                  + gather(h1, w0) * (dh[:, None] * (1 - dw)[None, :]).reshape(-1, 1)
-                  + gather(h1, w1) * (dh[:, None] * dw[None, :]).reshape(-1, 1))
+            def flat(hh, ww):
+                return (hh[:, None] * side + ww[None, :]).reshape(-1)
+            idx4 = torch.stack([flat(h0, w0), flat(h0, w1), flat(h1, w0), flat(h1, w1)], dim=1)
+            w4 = torch.stack([((1 - dh)[:, None] * (1 - dw)[None, :]).reshape(-1),
+                              ((1 - dh)[:, None] * dw[None, :]).reshape(-1),
+                              (dh[:, None] * (1 - dw)[None, :]).reshape(-1),
+                              (dh[:, None] * dw[None, :]).reshape(-1)], dim=1)
+            pe = Fn.gather4(table, idx4, w4)
             pe = pe.repeat(t, 1).view(t, h // m, m, w // m, m, -1).permute(0, 1, 3, 2, 4, 5).reshape(t * h * w, -1)
             outs.append(pe)
         return torch.cat(outs)

@@ -65,6 +65,10 @@ __global__ void router_topk_kernel(const bf16* __restrict__ logits, float* __res
       for (int i = 0; i < kMaxEPL; ++i)
         if (i == (bi >> 5)) v[i] = -1.f;   // taken
     }
+    if (bi >= E) {  // only with NaN probabilities (no comparison succeeds): keep the ids in range
+      bi = r;
+      best = 0.f;
+    }
     if (lane == r) { wsel = best; isel = bi; }
     tot += best;
   }
@@ -151,17 +155,19 @@ __global__ void moe_offsets_kernel(const int* __restrict__ counts, int* __restri
   if (t == 0) offsets[0] = 0;
 }
 
-__global__ void moe_count_kernel(const int* __restrict__ idx, int* __restrict__ counts, long long P) {
-  const long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  if (p < P) atomicAdd(counts + idx[p], 1);
-}
-
-__global__ void moe_dest_kernel(const int* __restrict__ idx, const int* __restrict__ offsets, int* __restrict__ cursor,
-                                int* __restrict__ dest, long long P) {
+__global__ void moe_count_kernel(const int* __restrict__ idx, int* __restrict__ counts, long long P, int E) {
   const long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (p >= P) return;
   const int e = idx[p];
-  dest[p] = offsets[e] + atomicAdd(cursor + e, 1);
+  if (e >= 0 && e < E) atomicAdd(counts + e, 1);   // ids out of range are ignored, never dereferenced
+}
+
+__global__ void moe_dest_kernel(const int* __restrict__ idx, const int* __restrict__ offsets, int* __restrict__ cursor,
+                                int* __restrict__ dest, long long P, int E) {
+  const long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (p >= P) return;
+  const int e = idx[p];
+  dest[p] = (e >= 0 && e < E) ? offsets[e] + atomicAdd(cursor + e, 1) : -1;   // -1: dropped by the row movers
 }
 
 // Expert-parallel plan.  allc [W][E] holds every rank's pick counts.  For expert e owned by rank
@@ -202,10 +208,15 @@ __global__ void ep_plan_kernel(const int* __restrict__ allc, int* __restrict__ s
 
 __global__ void ep_dest_kernel(const int* __restrict__ idx, const int* __restrict__ start, int* __restrict__ cursor,
                                int* __restrict__ dst_rank, int* __restrict__ dst_row, long long P, int El,
-                               int capacity) {
+                               int capacity, int E) {
   const long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (p >= P) return;
   const int e = idx[p];
+  if (e < 0 || e >= E) {  // never dereference an id that is out of range
+    dst_rank[p] = 0;
+    dst_row[p] = -1;
+    return;
+  }
   dst_rank[p] = e / El;
   const int row = start[e] + atomicAdd(cursor + e, 1);
   dst_row[p] = row < capacity ? row : -1;   // beyond the receive buffer: dropped (the overflow flag is set)
@@ -246,12 +257,12 @@ int ob_moe_plan(const int* idx, int* counts, int* offsets, int* cursor, int* des
   if (E > 1024 || E <= 0) return 6001;
   if (compute_counts) {
     cudaMemsetAsync(counts, 0, sizeof(int) * E, s);
-    if (P > 0) moe_count_kernel<<<(unsigned)((P + 255) / 256), 256, 0, s>>>(idx, counts, P);
+    if (P > 0) moe_count_kernel<<<(unsigned)((P + 255) / 256), 256, 0, s>>>(idx, counts, P, E);
   }
   moe_offsets_kernel<<<1, 1024, 0, s>>>(counts, offsets, cursor, E, pad);
   OB_CHECK_LAUNCH();
   if (P > 0) {
-    moe_dest_kernel<<<(unsigned)((P + 255) / 256), 256, 0, s>>>(idx, offsets, cursor, dest, P);
+    moe_dest_kernel<<<(unsigned)((P + 255) / 256), 256, 0, s>>>(idx, offsets, cursor, dest, P, E);
     OB_CHECK_LAUNCH();
   }
   return 0;
@@ -261,7 +272,7 @@ int ob_moe_plan(const int* idx, int* counts, int* offsets, int* cursor, int* des
 int ob_moe_count(const int* idx, int* counts, long long P, int E, cudaStream_t s) {
   cudaMemsetAsync(counts, 0, sizeof(int) * E, s);
   if (P > 0) {
-    moe_count_kernel<<<(unsigned)((P + 255) / 256), 256, 0, s>>>(idx, counts, P);
+    moe_count_kernel<<<(unsigned)((P + 255) / 256), 256, 0, s>>>(idx, counts, P, E);
     OB_CHECK_LAUNCH();
   }
   return 0;
@@ -275,7 +286,7 @@ int ob_ep_plan(const int* idx, const int* allc, int* scratch, int* offsets_local
   ep_plan_kernel<<<1, 1024, 0, s>>>(allc, scratch, scratch + E, offsets_local, overflow, W, E, El, rank, pad, capacity);
   OB_CHECK_LAUNCH();
   if (P > 0) {
-    ep_dest_kernel<<<(unsigned)((P + 255) / 256), 256, 0, s>>>(idx, scratch, scratch + E, dst_rank, dst_row, P, El, capacity);
+    ep_dest_kernel<<<(unsigned)((P + 255) / 256), 256, 0, s>>>(idx, scratch, scratch + E, dst_rank, dst_row, P, El, capacity, E);
     OB_CHECK_LAUNCH();
   }
   return 0;

@@ -245,6 +245,79 @@ def layernorm(x, w, b, eps: float):
     return R.layernorm(x, w, b, eps)
 
 
+# ----------------------------------------------------------------------------- gelu, row gather / scatter
+class _GeluTanhFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        ctx.save_for_backward(x)
+        return K.gelu_tanh_fwd(x)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        return K.gelu_tanh_bwd(x, dy.contiguous())
+
+
+def gelu_tanh(x):
+    if use_kernels(x) and x.numel() % 8 == 0:
+        return _GeluTanhFn.apply(x.contiguous())
+    return R.gelu_tanh(x)
+
+
+class _ScatterRowsFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, pos32, src, replace):
+        out = x.clone()
+        K.scatter_rows_(out, pos32, src, replace)
+        ctx.save_for_backward(pos32)
+        ctx.replace = replace
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        (pos32,) = ctx.saved_tensors
+        dy = dy.contiguous()
+        dsrc = K.gather_rows(dy, pos32)
+        dx = dy
+        if ctx.replace:
+            dx = dy.clone()
+            K.scatter_rows_(dx, pos32, torch.zeros_like(dsrc), True)
+        return dx, None, dsrc, None
+
+
+def scatter_rows(x, pos, src, replace: bool = False):
+    """x with rows ``pos`` (unique) replaced by / increased by the rows of ``src``."""
+    if use_kernels(x) and x.dim() == 2 and x.shape[1] % 8 == 0 and src.dtype == x.dtype:
+        return _ScatterRowsFn.apply(x.contiguous(), pos.to(torch.int32), src.contiguous(), bool(replace))
+    if replace:
+        keep = torch.ones(x.shape[0], 1, dtype=x.dtype, device=x.device).index_fill(0, pos, 0.0)
+        x = x * keep
+    return x.index_add(0, pos, src.to(x.dtype))
+
+
+class _Gather4Fn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, table, idx, w):
+        ctx.save_for_backward(idx, w)
+        ctx.t_ref, ctx.shape = table, table.shape
+        return K.gather4_fwd(table, idx, w)
+
+    @staticmethod
+    def backward(ctx, dout):
+        idx, w = ctx.saved_tensors
+        mg = getattr(ctx.t_ref, "main_grad", None)
+        dt = mg if mg is not None else torch.zeros(ctx.shape, dtype=torch.float32, device=dout.device)
+        K.gather4_bwd(dout.contiguous(), idx, w, dt)
+        return (None if mg is not None else dt.to(ctx.t_ref.dtype)), None, None
+
+
+def gather4(table, idx_N4, w_N4):
+    """out[i] = sum_k w[i,k] * table[idx[i,k]] (four-neighbour interpolation of a learned table)."""
+    if use_kernels(table) and table.shape[1] % 8 == 0:
+        return _Gather4Fn.apply(table, idx_N4.to(torch.int32).contiguous(), w_N4.float().contiguous())
+    return (table[idx_N4.reshape(-1).long()].view(idx_N4.shape[0], 4, -1).float() * w_N4.float().unsqueeze(-1)).sum(1).to(table.dtype)
+
+
 # ----------------------------------------------------------------------------- swiglu
 class _SwiGLUFn(torch.autograd.Function):
     @staticmethod

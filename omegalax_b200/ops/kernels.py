@@ -468,3 +468,40 @@ def moe_plan(idx32, E, pad=128, counts=None):
     _call("ob_moe_plan", idx32.data_ptr(), counts.data_ptr(), offsets.data_ptr(), cursor.data_ptr(), dest.data_ptr(), Pn,
           E, pad, int(not have), lib.stream_ptr())
     return offsets, dest
+
+
+def gather_rows(src, idx32):
+    out = torch.empty(idx32.numel(), src.shape[1], dtype=src.dtype, device=src.device)
+    _call("ob_gather_rows", src.data_ptr(), idx32.data_ptr(), out.data_ptr(), idx32.numel(), src.shape[1], lib.stream_ptr())
+    return out
+
+
+def scatter_rows_(dst, idx32, src, replace: bool):
+    _call("ob_scatter_rows", dst.data_ptr(), idx32.data_ptr(), src.data_ptr(), idx32.numel(), dst.shape[1], int(replace),
+          lib.stream_ptr())
+    return dst
+
+
+def gather4_fwd(table, idx32_N4, w_N4):
+    n = idx32_N4.shape[0]
+    out = torch.empty(n, table.shape[1], dtype=table.dtype, device=table.device)
+    _call("ob_gather4_fwd", table.data_ptr(), idx32_N4.data_ptr(), w_N4.data_ptr(), out.data_ptr(), n, table.shape[1],
+          lib.stream_ptr())
+    return out
+
+
+def gather4_bwd(dout, idx32_N4, w_N4, dtable_f32):
+    _call("ob_gather4_bwd", dout.data_ptr(), idx32_N4.data_ptr(), w_N4.data_ptr(), dtable_f32.data_ptr(), idx32_N4.shape[0],
+          dout.shape[1], lib.stream_ptr())
+
+
+def gelu_tanh_fwd(x):
+    y = torch.empty_like(x)
+    _call("ob_gelu_tanh_fwd", x.data_ptr(), y.data_ptr(), x.numel(), lib.stream_ptr())
+    return y
+
+
+def gelu_tanh_bwd(x, dy):
+    dx = torch.empty_like(x)
+    _call("ob_gelu_tanh_bwd", x.data_ptr(), dy.data_ptr(), dx.data_ptr(), x.numel(), lib.stream_ptr())
+    return dx

@@ -44,6 +44,12 @@ _SIGS = {
     "ob_layernorm_bwd": [P, P, P, P, P, P, P, P, L, I, P],
     "ob_router_topk": [P, P, P, P, P, L, I, I, I, P],
     "ob_router_topk_bwd": [P, P, P, P, P, P, L, I, I, I, P],
+    "ob_gather_rows": [P, P, P, L, I, P],
+    "ob_scatter_rows": [P, P, P, L, I, I, P],
+    "ob_gather4_fwd": [P, P, P, P, L, I, P],
+    "ob_gather4_bwd": [P, P, P, P, L, I, P],
+    "ob_gelu_tanh_fwd": [P, P, L, P],
+    "ob_gelu_tanh_bwd": [P, P, P, L, P],
     "ob_moe_count": [P, P, L, I, P],
     "ob_ep_plan": [P, P, P, P, P, P, P, L, I, I, I, I, I, P],
     "ob_moe_plan": [P, P, P, P, P, L, I, I, I, P],

@@ -538,3 +538,48 @@ def test_gated_delta_rule_strong_decay_against_fp64_recurrence():
         ek = float((tk.double() - t64).norm() / (t64.norm() + 1e-30))
         er = float((tr.double() - t64).norm() / (t64.norm() + 1e-30))
         assert ek < max(5e-4, 5 * er), (name, ek, er)
+
+
+def test_gather_scatter_gelu_kernels():
+    from omegalax_b200.ops import functional as Fn, reference as R, lib
+    torch.manual_seed(2)
+    dev = _dev()
+    M, D, n = 500, 256, 77
+    x = torch.randn(M, D, device=dev).to(bf16).requires_grad_(True)
+    src = torch.randn(n, D, device=dev).to(bf16).requires_grad_(True)
+    pos = torch.randperm(M, device=dev)[:n].sort().values
+    for replace in (False, True):
+        y = Fn.scatter_rows(x, pos, src, replace=replace)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        xr, sr = x.detach().float().requires_grad_(True), src.detach().float().requires_grad_(True)
+        base = xr
+        if replace:
+            keep = torch.ones(M, 1, device=dev).index_fill(0, pos, 0.0)
+            base = xr * keep
+        yr = base.index_add(0, pos, sr)
+        yr.backward(dy.float())
+        assert _rel_err(y, yr) < 1e-2
+        assert _rel_err(x.grad, xr.grad) < 1e-2 and _rel_err(src.grad, sr.grad) < 1e-2
+        x.grad = None
+        src.grad = None
+    table = torch.randn(48 * 48, D, device=dev).to(bf16).requires_grad_(True)
+    N = 300
+    idx = torch.randint(0, 48 * 48, (N, 4), device=dev)
+    w = torch.rand(N, 4, device=dev)
+    o = Fn.gather4(table, idx, w)
+    do = torch.randn_like(o)
+    o.backward(do)
+    tr = table.detach().float().requires_grad_(True)
+    orf = (tr[idx.reshape(-1)].view(N, 4, D) * w.unsqueeze(-1)).sum(1)
+    orf.backward(do.float())
+    assert _rel_err(o, orf) < 1e-2 and _rel_err(table.grad, tr.grad) < 2e-2
+    z = (torch.randn(1000, 64, device=dev) * 2).to(bf16).requires_grad_(True)
+    g = Fn.gelu_tanh(z)
+    dg = torch.randn_like(g)
+    g.backward(dg)
+    zr = z.detach().float().requires_grad_(True)
+    gr = R.gelu_tanh(zr)
+    gr.backward(dg.float())
+    assert _rel_err(g, gr) < 1e-2 and _rel_err(z.grad, zr.grad) < 2e-2
+    _check(lib)

@@ -139,3 +139,62 @@ def test_training_engine_reduces_loss(name):
     lib.check_status()
     assert all(l == l for l in losses), losses
     assert losses[-1] < losses[0] - 0.05, losses
+
+
+def test_qwen3_vl_kernels_match_reference_ops():
+    """Qwen3-VL with an image: vision tower (LayerNorm, tanh-GELU, non-causal varlen attention,
+    interpolated position table), feature scatter, DeepStack adds and the 3-D MRoPE decoder."""
+    import numpy as np
+
+    from omegalax_b200.models.qwen3_vl.config import Qwen3VLVisionConfig, make_vl_config
+    from omegalax_b200.models.qwen3_vl.model import get_rope_index
+    from omegalax_b200.ops import lib
+    from omegalax_b200.vlm import api as vlm_api
+
+    dev = _dev()
+    base = make_vl_config("qwen3-vl-smoke")
+    vis = Qwen3VLVisionConfig(hidden_size=256, intermediate_size=512, num_heads=4, patch_size=16, temporal_patch_size=2,
+                              in_channels=3, spatial_merge_size=2, out_hidden_size=256, depth=2,
+                              hidden_act="gelu_pytorch_tanh", num_position_embeddings=256, deepstack_visual_indexes=(0,))
+    cfg = dataclasses.replace(base, emb_dim=256, mlp_dim=512, num_heads=4, num_kv_heads=2, head_dim=128, vocab_size=2048,
+                              mrope_section=(24, 20, 20), vision=vis)
+    torch.manual_seed(0)
+    model, cfg = vlm_api.init_model(cfg, 0, tp_size=1, fsdp_size=1, dp_size=1)
+    model = model.to(dev).to(bf16)
+    B, T, n_img = 2, 96, 16
+    tok = torch.randint(5, cfg.vocab_size, (B, T), dtype=torch.int32)
+    tok[:, 0] = cfg.vision_start_token_id
+    tok[:, 1:1 + n_img] = cfg.image_token_id
+    grid = np.tile(np.array([[1, 8, 8]], dtype=np.int64), (B, 1))
+    pos, _ = get_rope_index(tok.numpy(), grid, None, None, 2, cfg.image_token_id, cfg.video_token_id,
+                            cfg.vision_start_token_id)
+    kw = dict(attention_mask_BT=torch.ones(B, T, dtype=torch.int32, device=dev),
+              pixel_values=torch.randn(64 * B, 3 * 2 * 16 * 16, device=dev),
+              image_grid_thw=[(1, 8, 8)] * B,
+              vision_cu_seqlens=torch.arange(B + 1, dtype=torch.int32, device=dev) * 64,
+              position_ids_ZBT=torch.from_numpy(pos).to(torch.int32).to(dev))
+    tok = tok.to(dev)
+
+    def run(reference):
+        if reference:
+            os.environ["OMEGALAX_B200_REFERENCE_OPS"] = "1"
+        else:
+            os.environ.pop("OMEGALAX_B200_REFERENCE_OPS", None)
+        for p in model.parameters():
+            p.grad = None
+        hidden, _ = vlm_api.forward(model, tok, 0, cfg, **kw)
+        logits = model.lm_head(hidden)
+        torch.nn.functional.cross_entropy(logits.float().view(-1, logits.shape[-1]), tok.view(-1).long()).backward()
+        return logits.detach().float(), {n: p.grad.detach().float().clone() for n, p in model.named_parameters()
+                                         if p.grad is not None}
+
+    lk, gk = run(False)
+    lib.check_status()
+    lr, gr = run(True)
+    err = (lk - lr).abs()
+    assert err.max() < 0.5 * max(1.0, float(lr.abs().max()) / 8), float(err.max())
+    assert err.median() < 0.02
+    assert set(gk) == set(gr)
+    bad = [(n, float((gk[n] - gr[n]).norm() / (gr[n].norm() + 1e-6))) for n in gk if float(gr[n].norm()) > 1e-4]
+    bad = [b for b in bad if b[1] > 0.2]
+    assert not bad, bad[:8]
