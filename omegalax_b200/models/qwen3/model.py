@@ -216,6 +216,10 @@ class DecoderLayer(nn.Module):
         return x, aux
 
 
+def vocab_parallel_head(cfg, tp_size: int) -> bool:
+    return tp_size > 1 and not cfg.tie_word_embeddings and cfg.vocab_size % (8 * tp_size) == 0
+
+
 class Qwen3(nn.Module):
     """Returns the final hidden states (before lm_head) and the summed auxiliary loss; the
     lm_head is a separate projection applied by callers (loss, decode)."""
@@ -229,7 +233,11 @@ class Qwen3(nn.Module):
         self.layers = nn.ModuleList(DecoderLayer(cfg, i, device=device, dtype=dtype, tp_size=tp_size)
                                     for i in range(cfg.num_layers))
         self.final_norm = RMSNorm(cfg.emb_dim, cfg.norm_eps, device=device, dtype=dtype)
-        self.lm_head = Linear(cfg.emb_dim, cfg.vocab_size, device=device, dtype=dtype)
+        # untied head under tensor parallelism: split over the vocabulary (vocab-parallel loss)
+        self.vocab_parallel = vocab_parallel_head(cfg, tp_size)
+        self.lm_head = Linear(cfg.emb_dim, cfg.vocab_size // tp_size if self.vocab_parallel else cfg.vocab_size,
+                              device=device, dtype=dtype)
+        self.lm_head.tp_sharded = self.vocab_parallel
         self.layer_runner = None  # installed by the training engine (remat / FSDP gather)
 
     def make_ctx(self, token_ids, segment_ids, position_offset: int = 0, start_ind=None) -> ForwardCtx:

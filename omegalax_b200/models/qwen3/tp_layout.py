@@ -23,7 +23,15 @@ def tp_slice(name: str, tensor: torch.Tensor, cfg, tp: int, rank: int) -> torch.
         return tensor[tp_lib.gate_up_rows_for_rank(tensor.shape[0] // 2, tp, rank)]
     if name.endswith("mlp.down_proj.weight"):
         return tp_lib.slice_cols(tensor, tp, rank)
+    if name == "lm_head.weight" and _vocab_parallel(cfg, tp):
+        return tp_lib.slice_rows(tensor, tp, rank)
     return tensor
+
+
+def _vocab_parallel(cfg, tp: int) -> bool:
+    from .model import vocab_parallel_head
+
+    return vocab_parallel_head(cfg, tp)
 
 
 def tp_unslice(name: str, parts: list[torch.Tensor], cfg) -> torch.Tensor:
@@ -31,6 +39,8 @@ def tp_unslice(name: str, parts: list[torch.Tensor], cfg) -> torch.Tensor:
     tp = len(parts)
     if tp == 1:
         return parts[0]
+    if name == "lm_head.weight" and _vocab_parallel(cfg, tp):
+        return torch.cat(parts, dim=0)
     if name.endswith("attn.o_proj.weight") or name.endswith("mlp.down_proj.weight"):
         return torch.cat(parts, dim=1)
     if name.endswith("attn.qkv_proj.weight") or name.endswith("attn.qkv_proj.bias"):

@@ -428,6 +428,75 @@ __global__ void ce_fwd_bwd_kernel(bf16* __restrict__ logits, long long ld, int V
   }
 }
 
+// Vocabulary-parallel variant, two passes around an all-reduce of the row statistics.  This GPU
+// holds the logits of vocabulary ids [v0, v0 + V).  Pass 1: row maximum, sum of exp(x - max) and
+// the target's logit (zero when another GPU owns the target).  Pass 2 (after the caller has
+// combined the statistics into the global log-sum-exp): overwrite with dlogits.
+__global__ void ce_vp_stats_kernel(const bf16* __restrict__ logits, long long ld, int V, int v0,
+                                   const int* __restrict__ targets, float* __restrict__ max_out,
+                                   float* __restrict__ sum_out, float* __restrict__ tgt_out) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const bf16* lr = logits + row * ld;
+  const int nv = V >> 3;
+  const uint4* lv = reinterpret_cast<const uint4*>(lr);
+  float mx = -INFINITY, sm = 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    uint4 q = lv[i];
+    uint32_t u[4] = {q.x, q.y, q.z, q.w};
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = unpack_bf16(u[j]);
+      f[2 * j] = t.x; f[2 * j + 1] = t.y;
+    }
+    float lm = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
+    if (lm > mx) {
+      sm *= __expf(mx - lm);
+      mx = lm;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sm += __expf(f[j] - mx);
+  }
+  const float gmx = block_max(mx, red);
+  sm *= (mx == -INFINITY) ? 0.f : __expf(mx - gmx);
+  const float gsum = block_sum(sm, red);
+  if (threadIdx.x == 0) {
+    const int t = targets[row] - v0;
+    max_out[row] = gmx;
+    sum_out[row] = gsum;
+    tgt_out[row] = (t >= 0 && t < V) ? __bfloat162float(lr[t]) : 0.f;
+  }
+}
+
+__global__ void ce_vp_grad_kernel(bf16* __restrict__ logits, long long ld, int V, int v0,
+                                  const int* __restrict__ targets, const float* __restrict__ lse_in,
+                                  const float* __restrict__ mask, const float* __restrict__ grad_scale) {
+  const long long row = blockIdx.x;
+  bf16* lr = logits + row * ld;
+  const int tgt = targets[row] - v0;
+  const float lse = lse_in[row];
+  const float gs = (mask ? mask[row] : 1.f) * (grad_scale ? *grad_scale : 1.f);
+  const int nv = V >> 3;
+  uint4* ov = reinterpret_cast<uint4*>(lr);
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    uint4 q = ov[i], o;
+    uint32_t u[4] = {q.x, q.y, q.z, q.w}, ou[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 t = unpack_bf16(u[j]);
+      int c0 = i * 8 + 2 * j;
+      float p0 = __expf(t.x - lse) - (c0 == tgt ? 1.f : 0.f);
+      float p1 = __expf(t.y - lse) - (c0 + 1 == tgt ? 1.f : 0.f);
+      ou[j] = pack_bf16(p0 * gs, p1 * gs);
+    }
+    o.x = ou[0]; o.y = ou[1]; o.z = ou[2]; o.w = ou[3];
+    ov[i] = o;
+  }
+}
+
 // ------------------------------------------------------------------ embedding (K13)
 __global__ void embedding_fwd_kernel(const int* __restrict__ ids, const bf16* __restrict__ table,
                                      bf16* __restrict__ out, long long M, int D) {
@@ -688,6 +757,24 @@ int ob_ce_fwd_bwd(void* logits, long long ld, long long R, int V, const int* tar
   if (R <= 0) return 0;
   ce_fwd_bwd_kernel<<<(unsigned)R, 512, 0, s>>>((bf16*)logits, ld, V, targets, mask, grad_scale,
                                                 loss_sum, lse_out, write_grad);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_ce_vp_stats(const void* logits, long long R, int V, long long ld, int v0, const int* targets, float* mx,
+                   float* sm, float* tg, cudaStream_t s) {
+  if (V % 8 || ld % 8) return 6001;
+  if (R <= 0) return 0;
+  ce_vp_stats_kernel<<<(unsigned)R, 512, 0, s>>>((const bf16*)logits, ld, V, v0, targets, mx, sm, tg);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_ce_vp_grad(void* logits, long long R, int V, long long ld, int v0, const int* targets, const float* lse,
+                  const float* mask, const float* grad_scale, cudaStream_t s) {
+  if (V % 8 || ld % 8) return 6001;
+  if (R <= 0) return 0;
+  ce_vp_grad_kernel<<<(unsigned)R, 512, 0, s>>>((bf16*)logits, ld, V, v0, targets, lse, mask, grad_scale);
   OB_CHECK_LAUNCH();
   return 0;
 }

@@ -541,6 +541,97 @@ class _LinearCEFn(torch.autograd.Function):
         return gh, gw, None, None, None, None
 
 
+class _VocabParallelCEFn(torch.autograd.Function):
+    """Cross-entropy with the head split over the tensor-parallel ranks on the vocabulary and
+    the hidden rows split on the sequence.  h [M/tp, D] (this rank's rows), w [V/tp, D] (this
+    rank's vocabulary slice), targets / mask [M] for all rows.  The rows are gathered, every rank
+    scores them against its slice, the per-row (max, sum-exp, target logit) are combined with
+    two small all-reduces, and the gradients are produced in the same sweep: dW stays local,
+    the partial dH of the slices is reduce-scattered back to the row owners.  The returned loss
+    is 1/tp of the full loss (the ranks' values add up to it); the stored gradients are those
+    of the full loss."""
+
+    @staticmethod
+    def forward(ctx, h, w, targets, mask, scale_t, tp, chunk):
+        import torch.distributed as dist
+
+        from ..parallel import tp as tp_lib
+
+        use_k = use_kernels(h) and w.dtype == bf16
+        h_full = tp_lib._ag_rows(h.contiguous(), tp)
+        M, D = h_full.shape
+        Vl = w.shape[0]
+        v0 = tp.rank * Vl
+        dev = h.device
+        need_grad = h.requires_grad or w.requires_grad
+        mg = getattr(w, "main_grad", None)
+        pg = getattr(w, "peer_grad", None)
+        dh_full = torch.empty_like(h_full) if need_grad else None
+        dw = None
+        if need_grad and w.requires_grad and pg is None:
+            dw = mg if mg is not None else torch.zeros(Vl, D, dtype=torch.float32, device=dev)
+        t32 = targets.to(torch.int32).contiguous()
+        mk = mask.to(torch.float32).contiguous()
+        loss_sum = torch.zeros(1, dtype=torch.float32, device=dev)
+        for r0 in range(0, M, chunk):
+            r1 = min(M, r0 + chunk)
+            hc = h_full[r0:r1]
+            if use_k:
+                lg = K.gemm(hc, w)
+                mx, sm, tg = K.ce_vp_stats(lg, t32[r0:r1], v0)
+            else:
+                lg = (hc.float() @ w.float().t())
+                mx = lg.max(-1).values
+                sm = torch.exp(lg - mx[:, None]).sum(-1)
+                loc = t32[r0:r1].long() - v0
+                ok = (loc >= 0) & (loc < Vl)
+                tg = torch.where(ok, lg.gather(1, loc.clamp(0, Vl - 1)[:, None]).squeeze(1), torch.zeros_like(mx))
+            gmax = mx.clone()
+            dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=tp.group)
+            pack = torch.stack([sm * torch.exp(mx - gmax), tg])
+            dist.all_reduce(pack, group=tp.group)
+            lse = gmax + torch.log(pack[0])
+            loss_sum += (mk[r0:r1] * (lse - pack[1])).sum()
+            if not need_grad:
+                continue
+            if use_k:
+                K.ce_vp_grad_(lg, t32[r0:r1], v0, lse.contiguous(), mk[r0:r1], scale_t)
+                K.gemm(lg, w, b_mn=True, out=dh_full[r0:r1])
+                if pg is not None:
+                    K.gemm_peer_reduce(lg, hc, pg[0], pg[1], pg[2], a_mn=True, b_mn=True)
+                elif dw is not None:
+                    K.gemm(lg, hc, a_mn=True, b_mn=True, out=dw, accumulate=True)
+            else:
+                p_ = torch.exp(lg - lse[:, None])
+                loc = t32[r0:r1].long() - v0
+                ok = (loc >= 0) & (loc < Vl)
+                p_[ok.nonzero().squeeze(1), loc[ok]] -= 1.0
+                dl = p_ * (mk[r0:r1] * scale_t)[:, None]
+                dh_full[r0:r1] = (dl @ w.float()).to(h.dtype)
+                if dw is not None:
+                    dw += dl.t() @ hc.float()
+        dh = tp_lib._rs_rows(dh_full, tp) if need_grad else None
+        ctx.save_for_backward(dh)
+        ctx.dw = None if (mg is not None or dw is None) else dw
+        ctx.w_dtype = w.dtype
+        return (loss_sum * scale_t).squeeze(0) / tp.size
+
+    @staticmethod
+    def backward(ctx, g):
+        (dh,) = ctx.saved_tensors
+        dw = ctx.dw
+        gh = None if dh is None else (dh * g.to(dh.dtype))
+        gw = None if dw is None else (dw * g).to(ctx.w_dtype)
+        return gh, gw, None, None, None, None, None
+
+
+def linear_cross_entropy_vocab_parallel(h_local, w_local, targets, mask, scale, tp, chunk: int = 4096):
+    """Vocabulary-parallel fused linear + cross-entropy (see ``_VocabParallelCEFn``)."""
+    if not torch.is_tensor(scale):
+        scale = torch.tensor([float(scale)], dtype=torch.float32, device=h_local.device)
+    return _VocabParallelCEFn.apply(h_local, w_local, targets, mask, scale.reshape(1).to(torch.float32), tp, chunk)
+
+
 def linear_cross_entropy(h, w, targets, mask, scale, chunk: int = 4096):
     """scale * sum_i mask_i * CE(h_i W^T, targets_i).
 

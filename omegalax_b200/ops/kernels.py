@@ -505,3 +505,18 @@ def gelu_tanh_bwd(x, dy):
     dx = torch.empty_like(x)
     _call("ob_gelu_tanh_bwd", x.data_ptr(), dy.data_ptr(), dx.data_ptr(), x.numel(), lib.stream_ptr())
     return dx
+
+
+def ce_vp_stats(logits, targets32, v0):
+    R, V = logits.shape
+    mx, sm, tg = (torch.empty(R, dtype=torch.float32, device=logits.device) for _ in range(3))
+    _call("ob_ce_vp_stats", logits.data_ptr(), R, V, logits.stride(0), int(v0), targets32.data_ptr(), mx.data_ptr(),
+          sm.data_ptr(), tg.data_ptr(), lib.stream_ptr())
+    return mx, sm, tg
+
+
+def ce_vp_grad_(logits, targets32, v0, lse, mask, grad_scale):
+    R, V = logits.shape
+    _call("ob_ce_vp_grad", logits.data_ptr(), R, V, logits.stride(0), int(v0), targets32.data_ptr(), lse.data_ptr(),
+          lib.ptr(mask), lib.ptr(grad_scale), lib.stream_ptr())
+    return logits

@@ -50,6 +50,8 @@ _SIGS = {
     "ob_gather4_bwd": [P, P, P, P, L, I, P],
     "ob_gelu_tanh_fwd": [P, P, L, P],
     "ob_gelu_tanh_bwd": [P, P, P, L, P],
+    "ob_ce_vp_stats": [P, L, I, L, I, P, P, P, P, P],
+    "ob_ce_vp_grad": [P, L, I, L, I, P, P, P, P, P],
     "ob_moe_count": [P, P, L, I, P],
     "ob_ep_plan": [P, P, P, P, P, P, P, L, I, I, I, I, I, P],
     "ob_moe_plan": [P, P, P, P, P, L, I, I, I, P],

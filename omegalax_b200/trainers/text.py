@@ -105,7 +105,12 @@ def _loss_and_count(model, cfg, batch, pad_id: int, group):
         msk = torch.roll(mask, -1, dims=1).to(torch.float32)
         msk[:, -1] = 0
         sl = slice(tp.rank * m, (tp.rank + 1) * m)
-        ce = Fn.linear_cross_entropy(rows, model.lm_head.weight, tgt[sl], msk.reshape(-1)[sl], 1.0 / count.clamp_min(1.0))
+        if getattr(model, "vocab_parallel", False):   # head split over the vocabulary: all rows, this rank's slice
+            ce = Fn.linear_cross_entropy_vocab_parallel(rows, model.lm_head.weight, tgt, msk.reshape(-1),
+                                                        1.0 / count.clamp_min(1.0), tp)
+        else:
+            ce = Fn.linear_cross_entropy(rows, model.lm_head.weight, tgt[sl], msk.reshape(-1)[sl],
+                                         1.0 / count.clamp_min(1.0))
         return ce, aux / tp.size, count
     hidden, aux = text_api.forward(model, tok, pad_id, cfg)
     ce = chunked_cross_entropy_loss(hidden, model.lm_head.weight, tok, mask, num_tiles=_NUM_LOSS_TILES, count=count)

@@ -53,7 +53,7 @@ def fsdp_train(rank, world, port, model_id, steps, out_path, ckpt_dir=None, resu
     dist.destroy_process_group()
 
 
-def tp_train(rank, world, port, tp, steps, out_path):
+def tp_train(rank, world, port, tp, steps, out_path, untied=False):
     """Same weights, same batch: tensor-parallel (tp) x fsdp (world/tp) run on CPU ranks."""
     _init(rank, world, port)
     import dataclasses
@@ -69,6 +69,8 @@ def tp_train(rank, world, port, tp, steps, out_path):
     tp_lib.set_current(None)
     mesh = mesh_lib.ensure_mesh(tp_size=tp, fsdp_size=world // tp, dp_size=1)
     cfg = dataclasses.replace(make_config("qwen3-smoke"), num_kv_heads=2)
+    if untied:   # a separate head: split over the vocabulary under tp (vocab-parallel loss)
+        cfg = dataclasses.replace(cfg, tie_word_embeddings=False)
     torch.manual_seed(0)
     full = Qwen3(cfg, dtype=torch.float32)                       # identical on every rank
     tcfg = trainer.TrainConfig(seed=0, batch_size=2 * (world // tp), seq_len=32, num_steps=100, learning_rate=1e-2,
@@ -94,7 +96,8 @@ def tp_train(rank, world, port, tp, steps, out_path):
     batch = {"token_ids_BT": tok[sl], "attention_mask_BT": torch.ones(2, 32, dtype=torch.int32), "loss_mask_BT": lm[sl]}
     losses = [float(step(opt, batch)[0]) for _ in range(steps)]
     if rank == 0:
-        torch.save({"losses": losses, "grad_norm": float(opt.last_grad_norm)}, out_path)
+        torch.save({"losses": losses, "grad_norm": float(opt.last_grad_norm),
+                    "vocab_parallel": bool(getattr(model, "vocab_parallel", False))}, out_path)
     dist.barrier()
     tp_lib.set_current(None)
     dist.destroy_process_group()

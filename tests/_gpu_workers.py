@@ -168,7 +168,9 @@ def tp_train_gpu(rank, world, port, tp, steps, out_path):
     lib.check_status()
     ctx = tp_lib.current()
     if rank == 0:
-        torch.save({"losses": losses, "transport": ctx.transport if ctx else "none"}, out_path)
+        torch.save({"losses": losses, "transport": ctx.transport if ctx else "none",
+                    "vocab_parallel": bool(getattr(model, "vocab_parallel", False)),
+                    "fused_gathers": int(getattr(ctx, "_ag_calls", 0)) if ctx else 0}, out_path)
     if world > 1:
         dist.barrier()
     tp_lib.set_current(None)

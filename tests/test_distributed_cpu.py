@@ -57,6 +57,20 @@ def test_tensor_parallel_matches_single_rank(tmp_path):
     assert one["grad_norm"] == pytest.approx(two["grad_norm"], rel=2e-3)
 
 
+def test_vocab_parallel_head_matches_single_rank(tmp_path):
+    """Untied head under tp=2: the head is split over the vocabulary and the loss combines the
+    per-slice softmax statistics; loss curve and gradient norm match the tp=1 run."""
+    def run(world, tp, name):
+        mp.spawn(W.tp_train, args=(world, _port(), tp, 3, str(tmp_path / name), True), nprocs=world, join=True)
+        return torch.load(tmp_path / name)
+
+    one = run(1, 1, "a.pt")
+    two = run(2, 2, "b.pt")
+    assert two["vocab_parallel"] and not one["vocab_parallel"]
+    assert one["losses"] == pytest.approx(two["losses"], rel=3e-4, abs=3e-4)
+    assert one["grad_norm"] == pytest.approx(two["grad_norm"], rel=2e-3)
+
+
 def test_tp_slices_roundtrip():
     from omegalax_b200.models.qwen3.config import make_config
     from omegalax_b200.models.qwen3.model import Qwen3

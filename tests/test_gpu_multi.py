@@ -90,5 +90,7 @@ def test_tensor_parallel_two_gpus_matches_one(tmp_path):
     mp.spawn(W.tp_train_gpu, args=(2, _port(), 2, 4, str(tmp_path / "two.pt")), nprocs=2, join=True)
     a, b = torch.load(tmp_path / "one.pt"), torch.load(tmp_path / "two.pt")
     assert b["transport"] == "p2p"
+    assert b["vocab_parallel"]          # untied head: split over the vocabulary, CE statistics combined over tp
+    assert b["fused_gathers"] > 0       # column-parallel projections gather inside their GEMM launch
     assert b["losses"][-1] < b["losses"][0]
     assert a["losses"] == pytest.approx(b["losses"], rel=3e-2, abs=3e-2)
