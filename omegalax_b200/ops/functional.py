@@ -441,6 +441,12 @@ def _attn_bwd_dispatch(q, k, v, o, lse, do, cu_seqlens, max_seqlen, scale, causa
     """dq, dk, dv of packed-row attention."""
     if q.shape[-1] == 128 and os.environ.get("OMEGALAX_B200_ATTN_BWD", "sm100") == "sm100":
         return K.attn_bwd(q, k, v, o, lse, do, cu_seqlens, max_seqlen, scale, causal)
+    if q.shape[-1] == 64 and os.environ.get("OMEGALAX_B200_ATTN_BWD", "sm100") == "sm100":
+        # 64-wide heads (vision tower): run the 128-wide kernel on zero-padded heads.  The padding
+        # channels add nothing to q.k and receive zero gradients; the scale stays that of width 64.
+        pad = lambda t: F.pad(t, (0, 64))
+        dq, dk, dv = K.attn_bwd(pad(q), pad(k), pad(v), pad(o), lse, pad(do), cu_seqlens, max_seqlen, scale, causal)
+        return dq[..., :64].contiguous(), dk[..., :64].contiguous(), dv[..., :64].contiguous()
     # recompute through the PyTorch definition (reference quality; used only until the
     # tcgen05 backward is selected)
     with torch.enable_grad():

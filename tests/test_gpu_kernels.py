@@ -583,3 +583,25 @@ def test_gather_scatter_gelu_kernels():
     gr.backward(dg.float())
     assert _rel_err(g, gr) < 1e-2 and _rel_err(z.grad, zr.grad) < 2e-2
     _check(lib)
+
+
+def test_attention_backward_head_dim_64_varlen():
+    """64-wide heads (vision tower): non-causal packed sequences of different lengths."""
+    from omegalax_b200.ops import functional as Fn, reference as R, lib
+    torch.manual_seed(12)
+    dev = _dev()
+    H, HD = 4, 64
+    lens = [200, 64, 333]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=dev, dtype=torch.int32)
+    N = sum(lens)
+    q, k, v = (torch.randn(N, H, HD, device=dev).to(bf16).requires_grad_(True) for _ in range(3))
+    o = Fn.flash_attention(q, k, v, cu, max(lens), scale=HD ** -0.5, causal=False)
+    do = torch.randn_like(o)
+    o.backward(do)
+    _check(lib)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = R.attention_varlen(qr, kr, vr, cu, causal=False, scale=HD ** -0.5)
+    ref.backward(do.float())
+    assert _rel_err(o, ref) < 2e-2
+    for a, b in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
+        assert _rel_err(a, b) < 3e-2
