@@ -364,6 +364,110 @@ __global__ void qknorm_rope_bwd_kernel(const bf16* __restrict__ qkv, const bf16*
     for (int i = threadIdx.x; i < K; i += blockDim.x) atomicAdd(dkw + i, dw_sm[K + i]);
 }
 
+// Fast path for head_dim 128 with full rotation (Qwen3 / Qwen3-VL text): every lane owns the
+// channel pairs (2l, 2l+1) and (64+2l, 65+2l), i.e. both partners of its rotations, so a head
+// is read once with 4-byte accesses, and the weight gradients are accumulated in registers over
+// all the (row, head) items a warp visits.
+__device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
+template <bool kOnePlus>
+__global__ void qknorm_rope_fwd128_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw,
+                                          const bf16* __restrict__ kw, const float* __restrict__ cosT,
+                                          const float* __restrict__ sinT, bf16* __restrict__ q_out,
+                                          bf16* __restrict__ k_out, long long M, int H, int G, float eps) {
+  constexpr int K = 128;
+  const int lane = threadIdx.x & 31;
+  const long long wid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int HG = H + G;
+  if (wid >= M * HG) return;
+  const long long m = wid / HG;
+  const int h = (int)(wid - m * HG);
+  const bool is_q = h < H;
+  const bf16* src = qkv + m * (long long)(H + 2 * G) * K + (long long)h * K;
+  const bf16* w = is_q ? qw : kw;
+  bf16* dst = is_q ? q_out + (m * H + h) * K : k_out + (m * G + (h - H)) * K;
+  const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(src + 2 * lane));
+  const float2 b = unpack_bf16(*reinterpret_cast<const uint32_t*>(src + 64 + 2 * lane));
+  float ss = a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+  ss = warp_sum(ss);
+  const float rstd = w ? rsqrtf(ss / (float)K + eps) : 1.f;
+  float2 wa = make_float2(1.f, 1.f), wb = wa;
+  if (w) {
+    wa = unpack_bf16(*reinterpret_cast<const uint32_t*>(w + 2 * lane));
+    wb = unpack_bf16(*reinterpret_cast<const uint32_t*>(w + 64 + 2 * lane));
+    if (kOnePlus) { wa.x += 1.f; wa.y += 1.f; wb.x += 1.f; wb.y += 1.f; }
+  }
+  const float2 c = *reinterpret_cast<const float2*>(cosT + m * 64 + 2 * lane);
+  const float2 sn = *reinterpret_cast<const float2*>(sinT + m * 64 + 2 * lane);
+  const float x1a = bf16r(a.x * rstd * wa.x), x1b = bf16r(a.y * rstd * wa.y);
+  const float x2a = bf16r(b.x * rstd * wb.x), x2b = bf16r(b.y * rstd * wb.y);
+  *reinterpret_cast<uint32_t*>(dst + 2 * lane) = pack_bf16(x1a * c.x - x2a * sn.x, x1b * c.y - x2b * sn.y);
+  *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = pack_bf16(x2a * c.x + x1a * sn.x, x2b * c.y + x1b * sn.y);
+}
+
+template <bool kOnePlus>
+__global__ void qknorm_rope_bwd128_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw,
+                                          const bf16* __restrict__ kw, const float* __restrict__ cosT,
+                                          const float* __restrict__ sinT, const bf16* __restrict__ dq_rot,
+                                          const bf16* __restrict__ dk_rot, bf16* __restrict__ dqkv,
+                                          float* __restrict__ dqw, float* __restrict__ dkw, long long M, int H,
+                                          int G, float eps) {
+  constexpr int K = 128;
+  __shared__ float red[8][2 * K];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  const int HG = H + G;
+  const long long row_stride = (long long)(H + 2 * G) * K;
+  float gq[4] = {0.f, 0.f, 0.f, 0.f}, gk[4] = {0.f, 0.f, 0.f, 0.f};
+  for (long long item = blockIdx.x * (long long)(blockDim.x >> 5) + warp; item < M * HG; item += nwarps) {
+    const long long m = item / HG;
+    const int h = (int)(item - m * HG);
+    const bool is_q = h < H;
+    const bf16* src = qkv + m * row_stride + (long long)h * K;
+    const bf16* w = is_q ? qw : kw;
+    const bf16* dsrc = is_q ? dq_rot + (m * H + h) * K : dk_rot + (m * G + (h - H)) * K;
+    bf16* ddst = dqkv + m * row_stride + (long long)h * K;
+    const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(src + 2 * lane));
+    const float2 b = unpack_bf16(*reinterpret_cast<const uint32_t*>(src + 64 + 2 * lane));
+    const float2 da = unpack_bf16(*reinterpret_cast<const uint32_t*>(dsrc + 2 * lane));
+    const float2 db = unpack_bf16(*reinterpret_cast<const uint32_t*>(dsrc + 64 + 2 * lane));
+    const float2 c = *reinterpret_cast<const float2*>(cosT + m * 64 + 2 * lane);
+    const float2 sn = *reinterpret_cast<const float2*>(sinT + m * 64 + 2 * lane);
+    float ss = a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+    ss = warp_sum(ss);
+    const float rstd = w ? rsqrtf(ss / (float)K + eps) : 1.f;
+    float2 wa = make_float2(1.f, 1.f), wb = wa;
+    if (w) {
+      wa = unpack_bf16(*reinterpret_cast<const uint32_t*>(w + 2 * lane));
+      wb = unpack_bf16(*reinterpret_cast<const uint32_t*>(w + 64 + 2 * lane));
+      if (kOnePlus) { wa.x += 1.f; wa.y += 1.f; wb.x += 1.f; wb.y += 1.f; }
+    }
+    // un-rotate: gradient w.r.t. the normalised, weighted values
+    const float n1a = da.x * c.x + db.x * sn.x, n1b = da.y * c.y + db.y * sn.y;
+    const float n2a = db.x * c.x - da.x * sn.x, n2b = db.y * c.y - da.y * sn.y;
+    if (w) {
+      float* gw = is_q ? gq : gk;
+      gw[0] = fmaf(n1a * a.x, rstd, gw[0]); gw[1] = fmaf(n1b * a.y, rstd, gw[1]);
+      gw[2] = fmaf(n2a * b.x, rstd, gw[2]); gw[3] = fmaf(n2b * b.y, rstd, gw[3]);
+    }
+    float dot = n1a * wa.x * a.x + n1b * wa.y * a.y + n2a * wb.x * b.x + n2b * wb.y * b.y;
+    dot = warp_sum(dot);
+    const float cc = w ? dot * rstd * rstd * rstd / (float)K : 0.f;
+    *reinterpret_cast<uint32_t*>(ddst + 2 * lane) = pack_bf16(n1a * wa.x * rstd - a.x * cc, n1b * wa.y * rstd - a.y * cc);
+    *reinterpret_cast<uint32_t*>(ddst + 64 + 2 * lane) = pack_bf16(n2a * wb.x * rstd - b.x * cc, n2b * wb.y * rstd - b.y * cc);
+  }
+  float* r = red[warp];
+  r[2 * lane] = gq[0]; r[2 * lane + 1] = gq[1]; r[64 + 2 * lane] = gq[2]; r[65 + 2 * lane] = gq[3];
+  r[K + 2 * lane] = gk[0]; r[K + 2 * lane + 1] = gk[1]; r[K + 64 + 2 * lane] = gk[2]; r[K + 65 + 2 * lane] = gk[3];
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2 * K; i += blockDim.x) {
+    float sacc = 0.f;
+    for (int wi = 0; wi < (int)(blockDim.x >> 5); ++wi) sacc += red[wi][i];
+    if (i < K) { if (qw && dqw) atomicAdd(dqw + i, sacc); }
+    else if (kw && dkw) atomicAdd(dkw + i - K, sacc);
+  }
+}
+
 // ------------------------------------------------------------------ softmax cross-entropy
 // One CTA per row of a bf16 logits chunk [R, V] (pitch ld).  Adds mask*nll to loss_sum and
 // overwrites the row with dlogits = (softmax - onehot) * mask * (*grad_scale).
@@ -715,6 +819,16 @@ int ob_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw, const fl
   long long warps = M * (H + G);
   int threads = 256;
   long long blocks = (warps * 32 + threads - 1) / threads;
+  if (K == 128 && rot == 128 && q_stride_heads == 1) {
+    if (one_plus)
+      qknorm_rope_fwd128_kernel<true><<<(unsigned)blocks, threads, 0, s>>>(
+          (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (bf16*)q_out, (bf16*)k_out, M, H, G, eps);
+    else
+      qknorm_rope_fwd128_kernel<false><<<(unsigned)blocks, threads, 0, s>>>(
+          (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (bf16*)q_out, (bf16*)k_out, M, H, G, eps);
+    OB_CHECK_LAUNCH();
+    return 0;
+  }
   if (one_plus)
     qknorm_rope_fwd_kernel<true><<<(unsigned)blocks, threads, 0, s>>>(
         (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (bf16*)q_out, (bf16*)k_out,
@@ -733,6 +847,20 @@ int ob_qknorm_rope_bwd(const void* qkv, const void* qw, const void* kw, const fl
                        float eps, int one_plus, int q_stride_heads, cudaStream_t s) {
   if (M <= 0) return 0;
   const int threads = 256;
+  if (K == 128 && rot == 128 && q_stride_heads == 1) {
+    long long want = (M * (H + G) + 7) / 8;
+    const unsigned nb = (unsigned)(want < (long long)num_sms() * 8 ? want : (long long)num_sms() * 8);
+    if (one_plus)
+      qknorm_rope_bwd128_kernel<true><<<nb, threads, 0, s>>>(
+          (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (const bf16*)dq_rot, (const bf16*)dk_rot,
+          (bf16*)dqkv, dqw, dkw, M, H, G, eps);
+    else
+      qknorm_rope_bwd128_kernel<false><<<nb, threads, 0, s>>>(
+          (const bf16*)qkv, (const bf16*)qw, (const bf16*)kw, cosT, sinT, (const bf16*)dq_rot, (const bf16*)dk_rot,
+          (bf16*)dqkv, dqw, dkw, M, H, G, eps);
+    OB_CHECK_LAUNCH();
+    return 0;
+  }
   const int rows_per_block = 16;
   long long blocks = (M + rows_per_block - 1) / rows_per_block;
   size_t sm = 2 * K * sizeof(float);

@@ -152,6 +152,20 @@ def bench_elementwise(a, dev, flush):
     w = torch.ones(D, device=dev).to(bf16)
     by = 2.0 * M * D * 2
     _report("rmsnorm fwd", timeit(lambda: K.rmsnorm_fwd(x, w, 1e-6), a.iters, a.warmup, flush), None, by, rows=M, cols=D)
+    H, G, Kd = 32, 8, 128
+    qkv = torch.randn(M, (H + 2 * G) * Kd, device=dev).to(bf16)
+    qw, kw = torch.ones(Kd, device=dev).to(bf16), torch.ones(Kd, device=dev).to(bf16)
+    ang = torch.rand(M, Kd // 2, device=dev) * 6.28
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    q, k = K.qknorm_rope_fwd(qkv, qw, kw, cos, sin, H, G, Kd, Kd, 1e-6)
+    qb = 2.0 * M * (H + G) * Kd * 2
+    _report("qk-norm + rope fwd", timeit(lambda: K.qknorm_rope_fwd(qkv, qw, kw, cos, sin, H, G, Kd, Kd, 1e-6),
+                                         a.iters, a.warmup, flush), None, qb, rows=M, heads=H, kv_heads=G)
+    dqkv = torch.zeros_like(qkv)
+    dqw, dkw = torch.zeros(Kd, device=dev), torch.zeros(Kd, device=dev)
+    _report("qk-norm + rope bwd",
+            timeit(lambda: K.qknorm_rope_bwd(qkv, qw, kw, cos, sin, q, k, dqkv, dqw, dkw, H, G, Kd, Kd, 1e-6),
+                   a.iters, a.warmup, flush), None, 1.5 * qb)
     gu = torch.randn(M, 2 * D, device=dev).to(bf16)
     _report("swiglu fwd", timeit(lambda: K.swiglu_fwd(gu), a.iters, a.warmup, flush), None, 3.0 * M * D * 2)
 
