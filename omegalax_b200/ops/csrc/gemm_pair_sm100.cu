@@ -1,0 +1,307 @@
+// K1, CTA-pair variant: one 256 x 256 output tile per cluster of two CTAs (tcgen05 cta_group::2).
+//
+//   C[M,N] (+)= op(A) * op(B)^T       fp32 accumulation in TMEM, same operand layouts as gemm_sm100.cu
+//
+// Each CTA stages its own 128 rows of the A tile and its own 128 rows of the B tile (the MMA reads
+// both CTAs' shared memory), so a k-block moves 32 KB into each SM for 2 x 128 x 256 x 64 MACs:
+// two thirds of the shared-memory / L2 traffic per FLOP of the single-CTA 128 x 256 tile, and a
+// six-stage ring fits.  No load is multicast: every CTA fetches what it needs itself.
+//
+// Roles per CTA (192 threads): warp 0 = TMA producer (both CTAs), warp 1 = TMEM allocation (both)
+// and MMA issue (even CTA only), warps 2..5 = epilogue (both; each CTA drains its 128 rows).
+// Barriers: the "stage full" and "accumulator empty" barriers that the issuing thread waits on
+// live in the even CTA; the odd CTA's TMA loads and epilogue warps signal them through their
+// shared::cluster addresses.  "Stage empty" and "accumulator full" are signalled in both CTAs by
+// two tcgen05.commit, one per CTA.  Every wait is bounded.
+#include "gemm_common.cuh"
+#include "host_utils.h"
+
+namespace ob {
+
+constexpr int kPairStages = 6;
+constexpr int kPairBN = 256;        // tile columns (per pair)
+constexpr int kPairBNL = 128;       // B rows staged per CTA
+
+struct PairSmem {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = kPairBNL * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOff = kPairStages * kStageBytes;
+  static constexpr int kTotal = kBarOff + 256 + 1024;
+};
+
+struct PairTile {
+  int row0;        // first row of this CTA's half of the tile (A rows and C rows)
+  int b_row0;      // first B row (= output column) this CTA stages
+  int c_col0;      // first output column of the tile
+  int rows_valid, cols_valid;
+};
+
+__device__ __forceinline__ PairTile pair_tile(const GemmArgs& p, int t, int rank) {
+  // 4 tile rows (1024 output rows) share a sweep over the tile columns for L2 reuse
+  const int GM = 4;
+  const int per_group = GM * p.num_n_blocks;
+  const int g = t / per_group;
+  const int first_m = g * GM;
+  const int gm = min(GM, p.num_m_blocks - first_m);
+  const int r = t - g * per_group;
+  const int mb = first_m + (r % gm);
+  const int nb = r / gm;
+  PairTile ti;
+  ti.row0 = mb * 256 + rank * 128;
+  ti.b_row0 = nb * kPairBN + rank * kPairBNL;
+  ti.c_col0 = nb * kPairBN;
+  ti.rows_valid = min(128, p.M - ti.row0);
+  ti.cols_valid = min(kPairBN, p.N - ti.c_col0);
+  return ti;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const GemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  using L = PairSmem;
+  uint64_t* full_bar = (uint64_t*)(smem + L::kBarOff);
+  uint64_t* empty_bar = full_bar + kPairStages;
+  uint64_t* tfull_bar = empty_bar + kPairStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = (uint32_t*)(tempty_bar + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int rank = (int)cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair0 = (int)(blockIdx.x >> 1);
+  const int pair_step = (int)(gridDim.x >> 1);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kPairStages; ++i) {
+      mbar_init(&full_bar[i], 1);    // the even CTA's expect_tx arrival (bytes of both CTAs)
+      mbar_init(&empty_bar[i], 1);   // one tcgen05.commit per CTA
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 8);  // 4 epilogue warps of each CTA (used in the even CTA only)
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 2 * kPairBN);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();   // both CTAs' barriers are initialised before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair0; t < p.total_tiles && ok; t += pair_step) {
+        const PairTile ti = pair_tile(p, t, rank);
+        for (int k0 = 0; k0 < p.K; k0 += BK) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_EMPTY);
+          if (!ok) break;
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
+          const uint32_t fb = mapa_shared(smem_u32(&full_bar[stage]), 0);   // the even CTA's barrier
+          if (!A_MN) {
+            tma_load_2d_pair(sa, &tmA, fb, k0, ti.row0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * (BK * 128), &tmA, fb, ti.row0 + j * 64, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(sb, &tmB, fb, k0, ti.b_row0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kPairBNL / 64; ++j)
+              tma_load_2d_pair(sb + j * (BK * 128), &tmB, fb, ti.b_row0 + j * 64, k0);
+          }
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_bf16(256, kPairBN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair0; t < p.total_tiles && ok; t += pair_step) {
+        ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kPairBN;
+        uint32_t accumulate = 0;
+        for (int k0 = 0; k0 < p.K; k0 += BK) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, OB_ERR_WAIT_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            uint64_t adesc = A_MN ? make_smem_desc(sa + k * 2048, BK * 128, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
+            uint64_t bdesc = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
+            umma_ss_pair(d_tmem, adesc, bdesc, idesc, accumulate);
+            accumulate = 1;
+          }
+          // the stage is free in both CTAs once these MMAs retire
+          umma_commit_pair(mapa_shared(smem_u32(&empty_bar[stage]), 0));
+          umma_commit_pair(mapa_shared(smem_u32(&empty_bar[stage]), 1));
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(mapa_shared(smem_u32(&tfull_bar[acc]), 0));
+        umma_commit_pair(mapa_shared(smem_u32(&tfull_bar[acc]), 1));
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quad = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int t = pair0; t < p.total_tiles && ok; t += pair_step) {
+      const PairTile ti = pair_tile(p, t, rank);
+      ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      const int r = quad * 32 + lane;
+      const bool row_ok = r < ti.rows_valid;
+      const long long grow = (long long)ti.row0 + r;
+#pragma unroll 1
+      for (int c = 0; c < kPairBN / 32; ++c) {
+        uint32_t v[32];
+        if (p.K > 0) {
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * kPairBN + c * 32, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0;
+        }
+        const int col0 = ti.c_col0 + c * 32;
+        const int ncols = min(32, ti.cols_valid - c * 32);
+        if (row_ok && ncols > 0) gemm_store_slice(p, 0, grow, col0, ncols, v);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    long long t0 = clock64();
+    while (clock64() - t0 < 2000000) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_sync_all();   // nobody leaves while its partner may still signal its barriers
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 2 * kPairBN);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_pair(const void* A, const void* B, const GemmArgs& args, long long a_rows, long long a_cols,
+                       long long lda, long long b_rows, long long b_cols, long long ldb, cudaStream_t stream) {
+  CUtensorMap tmA, tmB;
+  int e;
+  if (!A_MN) e = make_tmap_2d(&tmA, A, a_rows, a_cols, lda, BM, BK);
+  else e = make_tmap_2d(&tmA, A, a_rows, a_cols, lda, BK, 64);
+  if (e) return 2000 + e;
+  if (!B_MN) e = make_tmap_2d(&tmB, B, b_rows, b_cols, ldb, kPairBNL, BK);
+  else e = make_tmap_2d(&tmB, B, b_rows, b_cols, ldb, BK, 64);
+  if (e) return 3000 + e;
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kTotal);
+    if (ce != cudaSuccess) return 4000 + (int)ce;
+    attr_set = true;
+  }
+  static int max_pairs = 0;   // clusters of two that can be resident at once (one CTA per SM)
+  if (max_pairs == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_sms(), 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = PairSmem::kTotal;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = num_sms() / 2;
+    (void)cudaGetLastError();
+    max_pairs = n;
+  }
+  int pairs = max_pairs;
+  if (pairs > args.total_tiles) pairs = args.total_tiles;
+  if (pairs <= 0) return 0;
+  kern<<<2 * pairs, kGemmThreads, PairSmem::kTotal, stream>>>(tmA, tmB, args);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // namespace ob
+
+using namespace ob;
+
+extern "C" {
+
+// Same contract as ob_gemm_bf16 (plain mode), computed by CTA pairs on 256 x 256 tiles.
+int ob_gemm_bf16_pair(const void* A, const void* B, void* C, const void* residual, int M, int N, int K, long long lda,
+                      long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int out_mode, int* status,
+                      cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((lda & 7) || (ldb & 7)) return 6001;
+  if ((((uintptr_t)A) & 15) || (((uintptr_t)B) & 15)) return 6002;
+  if (out_mode < 0 || out_mode > 2) return 6005;
+  GemmArgs g = {};
+  g.M = M; g.N = N; g.K = K; g.mode = 0;
+  g.num_m_blocks = (M + 255) / 256;
+  g.num_n_blocks = (N + kPairBN - 1) / kPairBN;
+  g.total_tiles = g.num_m_blocks * g.num_n_blocks;
+  g.C = C; g.ldc = ldc; g.out_mode = out_mode;
+  g.residual = (const bf16*)residual; g.ldr = ldr;
+  g.status = status;
+  const long long a_rows = a_mn ? K : M, a_cols = a_mn ? M : K;
+  const long long b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;
+  if (!a_mn && !b_mn) return launch_pair<false, false>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
+  if (!a_mn && b_mn) return launch_pair<false, true>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
+  if (a_mn && b_mn) return launch_pair<true, true>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
+  return launch_pair<true, false>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
+}
+
+}  // extern "C"

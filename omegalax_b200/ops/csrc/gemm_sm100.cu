@@ -32,56 +32,10 @@
 // ring of shared-memory buffers into this GPU's full operand and bumps a per-chunk counter.  The
 // TMA producer of a computing CTA waits (bounded) for the counter of the chunk its tile reads;
 // tiles are visited own chunk first, then in the order the chunks arrive.
+#include "gemm_common.cuh"
 #include "host_utils.h"
-#include "sm100_common.cuh"
 
 namespace ob {
-
-constexpr int BM = 128;
-constexpr int BK = 64;
-constexpr int kStages = 4;
-constexpr int kGemmThreads = 192;
-constexpr int kMaxPeers = 8;
-
-struct GemmArgs {
-  int M, N, K;
-  int mode;                  // 0 plain, 1 grouped rows, 2 grouped reduction
-  int num_groups;
-  const int* group_offsets;  // [G+1] device, multiples of 128
-  int b_group_rows;          // rows per group in B's stacked 2-D view
-  int b_mn;                  // B operand major-ness (needed for the grouped row offset)
-  int num_m_blocks, num_n_blocks, total_tiles;
-  void* C;
-  long long ldc;
-  long long c_group_stride;  // mode 2: elements between consecutive groups' outputs
-  int out_mode;              // 0 bf16, 1 fp32 store, 2 fp32 accumulate, 3 fp32 peer red.add
-  const bf16* residual;
-  long long ldr;
-  // out_mode 3: rows [r*rows_per_peer, (r+1)*rows_per_peer) live on peer r at peer_ptr[r]
-  float* peer_ptr[kMaxPeers];
-  int rows_per_peer;
-  // gather mode: ag_side 1 = rows of A, 2 = rows of B are assembled inside this launch
-  int ag_side, ag_world, ag_rank, ag_copy_ctas;
-  int ag_rows_per_rank;            // multiple of the tile extent on that side
-  const void* ag_src[kMaxPeers];   // every rank's chunk (contiguous rows)
-  void* ag_dst;                    // this GPU's full operand (what the tensor map covers)
-  long long ag_chunk_bytes;
-  uint32_t* ag_flags;              // [world] counters, only ever incremented
-  uint32_t ag_target;              // value a chunk's counter has when the chunk is complete
-  int* status;
-};
-
-struct TileInfo {
-  int a_row0;    // first row (K-major) / first column (MN-major) of the A tile
-  int b_row0;    // same for B (K-major: already offset by the group)
-  int b_k_off;   // MN-major B in grouped mode: row offset of the group's matrix
-  int c_row0;    // first output row
-  int c_col0;    // first output column
-  int rows_valid, cols_valid;
-  int k_begin, k_end;
-  long long c_off;  // extra element offset into C (mode 2)
-  bool valid;
-};
 
 __device__ __forceinline__ int find_group(const int* offs, int G, int row) {
   int lo = 0, hi = G;  // invariant: offs[lo] <= row < offs[hi] (if row < offs[G])
@@ -419,77 +373,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         const int col0 = ti.c_col0 + c * 32;
         const int ncols = min(32, ti.cols_valid - c * 32);
-        if (row_ok && ncols > 0) {
-          if (p.residual) {
-            const bf16* rp = p.residual + grow * p.ldr + col0;
-            if (ncols == 32 && ((((uintptr_t)rp) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                uint4 q = *reinterpret_cast<const uint4*>(rp + i * 8);
-                uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  float2 f = unpack_bf16(w[j]);
-                  v[i * 8 + j * 2] = __float_as_uint(__uint_as_float(v[i * 8 + j * 2]) + f.x);
-                  v[i * 8 + j * 2 + 1] =
-                      __float_as_uint(__uint_as_float(v[i * 8 + j * 2 + 1]) + f.y);
-                }
-              }
-            } else {
-              for (int i = 0; i < ncols; ++i)
-                v[i] = __float_as_uint(__uint_as_float(v[i]) + __bfloat162float(rp[i]));
-            }
-          }
-          if (p.out_mode == 0) {
-            bf16* cp = (bf16*)p.C + ti.c_off + grow * p.ldc + col0;
-            if (ncols == 32 && ((((uintptr_t)cp) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                uint4 q;
-                q.x = pack_bf16(__uint_as_float(v[i * 8 + 0]), __uint_as_float(v[i * 8 + 1]));
-                q.y = pack_bf16(__uint_as_float(v[i * 8 + 2]), __uint_as_float(v[i * 8 + 3]));
-                q.z = pack_bf16(__uint_as_float(v[i * 8 + 4]), __uint_as_float(v[i * 8 + 5]));
-                q.w = pack_bf16(__uint_as_float(v[i * 8 + 6]), __uint_as_float(v[i * 8 + 7]));
-                *reinterpret_cast<uint4*>(cp + i * 8) = q;
-              }
-            } else {
-              for (int i = 0; i < ncols; ++i) cp[i] = __float2bfloat16(__uint_as_float(v[i]));
-            }
-          } else if (p.out_mode == 3) {
-            const int owner = (int)(grow / p.rows_per_peer);
-            const long long lrow = grow - (long long)owner * p.rows_per_peer;
-            float* cp = p.peer_ptr[owner] + lrow * p.ldc + col0;
-            if (ncols == 32 && ((((uintptr_t)cp) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + i * 4),
-                             "f"(__uint_as_float(v[i * 4 + 0])), "f"(__uint_as_float(v[i * 4 + 1])),
-                             "f"(__uint_as_float(v[i * 4 + 2])), "f"(__uint_as_float(v[i * 4 + 3]))
-                             : "memory");
-              }
-            } else {
-              for (int i = 0; i < ncols; ++i) atomicAdd(cp + i, __uint_as_float(v[i]));
-            }
-          } else {
-            float* cp = (float*)p.C + ti.c_off + grow * p.ldc + col0;
-            const bool accum = p.out_mode == 2;
-            if (ncols == 32 && ((((uintptr_t)cp) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                float4 q = make_float4(__uint_as_float(v[i * 4 + 0]), __uint_as_float(v[i * 4 + 1]),
-                                       __uint_as_float(v[i * 4 + 2]), __uint_as_float(v[i * 4 + 3]));
-                if (accum) {
-                  float4 o = *reinterpret_cast<const float4*>(cp + i * 4);
-                  q.x += o.x; q.y += o.y; q.z += o.z; q.w += o.w;
-                }
-                *reinterpret_cast<float4*>(cp + i * 4) = q;
-              }
-            } else {
-              for (int i = 0; i < ncols; ++i)
-                cp[i] = __uint_as_float(v[i]) + (accum ? cp[i] : 0.f);
-            }
-          }
-        }
+        if (row_ok && ncols > 0) gemm_store_slice(p, ti.c_off, grow, col0, ncols, v);
       }
       tc_fence_before();
       __syncwarp();

@@ -6,6 +6,8 @@ launched since the last ``reset_launch_count()``.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import lib
@@ -37,8 +39,20 @@ def _row_major_2d(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
+_PAIR_MODE = os.environ.get("OMEGALAX_B200_GEMM_PAIR", "0")   # "0" never, "1" always, "auto" by shape
+
+
+def _use_pair(M: int, N: int, K: int) -> bool:
+    """CTA-pair (256 x 256 tile) kernel for GEMMs with enough tiles to fill every SM pair."""
+    if _PAIR_MODE == "0":
+        return False
+    if _PAIR_MODE == "1":
+        return True
+    return (-(-M // 256)) * (-(-N // 256)) >= 74 and N >= 512 and K >= 256
+
+
 def gemm(a, b, *, a_mn: bool = False, b_mn: bool = False, out=None, out_dtype=bf16,
-         accumulate: bool = False, residual=None, bn: int = 0):
+         accumulate: bool = False, residual=None, bn: int = 0, pair: bool | None = None):
     """C = op(A) op(B)^T on the tcgen05 kernel.
 
     a: [M,K] (a_mn False) or [K,M] (a_mn True); b: [N,K] (b_mn False) or [K,N] (b_mn True).
@@ -69,6 +83,13 @@ def gemm(a, b, *, a_mn: bool = False, b_mn: bool = False, out=None, out_dtype=bf
             residual = residual.contiguous()
         res_ptr, ldr = residual.data_ptr(), residual.stride(0)
     st = lib.status_tensor(a.device)
+    if pair is None:
+        pair = bn == 0 and _use_pair(M, N, K)
+    if pair:
+        _call("ob_gemm_bf16_pair", a.data_ptr(), b.data_ptr(), out.data_ptr(), res_ptr, M, N, K,
+              a.stride(0), b.stride(0), out.stride(0), ldr, int(a_mn), int(b_mn), mode, st.data_ptr(),
+              lib.stream_ptr())
+        return out
     _call("ob_gemm_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), res_ptr, M, N, K,
           a.stride(0), b.stride(0), out.stride(0), ldr, int(a_mn), int(b_mn), mode, bn,
           st.data_ptr(), lib.stream_ptr())

@@ -605,3 +605,34 @@ def test_attention_backward_head_dim_64_varlen():
     assert _rel_err(o, ref) < 2e-2
     for a, b in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
         assert _rel_err(a, b) < 3e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (1000, 768, 384), (4096, 1536, 2048), (256, 256, 64)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_cta_pair_layouts(M, N, K, a_mn, b_mn):
+    from omegalax_b200.ops import kernels as Kn, lib
+    torch.manual_seed(1)
+    a = torch.randn((K, M) if a_mn else (M, K), device=_dev()).to(bf16)
+    b = torch.randn((K, N) if b_mn else (N, K), device=_dev()).to(bf16)
+    c = Kn.gemm(a, b, a_mn=a_mn, b_mn=b_mn, pair=True)
+    torch.cuda.synchronize()
+    _check(lib)
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float() if b_mn else b.float().t()
+    assert _rel_err(c, af @ bf) < 1e-2
+
+
+def test_gemm_cta_pair_epilogues():
+    from omegalax_b200.ops import kernels as Kn, lib
+    torch.manual_seed(2)
+    M, N, K = 1024, 1024, 512
+    a = torch.randn(M, K, device=_dev()).to(bf16)
+    b = torch.randn(N, K, device=_dev()).to(bf16)
+    res = torch.randn(M, N, device=_dev()).to(bf16)
+    ref = a.float() @ b.float().t()
+    c = Kn.gemm(a, b, residual=res, pair=True)
+    assert _rel_err(c, ref + res.float()) < 1e-2
+    acc = torch.ones(M, N, device=_dev())
+    Kn.gemm(a, b, out=acc, accumulate=True, pair=True)
+    assert _rel_err(acc, ref + 1.0) < 1e-2
+    _check(lib)
