@@ -80,6 +80,9 @@ def bench_gemm(a, dev, flush):
     _report("gemm wgrad  dw+=dy^T x (fp32 accumulate)",
             timeit(lambda: K.gemm(dy, x, a_mn=True, b_mn=True, out=acc, accumulate=True), a.iters, a.warmup, flush),
             fl, None, m=m, n=n, k=k)
+    for nm, fn in (("fprop", lambda: K.gemm(x, w, pair=True)), ("dgrad", lambda: K.gemm(dy, w, b_mn=True, pair=True)),
+                   ("wgrad fp32 accumulate", lambda: K.gemm(dy, x, a_mn=True, b_mn=True, out=acc, accumulate=True, pair=True))):
+        _report(f"gemm {nm}, CTA pairs (256x256 tiles)", timeit(fn, a.iters, a.warmup, flush), fl, None, m=m, n=n, k=k)
     if a.baseline:
         _report("cuBLAS fprop", timeit(lambda: torch.matmul(x, w.t()), a.iters, a.warmup, flush), fl, by)
         _report("cuBLAS dgrad", timeit(lambda: torch.matmul(dy, w), a.iters, a.warmup, flush), fl, by)
