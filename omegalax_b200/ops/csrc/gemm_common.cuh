@@ -90,7 +90,26 @@ __device__ __forceinline__ void gemm_store_slice(const GemmArgs& p, long long c_
               } else {
                 for (int i = 0; i < ncols; ++i) cp[i] = __float2bfloat16(__uint_as_float(v[i]));
               }
-            } else if (p.out_mode == 3) {
+            } else if (p.out_mode == 4) {
+    // bf16 peer reduction: two columns per 32-bit reduction, eight per instruction
+    const int owner = (int)(grow / p.rows_per_peer);
+    const long long lrow = grow - (long long)owner * p.rows_per_peer;
+    bf16* cp = reinterpret_cast<bf16*>(p.peer_ptr[owner]) + lrow * p.ldc + col0;
+    if (ncols == 32 && ((((uintptr_t)cp) & 15) == 0)) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t q0 = pack_bf16(__uint_as_float(v[i * 8 + 0]), __uint_as_float(v[i * 8 + 1]));
+        const uint32_t q1 = pack_bf16(__uint_as_float(v[i * 8 + 2]), __uint_as_float(v[i * 8 + 3]));
+        const uint32_t q2 = pack_bf16(__uint_as_float(v[i * 8 + 4]), __uint_as_float(v[i * 8 + 5]));
+        const uint32_t q3 = pack_bf16(__uint_as_float(v[i * 8 + 6]), __uint_as_float(v[i * 8 + 7]));
+        asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(cp + i * 8), "r"(q0), "r"(q1),
+                     "r"(q2), "r"(q3)
+                     : "memory");
+      }
+    } else {
+      for (int i = 0; i < ncols; ++i) atomicAdd(reinterpret_cast<__nv_bfloat16*>(cp + i), __float2bfloat16(__uint_as_float(v[i])));
+    }
+  } else if (p.out_mode == 3) {
               const int owner = (int)(grow / p.rows_per_peer);
               const long long lrow = grow - (long long)owner * p.rows_per_peer;
               float* cp = p.peer_ptr[owner] + lrow * p.ldc + col0;

@@ -304,4 +304,28 @@ int ob_gemm_bf16_pair(const void* A, const void* B, void* C, const void* residua
   return launch_pair<true, false>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
 }
 
+// Same contract as ob_gemm_bf16_peer_reduce (fp32 result rows added into the owning GPUs' buffers
+// with vector reductions over NVLink), computed by CTA pairs.
+int ob_gemm_bf16_pair_peer_reduce(const void* A, const void* B, void* const* peer_ptrs, int world, int rows_per_peer,
+                                  int M, int N, int K, long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
+                                  int bf16_out, int* status, cudaStream_t stream) {
+  if (world > kMaxPeers) return 6003;
+  if ((lda & 7) || (ldb & 7)) return 6001;
+  GemmArgs g = {};
+  g.M = M; g.N = N; g.K = K; g.mode = 0;
+  g.num_m_blocks = (M + 255) / 256;
+  g.num_n_blocks = (N + kPairBN - 1) / kPairBN;
+  g.total_tiles = g.num_m_blocks * g.num_n_blocks;
+  g.C = nullptr; g.ldc = ldc; g.out_mode = bf16_out ? 4 : 3;
+  for (int i = 0; i < world; ++i) g.peer_ptr[i] = (float*)peer_ptrs[i];
+  g.rows_per_peer = rows_per_peer;
+  g.status = status;
+  const long long a_rows = a_mn ? K : M, a_cols = a_mn ? M : K;
+  const long long b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;
+  if (!a_mn && !b_mn) return launch_pair<false, false>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
+  if (!a_mn && b_mn) return launch_pair<false, true>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
+  if (a_mn && b_mn) return launch_pair<true, true>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
+  return launch_pair<true, false>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
+}
+
 }  // extern "C"

@@ -505,7 +505,7 @@ int ob_gemm_bf16(const void* A, const void* B, void* C, const void* residual, in
 // sum) before any rank launches; completion is published by the caller's barrier.
 int ob_gemm_bf16_peer_reduce(const void* A, const void* B, void* const* peer_ptrs, int world,
                              int rows_per_peer, int M, int N, int K, long long lda, long long ldb,
-                             long long ldc, int a_mn, int b_mn, int* status, cudaStream_t stream) {
+                             long long ldc, int a_mn, int b_mn, int bf16_out, int* status, cudaStream_t stream) {
   if (world > kMaxPeers) return 6003;
   if ((lda & 7) || (ldb & 7)) return 6001;
   int bn = pick_bn(M, N);
@@ -514,7 +514,7 @@ int ob_gemm_bf16_peer_reduce(const void* A, const void* B, void* const* peer_ptr
   g.num_m_blocks = (M + BM - 1) / BM;
   g.num_n_blocks = (N + bn - 1) / bn;
   g.total_tiles = g.num_m_blocks * g.num_n_blocks;
-  g.C = nullptr; g.ldc = ldc; g.out_mode = 3;
+  g.C = nullptr; g.ldc = ldc; g.out_mode = bf16_out ? 4 : 3;
   for (int i = 0; i < world; ++i) g.peer_ptr[i] = (float*)peer_ptrs[i];
   g.rows_per_peer = rows_per_peer;
   g.status = status;

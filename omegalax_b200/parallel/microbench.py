@@ -141,14 +141,14 @@ def main():
     # ---- tensor parallel, row projection: GEMM -> reduce-scatter over rows in the epilogue
     h = torch.randn(M, max(512, 12288 // W), device=dev).to(bf16)              # [M, F/tp] activation slice
     w_row = torch.randn(D, h.shape[1], device=dev).to(bf16)
-    rs = symm.SymmetricBuffer(m * D * 4)
-    acc = rs.view(torch.float32, m * D)
+    rs = symm.SymmetricBuffer(m * D * 2)
+    acc = rs.view(bf16, m * D)
     ptrs = rs.peer_ptr_list(0)
 
     def fused_rs():
         acc.zero_()
         bar()
-        K.gemm_peer_reduce(h, w_row, ptrs, m, D)
+        K.gemm_peer_reduce(h, w_row, ptrs, m, D, bf16_out=True)
         bar()
 
     y_full = torch.empty(M, D, dtype=bf16, device=dev)
@@ -160,8 +160,8 @@ def main():
             dist.reduce_scatter_tensor(y_loc, y_full)
 
     fl3 = 2.0 * M * D * h.shape[1]
-    link3 = (W - 1) * m * D * 4.0
-    _report(rank, "TP row: GEMM -> reduce-scatter in the epilogue (fp32 adds over NVLink, incl. clear + 2 barriers)",
+    link3 = (W - 1) * m * D * 2.0
+    _report(rank, "TP row: GEMM -> reduce-scatter in the epilogue (bf16 adds over NVLink, incl. clear + 2 barriers)",
             _time(fused_rs, a.iters, a.warmup, W), fl3, link3, M=M, N=D, K=h.shape[1], world=W)
     _report(rank, "  GEMM, then NCCL reduce_scatter (bf16)", _time(gemm_then_nccl, a.iters, a.warmup, W), fl3,
             (W - 1) * m * D * 2.0, M=M, N=D, K=h.shape[1], world=W)

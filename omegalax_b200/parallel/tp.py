@@ -82,7 +82,7 @@ class TPContext:
         return self._ag_bufs[i], self._ag_flags
 
     def rs_buffer(self, rows_local: int, cols: int):
-        n = rows_local * cols * 4
+        n = rows_local * cols * 2
         if self._rs_buf is None or self._rs_buf.nbytes < n:
             self._rs_buf = self._symm().SymmetricBuffer(n, self.group)
             if self._barrier is None:
@@ -159,14 +159,12 @@ class _RowParallelLinearFn(torch.autograd.Function):
         M, N = x.shape[0], w.shape[0]
         m = M // tp.size
         buf = tp.rs_buffer(m, N)
-        acc = buf.view(torch.float32, m * N)
+        acc = buf.view(torch.bfloat16, m * N)
         acc.zero_()
         tp._barrier()                                   # every owner has cleared its rows
-        K.gemm_peer_reduce(x, w, buf.peer_ptr_list(0), m, N)
+        K.gemm_peer_reduce(x, w, buf.peer_ptr_list(0), m, N, bf16_out=True)
         tp._barrier()                                   # all contributions have landed
-        y = acc.view(m, N).to(x.dtype)
-        if residual is not None:
-            y = y + residual
+        y = acc.view(m, N) + residual if residual is not None else acc.view(m, N).clone()
         ctx.save_for_backward(x, w)
         ctx.tp, ctx.w_ref, ctx.has_res = tp, w, residual is not None
         return y
@@ -217,12 +215,12 @@ class _ColumnParallelLinearFn(torch.autograd.Function):
         M, Kd = full.shape
         m = M // tp.size
         buf = tp.rs_buffer(m, Kd)
-        acc = buf.view(torch.float32, m * Kd)
+        acc = buf.view(torch.bfloat16, m * Kd)
         acc.zero_()
         tp._barrier()
-        K.gemm_peer_reduce(dy, w, buf.peer_ptr_list(0), m, Kd, b_mn=True)   # dx rows land on their owners
+        K.gemm_peer_reduce(dy, w, buf.peer_ptr_list(0), m, Kd, b_mn=True, bf16_out=True)   # dx rows land on their owners
         tp._barrier()
-        dx = acc.view(m, Kd).to(dy.dtype)
+        dx = acc.view(m, Kd).clone()
         mg = getattr(ctx.w_ref, "main_grad", None)
         pg = getattr(ctx.w_ref, "peer_grad", None)
         dw = None

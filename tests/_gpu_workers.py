@@ -46,6 +46,21 @@ def symm_primitives(rank, world, port, out_path):
     dist.all_reduce(ref_local)
     ref = ref_local[rank * (N // world):(rank + 1) * (N // world)]
     res["peer_reduce_err"] = float((got - ref).abs().max() / ref.abs().max())
+    # the same through the CTA-pair kernel (enough tiles for every SM pair)
+    M2, N2, K2 = 512, 2048 * world, 2048
+    a2 = torch.randn(M2, K2, device=dev).to(torch.bfloat16)
+    dy2 = torch.randn(M2, N2, device=dev).to(torch.bfloat16)
+    g2 = symm.SymmetricBuffer((N2 // world) * K2 * 4)
+    g2.view(torch.float32, (N2 // world) * K2).zero_()
+    bar()
+    K.gemm_peer_reduce(dy2, a2, g2.peer_ptr_list(0), N2 // world, K2, a_mn=True, b_mn=True)
+    bar()
+    torch.cuda.synchronize()
+    got2 = g2.view(torch.float32, (N2 // world) * K2).view(N2 // world, K2)
+    ref2 = dy2.float().t() @ a2.float()
+    dist.all_reduce(ref2)
+    ref2 = ref2[rank * (N2 // world):(rank + 1) * (N2 // world)]
+    res["pair_peer_reduce_err"] = float((got2 - ref2).abs().max() / ref2.abs().max())
     lib.check_status()
     if rank == 0:
         torch.save(res, out_path)

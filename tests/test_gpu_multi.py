@@ -54,6 +54,7 @@ def test_symmetric_memory_primitives(tmp_path):
     r = torch.load(tmp_path / "r.pt")
     assert r["allgather_ok"]
     assert r["peer_reduce_err"] < 2e-2
+    assert r["pair_peer_reduce_err"] < 2e-2
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
