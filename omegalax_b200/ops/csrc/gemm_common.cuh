@@ -145,4 +145,57 @@ __device__ __forceinline__ void gemm_store_slice(const GemmArgs& p, long long c_
             }
 }
 
+// Gather-mode copy role (one thread): chunk by chunk, own chunk first, this CTA's share of every
+// chunk travels owner -> shared-memory ring -> local full operand in 32 KB bulk copies.
+__device__ __forceinline__ void ag_copy_role(const GemmArgs& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag) {
+  constexpr int kPiece = 32768;
+  constexpr int kRing = 6;      // ring slots
+  constexpr int kLoads = 4;     // loads in flight; the other two slots may still be draining to memory
+  for (int i = 0; i < kRing; ++i) mbar_init(&bars[i], 1);
+  *abort_flag = 0;
+  mbar_fence_init();
+  const int W = p.ag_world, C = p.ag_copy_ctas, cta = blockIdx.x;
+  const long long per = ((p.ag_chunk_bytes + C - 1) / C + 15) & ~15ll;
+  const long long lo = (long long)cta * per;
+  const long long hi = lo + per < p.ag_chunk_bytes ? lo + per : p.ag_chunk_bytes;
+  const long long npc = hi > lo ? (hi - lo + kPiece - 1) / kPiece : 0;
+  if (npc == 0) {
+    for (int r = 0; r < W; ++r) red_release_gpu_add(p.ag_flags + r, 1);
+    return;
+  }
+  const long long total = npc * W;
+  long long head = 0, tail = 0;
+  bool ok = true;
+  while (tail < total && ok) {
+    while (head < total && head - tail < kLoads) {
+      // slot head % kRing was last read by store head - kRing; stores 0 .. tail-1 are committed, so at
+      // most tail-1 - (head-kRing) >= kRing - kLoads of the newest ones may still be pending
+      if (head >= kRing) tma_store_wait_read<kRing - kLoads>();
+      const int r = (p.ag_rank + 1 + (int)(head / npc)) % W;   // own chunk last: nobody waits for it
+      const long long off = lo + (head % npc) * kPiece;
+      const uint32_t n = (uint32_t)(hi - off < kPiece ? hi - off : kPiece);
+      const int slot = (int)(head % kRing);
+      mbar_expect_tx(&bars[slot], n);
+      bulk_g2s(smem + slot * kPiece, (const char*)p.ag_src[r] + off, n, &bars[slot]);
+      ++head;
+    }
+    const int slot = (int)(tail % kRing);
+    ok = mbar_wait(&bars[slot], (uint32_t)((tail / kRing) & 1), abort_flag, p.status, OB_ERR_WAIT_MISC);
+    if (!ok) break;
+    const int r = (p.ag_rank + 1 + (int)(tail / npc)) % W;
+    const long long pi = tail % npc;
+    const long long off = lo + pi * kPiece;
+    const uint32_t n = (uint32_t)(hi - off < kPiece ? hi - off : kPiece);
+    bulk_s2g((char*)p.ag_dst + (long long)r * p.ag_chunk_bytes + off, smem + slot * kPiece, n);
+    tma_store_commit();
+    if (pi == npc - 1) {  // this CTA's share of chunk r is in place
+      tma_store_wait_all<0>();
+      __threadfence();
+      red_release_gpu_add(p.ag_flags + r, 1);
+    }
+    ++tail;
+  }
+  tma_store_wait_all<0>();
+}
+
 }  // namespace ob

@@ -45,8 +45,22 @@ __device__ __forceinline__ PairTile pair_tile(const GemmArgs& p, int t, int rank
   const int first_m = g * GM;
   const int gm = min(GM, p.num_m_blocks - first_m);
   const int r = t - g * per_group;
-  const int mb = first_m + (r % gm);
-  const int nb = r / gm;
+  int mb = first_m + (r % gm);
+  int nb = r / gm;
+  if (p.ag_side == 2) {  // B is gathered: sweep the tile rows for 4 tile columns of one chunk at a time
+    const int pg = GM * p.num_m_blocks;
+    const int g2 = t / pg;
+    const int first_n = g2 * GM;
+    const int gn = min(GM, p.num_n_blocks - first_n);
+    const int r2 = t - g2 * pg;
+    nb = first_n + (r2 % gn);
+    mb = r2 / gn;
+    nb += p.ag_rank * (p.ag_rows_per_rank / kPairBN);
+    if (nb >= p.num_n_blocks) nb -= p.num_n_blocks;
+  } else if (p.ag_side == 1) {  // own chunk of A first, then the chunks in arrival order
+    mb += p.ag_rank * (p.ag_rows_per_rank / 256);
+    if (mb >= p.num_m_blocks) mb -= p.num_m_blocks;
+  }
   PairTile ti;
   ti.row0 = mb * 256 + rank * 128;
   ti.b_row0 = nb * kPairBN + rank * kPairBNL;
@@ -59,7 +73,7 @@ __device__ __forceinline__ PairTile pair_tile(const GemmArgs& p, int t, int rank
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      const GemmArgs p) {
+                      const __grid_constant__ CUtensorMap tmL, const GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   using L = PairSmem;
@@ -74,8 +88,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int lane = threadIdx.x & 31;
   const int rank = (int)cluster_ctarank();
   const bool leader = rank == 0;
-  const int pair0 = (int)(blockIdx.x >> 1);
-  const int pair_step = (int)(gridDim.x >> 1);
+  // gather mode: the first clusters of the grid only move data (an even number of CTAs, so a
+  // cluster is either all copy or all compute)
+  const int ncopy = p.ag_side ? p.ag_copy_ctas : 0;
+  if ((int)blockIdx.x < ncopy) {
+    if (threadIdx.x == 0) ag_copy_role(p, smem, full_bar, abort_flag);
+    return;
+  }
+  const int pair0 = (int)((blockIdx.x - ncopy) >> 1);
+  const int pair_step = (int)((gridDim.x - ncopy) >> 1);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kPairStages; ++i) {
@@ -103,11 +124,30 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     if (lane == 0) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
+      if (p.ag_side) tma_prefetch_desc(&tmL);
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t ag_seen = 0;
       bool ok = true;
       for (int t = pair0; t < p.total_tiles && ok; t += pair_step) {
         const PairTile ti = pair_tile(p, t, rank);
+        bool ag_local = false;   // tile of this GPU's own chunk: read it where it already is
+        int ag_row = 0;
+        if (p.ag_side) {  // the chunk this CTA's part of the tile reads must have arrived
+          const int row0 = p.ag_side == 1 ? ti.row0 : ti.b_row0;
+          const int ch = row0 / p.ag_rows_per_rank;
+          ag_local = ch == p.ag_rank;
+          ag_row = row0 - ch * p.ag_rows_per_rank;
+          if (!ag_local && !((ag_seen >> ch) & 1u)) {
+            ok = flag_wait_ge<false>(p.ag_flags + ch, p.ag_target, OB_WAIT_CYCLES, p.status, OB_ERR_WAIT_FLAG);
+            if (!ok) {
+              *abort_flag = 1;
+              break;
+            }
+            fence_proxy_async_all();
+            ag_seen |= 1u << ch;
+          }
+        }
         for (int k0 = 0; k0 < p.K; k0 += BK) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_EMPTY);
           if (!ok) break;
@@ -116,13 +156,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
           const uint32_t fb = mapa_shared(smem_u32(&full_bar[stage]), 0);   // the even CTA's barrier
           if (!A_MN) {
-            tma_load_2d_pair(sa, &tmA, fb, k0, ti.row0);
+            if (ag_local && p.ag_side == 1) tma_load_2d_pair(sa, &tmL, fb, k0, ag_row);
+            else tma_load_2d_pair(sa, &tmA, fb, k0, ti.row0);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * (BK * 128), &tmA, fb, ti.row0 + j * 64, k0);
           }
           if (!B_MN) {
-            tma_load_2d_pair(sb, &tmB, fb, k0, ti.b_row0);
+            if (ag_local && p.ag_side == 2) tma_load_2d_pair(sb, &tmL, fb, k0, ag_row);
+            else tma_load_2d_pair(sb, &tmB, fb, k0, ti.b_row0);
           } else {
 #pragma unroll
             for (int j = 0; j < kPairBNL / 64; ++j)
@@ -244,6 +286,12 @@ static int launch_pair(const void* A, const void* B, const GemmArgs& args, long 
   if (!B_MN) e = make_tmap_2d(&tmB, B, b_rows, b_cols, ldb, kPairBNL, BK);
   else e = make_tmap_2d(&tmB, B, b_rows, b_cols, ldb, BK, 64);
   if (e) return 3000 + e;
+  CUtensorMap tmL = tmA;  // gather mode: this GPU's own chunk of the gathered operand, in place
+  if (args.ag_side) {
+    e = make_tmap_2d(&tmL, args.ag_src[args.ag_rank], args.ag_rows_per_rank, args.K, args.K,
+                     args.ag_side == 1 ? BM : kPairBNL, BK);
+    if (e) return 3500 + e;
+  }
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -267,9 +315,14 @@ static int launch_pair(const void* A, const void* B, const GemmArgs& args, long 
     max_pairs = n;
   }
   int pairs = max_pairs;
+  int copy = 0;
+  if (args.ag_side) {  // copy clusters come first in the grid; every cluster is resident from the start
+    copy = args.ag_copy_ctas;
+    pairs -= copy / 2;
+  }
   if (pairs > args.total_tiles) pairs = args.total_tiles;
-  if (pairs <= 0) return 0;
-  kern<<<2 * pairs, kGemmThreads, PairSmem::kTotal, stream>>>(tmA, tmB, args);
+  if (pairs <= 0) return args.ag_side ? 6006 : 0;
+  kern<<<2 * pairs + copy, kGemmThreads, PairSmem::kTotal, stream>>>(tmA, tmB, tmL, args);
   OB_CHECK_LAUNCH();
   return 0;
 }
@@ -326,6 +379,35 @@ int ob_gemm_bf16_pair_peer_reduce(const void* A, const void* B, void* const* pee
   if (!a_mn && b_mn) return launch_pair<false, true>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
   if (a_mn && b_mn) return launch_pair<true, true>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
   return launch_pair<true, false>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
+}
+
+// Same contract as ob_gemm_bf16_ag (all-gather -> GEMM in one launch), computed by CTA pairs.  The
+// chunk of each rank must be a multiple of 256 rows and copy_ctas even.
+int ob_gemm_bf16_pair_ag(const void* other, void* full, void* const* src_ptrs, void* C, const void* residual, int M,
+                         int N, int K, long long ldc, long long ldr, int out_mode, int side, int world, int rank,
+                         int rows_per_rank, unsigned* flags, unsigned target, int copy_ctas, int* status,
+                         cudaStream_t stream) {
+  if (world > kMaxPeers || world <= 0 || copy_ctas <= 0 || copy_ctas > 32 || (copy_ctas & 1)) return 6003;
+  if (side != 1 && side != 2) return 6005;
+  if ((K & 7) || (rows_per_rank % 256)) return 6007;
+  if ((long long)rows_per_rank * world != (side == 1 ? M : N)) return 6007;
+  GemmArgs g = {};
+  g.M = M; g.N = N; g.K = K; g.mode = 0;
+  g.num_m_blocks = (M + 255) / 256;
+  g.num_n_blocks = (N + kPairBN - 1) / kPairBN;
+  g.total_tiles = g.num_m_blocks * g.num_n_blocks;
+  g.C = C; g.ldc = ldc; g.out_mode = out_mode;
+  g.residual = (const bf16*)residual; g.ldr = ldr;
+  g.ag_side = side; g.ag_world = world; g.ag_rank = rank; g.ag_copy_ctas = copy_ctas;
+  g.ag_rows_per_rank = rows_per_rank;
+  for (int i = 0; i < world; ++i) g.ag_src[i] = src_ptrs[i];
+  g.ag_dst = full;
+  g.ag_chunk_bytes = (long long)rows_per_rank * K * 2;
+  g.ag_flags = flags; g.ag_target = target;
+  g.status = status;
+  const void* A = side == 1 ? full : other;
+  const void* B = side == 2 ? full : other;
+  return launch_pair<false, false>(A, B, g, M, K, K, N, K, K, stream);
 }
 
 }  // extern "C"

@@ -42,6 +42,9 @@ def _row_major_2d(t: torch.Tensor) -> torch.Tensor:
 _PAIR_MODE = os.environ.get("OMEGALAX_B200_GEMM_PAIR", "all")   # "0" never, "1" always, "all" / "auto" by shape
 
 
+_PAIR_AG = os.environ.get("OMEGALAX_B200_GEMM_PAIR_AG", "0") == "1"   # gather mode on the pair kernel
+
+
 def _use_pair(M: int, N: int, K: int, wgrad: bool = False) -> bool:
     """CTA-pair (256 x 256 tile) kernel for GEMMs with enough tiles to fill every SM pair."""
     if _PAIR_MODE == "0":
@@ -128,7 +131,8 @@ def ag_copy_ctas(M: int, N: int, Kd: int, total_bytes: float) -> int:
     flight)."""
     t_gemm = 2.0 * M * N * Kd / 1.1e15
     need = total_bytes / max(0.8 * t_gemm, 1e-6) / 45e9
-    return int(min(16, max(2, -(-need // 1))))
+    n = int(min(16, max(2, -(-need // 1))))
+    return n + (n & 1)          # even: the CTA-pair kernel gives up whole clusters
 
 
 def gemm_ag(other, full, src_ptrs, *, side: int, rank: int, rows_per_rank: int, flags, target: int,
@@ -151,7 +155,10 @@ def gemm_ag(other, full, src_ptrs, *, side: int, rank: int, rows_per_rank: int, 
         out = torch.empty(M, N, dtype=bf16, device=full.device)
     arr = (ctypes.c_void_p * W)(*src_ptrs)
     st = lib.status_tensor(full.device)
-    _call("ob_gemm_bf16_ag", other.data_ptr(), full.data_ptr(), ctypes.cast(arr, ctypes.c_void_p), out.data_ptr(),
+    name = "ob_gemm_bf16_ag"
+    if _PAIR_AG and rows_per_rank % 256 == 0 and copy_ctas % 2 == 0 and _use_pair(M, N, Kd):
+        name = "ob_gemm_bf16_pair_ag"
+    _call(name, other.data_ptr(), full.data_ptr(), ctypes.cast(arr, ctypes.c_void_p), out.data_ptr(),
           lib.ptr(residual), M, N, Kd, out.stride(0), residual.stride(0) if residual is not None else 0, 0, side, W,
           rank, rows_per_rank, flags.data_ptr(), int(target) & 0xFFFFFFFF, copy_ctas, st.data_ptr(), lib.stream_ptr())
     return out

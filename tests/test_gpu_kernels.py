@@ -462,20 +462,21 @@ def test_moe_mlp_kernel_path_matches_dense_loop():
     assert _rel_err(wd.grad, wdr.grad) < 4e-2
 
 
+@pytest.mark.parametrize("rows,other_rows", [(256, None), (1024, 2048)])
 @pytest.mark.parametrize("side", [1, 2])
-def test_gemm_with_in_kernel_all_gather(side):
+def test_gemm_with_in_kernel_all_gather(side, rows, other_rows):
     """Gather mode on one GPU: the 'ranks' are four buffers of this GPU, so the copy CTAs, the
     per-chunk counters and the chunk-ordered tile walk are exercised without a second device."""
     from omegalax_b200.ops import kernels as K, lib
     torch.manual_seed(17)
     dev = _dev()
-    W, Kd, rank = 4, 512, 1
-    rows = 256
+    K._PAIR_AG = True              # exercise the CTA-pair kernel's gather mode where the shape allows
+    W, Kd, rank = 4, 512, 1        # rows 1024 x 2048 other rows: enough tiles for the CTA-pair kernel
     flags = torch.zeros(W, dtype=torch.int32, device=dev)
     for call in range(2):
         chunks = [torch.randn(rows, Kd, device=dev).to(bf16) for _ in range(W)]
         full = torch.zeros(rows * W, Kd, dtype=bf16, device=dev)
-        other = torch.randn(384 if side == 1 else 300, Kd, device=dev).to(bf16)
+        other = torch.randn(other_rows or (384 if side == 1 else 300), Kd, device=dev).to(bf16)
         y = K.gemm_ag(other, full, [c.data_ptr() for c in chunks], side=side, rank=rank, rows_per_rank=rows,
                       flags=flags, target=8 * (call + 1), copy_ctas=8)
         torch.cuda.synchronize()
