@@ -464,13 +464,13 @@ def test_moe_mlp_kernel_path_matches_dense_loop():
 
 @pytest.mark.parametrize("rows,other_rows", [(256, None), (1024, 2048)])
 @pytest.mark.parametrize("side", [1, 2])
-def test_gemm_with_in_kernel_all_gather(side, rows, other_rows):
+def test_gemm_with_in_kernel_all_gather(side, rows, other_rows, monkeypatch):
     """Gather mode on one GPU: the 'ranks' are four buffers of this GPU, so the copy CTAs, the
     per-chunk counters and the chunk-ordered tile walk are exercised without a second device."""
     from omegalax_b200.ops import kernels as K, lib
     torch.manual_seed(17)
     dev = _dev()
-    K._PAIR_AG = True              # exercise the CTA-pair kernel's gather mode where the shape allows
+    monkeypatch.setattr(K, "_PAIR_AG", True)   # exercise the CTA-pair kernel's gather mode where the shape allows
     W, Kd, rank = 4, 512, 1        # rows 1024 x 2048 other rows: enough tiles for the CTA-pair kernel
     flags = torch.zeros(W, dtype=torch.int32, device=dev)
     for call in range(2):
