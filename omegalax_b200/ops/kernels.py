@@ -42,7 +42,7 @@ def _row_major_2d(t: torch.Tensor) -> torch.Tensor:
 _PAIR_MODE = os.environ.get("OMEGALAX_B200_GEMM_PAIR", "all")   # "0" never, "1" always, "all" / "auto" by shape
 
 
-_PAIR_AG = os.environ.get("OMEGALAX_B200_GEMM_PAIR_AG", "0") == "1"   # gather mode on the pair kernel
+_PAIR_AG = os.environ.get("OMEGALAX_B200_GEMM_PAIR_AG", "1") == "1"   # gather mode on the pair kernel
 
 
 def _use_pair(M: int, N: int, K: int, wgrad: bool = False) -> bool:
