@@ -147,10 +147,12 @@ __device__ __forceinline__ void gemm_store_slice(const GemmArgs& p, long long c_
 
 // Gather-mode copy role (one thread): chunk by chunk, own chunk first, this CTA's share of every
 // chunk travels owner -> shared-memory ring -> local full operand in 32 KB bulk copies.
+// kRing 32 KB slots must fit below the barrier area of the launching kernel's shared memory.
+template <int kRing>
 __device__ __forceinline__ void ag_copy_role(const GemmArgs& p, uint8_t* smem, uint64_t* bars, volatile int* abort_flag) {
   constexpr int kPiece = 32768;
-  constexpr int kRing = 6;      // ring slots
-  constexpr int kLoads = 4;     // loads in flight; the other two slots may still be draining to memory
+  static_assert(kRing >= 3 && kRing <= 6, "ring of 3 to 6 slots");
+  constexpr int kLoads = kRing - 2;   // loads in flight; the other two slots may still be draining to memory
   for (int i = 0; i < kRing; ++i) mbar_init(&bars[i], 1);
   *abort_flag = 0;
   mbar_fence_init();

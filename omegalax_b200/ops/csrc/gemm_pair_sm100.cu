@@ -92,7 +92,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   // cluster is either all copy or all compute)
   const int ncopy = p.ag_side ? p.ag_copy_ctas : 0;
   if ((int)blockIdx.x < ncopy) {
-    if (threadIdx.x == 0) ag_copy_role(p, smem, full_bar, abort_flag);
+    if (threadIdx.x == 0) ag_copy_role<(L::kBarOff / 32768 < 6 ? L::kBarOff / 32768 : 6)>(p, smem, full_bar, abort_flag);
     return;
   }
   const int pair0 = (int)((blockIdx.x - ncopy) >> 1);

@@ -158,7 +158,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int ncopy = p.ag_side ? p.ag_copy_ctas : 0;
   if ((int)blockIdx.x < ncopy) {  // gather mode: this CTA only moves data
-    if (threadIdx.x == 0) ag_copy_role(p, smem, full_bar, abort_flag);
+    // the copy ring lives in the stage area: 6 slots under a 192 KB ring, 4 under the 128 KB one
+    if (threadIdx.x == 0) ag_copy_role<(L::kBarOff / 32768 < 6 ? L::kBarOff / 32768 : 6)>(p, smem, full_bar, abort_flag);
     return;
   }
   const int cta0 = (int)blockIdx.x - ncopy;

@@ -462,7 +462,7 @@ def test_moe_mlp_kernel_path_matches_dense_loop():
     assert _rel_err(wd.grad, wdr.grad) < 4e-2
 
 
-@pytest.mark.parametrize("rows,other_rows", [(256, None), (1024, 2048)])
+@pytest.mark.parametrize("rows,other_rows", [(256, None), (1024, 2048), (384, None), (640, 2048)])
 @pytest.mark.parametrize("side", [1, 2])
 def test_gemm_with_in_kernel_all_gather(side, rows, other_rows, monkeypatch):
     """Gather mode on one GPU: the 'ranks' are four buffers of this GPU, so the copy CTAs, the
