@@ -214,13 +214,16 @@ class _ColumnParallelLinearFn(torch.autograd.Function):
         dy = dy.contiguous()
         M, Kd = full.shape
         m = M // tp.size
-        buf = tp.rs_buffer(m, Kd)
-        acc = buf.view(torch.bfloat16, m * Kd)
-        acc.zero_()
-        tp._barrier()
-        K.gemm_peer_reduce(dy, w, buf.peer_ptr_list(0), m, Kd, b_mn=True, bf16_out=True)   # dx rows land on their owners
-        tp._barrier()
-        dx = acc.view(m, Kd).clone()
+        if tp.size <= 2:
+            buf = tp.rs_buffer(m, Kd)
+            acc = buf.view(torch.bfloat16, m * Kd)
+            acc.zero_()
+            tp._barrier()
+            K.gemm_peer_reduce(dy, w, buf.peer_ptr_list(0), m, Kd, b_mn=True, bf16_out=True)   # dx rows land on their owners
+            tp._barrier()
+            dx = acc.view(m, Kd).clone()
+        else:
+            dx = _rs_rows(K.gemm(dy, w, b_mn=True), tp)
         mg = getattr(ctx.w_ref, "main_grad", None)
         pg = getattr(ctx.w_ref, "peer_grad", None)
         dw = None
@@ -246,8 +249,10 @@ def row_parallel_linear(x_cols, w_local, residual_local, tp: TPContext | None):
     """projection over this rank's input columns -> reduce-scatter over rows (+ residual)."""
     if tp is None or tp.size == 1:
         return Fn.linear(x_cols, w_local, residual=residual_local)
-    if tp.transport == "p2p" and Fn.use_kernels(x_cols) and w_local.dtype == torch.bfloat16 \
-            and (x_cols.shape[0] // tp.size) % 1 == 0:
+    # The epilogue reduction uses vector atomics over NVLink: measured 0.9x the time of GEMM + NCCL
+    # reduce-scatter at tp = 2, but several times slower at tp = 8 (atomic rate, not link rate),
+    # so wider groups take the unfused path.
+    if tp.transport == "p2p" and tp.size <= 2 and Fn.use_kernels(x_cols) and w_local.dtype == torch.bfloat16:
         return _RowParallelLinearFn.apply(x_cols.contiguous(), w_local, residual_local, tp)
     y = reduce_scatter_rows(Fn.linear(x_cols, w_local), tp)
     return y if residual_local is None else y + residual_local
