@@ -165,10 +165,14 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
             tp_size: int | None = None, fsdp_size: int | None = None, dp_size: int | None = None,
             profile_dir=None, profile_steps: tuple[int, int] = (3, 8), wandb_run=None, val_data_iter=None,
             val_every: int | None = None, val_steps: int = 10, device=None, log_file=None, _family=None,
-            pretrained_loader=None, stop_after_step: int | None = None):
+            pretrained_loader=None, stop_after_step: int | None = None, step_deadline_s: float | None = None,
+            heartbeat_s: float | None = None):
     """SFT from a checkpointable iterator of batch dicts (numpy / CPU tensors, this rank's
     rows).  Returns (optimizer, last logged metrics).  ``stop_after_step`` ends this invocation
-    early (after the usual final checkpoint) while keeping the schedule of ``num_steps``."""
+    early (after the usual final checkpoint) while keeping the schedule of ``num_steps``.
+    ``step_deadline_s`` arms a watchdog that dumps all stacks and exits with code 124 when a step
+    takes longer; ``heartbeat_s`` makes every rank publish a heartbeat in the rendezvous store and
+    check its peers between steps (``PeerFailure`` instead of a collective that never returns)."""
     fam = _family or _TEXT_FAMILY
     save_path = Path(save_dir).expanduser().resolve() if save_dir is not None else None
     if resume:
@@ -239,12 +243,22 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
             if is_primary():
                 print(" ".join(f"{k}={v:.6g}" if isinstance(v, float) else f"{k}={v}" for k, v in res.items()), flush=True)
 
+    from ..utils.failure import PeerHeartbeat, StepWatchdog
+
+    watchdog = StepWatchdog(step_deadline_s).start() if step_deadline_s else None
+    hb = None
+    if heartbeat_s and dist.is_initialized() and dist.get_world_size() > 1:
+        hb = PeerHeartbeat(dist.get_rank(), dist.get_world_size(), interval_s=heartbeat_s / 4,
+                           max_age_s=heartbeat_s).start()
+        hb.wait_all_alive(max(30.0, 4 * heartbeat_s))
     prof = None
     p0, p1 = profile_steps
     startup_log("entering training loop")
     end_step = train_cfg.num_steps if stop_after_step is None else min(train_cfg.num_steps, stop_after_step)
     for step_idx in range(start_step, end_step):
         step = step_idx + 1
+        if hb is not None:
+            hb.check()   # learn of a lost peer on the host, before launching anything that waits for it
         if profile_dir is not None and step_idx == p0 and prof is None:
             prof = _start_profiler(profile_dir)
         acc_loss = acc_sup = acc_gn = 0.0
@@ -267,6 +281,9 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
         window = {"loss": acc_loss / accum, "grad_norm": acc_gn, "supervised_tokens": acc_sup, "lr": lr}
         log_prev()
         prev = (step, window, acc_time, acc_flops)
+        if watchdog is not None:
+            watchdog.beat(step)
+            watchdog.pause()      # checkpoint writes and evaluation are not steps
         if manager is not None and save_every and step % save_every == 0:
             manager.save(step, optimizer, data_iter)
         if eval_step is not None and val_every and step % val_every == 0:
@@ -280,6 +297,13 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
                 print(f"val step={step} loss={tot / val_steps:.6g} sup_tokens={sup:.0f}", flush=True)
             if wandb_run is not None and is_primary():
                 wandb_run.log({"val/loss": tot / val_steps, "val/sup_tokens": sup}, step=step)
+        if watchdog is not None:
+            watchdog.resume()
+    if watchdog is not None:
+        watchdog.stop()
+    if hb is not None:
+        hb.leave()
+        hb.stop()
     if prof is not None:
         _stop_profiler(prof, profile_dir)
     log_prev(force=True)

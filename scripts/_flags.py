@@ -62,6 +62,8 @@ def common_train_flags(p: Flags, *, batch_size: int, workers: int, worker_buffer
     p.define("profile_start", 3)
     p.define("profile_end", 8)
     p.define("resume", False)
+    p.define("step_deadline_s", None, "watchdog: dump all stacks and exit 124 when a step takes longer", type=float)
+    p.define("heartbeat_s", None, "peers publish a heartbeat; a rank silent for this long raises PeerFailure", type=float)
     p.define("pad_id", 0)
     p.define("peak_tflops", None, "preset name (e.g. b200) or a number", type=str)
     p.define("wandb_entity", None, type=str)

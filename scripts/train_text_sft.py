@@ -63,7 +63,7 @@ def main(argv=None):
                                        fsdp_size=a.fsdp_size, dp_size=a.dp_size, profile_dir=a.profile_dir,
                                        profile_steps=(a.profile_start, a.profile_end), wandb_run=wandb_run,
                                        val_data_iter=val_iter, val_every=a.val_every, val_steps=a.val_steps,
-                                       log_file=a.log_file)
+                                       log_file=a.log_file, step_deadline_s=a.step_deadline_s, heartbeat_s=a.heartbeat_s)
     finally:
         if wandb_run is not None:
             wandb_run.finish()

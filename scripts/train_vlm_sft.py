@@ -72,7 +72,7 @@ def main(argv=None):
                                   peak_tflops=resolve_peak_tflops(a.peak_tflops), tp_size=a.tp_size, fsdp_size=a.fsdp_size,
                                   dp_size=a.dp_size, profile_dir=a.profile_dir,
                                   profile_steps=(a.profile_start, a.profile_end), val_data_iter=val_iter,
-                                  val_every=a.val_every, val_steps=a.val_steps, log_file=a.log_file)
+                                  val_every=a.val_every, val_steps=a.val_steps, log_file=a.log_file, step_deadline_s=a.step_deadline_s, heartbeat_s=a.heartbeat_s)
     if last and mesh_lib.rank() == 0:
         print(f"finished step={int(last['step'])} loss={last['loss']:.4f}")
 
