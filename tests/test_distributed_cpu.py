@@ -76,8 +76,15 @@ def test_tp_slices_roundtrip():
     from omegalax_b200.models.qwen3.model import Qwen3
     from omegalax_b200.models.qwen3.tp_layout import tp_slice, tp_unslice
 
-    cfg = make_config("qwen3-smoke")
-    m = Qwen3(cfg)
-    for n, p in m.named_parameters():
-        parts = [tp_slice(n, p.detach(), cfg, 2, r) for r in range(2)]
-        assert torch.equal(tp_unslice(n, parts, cfg), p.detach()), n
+    import dataclasses
+
+    for cfg in (make_config("qwen3-smoke"), dataclasses.replace(make_config("qwen3-smoke"), tie_word_embeddings=False)):
+        m = Qwen3(cfg)
+        for n, p in m.named_parameters():
+            parts = [tp_slice(n, p.detach(), cfg, 2, r) for r in range(2)]
+            assert torch.equal(tp_unslice(n, parts, cfg), p.detach()), n
+            if n == "lm_head.weight" and not cfg.tie_word_embeddings:   # split over the vocabulary
+                assert parts[0].shape[0] == p.shape[0] // 2
+        tp_model = Qwen3(cfg, tp_size=2)
+        for n, p in tp_model.named_parameters():                       # the tp model's shapes are the slices'
+            assert tuple(p.shape) == tuple(tp_slice(n, dict(m.named_parameters())[n].detach(), cfg, 2, 0).shape), n
