@@ -231,8 +231,8 @@ def main() -> int:
                      "loss_mask_BT": lm.pin_memory()})
     h2d_bytes = sum(v.numel() * v.element_size() for v in pool[0].values()) * accum
 
-    def to_dev(b):
-        return {k: v.to(device, non_blocking=True) for k, v in b.items()}
+    def to_dev(b):   # the image grid drives host-side loops and stays on the host
+        return {k: (v if k == "image_grid_thw" else v.to(device, non_blocking=True)) for k, v in b.items()}
 
     def barrier():
         if N > 1:

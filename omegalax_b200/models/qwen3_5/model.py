@@ -179,7 +179,11 @@ class Qwen3_5ForConditionalGeneration(nn.Module):
         if pixel_values is not None and pixel_values.numel() > 0:
             feats = self.visual(pixel_values.to(embeds.dtype), image_grid_thw).to(embeds.dtype)
             is_img = (token_ids.reshape(-1) == self.cfg.image_token_id)
-            pos = torch.nonzero(is_img, as_tuple=False).squeeze(-1)[: feats.shape[0]]
             embeds = embeds * (~is_img).unsqueeze(-1).to(embeds.dtype)
-            embeds = embeds.index_add(0, pos, feats[: pos.numel()])
+            if is_img.is_cuda:   # no host synchronisation; surplus (padded) feature rows add zeros
+                pos, ok = Fn.first_true_rows(is_img, feats.shape[0])
+                embeds = embeds.index_add(0, pos, feats[: pos.numel()] * ok.to(embeds.dtype))
+            else:
+                pos = torch.nonzero(is_img, as_tuple=False).squeeze(-1)[: feats.shape[0]]
+                embeds = embeds.index_add(0, pos, feats[: pos.numel()])
         return self.model(token_ids, segment_ids, position_ids_ZBT, inputs_embeds=embeds.view(B, T, -1))

@@ -131,14 +131,22 @@ class Qwen3VL(nn.Module):
         if attention_mask is None:
             attention_mask = torch.ones_like(token_ids)
         x = self.embedder(token_ids.reshape(-1))
-        deep, vis_pos = [], None
+        deep, vis_pos, vis_ok = [], None, None
         if pixel_values is not None and pixel_values.numel() > 0:
             if vision_cu_seqlens is None:
                 raise ValueError("vision_cu_seqlens is required when pixel_values are given")
             feats, deep = self.visual(pixel_values.to(x.dtype), image_grid_thw, vision_cu_seqlens.to(torch.int32))
             is_img = token_ids.reshape(-1) == self.cfg.image_token_id
-            vis_pos = torch.nonzero(is_img, as_tuple=False).squeeze(-1)[: feats.shape[0]]
-            x = Fn.scatter_rows(x, vis_pos, feats[: vis_pos.numel()].to(x.dtype), replace=True)
+            if is_img.is_cuda:
+                # no host synchronisation: the first n image-token positions by a stable sort; when the
+                # (padded) feature rows outnumber the image tokens the surplus rows are made no-ops
+                vis_pos, vis_ok = Fn.first_true_rows(is_img, feats.shape[0])
+                src = torch.where(vis_ok, feats[: vis_pos.numel()].to(x.dtype), x.index_select(0, vis_pos))
+                x = Fn.scatter_rows(x, vis_pos, src, replace=True)
+            else:
+                vis_ok = None
+                vis_pos = torch.nonzero(is_img, as_tuple=False).squeeze(-1)[: feats.shape[0]]
+                x = Fn.scatter_rows(x, vis_pos, feats[: vis_pos.numel()].to(x.dtype), replace=True)
         if position_ids_ZBT is None:
             pos = (attention_mask.cumsum(-1) - 1).clamp_min(0) * (attention_mask != 0)
             position_ids_ZBT = pos[None].expand(3, B, T)
@@ -157,5 +165,6 @@ class Qwen3VL(nn.Module):
                 x, aux = layer(x, ctx)
             aux_total = aux_total + aux
             if vis_pos is not None and i < len(deep):  # DeepStack: add tapped vision features
-                x = Fn.scatter_rows(x, vis_pos, deep[i][: vis_pos.numel()].to(x.dtype))
+                d = deep[i][: vis_pos.numel()].to(x.dtype)
+                x = Fn.scatter_rows(x, vis_pos, d if vis_ok is None else d * vis_ok.to(x.dtype))
         return self.final_norm(x).view(B, T, -1), aux_total

@@ -72,6 +72,11 @@ def shard_batch(token_ids_BT, shd_cfg=None, mesh=None, device=None):
     return _to_device(token_ids_BT, device)
 
 
+_HOST_KEYS = ("image_grid_thw", "video_grid_thw")
+
+
 def shard_batch_dict(batch: dict, shd_cfg=None, mesh=None, device=None) -> dict:
     device = device or ("cuda" if torch.cuda.is_available() else "cpu")
-    return {k: _to_device(v, device) for k, v in batch.items()}
+    # image_grid_thw drives host-side loops (patch counts, position tables): it stays on the host,
+    # reading it back from the device would stall the step on a synchronisation
+    return {k: (_to_device(v, "cpu") if k in _HOST_KEYS else _to_device(v, device)) for k, v in batch.items()}

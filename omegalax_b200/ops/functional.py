@@ -285,6 +285,15 @@ class _ScatterRowsFn(torch.autograd.Function):
         return dx, None, dsrc, None
 
 
+def first_true_rows(mask, n: int):
+    """Positions of the first ``n`` true entries of a 1-D bool mask, in order, without a host
+    synchronisation (a stable sort instead of ``nonzero``), and a bool [len, 1] that is false
+    where the mask has fewer than that many true entries (those positions are arbitrary)."""
+    n = min(int(n), mask.numel())
+    pos = torch.argsort((~mask).to(torch.uint8), stable=True)[:n]
+    return pos, mask.index_select(0, pos).unsqueeze(-1)
+
+
 def scatter_rows(x, pos, src, replace: bool = False):
     """x with rows ``pos`` (unique) replaced by / increased by the rows of ``src``."""
     if use_kernels(x) and x.dim() == 2 and x.shape[1] % 8 == 0 and src.dtype == x.dtype:

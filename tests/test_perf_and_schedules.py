@@ -83,3 +83,27 @@ def test_process_local_batch_size():
     assert mesh_lib.process_local_batch_size(16, dp_size=4) == 4
     with pytest.raises(ValueError):
         mesh_lib.process_local_batch_size(10, dp_size=4)
+
+
+def test_first_true_rows_matches_nonzero_with_surplus_rows():
+    """Sync-free image-token positions: same scatter result as the nonzero-based path, also when
+    the (padded) feature rows outnumber the image tokens."""
+    import torch
+
+    from omegalax_b200.ops import functional as Fn
+
+    torch.manual_seed(0)
+    mask = torch.rand(200) < 0.2
+    k = int(mask.sum())
+    x = torch.randn(200, 8)
+    for n in (k, k + 7, k - 3):
+        feats = torch.randn(n, 8)
+        pos_ref = torch.nonzero(mask).squeeze(-1)[:n]
+        want = Fn.scatter_rows(x, pos_ref, feats[: pos_ref.numel()], replace=True)
+        pos, ok = Fn.first_true_rows(mask, n)
+        src = torch.where(ok, feats[: pos.numel()], x.index_select(0, pos))
+        got = Fn.scatter_rows(x, pos, src, replace=True)
+        assert torch.equal(got, want)
+        add_want = x.index_add(0, pos_ref, feats[: pos_ref.numel()])
+        add_got = x.index_add(0, pos, feats[: pos.numel()] * ok.to(x.dtype))
+        assert torch.allclose(add_got, add_want)
