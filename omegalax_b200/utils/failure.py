@@ -5,9 +5,9 @@ Two pieces, both pure host code so that nothing ever waits on a GPU for a peer t
 
 ``StepWatchdog``   a daemon thread with a per-step deadline.  The training loop calls ``beat(step)``
                    once per step; if no beat arrives in time the watchdog dumps every Python stack
-                   to stderr (it never touches the device, which may be the thing that is stuck), runs ``on_timeout`` (default: leave the
-                   process with exit code 124 so that a launcher can restart from the last
-                   checkpoint).
+                   to stderr (it never touches the device, which may be the thing that is stuck)
+                   and runs ``on_timeout`` (default: leave the process with exit code 124 so
+                   that a launcher can restart from the last checkpoint).
 ``PeerHeartbeat``  liveness over the rendezvous key-value store (``torch.distributed`` TCPStore /
                    FileStore / HashStore): every rank publishes a counter from a daemon thread and
                    ``check()`` -- called between steps, before the next collective or kernel that
