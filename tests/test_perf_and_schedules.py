@@ -107,3 +107,30 @@ def test_first_true_rows_matches_nonzero_with_surplus_rows():
         add_want = x.index_add(0, pos_ref, feats[: pos_ref.numel()])
         add_got = x.index_add(0, pos, feats[: pos.numel()] * ok.to(x.dtype))
         assert torch.allclose(add_got, add_want)
+
+
+def test_stash_records_replays_and_skips():
+    """Selective rematerialisation bookkeeping: tagged outputs are stored in the first pass and
+    handed back in the re-run; a tag written "name!" is never stored and replays as a placeholder."""
+    import torch
+
+    from omegalax_b200.ops import functional as Fn
+
+    st = Fn._Stash(("qkv", "down!"))
+    a, b = torch.randn(2, 3), torch.randn(2, 3)
+    with Fn.stash_scope(st, "record"):
+        k1, v1 = Fn._stash_lookup("qkv")
+        assert v1 is None
+        Fn._stash_store(k1, a)
+        k2, v2 = Fn._stash_lookup("qkv")          # second call with the same tag: its own slot
+        Fn._stash_store(k2, b)
+        k3, v3 = Fn._stash_lookup("down")
+        assert v3 is None
+        Fn._stash_store(k3, torch.zeros(1))
+        assert Fn._stash_lookup("gate_up") == (None, None)   # not a tag of this stash
+    assert len(st.items) == 2
+    with Fn.stash_scope(st, "replay"):
+        assert Fn._stash_lookup("qkv")[1] is a
+        assert Fn._stash_lookup("qkv")[1] is b
+        assert Fn._stash_lookup("down")[1] is Fn._SKIP
+    assert Fn._stash_lookup("qkv") == (None, None)           # no active stash outside the scopes
