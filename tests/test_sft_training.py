@@ -110,3 +110,23 @@ class _Plain:
 
     def set_state(self, s):
         pass
+
+
+def test_text_cli_runs_with_watchdog_and_heartbeat_flags(tmp_path):
+    """The command-line trainer end to end on CPU, with the failure-detection flags set."""
+    import os
+    import subprocess
+    import sys
+
+    _dataset(tmp_path)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    log = tmp_path / "m.jsonl"
+    cmd = [sys.executable, os.path.join(root, "scripts", "train_text_sft.py"), "--model_id", "qwen3-smoke",
+           "--data_path", str(tmp_path / "index"), "--tokenizer", "stub", "--max_length", "96", "--num_steps", "3",
+           "--batch-size", "2", "--log_every", "1", "--save_every", "0", "--log_file", str(log),
+           "--step_deadline_s", "120", "--heartbeat_s", "5"]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    losses = [json.loads(l)["loss"] for l in log.read_text().splitlines()]
+    assert len(losses) == 3 and all(np.isfinite(losses))
