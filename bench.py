@@ -204,7 +204,9 @@ def main() -> int:
     # first forward.  With the state sharded there is room to keep the wide MLP activation too.
     remat = args.remat or ("save:qkv,attn" if N == 1 else "selective")
     if args.model != "qwen3-8b" and args.remat is None:
-        remat = "full"
+        # the small-hidden models have room for the stashed attention-side outputs; the Qwen3.5 slice
+        # (117 GB of expert state per GPU at 8 GPUs) recomputes whole layers
+        remat = "full" if args.model == "qwen3.5-8l" else "selective"
     tcfg = trainer.TrainConfig(seed=0, batch_size=micro * N, seq_len=T, num_steps=10_000, learning_rate=1e-5,
                                weight_decay=0.01, warmup_steps=0, lr_schedule="linear", max_grad_norm=1.0,
                                grad_accum_steps=accum, remat_policy=remat)

@@ -609,7 +609,7 @@ class _LazyEP:
 
             eng._ep = ExpertParallel(eng.group, self.module.E, x.shape[1], x.shape[0], idx.shape[1],
                                      capacity_factor=eng.ep_capacity_factor, dtype=x.dtype,
-                                     reuse_buffers=(eng.remat == "full"))
+                                     reuse_buffers=(eng.remat != "none"))
             eng._ep.max_tokens = x.shape[0]
         return eng._ep.moe_mlp(x, w, idx, gate_up_local, down_local)
 

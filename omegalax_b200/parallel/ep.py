@@ -131,8 +131,9 @@ class ExpertParallel:
         self.dtype = dtype
         self.overflow_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
         self._src_tok = {}
-        # With layer-by-layer rematerialisation a layer's exchange buffers are consumed before the
-        # next layer touches them, so the expert MLP can read and write them in place.  The
+        # With layer-by-layer rematerialisation (every policy but "none": the layer is re-run in its
+        # backward, with or without stashed outputs) a layer's exchange buffers are consumed before
+        # the next layer touches them, so the expert MLP can read and write them in place.  The
         # buffers start zeroed and only ever hold finite activations afterwards: padding rows may
         # then carry stale values, which is harmless because the gradient of the expert output is
         # always zero on padding rows (so no weight gradient sees them).
