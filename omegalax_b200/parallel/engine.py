@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import dataclasses
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -33,6 +34,11 @@ from ..ops import functional as Fn
 from ..ops import kernels as K
 
 bf16 = torch.bfloat16
+
+
+# OMEGALAX_B200_POISON=1 fills every gathered-layer buffer with NaN before it is (re)filled, so a read
+# of an element that no gather has written (a stale or skipped slot) turns the loss into NaN
+_POISON = os.environ.get("OMEGALAX_B200_POISON", "0") == "1"
 
 
 @dataclasses.dataclass
@@ -412,6 +418,8 @@ class TrainEngine:
         ready.record(cur)  # the previous user of this ring slot has been enqueued before this point
         with torch.cuda.stream(self._comm_stream):
             self._comm_stream.wait_event(ready)
+            if _POISON:   # debugging aid: a weight element that no gather writes shows up as NaN
+                self._ring[idx].fill_(float("nan"))
             self._symm.allgather_pull(self._shard_buf, self._ring[idx], self._seg_table(u))
             ev = torch.cuda.Event()
             ev.record(self._comm_stream)
