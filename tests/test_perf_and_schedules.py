@@ -134,3 +134,17 @@ def test_stash_records_replays_and_skips():
         assert Fn._stash_lookup("qkv")[1] is b
         assert Fn._stash_lookup("down")[1] is Fn._SKIP
     assert Fn._stash_lookup("qkv") == (None, None)           # no active stash outside the scopes
+
+
+def test_gemm_dispatch_heuristics():
+    """Host-side choices of the GEMM wrappers: CTA-pair kernel for GEMMs that fill every SM pair,
+    an even number of copy CTAs that grows with the bytes to gather per unit of GEMM time."""
+    from omegalax_b200.ops import kernels as K
+
+    if K._PAIR_MODE == "all":
+        assert K._use_pair(32768, 6144, 4096)
+        assert not K._use_pair(512, 512, 4096)        # 4 tiles: single-CTA kernel
+        assert not K._use_pair(32768, 128, 4096)      # narrow output
+    small = K.ag_copy_ctas(32768, 6144, 4096, 50e6)
+    big = K.ag_copy_ctas(32768, 3072, 4096, 268e6)
+    assert small % 2 == 0 and big % 2 == 0 and 2 <= small <= big <= 16
