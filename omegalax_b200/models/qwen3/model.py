@@ -174,6 +174,7 @@ class MoEFeedForward(nn.Module):
         self.experts_gate_up = nn.Parameter(torch.empty(E, 2 * F_, D, device=device, dtype=dtype))
         self.experts_down = nn.Parameter(torch.empty(E, D, F_, device=device, dtype=dtype))
         self.ep = None  # set by the expert-parallel runtime
+        self.aux_group = None  # data ranks over which the load-balance statistics are taken
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -188,7 +189,7 @@ class MoEFeedForward(nn.Module):
             y = self.ep.moe_mlp(x, w, idx, self.experts_gate_up, self.experts_down)
         else:
             y = moe_ops.moe_mlp(x, w, idx, self.experts_gate_up, self.experts_down)
-        aux = moe_ops.load_balance_loss_qwen3(probs, idx, self.E, self.coef)
+        aux = moe_ops.load_balance_loss_qwen3(probs, idx, self.E, self.coef, self.aux_group)
         if residual is not None:
             y = y + residual
         return y, aux

@@ -39,6 +39,7 @@ class MoEFeedForward(nn.Module):
         self.shared_expert = _SwiGLU(D, cfg.shared_expert_intermediate_size, **kw)
         self.shared_expert_gate = Linear(D, 1, **kw)
         self.ep = None
+        self.aux_group = None  # data ranks over which the load-balance statistics are taken
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -56,7 +57,7 @@ class MoEFeedForward(nn.Module):
         y = y + gate * self.shared_expert(x)
         if residual is not None:
             y = y + residual
-        return y, moe_ops.load_balance_loss_sq(probs, self.E, self.coef)
+        return y, moe_ops.load_balance_loss_sq(probs, self.E, self.coef, self.aux_group)
 
 
 class DecoderLayer(nn.Module):

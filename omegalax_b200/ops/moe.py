@@ -56,18 +56,41 @@ def route(router_logits, top_k: int, renormalize: bool):
     return probs, w, idx
 
 
-def load_balance_loss_qwen3(probs, idx, num_experts: int, coef: float):
+def _global_sum(local, group):
+    """Sum of ``local`` over the data ranks of ``group``.  The value is the global sum on every
+    rank; the derivative with respect to this rank's ``local`` is W (the group size), so that a
+    caller that adds loss/W on each of the W ranks -- gradients are summed over ranks -- ends up
+    with exactly the gradient of the global loss."""
+    import torch.distributed as dist
+
+    W = dist.get_world_size(group)
+    tot = local.detach().clone()
+    dist.all_reduce(tot, group=group)
+    return W * local + (tot - W * local.detach()), W
+
+
+def load_balance_loss_qwen3(probs, idx, num_experts: int, coef: float, group=None):
     """coef * E * sum_e (fraction of (token,slot) picks of e per token) * mean prob of e,
-    over all tokens including padding (omegalax/models/qwen3/model.py:120-124)."""
+    over all tokens including padding (omegalax/models/qwen3/model.py:120-124).  With ``group``
+    the two statistics are taken over the tokens of every data rank (one all-reduce of 2E
+    floats), which is what the reference computes under SPMD over the global batch."""
     M = probs.shape[0]
     counts = torch.zeros(num_experts, dtype=torch.float32, device=probs.device)
     counts.scatter_add_(0, idx.reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=probs.device))
-    return coef * num_experts * torch.sum((counts / M) * probs.mean(0))
+    if group is None or coef == 0.0:
+        return coef * num_experts * torch.sum((counts / M) * probs.mean(0))
+    stats, W = _global_sum(torch.cat([counts, probs.float().sum(0)]), group)
+    counts_g, psum_g = stats[:num_experts].detach(), stats[num_experts:]
+    return coef * num_experts * torch.sum((counts_g / (M * W)) * (psum_g / (M * W)))
 
 
-def load_balance_loss_sq(probs, num_experts: int, coef: float):
-    """coef * sum_e (mean prob of e - 1/E)^2 (omegalax/models/qwen3_5/model.py:172-174)."""
-    return coef * torch.sum((probs.mean(0) - 1.0 / num_experts) ** 2)
+def load_balance_loss_sq(probs, num_experts: int, coef: float, group=None):
+    """coef * sum_e (mean prob of e - 1/E)^2 (omegalax/models/qwen3_5/model.py:172-174); with
+    ``group`` the mean is over the tokens of every data rank."""
+    if group is None or coef == 0.0:
+        return coef * torch.sum((probs.mean(0) - 1.0 / num_experts) ** 2)
+    psum_g, W = _global_sum(probs.float().sum(0), group)
+    return coef * torch.sum((psum_g / (probs.shape[0] * W) - 1.0 / num_experts) ** 2)
 
 
 def build_permutation(idx, num_experts: int, pad: int = PAD):

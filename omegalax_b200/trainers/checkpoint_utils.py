@@ -93,8 +93,10 @@ class CheckpointManager:
             for suffix, t in ((".master", master), (".exp_avg", m1), (".exp_avg_sq", m2)):
                 tensors[slot.name + suffix] = t.detach().to("cpu", copy=True)
             params.append({"name": slot.name, "shape": list(slot.shape), "sharded": bool(slot.sharded),
-                           "shard_numel": int(slot.shard_numel)})
+                           "shard_numel": int(slot.shard_numel),
+                           "tp_sharded": bool(getattr(slot, "tp_sharded", False))})
         manifest = {"step": int(step), "world_size": w, "shard_world": int(engine.W),
+                    "tp_world": int(getattr(engine, "TP", 1)),
                     "optimizer_step": int(engine.step_count), "params": params, "extra": extra or {}}
         iter_state = input_iter.get_state() if input_iter is not None else None
         rng_state = {"cpu": torch.get_rng_state()}
@@ -162,27 +164,46 @@ class CheckpointManager:
         d = self.step_dir(step)
         manifest = json.loads((d / "manifest.json").read_text())
         saved_w = manifest["shard_world"]
+        saved_tp = int(manifest.get("tp_world", manifest["world_size"] // saved_w))
+        tp, tp_rank = int(getattr(engine, "TP", 1)), int(getattr(engine, "tp_rank", 0))
         meta = {p["name"]: p for p in manifest["params"]}
         files = [safe_open(str(d / f"rank{i:05d}.safetensors"), framework="pt") for i in range(manifest["world_size"])]
+        # ranks are laid out (shard, tp) with tp fastest: shard rank i, tensor-parallel rank t wrote
+        # the file of global rank i * saved_tp + t
+        per = saved_tp
+
+        def saved_full(key, pm, t):
+            """Tensor-parallel rank t's whole (un-sharded over fsdp) value, flat."""
+            if pm["sharded"]:
+                return torch.cat([files[i * per + t].get_tensor(key).reshape(-1) for i in range(saved_w)])
+            return files[t].get_tensor(key).reshape(-1)
+
         r = _rank()
+        model_names = {id(p): n for n, p in engine.model.named_parameters()} if saved_tp != tp else {}
         for slot, master, m1, m2 in engine.named_master_shards():
             if slot.name not in meta:
                 raise RuntimeError(f"checkpoint has no entry for parameter '{slot.name}'")
             pm = meta[slot.name]
-            if list(slot.shape) != pm["shape"]:
+            retile = saved_tp != tp and (pm.get("tp_sharded", False) or getattr(slot, "tp_sharded", False))
+            if list(slot.shape) != pm["shape"] and not retile:
                 raise RuntimeError(f"shape mismatch for '{slot.name}': {pm['shape']} vs {list(slot.shape)}")
+            t = tp_rank if (saved_tp == tp and pm.get("tp_sharded", False)) else 0
             for suffix, dst in ((".master", master), (".exp_avg", m1), (".exp_avg_sq", m2)):
                 key = slot.name + suffix
-                if pm["sharded"] == slot.sharded and (not slot.sharded or saved_w == engine.W):
-                    src = files[engine.rank if slot.sharded and len(files) > 1 else 0].get_tensor(key)
+                if retile:
+                    full = _retile_tp(model_names[id(slot.param)], [saved_full(key, pm, i).view(pm["shape"]) for i in range(saved_tp)],
+                                      engine, tp, tp_rank)
+                    if list(full.shape) != list(slot.shape):
+                        raise RuntimeError(f"shape mismatch for '{slot.name}' after changing the tensor-parallel "
+                                           f"degree {saved_tp} -> {tp}: {list(full.shape)} vs {list(slot.shape)}")
+                    full = full.reshape(-1)
+                    src = full[engine.rank * slot.shard_numel:(engine.rank + 1) * slot.shard_numel] if slot.sharded else full
+                elif pm["sharded"] == slot.sharded and (not slot.sharded or saved_w == engine.W):
+                    src = files[(engine.rank * per if slot.sharded and len(files) > 1 else 0) + t].get_tensor(key)
                     if slot.sharded and len(files) == 1 and saved_w == 1:
                         src = src.reshape(-1)
                 else:
-                    if pm["sharded"]:
-                        per = manifest["world_size"] // saved_w
-                        full = torch.cat([files[i * per].get_tensor(key).reshape(-1) for i in range(saved_w)])
-                    else:
-                        full = files[0].get_tensor(key).reshape(-1)
+                    full = saved_full(key, pm, t)
                     if slot.sharded:
                         src = full[engine.rank * slot.shard_numel:(engine.rank + 1) * slot.shard_numel]
                     else:
@@ -198,3 +219,15 @@ class CheckpointManager:
         if p.exists():
             torch.set_rng_state(torch.load(p, weights_only=False)["cpu"])
         return manifest
+
+
+def _retile_tp(name: str, parts: list, engine, tp: int, tp_rank: int):
+    """Per-rank slices written with one tensor-parallel degree -> the slice of rank ``tp_rank`` under
+    degree ``tp`` (moments are laid out like the weights, so the same rule serves all three)."""
+    from ..models.qwen3 import tp_layout
+
+    cfg = getattr(engine.model, "cfg", None)
+    if cfg is None or not hasattr(engine.model, "tp_size"):
+        raise RuntimeError("changing the tensor-parallel degree on restore needs a model with a tensor-parallel layout")
+    full = tp_layout.tp_unslice(name, parts, cfg) if len(parts) > 1 else parts[0]
+    return tp_layout.tp_slice(name, full, cfg, tp, tp_rank)

@@ -121,7 +121,8 @@ def make_sft_train_step(cfg, pad_id: int = 0):
     """Returns ``step(optimizer, batch) -> (loss, metrics)``.  ``batch`` holds device tensors
     ``token_ids_BT``, ``attention_mask_BT``, ``loss_mask_BT`` (this rank's rows).  The loss is
     the global masked mean (normalised by the supervised-token count over all data ranks)
-    plus the auxiliary router loss averaged over ranks."""
+    plus the auxiliary router loss (computed from the router statistics of all data ranks; each
+    rank adds its 1/W share)."""
 
     def sft_train_step(optimizer: MixedPrecisionOptimizer, batch: dict):
         group = optimizer.group
@@ -147,8 +148,9 @@ def make_sft_eval_step(cfg, pad_id: int = 0):
     def sft_eval_step(model, batch: dict, group=None):
         with torch.no_grad():
             ce, aux, count = _loss_and_count(model, cfg, batch, pad_id, group)
-            loss = ce + aux
-            if group is not None and dist.get_world_size(group) > 1:
+            W = dist.get_world_size(group) if group is not None else 1
+            loss = ce + aux / W          # ce is this rank's share of the global mean; aux is averaged
+            if W > 1:
                 dist.all_reduce(loss, group=group)
         return loss, count.squeeze(0)
 

@@ -65,8 +65,9 @@ def make_sft_eval_step(cfg, pad_id: int = 0):
     def sft_eval_step(model, batch: dict, group=None):
         with torch.no_grad():
             ce, aux, count = _forward_loss(model, cfg, batch, pad_id, group)
-            loss = ce + aux
-            if group is not None and dist.get_world_size(group) > 1:
+            W = dist.get_world_size(group) if group is not None else 1
+            loss = ce + aux / W
+            if W > 1:
                 dist.all_reduce(loss, group=group)
         return loss, count.squeeze(0)
 

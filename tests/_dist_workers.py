@@ -10,7 +10,7 @@ def _init(rank, world, port):
     dist.init_process_group("gloo", rank=rank, world_size=world)
 
 
-def fsdp_train(rank, world, port, model_id, steps, out_path, ckpt_dir=None, resume=False):
+def fsdp_train(rank, world, port, model_id, steps, out_path, ckpt_dir=None, resume=False, aux_coef=None):
     """Train `steps` optimizer steps with FSDP over `world` CPU ranks on a fixed global batch;
     rank 0 stores the loss curve and the gathered fp32 parameters."""
     _init(rank, world, port)
@@ -21,6 +21,12 @@ def fsdp_train(rank, world, port, model_id, steps, out_path, ckpt_dir=None, resu
     mesh_lib.set_default_mesh(None)
     mesh_lib.ensure_mesh(tp_size=1, fsdp_size=world, dp_size=1)
     tcfg = trainer.TrainConfig(seed=0, batch_size=4, seq_len=32, num_steps=100, learning_rate=1e-2, max_grad_norm=1.0)
+    if aux_coef is not None:   # a router loss large enough to steer the run
+        import dataclasses
+
+        from omegalax_b200.models.qwen3.config import make_config
+
+        model_id = dataclasses.replace(make_config(model_id), aux_loss_coef=aux_coef)
     model, cfg = trainer.init_model(model_id, 0, tp_size=1, fsdp_size=world, dp_size=1, meta=True)
     opt = trainer.build_optimizer(model, tcfg, device=torch.device("cpu"))
     step = trainer.make_sft_train_step(cfg)
@@ -53,7 +59,7 @@ def fsdp_train(rank, world, port, model_id, steps, out_path, ckpt_dir=None, resu
     dist.destroy_process_group()
 
 
-def tp_train(rank, world, port, tp, steps, out_path, untied=False):
+def tp_train(rank, world, port, tp, steps, out_path, untied=False, ckpt_dir=None, resume=False):
     """Same weights, same batch: tensor-parallel (tp) x fsdp (world/tp) run on CPU ranks."""
     _init(rank, world, port)
     import dataclasses
@@ -94,10 +100,46 @@ def tp_train(rank, world, port, tp, steps, out_path, untied=False):
     di = mesh_lib.data_parallel_index()
     sl = slice(di * 2, di * 2 + 2)
     batch = {"token_ids_BT": tok[sl], "attention_mask_BT": torch.ones(2, 32, dtype=torch.int32), "loss_mask_BT": lm[sl]}
+    mgr = None
+    if ckpt_dir:
+        from omegalax_b200.trainers import checkpoint_utils
+
+        mgr = checkpoint_utils.CheckpointManager(ckpt_dir, async_write=False)
+        if resume:
+            mgr.restore(None, opt)
     losses = [float(step(opt, batch)[0]) for _ in range(steps)]
+    if mgr is not None and not resume:
+        mgr.save(steps, opt)
+    if mgr is not None:
+        mgr.close()
     if rank == 0:
         torch.save({"losses": losses, "grad_norm": float(opt.last_grad_norm),
                     "vocab_parallel": bool(getattr(model, "vocab_parallel", False))}, out_path)
     dist.barrier()
     tp_lib.set_current(None)
+    dist.destroy_process_group()
+
+
+def aux_stats(rank, world, port, out_path):
+    """Load-balance losses from per-rank token slices with the group's statistics: value on each
+    rank and the summed gradient of sum_r aux_r / W."""
+    _init(rank, world, port)
+    from omegalax_b200.ops import moe as moe_ops
+
+    g = torch.Generator().manual_seed(0)
+    E, k, M = 8, 2, 64
+    logits = torch.randn(M, E, generator=g)
+    per = M // world
+    mine = logits[rank * per:(rank + 1) * per].clone().requires_grad_(True)
+    probs = torch.softmax(mine, -1)
+    idx = probs.topk(k, -1).indices
+    grp = dist.group.WORLD if world > 1 else None
+    a1 = moe_ops.load_balance_loss_qwen3(probs, idx, E, 0.5, grp)
+    a2 = moe_ops.load_balance_loss_sq(probs, E, 0.5, grp)
+    ((a1 + a2) / world).backward()
+    grads = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(grads, mine.grad)
+    if rank == 0:
+        torch.save({"a1": float(a1), "a2": float(a2), "grad": torch.cat(grads)}, out_path)
+    dist.barrier()
     dist.destroy_process_group()

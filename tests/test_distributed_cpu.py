@@ -32,6 +32,27 @@ def test_fsdp_matches_single_rank(tmp_path, model_id):
         torch.testing.assert_close(a["params"][k], b["params"][k], rtol=2e-3, atol=2e-4)
 
 
+def test_moe_aux_loss_uses_global_statistics(tmp_path):
+    """The router load-balance loss is taken over the tokens of every data rank: value and
+    gradient from 2 and 4 token slices equal the single-rank ones, and an FSDP run whose loss is
+    dominated by it follows the single-rank curve."""
+    outs = {}
+    for world in (1, 2, 4):
+        mp.spawn(W.aux_stats, args=(world, _port(), str(tmp_path / f"s{world}.pt")), nprocs=world, join=True)
+        outs[world] = torch.load(tmp_path / f"s{world}.pt")
+    for world in (2, 4):
+        assert outs[world]["a1"] == pytest.approx(outs[1]["a1"], rel=1e-5)
+        assert outs[world]["a2"] == pytest.approx(outs[1]["a2"], rel=1e-5)
+        torch.testing.assert_close(outs[world]["grad"], outs[1]["grad"], rtol=1e-4, atol=1e-7)
+    _run(1, "qwen3-smoke-moe", 3, str(tmp_path / "w1.pt"), None, False, 2.0)
+    _run(2, "qwen3-smoke-moe", 3, str(tmp_path / "w2.pt"), None, False, 2.0)
+    a, b = torch.load(tmp_path / "w1.pt"), torch.load(tmp_path / "w2.pt")
+    assert a["losses"] == pytest.approx(b["losses"], rel=2e-4, abs=2e-4)
+    assert a["grad_norm"] == pytest.approx(b["grad_norm"], rel=1e-3)
+    for k in a["params"]:
+        torch.testing.assert_close(a["params"][k], b["params"][k], rtol=2e-3, atol=2e-4)
+
+
 def test_checkpoint_resharding_4_to_2(tmp_path):
     ck = tmp_path / "ckpt"
     _run(4, "qwen3-smoke", 2, str(tmp_path / "a.pt"), str(ck), False)
@@ -69,6 +90,24 @@ def test_vocab_parallel_head_matches_single_rank(tmp_path):
     assert two["vocab_parallel"] and not one["vocab_parallel"]
     assert one["losses"] == pytest.approx(two["losses"], rel=3e-4, abs=3e-4)
     assert one["grad_norm"] == pytest.approx(two["grad_norm"], rel=2e-3)
+
+
+def test_checkpoint_across_tensor_parallel_degrees(tmp_path):
+    """A checkpoint written under tp=2 resumes under tp=2 (each rank reads its own slice) and under
+    tp=1 (slices re-assembled), and one written under tp=1 resumes under tp=2; the next step's loss
+    is the one of an uninterrupted run.  The head is untied, so it is split over the vocabulary."""
+    def run(world, tp, steps, name, ckpt=None, resume=False):
+        mp.spawn(W.tp_train, args=(world, _port(), tp, steps, str(tmp_path / name), True, ckpt, resume),
+                 nprocs=world, join=True)
+        return torch.load(tmp_path / name)
+
+    straight = run(1, 1, 3, "c.pt")
+    ck2, ck1 = str(tmp_path / "ck_tp2"), str(tmp_path / "ck_tp1")
+    run(2, 2, 2, "a.pt", ck2)
+    run(1, 1, 2, "a1.pt", ck1)
+    for world, tp, ck in ((2, 2, ck2), (1, 1, ck2), (2, 2, ck1)):
+        got = run(world, tp, 1, "r.pt", ck, True)
+        assert got["losses"][0] == pytest.approx(straight["losses"][2], rel=3e-4, abs=3e-4), (world, tp, ck)
 
 
 def test_tp_slices_roundtrip():
