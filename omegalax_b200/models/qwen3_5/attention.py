@@ -11,14 +11,22 @@ from torch import nn
 
 from ...ops import functional as Fn
 from ...ops import reference as R
+from ...parallel import tp as tp_lib
 from ..qwen3.model import Linear
 from .norms import RMSNorm
 
 
 class Attention(nn.Module):
-    def __init__(self, cfg, device=None, dtype=None):
+    def __init__(self, cfg, device=None, dtype=None, tp_size: int = 1):
         super().__init__()
-        H, G, Kd, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.hidden_size
+        if cfg.num_attention_heads % tp_size or cfg.num_key_value_heads % tp_size:
+            raise ValueError(f"heads ({cfg.num_attention_heads} q / {cfg.num_key_value_heads} kv) do not divide "
+                             f"over tp_size={tp_size}")
+        if tp_size > 1 and cfg.attention_bias:
+            raise ValueError("tensor-parallel attention with projection biases is not supported")
+        H, G = cfg.num_attention_heads // tp_size, cfg.num_key_value_heads // tp_size
+        Kd, D = cfg.head_dim, cfg.hidden_size
+        self.tp_size = tp_size
         self.H, self.G, self.Kd = H, G, Kd
         self.rot = int(Kd * cfg.partial_rotary_factor)
         kw = dict(device=device, dtype=dtype)
@@ -29,8 +37,12 @@ class Attention(nn.Module):
         self.k_norm = RMSNorm(Kd, cfg.rms_norm_eps, **kw)
         self.eps = cfg.rms_norm_eps
         self.scale = Kd ** -0.5
+        self.qkv_proj.tp_sharded = self.o_proj.tp_sharded = tp_size > 1
 
     def forward(self, x, ctx, residual=None):
+        tp = tp_lib.current() if self.tp_size > 1 else None
+        if tp is not None:
+            x = tp_lib.all_gather_rows(x, tp)      # sequence-parallel rows -> all rows, this rank's heads
         M = x.shape[0]
         B, T = ctx.B, ctx.T
         qkv = self.qkv_proj(x)
@@ -50,4 +62,6 @@ class Attention(nn.Module):
                             v.reshape(B, T, self.G, self.Kd), causal=True, scale=self.scale,
                             k_start=ks).reshape(M, self.H, self.Kd)
         o = o * torch.sigmoid(gate.to(o.dtype))
+        if tp is not None:
+            return tp_lib.row_parallel_linear(o.reshape(M, self.H * self.Kd), self.o_proj.weight, residual, tp)
         return self.o_proj(o.reshape(M, self.H * self.Kd), residual=residual)

@@ -9,6 +9,7 @@ import torch
 from torch import nn
 
 from ...ops import functional as Fn
+from ...parallel import tp as tp_lib
 from ...ops import moe as moe_ops
 from ..qwen3.model import Embedding, ForwardCtx, Linear
 from ..qwen3.model import MLP as _SwiGLU
@@ -61,14 +62,15 @@ class MoEFeedForward(nn.Module):
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: Qwen3_5TextConfig, layer_idx: int, device=None, dtype=None):
+    def __init__(self, cfg: Qwen3_5TextConfig, layer_idx: int, device=None, dtype=None, tp_size: int = 1):
         super().__init__()
         kw = dict(device=device, dtype=dtype)
+        self.tp_size = tp_size
         self.layer_type = cfg.layer_types[layer_idx]
         self.input_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **kw)
         self.post_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **kw)
         if self.layer_type == "full_attention":
-            self.attn = Attention(cfg, **kw)
+            self.attn = Attention(cfg, tp_size=tp_size, **kw)
         else:
             self.linear_attn = GatedDeltaNet(cfg, **kw)
         self.is_moe = cfg.is_moe
@@ -78,6 +80,14 @@ class DecoderLayer(nn.Module):
         h = self.input_norm(x)
         if self.layer_type == "full_attention":
             x = self.attn(h, ctx, residual=x)
+        elif self.tp_size > 1 and tp_lib.current() is not None:
+            # the recurrence runs over whole sequences: gather the sequence-parallel rows, run the
+            # (replicated) mixer and keep this rank's rows; the gather's backward sums the ranks'
+            # input gradients, each of which comes from its own output rows only
+            tp = tp_lib.current()
+            m = x.shape[0]
+            y = self.linear_attn(tp_lib.all_gather_rows(h, tp), ctx)
+            x = x + y[tp.rank * m:(tp.rank + 1) * m]
         else:
             x = self.linear_attn(h, ctx, residual=x)
         h = self.post_norm(x)
@@ -87,12 +97,13 @@ class DecoderLayer(nn.Module):
 
 
 class TextModel(nn.Module):
-    def __init__(self, cfg: Qwen3_5TextConfig, device=None, dtype=None):
+    def __init__(self, cfg: Qwen3_5TextConfig, device=None, dtype=None, tp_size: int = 1):
         super().__init__()
         self.cfg = cfg
+        self.tp_size = tp_size
         kw = dict(device=device, dtype=dtype or torch.float32)
         self.embedder = Embedding(cfg.vocab_size, cfg.hidden_size, **kw)
-        self.layers = nn.ModuleList(DecoderLayer(cfg, i, **kw) for i in range(cfg.num_hidden_layers))
+        self.layers = nn.ModuleList(DecoderLayer(cfg, i, tp_size=tp_size, **kw) for i in range(cfg.num_hidden_layers))
         self.final_norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, **kw)
         self.layer_runner = None
 
@@ -108,10 +119,19 @@ class TextModel(nn.Module):
         return ForwardCtx(B=B, T=T, sin=sin.reshape(B * T, -1), cos=cos.reshape(B * T, -1), cu_seqlens=cu,
                           segment_ids=segment_ids, k_start=None, positions=position_ids_ZBT)
 
-    def forward(self, token_ids, segment_ids, position_ids_ZBT=None, inputs_embeds=None):
+    def forward(self, token_ids, segment_ids, position_ids_ZBT=None, inputs_embeds=None, return_local_rows: bool = False):
+        """Under tensor parallelism the rows between the blocks are sequence-parallel (this rank
+        carries rows [r*M/tp, (r+1)*M/tp) of the flattened token rows); ``return_local_rows``
+        returns them [M/tp, D] instead of the gathered [B,T,D]."""
         B, T = segment_ids.shape
         ctx = self.make_ctx(segment_ids, position_ids_ZBT)
         x = self.embedder(token_ids.reshape(-1)) if inputs_embeds is None else inputs_embeds.reshape(B * T, -1)
+        tp = tp_lib.current() if self.tp_size > 1 else None
+        if tp is not None:
+            if (B * T) % tp.size:
+                raise ValueError("tensor parallelism needs B*T divisible by tp_size")
+            m = B * T // tp.size
+            x = x[tp.rank * m:(tp.rank + 1) * m]
         aux_total = torch.zeros((), dtype=torch.float32, device=x.device)
         for layer in self.layers:
             if self.layer_runner is not None:
@@ -119,16 +139,24 @@ class TextModel(nn.Module):
             else:
                 x, aux = layer(x, ctx)
             aux_total = aux_total + aux
-        return self.final_norm(x).view(B, T, -1), aux_total
+        x = self.final_norm(x)
+        if tp is not None:
+            if return_local_rows:
+                return x, aux_total
+            x = tp_lib.all_gather_rows(x, tp)
+        return x.view(B, T, -1), aux_total
 
 
 class Qwen3_5ForCausalLM(nn.Module):
     """Text-only model; forward returns hidden states before lm_head and the aux loss."""
 
-    def __init__(self, cfg: Qwen3_5TextConfig, device=None, dtype=None):
+    TP_LAYOUT = "omegalax_b200.models.qwen3_5.tp_layout"
+
+    def __init__(self, cfg: Qwen3_5TextConfig, device=None, dtype=None, tp_size: int = 1):
         super().__init__()
         self.cfg = cfg
-        self.model = TextModel(cfg, device=device, dtype=dtype)
+        self.tp_size = tp_size
+        self.model = TextModel(cfg, device=device, dtype=dtype, tp_size=tp_size)
         self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, device=device, dtype=dtype or torch.float32)
 
     @property
@@ -144,21 +172,25 @@ class Qwen3_5ForCausalLM(nn.Module):
         return [("embedder", [m.embedder])] + [(f"layers.{i}", [l]) for i, l in enumerate(m.layers)] + \
                [("head", [m.final_norm, self.lm_head])]
 
-    def forward(self, token_ids, segment_ids, cache=None, num_right_pads: int = 0, position_ids_ZBT=None):
-        return self.model(token_ids, segment_ids, position_ids_ZBT)
+    def forward(self, token_ids, segment_ids, cache=None, num_right_pads: int = 0, position_ids_ZBT=None,
+                return_local_rows: bool = False):
+        return self.model(token_ids, segment_ids, position_ids_ZBT, return_local_rows=return_local_rows)
 
 
 class Qwen3_5ForConditionalGeneration(nn.Module):
     """Vision tower + text model: image-token embeddings are replaced by vision features."""
 
-    def __init__(self, cfg: Qwen3_5Config, device=None, dtype=None):
+    TP_LAYOUT = "omegalax_b200.models.qwen3_5.tp_layout"
+
+    def __init__(self, cfg: Qwen3_5Config, device=None, dtype=None, tp_size: int = 1):
         super().__init__()
         from .vision import VisionModel
 
         self.cfg = cfg
+        self.tp_size = tp_size
         dtype = dtype or torch.float32
         self.visual = VisionModel(cfg.vision_config, device=device, dtype=dtype)
-        self.model = TextModel(cfg.text_config, device=device, dtype=dtype)
+        self.model = TextModel(cfg.text_config, device=device, dtype=dtype, tp_size=tp_size)
         self.lm_head = Linear(cfg.text_config.hidden_size, cfg.text_config.vocab_size, device=device, dtype=dtype)
 
     @property
@@ -174,7 +206,8 @@ class Qwen3_5ForConditionalGeneration(nn.Module):
         return [("visual", [self.visual]), ("embedder", [m.embedder])] + \
                [(f"layers.{i}", [l]) for i, l in enumerate(m.layers)] + [("head", [m.final_norm, self.lm_head])]
 
-    def forward(self, token_ids, segment_ids, pixel_values=None, image_grid_thw=None, position_ids_ZBT=None):
+    def forward(self, token_ids, segment_ids, pixel_values=None, image_grid_thw=None, position_ids_ZBT=None,
+                return_local_rows: bool = False):
         B, T = token_ids.shape
         embeds = self.model.embedder(token_ids.reshape(-1))
         if pixel_values is not None and pixel_values.numel() > 0:
@@ -187,4 +220,5 @@ class Qwen3_5ForConditionalGeneration(nn.Module):
             else:
                 pos = torch.nonzero(is_img, as_tuple=False).squeeze(-1)[: feats.shape[0]]
                 embeds = embeds.index_add(0, pos, feats[: pos.numel()])
-        return self.model(token_ids, segment_ids, position_ids_ZBT, inputs_embeds=embeds.view(B, T, -1))
+        return self.model(token_ids, segment_ids, position_ids_ZBT, inputs_embeds=embeds.view(B, T, -1),
+                          return_local_rows=return_local_rows)

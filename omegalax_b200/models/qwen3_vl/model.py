@@ -10,7 +10,8 @@ from torch import nn
 
 from ...ops import functional as Fn
 from ...ops import reference as R
-from ..qwen3.model import DecoderLayer, Embedding, ForwardCtx, Linear
+from ...parallel import tp as tp_lib
+from ..qwen3.model import DecoderLayer, Embedding, ForwardCtx, Linear, vocab_parallel_head
 from ..qwen3.norms import RMSNorm
 from ..qwen3_5.rope import interleave_mrope
 from .config import Qwen3VLConfig
@@ -106,17 +107,24 @@ class _TextCfgShim:
 
 
 class Qwen3VL(nn.Module):
-    def __init__(self, cfg: Qwen3VLConfig, device=None, dtype=None):
+    def __init__(self, cfg: Qwen3VLConfig, device=None, dtype=None, tp_size: int = 1):
+        """``tp_size`` > 1 splits the text decoder (heads, MLP width) over tensor-parallel ranks
+        with sequence-parallel activations between the blocks; the vision tower, the embedding
+        and the head are replicated (each rank back-propagates only its rows into them and the
+        engine sums those gradients over the tensor-parallel group)."""
         super().__init__()
         self.cfg = cfg
+        self.tp_size = tp_size
         dtype = dtype or torch.float32
         kw = dict(device=device, dtype=dtype)
         shim = _TextCfgShim(cfg)
         self.visual = VisionModel(cfg.vision, **kw)
         self.embedder = Embedding(cfg.vocab_size, cfg.emb_dim, **kw)
-        self.layers = nn.ModuleList(DecoderLayer(shim, i, **kw) for i in range(cfg.num_layers))
+        self.layers = nn.ModuleList(DecoderLayer(shim, i, tp_size=tp_size, **kw) for i in range(cfg.num_layers))
         self.final_norm = RMSNorm(cfg.emb_dim, cfg.norm_eps, **kw)
-        self.lm_head = Linear(cfg.emb_dim, cfg.vocab_size, **kw)
+        self.vocab_parallel = vocab_parallel_head(cfg, tp_size)   # untied head: split over the vocabulary
+        self.lm_head = Linear(cfg.emb_dim, cfg.vocab_size // tp_size if self.vocab_parallel else cfg.vocab_size, **kw)
+        self.lm_head.tp_sharded = self.vocab_parallel
         self.layer_runner = None
         self._attn_backend = "sm100"
 
@@ -125,7 +133,10 @@ class Qwen3VL(nn.Module):
                [(f"layers.{i}", [l]) for i, l in enumerate(self.layers)] + [("head", [self.final_norm, self.lm_head])]
 
     def forward(self, token_ids, attention_mask=None, position_ids_ZBT=None, pixel_values=None,
-                image_grid_thw=None, vision_cu_seqlens=None):
+                image_grid_thw=None, vision_cu_seqlens=None, return_local_rows: bool = False):
+        """Hidden states [B,T,D] before the head and the summed router loss.  Under tensor
+        parallelism ``return_local_rows`` returns this rank's rows [B*T/tp, D] of the flattened
+        token rows instead of gathering them (the trainer scores them in place)."""
         B, T = token_ids.shape
         dev = token_ids.device
         if attention_mask is None:
@@ -157,6 +168,17 @@ class Qwen3VL(nn.Module):
         ctx = ForwardCtx(B=B, T=T, sin=sin.reshape(B * T, -1), cos=cos.reshape(B * T, -1),
                          cu_seqlens=torch.arange(B + 1, device=dev, dtype=torch.int32) * T, segment_ids=seg,
                          k_start=first.to(torch.int64), positions=position_ids_ZBT)
+        tp = tp_lib.current() if self.tp_size > 1 else None
+        if tp is not None:
+            if (B * T) % tp.size:
+                raise ValueError("tensor parallelism needs B*T divisible by tp_size")
+            m = B * T // tp.size
+            x = x[tp.rank * m:(tp.rank + 1) * m]              # sequence-parallel rows of this rank
+            if vis_pos is not None:
+                # image rows that fall outside this rank's slice add zeros to its first row
+                mine = (vis_pos >= tp.rank * m) & (vis_pos < (tp.rank + 1) * m)
+                vis_ok = mine.unsqueeze(-1) if vis_ok is None else (vis_ok & mine.unsqueeze(-1))
+                vis_pos = torch.where(mine, vis_pos - tp.rank * m, torch.zeros_like(vis_pos))
         aux_total = torch.zeros((), dtype=torch.float32, device=x.device)
         for i, layer in enumerate(self.layers):
             if self.layer_runner is not None:
@@ -166,5 +188,13 @@ class Qwen3VL(nn.Module):
             aux_total = aux_total + aux
             if vis_pos is not None and i < len(deep):  # DeepStack: add tapped vision features
                 d = deep[i][: vis_pos.numel()].to(x.dtype)
-                x = Fn.scatter_rows(x, vis_pos, d if vis_ok is None else d * vis_ok.to(x.dtype))
-        return self.final_norm(x).view(B, T, -1), aux_total
+                d = d if vis_ok is None else d * vis_ok.to(x.dtype)
+                # under tp the masked-out rows all point at row 0: index_add tolerates the repeats,
+                # the row-scatter kernel wants unique rows
+                x = x.index_add(0, vis_pos, d) if tp is not None else Fn.scatter_rows(x, vis_pos, d)
+        x = self.final_norm(x)
+        if tp is not None:
+            if return_local_rows:
+                return x, aux_total
+            x = tp_lib.all_gather_rows(x, tp)
+        return x.view(B, T, -1), aux_total

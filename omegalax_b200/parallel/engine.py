@@ -127,12 +127,15 @@ class TrainEngine:
         self.tp_group = tp_group
         self.TP = dist.get_world_size(tp_group) if tp_group is not None else 1
         self.tp_rank = dist.get_rank(tp_group) if tp_group is not None else 0
-        if self.W > 1 and self.TP == 1:
-            # router load-balance statistics over the tokens of all data ranks (one small all-reduce
-            # per MoE layer), as the reference's global-batch SPMD loss does
+        # router load-balance statistics over the tokens of all ranks that hold different rows (data
+        # ranks, and tensor-parallel ranks with their sequence-parallel slices): one small all-reduce
+        # per MoE layer, as the reference's global-batch SPMD loss does
+        aux_group = shard_group if self.TP == 1 else tp_group if self.W == 1 else \
+            (dist.group.WORLD if dist.get_world_size() == self.W * self.TP else None)
+        if aux_group is not None:
             for mod in model.modules():
                 if hasattr(mod, "aux_group"):
-                    mod.aux_group = shard_group
+                    mod.aux_group = aux_group
         self.use_cuda_kernels = self.device.type == "cuda"
         self.compute_dtype = bf16 if self.device.type == "cuda" else torch.float32
         if comm == "auto":

@@ -224,8 +224,9 @@ class CheckpointManager:
 def _retile_tp(name: str, parts: list, engine, tp: int, tp_rank: int):
     """Per-rank slices written with one tensor-parallel degree -> the slice of rank ``tp_rank`` under
     degree ``tp`` (moments are laid out like the weights, so the same rule serves all three)."""
-    from ..models.qwen3 import tp_layout
+    import importlib
 
+    tp_layout = importlib.import_module(getattr(engine.model, "TP_LAYOUT", "omegalax_b200.models.qwen3.tp_layout"))
     cfg = getattr(engine.model, "cfg", None)
     if cfg is None or not hasattr(engine.model, "tp_size"):
         raise RuntimeError("changing the tensor-parallel degree on restore needs a model with a tensor-parallel layout")

@@ -87,31 +87,36 @@ def build_optimizer(model, train_cfg: TrainConfig, *, device=None, init_from_mod
         tp_group=tp_group)
 
 
+def tp_rows_loss(model, rows, tok, mask, count):
+    """Cross-entropy of this tensor-parallel rank's sequence-parallel rows [B*T/tp, D] against the
+    shifted tokens: its share of the global masked mean (the shares add up over the tp group).
+    A head split over the vocabulary scores all rows against its slice instead."""
+    from ..ops import functional as Fn
+    from ..parallel import tp as tp_lib
+
+    tp = tp_lib.current()
+    B, T = tok.shape
+    m = B * T // tp.size
+    tgt = torch.roll(tok, -1, dims=1).reshape(-1)
+    msk = torch.roll(mask, -1, dims=1).to(torch.float32)
+    msk[:, -1] = 0
+    sl = slice(tp.rank * m, (tp.rank + 1) * m)
+    if getattr(model, "vocab_parallel", False):   # head split over the vocabulary: all rows, this rank's slice
+        return Fn.linear_cross_entropy_vocab_parallel(rows, model.lm_head.weight, tgt, msk.reshape(-1),
+                                                      1.0 / count.clamp_min(1.0), tp)
+    return Fn.linear_cross_entropy(rows, model.lm_head.weight, tgt[sl], msk.reshape(-1)[sl],
+                                   1.0 / count.clamp_min(1.0))
+
+
 def _loss_and_count(model, cfg, batch, pad_id: int, group):
     tok = batch["token_ids_BT"]
     mask = batch["loss_mask_BT"]
     count = supervised_count(mask, group)
     if getattr(model, "tp_size", 1) > 1:
         # sequence-parallel rows: this tp rank scores its own slice of the (shifted) token rows
-        from ..ops import functional as Fn
-        from ..parallel import tp as tp_lib
-
-        tp = tp_lib.current()
         seg = (tok != pad_id).to(torch.int32)
         rows, aux = model(tok, seg, None, 0, return_local_rows=True)
-        B, T = tok.shape
-        m = B * T // tp.size
-        tgt = torch.roll(tok, -1, dims=1).reshape(-1)
-        msk = torch.roll(mask, -1, dims=1).to(torch.float32)
-        msk[:, -1] = 0
-        sl = slice(tp.rank * m, (tp.rank + 1) * m)
-        if getattr(model, "vocab_parallel", False):   # head split over the vocabulary: all rows, this rank's slice
-            ce = Fn.linear_cross_entropy_vocab_parallel(rows, model.lm_head.weight, tgt, msk.reshape(-1),
-                                                        1.0 / count.clamp_min(1.0), tp)
-        else:
-            ce = Fn.linear_cross_entropy(rows, model.lm_head.weight, tgt[sl], msk.reshape(-1)[sl],
-                                         1.0 / count.clamp_min(1.0))
-        return ce, aux / tp.size, count
+        return tp_rows_loss(model, rows, tok, mask, count), aux / model.tp_size, count
     hidden, aux = text_api.forward(model, tok, pad_id, cfg)
     ce = chunked_cross_entropy_loss(hidden, model.lm_head.weight, tok, mask, num_tiles=_NUM_LOSS_TILES, count=count)
     return ce, aux, count

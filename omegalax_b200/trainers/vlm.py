@@ -35,11 +35,14 @@ def _forward_loss(model, cfg, batch, pad_id, group):
     grid = batch.get("image_grid_thw")
     if torch.is_tensor(grid):
         grid = [tuple(int(v) for v in row) for row in grid.tolist()]
+    count = supervised_count(mask, group)
+    tp = getattr(model, "tp_size", 1)
     hidden, aux = vlm_api.forward(model, tok, pad_id, cfg, attention_mask_BT=batch.get("attention_mask_BT"),
                                   pixel_values=batch.get("pixel_values"), image_grid_thw=grid,
                                   vision_cu_seqlens=batch.get("vision_cu_seqlens"),
-                                  position_ids_ZBT=batch.get("position_ids_ZBT"))
-    count = supervised_count(mask, group)
+                                  position_ids_ZBT=batch.get("position_ids_ZBT"), return_local_rows=tp > 1)
+    if tp > 1:   # sequence-parallel rows of this tensor-parallel rank
+        return _text.tp_rows_loss(model, hidden, tok, mask, count), aux / tp, count
     ce = chunked_cross_entropy_loss(hidden, model.lm_head.weight, tok, mask, num_tiles=_NUM_LOSS_TILES, count=count)
     return ce, aux, count
 
@@ -55,6 +58,9 @@ def make_sft_train_step(cfg, pad_id: int = 0):
         if optimizer.W > 1:
             loss_d = loss_d.clone()
             dist.all_reduce(loss_d, group=group)
+        if getattr(optimizer, "tp_group", None) is not None:   # per-rank row shares add up over tp
+            loss_d = loss_d.clone()
+            dist.all_reduce(loss_d, group=optimizer.tp_group)
         return loss_d, {"loss": loss_d, "supervised_tokens": count.squeeze(0),
                         "grad_norm": gnorm if gnorm is not None else torch.zeros((), device=loss_d.device)}
 

@@ -93,16 +93,19 @@ def init_model(model_or_id, rng: int = 0, *, tp_size=None, fsdp_size=None, dp_si
 
 
 def forward(model, token_ids_BT, pad_id: int, cfg, *, attention_mask_BT=None, pixel_values=None,
-            image_grid_thw=None, vision_cu_seqlens=None, position_ids_ZBT=None):
-    """Hidden states before lm_head and the aux loss."""
+            image_grid_thw=None, vision_cu_seqlens=None, position_ids_ZBT=None, return_local_rows: bool = False):
+    """Hidden states before lm_head and the aux loss.  ``return_local_rows`` (tensor
+    parallelism): this rank's sequence-parallel rows instead of the gathered [B,T,D]."""
     if attention_mask_BT is None:
         attention_mask_BT = (token_ids_BT != pad_id).to(torch.int32)
     if isinstance(model, Qwen3_5ForConditionalGeneration):
         return model(token_ids_BT, attention_mask_BT.to(torch.int32), pixel_values=pixel_values,
-                     image_grid_thw=image_grid_thw, position_ids_ZBT=position_ids_ZBT)
+                     image_grid_thw=image_grid_thw, position_ids_ZBT=position_ids_ZBT,
+                     return_local_rows=return_local_rows)
     if isinstance(model, Qwen3VL):
         return model(token_ids_BT, attention_mask_BT, position_ids_ZBT=position_ids_ZBT, pixel_values=pixel_values,
-                     image_grid_thw=image_grid_thw, vision_cu_seqlens=vision_cu_seqlens)
+                     image_grid_thw=image_grid_thw, vision_cu_seqlens=vision_cu_seqlens,
+                     return_local_rows=return_local_rows)
     raise ValueError(f"Unsupported VLM model type: {type(model)}")
 
 

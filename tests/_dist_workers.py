@@ -59,7 +59,7 @@ def fsdp_train(rank, world, port, model_id, steps, out_path, ckpt_dir=None, resu
     dist.destroy_process_group()
 
 
-def tp_train(rank, world, port, tp, steps, out_path, untied=False, ckpt_dir=None, resume=False):
+def tp_train(rank, world, port, tp, steps, out_path, untied=False, ckpt_dir=None, resume=False, moe_aux=None):
     """Same weights, same batch: tensor-parallel (tp) x fsdp (world/tp) run on CPU ranks."""
     _init(rank, world, port)
     import dataclasses
@@ -77,6 +77,8 @@ def tp_train(rank, world, port, tp, steps, out_path, untied=False, ckpt_dir=None
     cfg = dataclasses.replace(make_config("qwen3-smoke"), num_kv_heads=2)
     if untied:   # a separate head: split over the vocabulary under tp (vocab-parallel loss)
         cfg = dataclasses.replace(cfg, tie_word_embeddings=False)
+    if moe_aux is not None:   # routed experts with a router loss large enough to steer the run
+        cfg = dataclasses.replace(make_config("qwen3-smoke-moe"), aux_loss_coef=moe_aux)
     torch.manual_seed(0)
     full = Qwen3(cfg, dtype=torch.float32)                       # identical on every rank
     tcfg = trainer.TrainConfig(seed=0, batch_size=2 * (world // tp), seq_len=32, num_steps=100, learning_rate=1e-2,
@@ -142,4 +144,115 @@ def aux_stats(rank, world, port, out_path):
     if rank == 0:
         torch.save({"a1": float(a1), "a2": float(a2), "grad": torch.cat(grads)}, out_path)
     dist.barrier()
+    dist.destroy_process_group()
+
+
+def vl_tp_train(rank, world, port, tp, steps, out_path, moe=False):
+    """Qwen3-VL on an image + text batch: the text decoder tensor-parallel over ``tp`` CPU ranks
+    (vision tower, embedding replicated), same weights and batch as the tp = 1 run."""
+    _init(rank, world, port)
+    import numpy as np
+
+    from omegalax_b200.models.qwen3.tp_layout import tp_slice
+    from omegalax_b200.models.qwen3_vl import Qwen3VL, get_rope_index, make_vl_config
+    from omegalax_b200.models.vision_common import vision_cu_seqlens
+    from omegalax_b200.parallel import mesh as mesh_lib
+    from omegalax_b200.parallel import tp as tp_lib
+    from omegalax_b200.trainers import vlm as trainer
+
+    IMG, VID, VSTART = 1000, 1001, 1002
+    mesh_lib.set_default_mesh(None)
+    tp_lib.set_current(None)
+    mesh = mesh_lib.ensure_mesh(tp_size=tp, fsdp_size=world // tp, dp_size=1)
+    cfg = make_vl_config("qwen3-vl-smoke-moe" if moe else "qwen3-vl-smoke")
+    torch.manual_seed(0)
+    full = Qwen3VL(cfg, dtype=torch.float32)                     # identical on every rank
+    tcfg = trainer.TrainConfig(seed=0, batch_size=2, seq_len=24, num_steps=100, learning_rate=1e-2, max_grad_norm=1.0)
+    model, cfg2 = trainer.init_model(cfg, 0, tp_size=tp, fsdp_size=world // tp, dp_size=1, meta=True)
+    opt = trainer.build_optimizer(model, tcfg, device=torch.device("cpu"))
+    src = dict(full.named_parameters())
+    names = {id(p): n for n, p in model.named_parameters()}
+    tpr = mesh.coords()["tp"]
+    for u in opt.units:
+        for s in u.slots:
+            n = names[id(s.param)]
+            opt.load_full_param(s, tp_slice(n, src[n].detach(), cfg, tp, tpr))
+    opt.sync_compute_from_master()
+    grid = [(1, 4, 6), (1, 4, 4)]
+    nm = [t * (h // 2) * (w // 2) for t, h, w in grid]
+    row0 = [7, 8, VSTART] + [IMG] * nm[0] + [1003, 9, 10, VSTART] + [IMG] * nm[1] + [1003, 11, 12, 13]
+    row1 = list(range(20, 20 + 19))
+    T = 24
+    tok = torch.tensor([row0 + [0] * (T - len(row0)), row1 + [0] * (T - len(row1))], dtype=torch.int32)
+    att = (tok != 0).to(torch.int32)
+    g = torch.Generator().manual_seed(3)
+    pix = torch.randn(sum(t * h * w for t, h, w in grid), 3 * 2 * 14 * 14, generator=g)
+    pos, _ = get_rope_index(tok.numpy().astype(np.int64), grid, None, att.numpy(), 2, IMG, VID, VSTART)
+    lm = att.clone()
+    lm[:, :4] = 0
+    batch = {"token_ids_BT": tok, "attention_mask_BT": att, "loss_mask_BT": lm, "pixel_values": pix,
+             "image_grid_thw": grid, "vision_cu_seqlens": vision_cu_seqlens(grid),
+             "position_ids_ZBT": torch.from_numpy(pos)}
+    step = trainer.make_sft_train_step(cfg2)
+    losses = [float(step(opt, batch)[0]) for _ in range(steps)]
+    if rank == 0:
+        torch.save({"losses": losses, "grad_norm": float(opt.last_grad_norm),
+                    "vocab_parallel": bool(getattr(model, "vocab_parallel", False))}, out_path)
+    dist.barrier()
+    tp_lib.set_current(None)
+    dist.destroy_process_group()
+
+
+def q35_tp_train(rank, world, port, tp, steps, out_path, ckpt_dir=None, resume=False):
+    """Qwen3.5 hybrid MoE (GatedDeltaNet + gated attention) with the attention heads over ``tp``
+    CPU ranks and sequence-parallel rows elsewhere; same weights and batch as the tp = 1 run."""
+    _init(rank, world, port)
+    from omegalax_b200.models.qwen3_5.config import make_config
+    from omegalax_b200.models.qwen3_5.model import Qwen3_5ForConditionalGeneration
+    from omegalax_b200.models.qwen3_5.tp_layout import tp_slice
+    from omegalax_b200.parallel import mesh as mesh_lib
+    from omegalax_b200.parallel import tp as tp_lib
+    from omegalax_b200.trainers import vlm as trainer
+
+    mesh_lib.set_default_mesh(None)
+    tp_lib.set_current(None)
+    mesh = mesh_lib.ensure_mesh(tp_size=tp, fsdp_size=world // tp, dp_size=1)
+    cfg = make_config("qwen3.5-smoke")
+    torch.manual_seed(0)
+    full = Qwen3_5ForConditionalGeneration(cfg, dtype=torch.float32)      # identical on every rank
+    tcfg = trainer.TrainConfig(seed=0, batch_size=2, seq_len=32, num_steps=100, learning_rate=1e-3, max_grad_norm=1.0)
+    model, cfg2 = trainer.init_model(cfg, 0, tp_size=tp, fsdp_size=world // tp, dp_size=1, meta=True)
+    opt = trainer.build_optimizer(model, tcfg, device=torch.device("cpu"))
+    src = dict(full.named_parameters())
+    names = {id(p): n for n, p in model.named_parameters()}
+    tpr = mesh.coords()["tp"]
+    for u in opt.units:
+        for s in u.slots:
+            n = names[id(s.param)]
+            opt.load_full_param(s, tp_slice(n, src[n].detach(), cfg, tp, tpr))
+    opt.sync_compute_from_master()
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(1, 1000, (2, 32), generator=g, dtype=torch.int32)
+    tok[1, 27:] = 0                                                       # right padding on one row
+    att = (tok != 0).to(torch.int32)
+    lm = att.clone()
+    lm[:, :5] = 0
+    batch = {"token_ids_BT": tok, "attention_mask_BT": att, "loss_mask_BT": lm}
+    step = trainer.make_sft_train_step(cfg2)
+    mgr = None
+    if ckpt_dir:
+        from omegalax_b200.trainers import checkpoint_utils
+
+        mgr = checkpoint_utils.CheckpointManager(ckpt_dir, async_write=False)
+        if resume:
+            mgr.restore(None, opt)
+    losses = [float(step(opt, batch)[0]) for _ in range(steps)]
+    if mgr is not None and not resume:
+        mgr.save(steps, opt)
+    if mgr is not None:
+        mgr.close()
+    if rank == 0:
+        torch.save({"losses": losses, "grad_norm": float(opt.last_grad_norm)}, out_path)
+    dist.barrier()
+    tp_lib.set_current(None)
     dist.destroy_process_group()

@@ -78,6 +78,21 @@ def test_tensor_parallel_matches_single_rank(tmp_path):
     assert one["grad_norm"] == pytest.approx(two["grad_norm"], rel=2e-3)
 
 
+def test_moe_tensor_parallel_aux_loss_matches_single_rank(tmp_path):
+    """Routed experts under tp=2 and tp=2 x fsdp=2: the router statistics are taken over every
+    rank's rows, so a run steered by the load-balance loss follows the one-rank curve."""
+    def run(world, tp, name):
+        mp.spawn(W.tp_train, args=(world, _port(), tp, 3, str(tmp_path / name), False, None, False, 2.0),
+                 nprocs=world, join=True)
+        return torch.load(tmp_path / name)
+
+    for world, tp in ((2, 2), (4, 2)):
+        ref = run(world // tp, 1, "a.pt")          # same global batch: 2 rows per data rank
+        got = run(world, tp, "b.pt")
+        assert ref["losses"] == pytest.approx(got["losses"], rel=3e-4, abs=3e-4), (world, tp)
+        assert ref["grad_norm"] == pytest.approx(got["grad_norm"], rel=2e-3)
+
+
 def test_vocab_parallel_head_matches_single_rank(tmp_path):
     """Untied head under tp=2: the head is split over the vocabulary and the loss combines the
     per-slice softmax statistics; loss curve and gradient norm match the tp=1 run."""
@@ -108,6 +123,41 @@ def test_checkpoint_across_tensor_parallel_degrees(tmp_path):
     for world, tp, ck in ((2, 2, ck2), (1, 1, ck2), (2, 2, ck1)):
         got = run(world, tp, 1, "r.pt", ck, True)
         assert got["losses"][0] == pytest.approx(straight["losses"][2], rel=3e-4, abs=3e-4), (world, tp, ck)
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_qwen3_vl_tensor_parallel_matches_single_rank(tmp_path, moe):
+    """Qwen3-VL with the text decoder over tp=2 (image features and DeepStack adds land on the rank
+    that owns the row; vision tower replicated; head split over the vocabulary) follows the tp=1
+    loss curve on an image + text batch."""
+    def run(world, tp, name):
+        mp.spawn(W.vl_tp_train, args=(world, _port(), tp, 3, str(tmp_path / name), moe), nprocs=world, join=True)
+        return torch.load(tmp_path / name)
+
+    one = run(1, 1, "a.pt")
+    two = run(2, 2, "b.pt")
+    assert two["vocab_parallel"] and not one["vocab_parallel"]
+    assert one["losses"] == pytest.approx(two["losses"], rel=3e-4, abs=3e-4)
+    assert one["grad_norm"] == pytest.approx(two["grad_norm"], rel=2e-3)
+
+
+def test_qwen3_5_attention_tensor_parallel_matches_single_rank(tmp_path):
+    """Qwen3.5 hybrid MoE with the gated-attention heads over tp=2 (GatedDeltaNet, experts and
+    head replicated on sequence-parallel rows) follows the tp=1 loss curve, and a tp=2 checkpoint
+    resumes under tp=1."""
+    def run(world, tp, steps, name, ckpt=None, resume=False):
+        mp.spawn(W.q35_tp_train, args=(world, _port(), tp, steps, str(tmp_path / name), ckpt, resume),
+                 nprocs=world, join=True)
+        return torch.load(tmp_path / name)
+
+    one = run(1, 1, 3, "a.pt")
+    two = run(2, 2, 3, "b.pt")
+    assert one["losses"] == pytest.approx(two["losses"], rel=3e-4, abs=3e-4)
+    assert one["grad_norm"] == pytest.approx(two["grad_norm"], rel=2e-3)
+    ck = str(tmp_path / "ck")
+    run(2, 2, 2, "c.pt", ck)
+    got = run(1, 1, 1, "d.pt", ck, True)
+    assert got["losses"][0] == pytest.approx(one["losses"][2], rel=3e-4, abs=3e-4)
 
 
 def test_tp_slices_roundtrip():
