@@ -190,3 +190,113 @@ def tp_train_gpu(rank, world, port, tp, steps, out_path):
         dist.barrier()
     tp_lib.set_current(None)
     dist.destroy_process_group()
+
+
+def _load_tp_slices(opt, model, full, cfg, tp, tpr, tp_slice):
+    src = dict(full.named_parameters())
+    names = {id(p): n for n, p in model.named_parameters()}
+    for u in opt.units:
+        for s in u.slots:
+            n = names[id(s.param)]
+            opt.load_full_param(s, tp_slice(n, src[n].detach(), cfg, tp, tpr))
+    opt.sync_compute_from_master()
+
+
+def q35_tp_train_gpu(rank, world, port, tp, steps, out_path):
+    """Qwen3.5 hybrid MoE: gated-attention heads over tp, GatedDeltaNet / experts replicated on
+    sequence-parallel rows, vs one GPU with the same weights."""
+    _init(rank, world, port)
+    import dataclasses
+
+    from omegalax_b200.models.qwen3_5.config import make_config
+    from omegalax_b200.models.qwen3_5.model import Qwen3_5ForCausalLM
+    from omegalax_b200.models.qwen3_5.tp_layout import tp_slice
+    from omegalax_b200.ops import lib
+    from omegalax_b200.parallel import mesh as mesh_lib
+    from omegalax_b200.parallel import tp as tp_lib
+    from omegalax_b200.trainers import text as trainer
+
+    mesh_lib.set_default_mesh(None)
+    tp_lib.set_current(None)
+    mesh = mesh_lib.ensure_mesh(tp_size=tp, fsdp_size=world // tp, dp_size=1)
+    cfg = dataclasses.replace(make_config("qwen3.5-smoke").text_config, hidden_size=256, vocab_size=2048,
+                              num_attention_heads=4, num_key_value_heads=2, head_dim=128, linear_key_head_dim=128,
+                              linear_value_head_dim=128, linear_num_key_heads=2, linear_num_value_heads=4,
+                              num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128,
+                              shared_expert_intermediate_size=128, mrope_section=(8, 4, 4))
+    torch.manual_seed(0)
+    full = Qwen3_5ForCausalLM(cfg, dtype=torch.float32)
+    tcfg = trainer.TrainConfig(seed=0, batch_size=2, seq_len=256, num_steps=100, learning_rate=1e-3, max_grad_norm=1.0)
+    model, cfg2 = trainer.init_model(cfg, 0, tp_size=tp, fsdp_size=world // tp, dp_size=1, meta=True)
+    opt = trainer.build_optimizer(model, tcfg, device=torch.device("cuda", rank))
+    _load_tp_slices(opt, model, full, cfg, tp, mesh.coords()["tp"], tp_slice)
+    step = trainer.make_sft_train_step(cfg2)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(1, cfg.vocab_size, (2, 256), generator=g, dtype=torch.int32).cuda()
+    batch = {"token_ids_BT": tok, "attention_mask_BT": torch.ones_like(tok), "loss_mask_BT": torch.ones_like(tok)}
+    losses = [float(step(opt, batch)[0]) for _ in range(steps)]
+    torch.cuda.synchronize()
+    lib.check_status()
+    if rank == 0:
+        torch.save({"losses": losses, "tp_size": int(getattr(model, "tp_size", 1))}, out_path)
+    if world > 1:
+        dist.barrier()
+    tp_lib.set_current(None)
+    dist.destroy_process_group()
+
+
+def vl_tp_train_gpu(rank, world, port, tp, steps, out_path):
+    """Qwen3-VL with one image per row: text decoder over tp (image rows of the second sequence
+    fall into the second rank's slice), vision tower replicated, vs one GPU with the same weights."""
+    _init(rank, world, port)
+    import dataclasses
+
+    import numpy as np
+
+    from omegalax_b200.models.qwen3.tp_layout import tp_slice
+    from omegalax_b200.models.qwen3_vl.config import Qwen3VLVisionConfig, make_vl_config
+    from omegalax_b200.models.qwen3_vl.model import Qwen3VL, get_rope_index
+    from omegalax_b200.ops import lib
+    from omegalax_b200.parallel import mesh as mesh_lib
+    from omegalax_b200.parallel import tp as tp_lib
+    from omegalax_b200.trainers import vlm as trainer
+
+    mesh_lib.set_default_mesh(None)
+    tp_lib.set_current(None)
+    mesh = mesh_lib.ensure_mesh(tp_size=tp, fsdp_size=world // tp, dp_size=1)
+    vis = Qwen3VLVisionConfig(hidden_size=256, intermediate_size=512, num_heads=4, patch_size=16, temporal_patch_size=2,
+                              in_channels=3, spatial_merge_size=2, out_hidden_size=256, depth=2,
+                              hidden_act="gelu_pytorch_tanh", num_position_embeddings=256, deepstack_visual_indexes=(0,))
+    cfg = dataclasses.replace(make_vl_config("qwen3-vl-smoke"), emb_dim=256, mlp_dim=512, num_heads=4, num_kv_heads=2,
+                              head_dim=128, vocab_size=2048, mrope_section=(24, 20, 20), vision=vis)
+    torch.manual_seed(0)
+    full = Qwen3VL(cfg, dtype=torch.float32)
+    B, T, n_img = 2, 256, 16
+    tcfg = trainer.TrainConfig(seed=0, batch_size=B, seq_len=T, num_steps=100, learning_rate=1e-3, max_grad_norm=1.0)
+    model, cfg2 = trainer.init_model(cfg, 0, tp_size=tp, fsdp_size=world // tp, dp_size=1, meta=True)
+    dev = torch.device("cuda", rank)
+    opt = trainer.build_optimizer(model, tcfg, device=dev)
+    _load_tp_slices(opt, model, full, cfg, tp, mesh.coords()["tp"], tp_slice)
+    step = trainer.make_sft_train_step(cfg2)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(5, 1000, (B, T), generator=g, dtype=torch.int32)
+    tok[:, 0] = cfg.vision_start_token_id
+    tok[:, 1:1 + n_img] = cfg.image_token_id
+    grid = [(1, 8, 8)] * B
+    pos, _ = get_rope_index(tok.numpy(), np.asarray(grid, dtype=np.int64), None, None, 2, cfg.image_token_id,
+                            cfg.video_token_id, cfg.vision_start_token_id)
+    lm = torch.ones(B, T, dtype=torch.int32)
+    lm[:, :1 + n_img] = 0
+    batch = {"token_ids_BT": tok.to(dev), "attention_mask_BT": torch.ones(B, T, dtype=torch.int32, device=dev),
+             "loss_mask_BT": lm.to(dev), "pixel_values": torch.randn(64 * B, 3 * 2 * 16 * 16, generator=g).to(dev),
+             "image_grid_thw": grid, "vision_cu_seqlens": torch.arange(B + 1, dtype=torch.int32, device=dev) * 64,
+             "position_ids_ZBT": torch.from_numpy(pos).to(torch.int32).to(dev)}
+    losses = [float(step(opt, batch)[0]) for _ in range(steps)]
+    torch.cuda.synchronize()
+    lib.check_status()
+    if rank == 0:
+        torch.save({"losses": losses, "vocab_parallel": bool(getattr(model, "vocab_parallel", False))}, out_path)
+    if world > 1:
+        dist.barrier()
+    tp_lib.set_current(None)
+    dist.destroy_process_group()

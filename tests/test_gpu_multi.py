@@ -95,3 +95,19 @@ def test_tensor_parallel_two_gpus_matches_one(tmp_path):
     assert b["fused_gathers"] > 0       # column-parallel projections gather inside their GEMM launch
     assert b["losses"][-1] < b["losses"][0]
     assert a["losses"] == pytest.approx(b["losses"], rel=3e-2, abs=3e-2)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("family", ["qwen3.5", "qwen3-vl"])
+def test_tensor_parallel_other_families_two_gpus_match_one(tmp_path, family):
+    """Qwen3.5 (attention heads over tp, GatedDeltaNet and experts on sequence-parallel rows) and
+    Qwen3-VL (text decoder over tp, image rows in both ranks' slices) against one GPU."""
+    from tests import _gpu_workers as W
+
+    fn = W.q35_tp_train_gpu if family == "qwen3.5" else W.vl_tp_train_gpu
+    mp.spawn(fn, args=(1, _port(), 1, 4, str(tmp_path / "one.pt")), nprocs=1, join=True)
+    mp.spawn(fn, args=(2, _port(), 2, 4, str(tmp_path / "two.pt")), nprocs=2, join=True)
+    a, b = torch.load(tmp_path / "one.pt"), torch.load(tmp_path / "two.pt")
+    assert all(l == l for l in b["losses"]), b["losses"]
+    assert b["losses"][-1] < b["losses"][0]
+    assert a["losses"] == pytest.approx(b["losses"], rel=4e-2, abs=4e-2)
