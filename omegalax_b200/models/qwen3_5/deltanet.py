@@ -21,6 +21,7 @@ from torch import nn
 
 from ...ops import functional as Fn
 from ...ops import reference as R
+from ...parallel import tp as tp_lib
 from ..qwen3.model import Linear
 from .norms import RMSNormGated
 
@@ -52,10 +53,17 @@ def tp_column_permutation(num_k_heads: int, num_v_heads: int, head_k: int, head_
 
 
 class GatedDeltaNet(nn.Module):
-    def __init__(self, cfg, device=None, dtype=None):
+    def __init__(self, cfg, device=None, dtype=None, tp_size: int = 1):
+        """``tp_size`` > 1: this rank holds nk/tp key heads and the nv/tp value heads that read
+        them (projection rows, conv channels, per-head decay parameters) and the matching input
+        columns of the output projection; the head-dim norm weight is replicated."""
         super().__init__()
         D = cfg.hidden_size
-        self.nk, self.nv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+        if cfg.linear_num_key_heads % tp_size or cfg.linear_num_value_heads % tp_size:
+            raise ValueError(f"linear-attention heads ({cfg.linear_num_key_heads} k / {cfg.linear_num_value_heads} v) "
+                             f"do not divide over tp_size={tp_size}")
+        self.tp_size = tp_size
+        self.nk, self.nv = cfg.linear_num_key_heads // tp_size, cfg.linear_num_value_heads // tp_size
         self.ak, self.av = cfg.linear_key_head_dim, cfg.linear_value_head_dim
         self.key_dim, self.value_dim = self.nk * self.ak, self.nv * self.av
         self.conv_dim = 2 * self.key_dim + self.value_dim
@@ -70,6 +78,10 @@ class GatedDeltaNet(nn.Module):
         self.A_log = nn.Parameter(torch.empty(self.nv, **kw))
         self.norm = RMSNormGated(self.av, cfg.rms_norm_eps, **kw)
         self.out_proj = Linear(self.value_dim, D, **kw)
+        if tp_size > 1:   # everything but the norm differs between tensor-parallel ranks
+            self.tp_sharded = True
+            for m in (self.in_proj_qkv, self.in_proj_z, self.in_proj_b, self.in_proj_a, self.out_proj):
+                m.tp_sharded = True
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -83,6 +95,9 @@ class GatedDeltaNet(nn.Module):
     def forward(self, x, ctx, residual=None):
         """x [M, D] packed rows of a [B, T] batch; ctx.segment_ids marks real tokens."""
         B, T = ctx.B, ctx.T
+        tp = tp_lib.current() if self.tp_size > 1 else None
+        if tp is not None:
+            x = tp_lib.all_gather_rows(x, tp)      # sequence-parallel rows -> whole sequences, this rank's heads
         mask = (ctx.segment_ids != 0).reshape(-1, 1).to(x.dtype)
         x = x * mask
         mixed = self.in_proj_qkv(x).view(B, T, self.conv_dim)
@@ -99,4 +114,6 @@ class GatedDeltaNet(nn.Module):
         core = Fn.gated_delta_rule(q, k, v, g, beta)               # key heads are shared by nv/nk value heads
 
         core = self.norm(core.reshape(-1, self.av), z.reshape(-1, self.av))
+        if tp is not None:
+            return tp_lib.row_parallel_linear(core.reshape(B * T, self.value_dim), self.out_proj.weight, residual, tp)
         return self.out_proj(core.reshape(B * T, self.value_dim), residual=residual)

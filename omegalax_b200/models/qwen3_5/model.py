@@ -29,7 +29,9 @@ class MoEFeedForward(nn.Module):
     """Top-k routed experts (always renormalised) + a shared expert scaled by
     sigmoid(shared_expert_gate(x)); aux = coef * sum_e (mean prob_e - 1/E)^2."""
 
-    def __init__(self, cfg: Qwen3_5TextConfig, device=None, dtype=None):
+    def __init__(self, cfg: Qwen3_5TextConfig, device=None, dtype=None, tp_size: int = 1):
+        """Under tensor parallelism the routed experts are replicated (every rank routes its own
+        sequence-parallel rows); the shared expert's width is split over tp."""
         super().__init__()
         E, D, F_ = cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size
         self.E, self.k, self.coef = E, cfg.num_experts_per_tok, cfg.router_aux_loss_coef
@@ -37,7 +39,7 @@ class MoEFeedForward(nn.Module):
         self.router = Linear(D, E, **kw)
         self.experts_gate_up = nn.Parameter(torch.empty(E, 2 * F_, D, **kw))
         self.experts_down = nn.Parameter(torch.empty(E, D, F_, **kw))
-        self.shared_expert = _SwiGLU(D, cfg.shared_expert_intermediate_size, **kw)
+        self.shared_expert = _SwiGLU(D, cfg.shared_expert_intermediate_size, tp_size=tp_size, **kw)
         self.shared_expert_gate = Linear(D, 1, **kw)
         self.ep = None
         self.aux_group = None  # data ranks over which the load-balance statistics are taken
@@ -72,22 +74,15 @@ class DecoderLayer(nn.Module):
         if self.layer_type == "full_attention":
             self.attn = Attention(cfg, tp_size=tp_size, **kw)
         else:
-            self.linear_attn = GatedDeltaNet(cfg, **kw)
+            self.linear_attn = GatedDeltaNet(cfg, tp_size=tp_size, **kw)
         self.is_moe = cfg.is_moe
-        self.mlp = MoEFeedForward(cfg, **kw) if cfg.is_moe else MLP(cfg.hidden_size, cfg.intermediate_size, **kw)
+        self.mlp = MoEFeedForward(cfg, tp_size=tp_size, **kw) if cfg.is_moe else \
+            MLP(cfg.hidden_size, cfg.intermediate_size, tp_size=tp_size, **kw)
 
     def forward(self, x, ctx: ForwardCtx, cache=None):
         h = self.input_norm(x)
         if self.layer_type == "full_attention":
             x = self.attn(h, ctx, residual=x)
-        elif self.tp_size > 1 and tp_lib.current() is not None:
-            # the recurrence runs over whole sequences: gather the sequence-parallel rows, run the
-            # (replicated) mixer and keep this rank's rows; the gather's backward sums the ranks'
-            # input gradients, each of which comes from its own output rows only
-            tp = tp_lib.current()
-            m = x.shape[0]
-            y = self.linear_attn(tp_lib.all_gather_rows(h, tp), ctx)
-            x = x + y[tp.rank * m:(tp.rank + 1) * m]
         else:
             x = self.linear_attn(h, ctx, residual=x)
         h = self.post_norm(x)

@@ -203,9 +203,10 @@ def vl_tp_train(rank, world, port, tp, steps, out_path, moe=False):
     dist.destroy_process_group()
 
 
-def q35_tp_train(rank, world, port, tp, steps, out_path, ckpt_dir=None, resume=False):
-    """Qwen3.5 hybrid MoE (GatedDeltaNet + gated attention) with the attention heads over ``tp``
-    CPU ranks and sequence-parallel rows elsewhere; same weights and batch as the tp = 1 run."""
+def q35_tp_train(rank, world, port, tp, steps, out_path, ckpt_dir=None, resume=False, model_id="qwen3.5-smoke"):
+    """Qwen3.5 hybrid (GatedDeltaNet + gated attention, MoE or dense) with attention heads,
+    linear-attention heads and MLP / shared-expert width over ``tp`` CPU ranks and
+    sequence-parallel rows in between; same weights and batch as the tp = 1 run."""
     _init(rank, world, port)
     from omegalax_b200.models.qwen3_5.config import make_config
     from omegalax_b200.models.qwen3_5.model import Qwen3_5ForConditionalGeneration
@@ -217,7 +218,7 @@ def q35_tp_train(rank, world, port, tp, steps, out_path, ckpt_dir=None, resume=F
     mesh_lib.set_default_mesh(None)
     tp_lib.set_current(None)
     mesh = mesh_lib.ensure_mesh(tp_size=tp, fsdp_size=world // tp, dp_size=1)
-    cfg = make_config("qwen3.5-smoke")
+    cfg = make_config(model_id)
     torch.manual_seed(0)
     full = Qwen3_5ForConditionalGeneration(cfg, dtype=torch.float32)      # identical on every rank
     tcfg = trainer.TrainConfig(seed=0, batch_size=2, seq_len=32, num_steps=100, learning_rate=1e-3, max_grad_norm=1.0)
@@ -253,6 +254,56 @@ def q35_tp_train(rank, world, port, tp, steps, out_path, ckpt_dir=None, resume=F
         mgr.close()
     if rank == 0:
         torch.save({"losses": losses, "grad_norm": float(opt.last_grad_norm)}, out_path)
+    dist.barrier()
+    tp_lib.set_current(None)
+    dist.destroy_process_group()
+
+
+def q35_tp_gradcheck(rank, world, port, model_id, out_path):
+    """fp64 gradients of a Qwen3.5 model split over ``world`` tensor-parallel ranks (no engine):
+    slices re-assembled / replicated gradients summed, against the unsplit model."""
+    _init(rank, world, port)
+    from omegalax_b200.models.qwen3_5.config import make_config
+    from omegalax_b200.models.qwen3_5.model import Qwen3_5ForCausalLM
+    from omegalax_b200.models.qwen3_5.tp_layout import tp_slice, tp_unslice
+    from omegalax_b200.parallel import tp as tp_lib
+
+    cfg = make_config(model_id).text_config
+    torch.manual_seed(0)
+    full = Qwen3_5ForCausalLM(cfg, dtype=torch.float64)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(1, 1000, (2, 32), generator=g, dtype=torch.int32)
+    seg = torch.ones_like(tok)
+    seg[1, 29:] = 0
+    wt = torch.randn(cfg.hidden_size, generator=g, dtype=torch.float64)
+    h, aux = full(tok, seg)
+    ((h.reshape(-1, h.shape[-1]) @ wt).tanh().sum() + 100.0 * aux).backward()
+    ref = {n: p.grad.clone() for n, p in full.named_parameters() if p.grad is not None}
+    tp_lib.set_current(tp_lib.TPContext(dist.group.WORLD))
+    m = Qwen3_5ForCausalLM(cfg, dtype=torch.float64, tp_size=world)
+    src = dict(full.named_parameters())
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            p.copy_(tp_slice(n, src[n].detach(), cfg, world, rank))
+    for mod in m.modules():
+        if hasattr(mod, "aux_group"):
+            mod.aux_group = dist.group.WORLD
+    h2, aux2 = m(tok, seg, return_local_rows=True)
+    ((h2 @ wt).tanh().sum() + 100.0 * aux2 / world).backward()
+    errs = {}
+    for n, p in m.named_parameters():
+        if n not in ref:
+            continue
+        if tuple(p.shape) != tuple(ref[n].shape):
+            parts = [torch.zeros_like(p.grad) for _ in range(world)]
+            dist.all_gather(parts, p.grad.contiguous())
+            got = tp_unslice(n, parts, cfg)
+        else:
+            got = p.grad.clone()
+            dist.all_reduce(got)
+        errs[n] = float((got - ref[n]).norm() / (ref[n].norm() + 1e-30))
+    if rank == 0:
+        torch.save({"errs": errs, "n_ref": len(ref)}, out_path)
     dist.barrier()
     tp_lib.set_current(None)
     dist.destroy_process_group()

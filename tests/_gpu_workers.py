@@ -203,8 +203,8 @@ def _load_tp_slices(opt, model, full, cfg, tp, tpr, tp_slice):
 
 
 def q35_tp_train_gpu(rank, world, port, tp, steps, out_path):
-    """Qwen3.5 hybrid MoE: gated-attention heads over tp, GatedDeltaNet / experts replicated on
-    sequence-parallel rows, vs one GPU with the same weights."""
+    """Qwen3.5 hybrid MoE: gated-attention heads, GatedDeltaNet heads and the shared expert's width
+    over tp, routed experts replicated on sequence-parallel rows, vs one GPU with the same weights."""
     _init(rank, world, port)
     import dataclasses
 

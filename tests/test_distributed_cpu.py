@@ -141,23 +141,37 @@ def test_qwen3_vl_tensor_parallel_matches_single_rank(tmp_path, moe):
     assert one["grad_norm"] == pytest.approx(two["grad_norm"], rel=2e-3)
 
 
-def test_qwen3_5_attention_tensor_parallel_matches_single_rank(tmp_path):
-    """Qwen3.5 hybrid MoE with the gated-attention heads over tp=2 (GatedDeltaNet, experts and
-    head replicated on sequence-parallel rows) follows the tp=1 loss curve, and a tp=2 checkpoint
-    resumes under tp=1."""
+@pytest.mark.parametrize("model_id", ["qwen3.5-smoke", "qwen3.5-smoke-dense"])
+def test_qwen3_5_tensor_parallel_matches_single_rank(tmp_path, model_id):
+    """Qwen3.5 hybrid (MoE and dense) under tp=2 -- gated-attention heads, GatedDeltaNet heads and
+    MLP / shared-expert width split, routed experts replicated on sequence-parallel rows --
+    follows the tp=1 loss curve, and a tp=2 checkpoint resumes under tp=1."""
     def run(world, tp, steps, name, ckpt=None, resume=False):
-        mp.spawn(W.q35_tp_train, args=(world, _port(), tp, steps, str(tmp_path / name), ckpt, resume),
+        mp.spawn(W.q35_tp_train, args=(world, _port(), tp, steps, str(tmp_path / name), ckpt, resume, model_id),
                  nprocs=world, join=True)
         return torch.load(tmp_path / name)
 
     one = run(1, 1, 3, "a.pt")
     two = run(2, 2, 3, "b.pt")
     assert one["losses"] == pytest.approx(two["losses"], rel=3e-4, abs=3e-4)
-    assert one["grad_norm"] == pytest.approx(two["grad_norm"], rel=2e-3)
+    # fp32 gate gradients of the recurrence amplify re-association differences; the fp64 check below
+    # is the exact one
+    assert one["grad_norm"] == pytest.approx(two["grad_norm"], rel=2e-2)
     ck = str(tmp_path / "ck")
     run(2, 2, 2, "c.pt", ck)
     got = run(1, 1, 1, "d.pt", ck, True)
     assert got["losses"][0] == pytest.approx(one["losses"][2], rel=3e-4, abs=3e-4)
+
+
+@pytest.mark.parametrize("model_id", ["qwen3.5-smoke", "qwen3.5-smoke-dense"])
+def test_qwen3_5_tensor_parallel_gradients_fp64(tmp_path, model_id):
+    """Every parameter gradient of the tp=2 model (slices re-assembled, replicated ones summed over
+    ranks) equals the unsplit model's in fp64, router loss included."""
+    mp.spawn(W.q35_tp_gradcheck, args=(2, _port(), model_id, str(tmp_path / "g.pt")), nprocs=2, join=True)
+    out = torch.load(tmp_path / "g.pt")
+    assert len(out["errs"]) == out["n_ref"] > 20
+    bad = {n: e for n, e in out["errs"].items() if e > 1e-5}
+    assert not bad, bad
 
 
 def test_tp_slices_roundtrip():

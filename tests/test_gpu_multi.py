@@ -100,7 +100,8 @@ def test_tensor_parallel_two_gpus_matches_one(tmp_path):
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("family", ["qwen3.5", "qwen3-vl"])
 def test_tensor_parallel_other_families_two_gpus_match_one(tmp_path, family):
-    """Qwen3.5 (attention heads over tp, GatedDeltaNet and experts on sequence-parallel rows) and
+    """Qwen3.5 (attention / GatedDeltaNet heads and shared-expert width over tp, routed experts on
+    sequence-parallel rows) and
     Qwen3-VL (text decoder over tp, image rows in both ranks' slices) against one GPU."""
     from tests import _gpu_workers as W
 
