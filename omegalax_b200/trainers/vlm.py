@@ -89,9 +89,19 @@ def _pretrained_loader(model_dir: str):
         model, _ = vlm_api.load_pretrained(model_dir, tp_size=None, fsdp_size=None, dp_size=None)
         values = dict(model.named_parameters())
         names = {id(p): n for n, p in optimizer.model.named_parameters()}
+        tp = int(getattr(optimizer, "TP", 1))
+        layout = None
+        if tp > 1:   # the checkpoint holds whole tensors: cut this tensor-parallel rank's slices
+            import importlib
+
+            layout = importlib.import_module(getattr(optimizer.model, "TP_LAYOUT", "omegalax_b200.models.qwen3.tp_layout"))
         for u in optimizer.units:
             for s in u.slots:
-                optimizer.load_full_param(s, values[names[id(s.param)]])
+                n = names[id(s.param)]
+                v = values[n].detach()
+                if layout is not None:
+                    v = layout.tp_slice(n, v, optimizer.model.cfg, tp, optimizer.tp_rank)
+                optimizer.load_full_param(s, v)
         optimizer.sync_compute_from_master()
         del model
         gc.collect()

@@ -307,3 +307,34 @@ def q35_tp_gradcheck(rank, world, port, model_id, out_path):
     dist.barrier()
     tp_lib.set_current(None)
     dist.destroy_process_group()
+
+
+def vl_tp_pretrained(rank, world, port, model_dir, out_path):
+    """Load a HuggingFace-format Qwen3-VL checkpoint into a tp = ``world`` engine through the
+    trainer's loader; rank 0 stores every rank's master copy of two split parameters."""
+    _init(rank, world, port)
+    from omegalax_b200.parallel import mesh as mesh_lib
+    from omegalax_b200.parallel import tp as tp_lib
+    from omegalax_b200.trainers import vlm as trainer
+
+    mesh_lib.set_default_mesh(None)
+    tp_lib.set_current(None)
+    mesh_lib.ensure_mesh(tp_size=world, fsdp_size=1, dp_size=1)
+    tcfg = trainer.TrainConfig(seed=0, batch_size=2, seq_len=24, num_steps=10, learning_rate=1e-3)
+    model, cfg = trainer.init_model(model_dir, 0, tp_size=world, fsdp_size=1, dp_size=1, meta=True)
+    opt = trainer.build_optimizer(model, tcfg, device=torch.device("cpu"))
+    trainer._pretrained_loader(model_dir)(opt, cfg)
+    names = {id(p): n for n, p in model.named_parameters()}
+    mine = {}
+    for u in opt.units:
+        for s in u.slots:
+            n = names[id(s.param)]
+            if n in ("layers.0.attn.qkv_proj.weight", "layers.1.mlp.down_proj.weight", "lm_head.weight", "final_norm.weight"):
+                mine[n] = opt.full_param(s).clone()
+    got = [None] * world
+    dist.all_gather_object(got, mine)
+    if rank == 0:
+        torch.save(got, out_path)
+    dist.barrier()
+    tp_lib.set_current(None)
+    dist.destroy_process_group()

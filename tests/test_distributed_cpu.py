@@ -174,6 +174,27 @@ def test_qwen3_5_tensor_parallel_gradients_fp64(tmp_path, model_id):
     assert not bad, bad
 
 
+def test_vlm_pretrained_loader_cuts_tensor_parallel_slices(tmp_path):
+    """A HuggingFace-format Qwen3-VL checkpoint loaded into a tp=2 engine: each rank's master
+    copy is its slice of the exported tensor."""
+    from omegalax_b200.models.qwen3.tp_layout import tp_slice
+    from omegalax_b200.models.qwen3_vl import Qwen3VL, make_vl_config
+    from omegalax_b200.models.qwen3_vl.params import export_qwen3_vl_to_safetensors
+
+    cfg = make_vl_config("qwen3-vl-smoke")
+    torch.manual_seed(5)
+    model = Qwen3VL(cfg)
+    export_qwen3_vl_to_safetensors(model, cfg, tmp_path / "hf")
+    mp.spawn(W.vl_tp_pretrained, args=(2, _port(), str(tmp_path / "hf"), str(tmp_path / "o.pt")), nprocs=2, join=True)
+    got = torch.load(tmp_path / "o.pt")
+    src = dict(model.named_parameters())
+    for r in range(2):
+        assert len(got[r]) == 4
+        for n, v in got[r].items():
+            torch.testing.assert_close(v, tp_slice(n, src[n].detach(), cfg, 2, r).float(), rtol=0, atol=0)
+    assert got[0]["lm_head.weight"].shape[0] == cfg.vocab_size // 2
+
+
 def test_tp_slices_roundtrip():
     from omegalax_b200.models.qwen3.config import make_config
     from omegalax_b200.models.qwen3.model import Qwen3
