@@ -24,8 +24,14 @@ def main(argv=None):
     api = text_api if registry.infer_arch(a.model_id) == registry.Arch.TEXT else vlm_api
     model, cfg = api.init_model(a.model_id, a.seed, tp_size=a.tp_size, fsdp_size=a.fsdp_size, dp_size=a.dp_size,
                                 device="cpu", dtype=torch.float32)
-    if mesh_lib.rank() == 0:
+    mesh = mesh_lib.current_mesh()
+    if a.tp_size > 1:   # collective over the tensor-parallel group: slices are re-assembled first
+        out = export.export_model_to_hf(model, cfg, a.out_dir, tp_group=mesh.group("tp"))
+    elif mesh_lib.rank() == 0:
         out = export.export_model_to_hf(model, cfg, a.out_dir)
+    else:
+        out = None
+    if mesh_lib.rank() == 0:
         print(f"exported {a.model_id} to {out}")
 
 

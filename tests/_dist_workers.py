@@ -338,3 +338,37 @@ def vl_tp_pretrained(rank, world, port, model_dir, out_path):
     dist.barrier()
     tp_lib.set_current(None)
     dist.destroy_process_group()
+
+
+def tp_export(rank, world, port, family, out_dir):
+    """Export a tensor-parallel model (slices of a seed-0 model) to the HuggingFace format."""
+    _init(rank, world, port)
+    import dataclasses
+
+    from omegalax_b200 import export
+    from omegalax_b200.parallel import tp as tp_lib
+
+    tp_lib.set_current(tp_lib.TPContext(dist.group.WORLD))
+    torch.manual_seed(0)
+    if family == "qwen3":
+        from omegalax_b200.models.qwen3.config import make_config
+        from omegalax_b200.models.qwen3.model import Qwen3 as cls
+        from omegalax_b200.models.qwen3.tp_layout import tp_slice
+
+        cfg = dataclasses.replace(make_config("qwen3-smoke"), num_kv_heads=2, tie_word_embeddings=False)
+    else:
+        from omegalax_b200.models.qwen3_5.config import make_config
+        from omegalax_b200.models.qwen3_5.model import Qwen3_5ForConditionalGeneration as cls
+        from omegalax_b200.models.qwen3_5.tp_layout import tp_slice
+
+        cfg = make_config("qwen3.5-smoke")
+    full = cls(cfg, dtype=torch.float32)
+    model = cls(cfg, dtype=torch.float32, tp_size=world)
+    src = dict(full.named_parameters())
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            p.copy_(tp_slice(n, src[n].detach(), cfg, world, rank))
+    export.export_model_to_hf(model, cfg, out_dir)
+    dist.barrier()
+    tp_lib.set_current(None)
+    dist.destroy_process_group()

@@ -195,6 +195,39 @@ def test_vlm_pretrained_loader_cuts_tensor_parallel_slices(tmp_path):
     assert got[0]["lm_head.weight"].shape[0] == cfg.vocab_size // 2
 
 
+@pytest.mark.parametrize("family", ["qwen3", "qwen3.5"])
+def test_export_of_tensor_parallel_model(tmp_path, family):
+    """A tp=2 model exported to the HuggingFace format (slices re-assembled over the group) loads
+    back as the unsplit model it was cut from."""
+    import dataclasses
+
+    out = tmp_path / "hf"
+    mp.spawn(W.tp_export, args=(2, _port(), family, str(out)), nprocs=2, join=True)
+    torch.manual_seed(0)
+    if family == "qwen3":
+        from omegalax_b200.models.qwen3.config import make_config
+        from omegalax_b200.models.qwen3.loader import create_qwen3_from_safetensors as load
+        from omegalax_b200.models.qwen3.model import Qwen3 as cls
+
+        cfg = dataclasses.replace(make_config("qwen3-smoke"), num_kv_heads=2, tie_word_embeddings=False)
+    else:
+        from omegalax_b200.models.qwen3_5.config import make_config
+        from omegalax_b200.models.qwen3_5.loader import create_qwen3_5_from_safetensors as load
+        from omegalax_b200.models.qwen3_5.model import Qwen3_5ForConditionalGeneration as cls
+
+        cfg = make_config("qwen3.5-smoke")
+    want = cls(cfg, dtype=torch.float32)
+    from omegalax_b200.parallel import mesh as mesh_lib
+
+    mesh_lib.set_default_mesh(None)
+    back = load(str(out), tp_size=1, fsdp_size=1, dp_size=1)
+    back = back[0] if isinstance(back, tuple) else back
+    mesh_lib.set_default_mesh(None)
+    got = dict(back.named_parameters())
+    for n, p in want.named_parameters():
+        torch.testing.assert_close(got[n].float(), p.detach(), rtol=0, atol=0, msg=n)
+
+
 def test_tp_slices_roundtrip():
     from omegalax_b200.models.qwen3.config import make_config
     from omegalax_b200.models.qwen3.model import Qwen3
