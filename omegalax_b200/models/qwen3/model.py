@@ -344,9 +344,17 @@ class Qwen3(nn.Module):
             ctx.extra["kv_valid"] = valid
         x = self.embed(token_ids)
         tp = tp_lib.current() if self.tp_size > 1 else None
+        if tp is not None and cache is not None:
+            # inference with a KV cache (this rank's kv heads): all rows on every rank
+            with tp_lib.replicated_rows(tp):
+                aux_total = torch.zeros((), dtype=torch.float32, device=x.device)
+                for i, layer in enumerate(self.layers):
+                    x, aux = layer(x, ctx, cache[i])
+                    aux_total = aux_total + aux
+                return self.final_norm(x).view(B, T, -1), aux_total
         if tp is not None:
-            if (B * T) % tp.size or cache is not None:
-                raise ValueError("tensor parallelism needs B*T divisible by tp_size and no decode cache")
+            if (B * T) % tp.size:
+                raise ValueError("tensor parallelism needs B*T divisible by tp_size")
             m = B * T // tp.size
             x = x[tp.rank * m:(tp.rank + 1) * m]
         aux_total = torch.zeros((), dtype=torch.float32, device=x.device)

@@ -137,8 +137,30 @@ class _ReduceScatterRows(torch.autograd.Function):
         return _ag_rows(g.contiguous(), ctx.tp), None
 
 
+class replicated_rows:
+    """Context manager for inference with a KV cache: every tensor-parallel rank carries all rows
+    (a decode step has too few rows to split), so the gathers become no-ops and a row-parallel
+    projection ends in an all-reduce instead of a reduce-scatter.  No autograd support."""
+
+    def __init__(self, tp: "TPContext | None"):
+        self.tp = tp
+
+    def __enter__(self):
+        if self.tp is not None:
+            self.prev, self.tp.replicated = getattr(self.tp, "replicated", False), True
+        return self
+
+    def __exit__(self, *a):
+        if self.tp is not None:
+            self.tp.replicated = self.prev
+
+
+def _replicated(tp) -> bool:
+    return tp is not None and getattr(tp, "replicated", False)
+
+
 def all_gather_rows(x, tp: TPContext | None):
-    if tp is None or tp.size == 1:
+    if tp is None or tp.size == 1 or _replicated(tp):
         return x
     return _AllGatherRows.apply(x, tp)
 
@@ -238,6 +260,8 @@ class _ColumnParallelLinearFn(torch.autograd.Function):
 
 def column_parallel_linear(x_local, w_local, tp: TPContext | None):
     """all-gather rows -> projection with this rank's output columns."""
+    if _replicated(tp):
+        return Fn.linear(x_local, w_local)
     if tp is not None and tp.size > 1 and tp.transport == "p2p" and Fn.use_kernels(x_local) \
             and w_local.dtype == torch.bfloat16 and x_local.dim() == 2 and x_local.shape[0] % 128 == 0 \
             and x_local.shape[1] % 8 == 0 and w_local.shape[0] % 8 == 0:
@@ -249,6 +273,10 @@ def row_parallel_linear(x_cols, w_local, residual_local, tp: TPContext | None):
     """projection over this rank's input columns -> reduce-scatter over rows (+ residual)."""
     if tp is None or tp.size == 1:
         return Fn.linear(x_cols, w_local, residual=residual_local)
+    if _replicated(tp):   # all rows on every rank: sum the partial products over tp
+        y = Fn.linear(x_cols, w_local).contiguous()
+        dist.all_reduce(y, group=tp.group)
+        return y if residual_local is None else y + residual_local
     # The epilogue reduction uses vector atomics over NVLink: measured 0.9x the time of GEMM + NCCL
     # reduce-scatter at tp = 2, but several times slower at tp = 8 (atomic rate, not link rate),
     # so wider groups take the unfused path.

@@ -122,15 +122,30 @@ def decode(model, cache: Cache, token_ids_BT, pad_id: int, cfg):
         hidden, aux = model(token_ids_BT, segment_ids, cache, nrp)
         col = token_ids_BT.shape[-1] - nrp - 1
         logits = model.lm_head(hidden[:, col])
+        if getattr(model, "vocab_parallel", False):   # this rank's slice of the vocabulary -> all of it
+            from ..parallel import tp as tp_lib
+
+            tp = tp_lib.current()
+            parts = [torch.empty_like(logits) for _ in range(tp.size)]
+            torch.distributed.all_gather(parts, logits.contiguous(), group=tp.group)
+            logits = torch.cat(parts, dim=-1)
     return logits, cache, aux
 
 
 def make_cache(cfg, batch_size: int, token_len: int, generate_steps: int, dtype=torch.bfloat16, device=None,
-               paged: bool | None = None, page_size: int = 64):
+               paged: bool | None = None, page_size: int = 64, tp_size: int = 1):
     """KV cache for ``decode``.  On CUDA with bf16 (head_dim 128) the paged cache + decode kernels
-    are used by default; otherwise the contiguous power-of-two cache of the reference."""
+    are used by default; otherwise the contiguous power-of-two cache of the reference.  With
+    ``tp_size`` > 1 the (contiguous) cache holds this tensor-parallel rank's kv heads."""
     if not isinstance(cfg, ModelConfig):
         raise NotImplementedError("Cache is only available for Qwen3 text models.")
+    if tp_size > 1:
+        import dataclasses
+
+        if cfg.num_kv_heads % tp_size:
+            raise ValueError(f"kv heads ({cfg.num_kv_heads}) do not divide over tp_size={tp_size}")
+        return init_cache(dataclasses.replace(cfg, num_kv_heads=cfg.num_kv_heads // tp_size), batch_size, token_len,
+                          generate_steps, dtype, device)
     if paged is None:
         paged = (device is not None and torch.device(device).type == "cuda" and dtype == torch.bfloat16
                  and cfg.head_dim == 128 and (cfg.num_heads // cfg.num_kv_heads) in (1, 2, 4, 8))

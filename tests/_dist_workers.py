@@ -372,3 +372,43 @@ def tp_export(rank, world, port, family, out_dir):
     dist.barrier()
     tp_lib.set_current(None)
     dist.destroy_process_group()
+
+
+def tp_decode(rank, world, port, out_path, moe=False):
+    """Prefill + greedy decode steps with a KV cache on a model split over ``world`` tensor-parallel
+    ranks (slices of a seed-0 model); rank 0 stores the logits of every call."""
+    _init(rank, world, port)
+    import dataclasses
+
+    from omegalax_b200.models.qwen3.config import make_config
+    from omegalax_b200.models.qwen3.model import Qwen3
+    from omegalax_b200.models.qwen3.tp_layout import tp_slice
+    from omegalax_b200.parallel import tp as tp_lib
+    from omegalax_b200.text import api as text_api
+
+    tp_lib.set_current(tp_lib.TPContext(dist.group.WORLD) if world > 1 else None)
+    cfg = dataclasses.replace(make_config("qwen3-smoke-moe" if moe else "qwen3-smoke"), num_kv_heads=2,
+                              tie_word_embeddings=False)
+    torch.manual_seed(0)
+    full = Qwen3(cfg, dtype=torch.float32)
+    model = Qwen3(cfg, dtype=torch.float32, tp_size=world)
+    src = dict(full.named_parameters())
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            p.copy_(tp_slice(n, src[n].detach(), cfg, world, rank))
+    g = torch.Generator().manual_seed(1)
+    tok = torch.randint(1, cfg.vocab_size, (2, 6), generator=g)
+    tok[1, :2] = 0                                   # left padding on one row
+    cache = text_api.make_cache(cfg, 2, 6, 4, dtype=torch.float32, device="cpu", tp_size=world)
+    outs = []
+    logits, cache, _ = text_api.decode(model, cache, tok, 0, cfg)
+    outs.append(logits.clone())
+    for _ in range(3):
+        nxt = logits.argmax(-1, keepdim=True)
+        logits, cache, _ = text_api.decode(model, cache, nxt, 0, cfg)
+        outs.append(logits.clone())
+    if rank == 0:
+        torch.save(outs, out_path)
+    dist.barrier()
+    tp_lib.set_current(None)
+    dist.destroy_process_group()

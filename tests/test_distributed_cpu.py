@@ -228,6 +228,19 @@ def test_export_of_tensor_parallel_model(tmp_path, family):
         torch.testing.assert_close(got[n].float(), p.detach(), rtol=0, atol=0, msg=n)
 
 
+@pytest.mark.parametrize("moe", [False, True])
+def test_decode_with_kv_cache_under_tensor_parallelism(tmp_path, moe):
+    """Prefill and greedy decode steps on a tp=2 model (kv heads of the cache split, all rows on
+    every rank, head split over the vocabulary) give the tp=1 logits."""
+    for world in (1, 2):
+        mp.spawn(W.tp_decode, args=(world, _port(), str(tmp_path / f"d{world}.pt"), moe), nprocs=world, join=True)
+    a, b = torch.load(tmp_path / "d1.pt"), torch.load(tmp_path / "d2.pt")
+    assert len(a) == len(b) == 4
+    for x, y in zip(a, b):
+        assert x.shape == y.shape
+        torch.testing.assert_close(x, y, rtol=2e-4, atol=2e-4)
+
+
 def test_tp_slices_roundtrip():
     from omegalax_b200.models.qwen3.config import make_config
     from omegalax_b200.models.qwen3.model import Qwen3
