@@ -82,7 +82,7 @@ def _worker(rank, world, port, mode, out_dir):
         result = f"{type(e).__name__}:{e.ranks}:step{step}"
     with open(os.path.join(out_dir, f"r{rank}.txt"), "w") as f:
         f.write(result)
-    # keep beating (rank 0 also hosts the store) until every survivor has reached its verdict
+    # keep beating (rank 0 also hosts the store) until every survivor has written its result
     t_end = time.monotonic() + 10.0
     while time.monotonic() < t_end and not all(os.path.exists(os.path.join(out_dir, f"r{r}.txt")) for r in range(world - 1)):
         time.sleep(0.05)
