@@ -157,6 +157,8 @@ def main() -> int:
     ap.add_argument("--micro-seqs", type=int, default=None, help="sequences per GPU per micro-batch")
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--remat", default=None, help="full | selective | save:<tags> (default depends on N)")
+    ap.add_argument("--kernel-table", default=None,
+                    help="after the timed regions, trace one more step and write its per-kernel device times here")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -280,6 +282,18 @@ def main() -> int:
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop() if rank == 0 else {}
     lib.check_status()
+
+    if args.kernel_table:   # outside both timed regions
+        from omegalax_b200.utils import profiling
+
+        def traced():
+            for a in range(accum):
+                step_fn(opt, dev_pool[a % len(dev_pool)])
+
+        rows = profiling.kernel_time_table(traced, top=60)
+        if rank == 0:
+            with open(args.kernel_table, "w") as f:
+                f.write(profiling.format_table(rows) + "\n")
 
     t = torch.tensor([ms, e2e_s * 1000.0], device=device)
     if N > 1:

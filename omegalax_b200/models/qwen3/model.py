@@ -23,6 +23,9 @@ from .norms import RMSNorm
 from .utils import compute_positions_from_segment_ids, count_left_pads
 
 
+from ...utils.profiling import scoped
+
+
 class Embedding(nn.Module):
     """Token embedding table, normal(0, 0.02) init."""
 
@@ -59,6 +62,18 @@ class Linear(nn.Module):
         return Fn.linear(x, self.weight, residual=residual, bias=self.bias, tag=tag)
 
 
+def left_pad_cu_seqlens(k_start, B: int, T: int) -> torch.Tensor:
+    """Packed-sequence boundaries for B rows of T positions whose first ``k_start[b]`` positions are
+    left padding: int32 [2B+1] = (b*T, b*T + k_start[b]) per row, then B*T.  Each row becomes two
+    causal sequences, its pads and its real tokens, so a real query never sees a pad key (what the
+    ``k_start`` mask of the PyTorch path does) while the kernels keep plain causal sequences.  Pad
+    positions attend among themselves; nothing downstream reads them.  Built on the device."""
+    base = torch.arange(B, device=k_start.device, dtype=torch.int64) * T
+    cu = torch.stack([base, base + k_start.to(torch.int64).clamp(0, T)], dim=1).reshape(-1)
+    end = torch.full((1,), B * T, device=k_start.device, dtype=torch.int64)
+    return torch.cat([cu, end]).to(torch.int32)
+
+
 @dataclasses.dataclass
 class ForwardCtx:
     """Per-call state shared by all layers."""
@@ -89,6 +104,7 @@ class Attention(nn.Module):
         self.scale = Kd ** -0.5
         self.qkv_proj.tp_sharded = self.o_proj.tp_sharded = tp_size > 1
 
+    @scoped("attention")
     def forward(self, x, ctx: ForwardCtx, residual=None, cache: LayerCache | None = None):
         tp = tp_lib.current() if self.tp_size > 1 else None
         if tp is not None:
@@ -150,6 +166,7 @@ class MLP(nn.Module):
         self.down_proj = Linear(hidden, dim, device=device, dtype=dtype)
         self.gate_up_proj.tp_sharded = self.down_proj.tp_sharded = tp_size > 1
 
+    @scoped("feed_forward")
     def forward(self, x, residual=None):
         tp = tp_lib.current() if self.tp_size > 1 else None
         if tp is not None:
@@ -182,6 +199,7 @@ class MoEFeedForward(nn.Module):
             nn.init.normal_(self.experts_gate_up, std=1.0 / math.sqrt(self.experts_gate_up.shape[2]))
             nn.init.normal_(self.experts_down, std=1.0 / math.sqrt(self.experts_down.shape[2]))
 
+    @scoped("moe_feed_forward")
     def forward(self, x, residual=None):
         logits = self.router(x)
         probs, w, idx = moe_ops.route(logits, self.k, self.norm_topk)
@@ -253,7 +271,7 @@ class Qwen3(nn.Module):
                                     torch.full_like(t.expand(B, T), 2 ** 30))
             k_start = start_ind.to(torch.int64)
         sin, cos = R.rope_tables(positions.reshape(-1), self.cfg.head_dim, self.cfg.rope_theta)
-        cu = torch.arange(B + 1, device=dev, dtype=torch.int32) * T
+        cu = left_pad_cu_seqlens(k_start, B, T)
         return ForwardCtx(B=B, T=T, sin=sin, cos=cos, cu_seqlens=cu, segment_ids=segment_ids,
                           k_start=k_start, positions=positions)
 

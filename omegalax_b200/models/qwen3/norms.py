@@ -7,6 +7,9 @@ from torch import nn
 from ...ops import functional as Fn
 
 
+from ...utils.profiling import scoped
+
+
 class RMSNorm(nn.Module):
     def __init__(self, dim: int, eps: float = 1e-6, *, one_plus: bool = False,
                  scale_in_dtype: bool = False, device=None, dtype=None):
@@ -20,5 +23,6 @@ class RMSNorm(nn.Module):
             with torch.no_grad():
                 self.weight.fill_(0.0 if self.one_plus else 1.0)
 
+    @scoped("rms_norm")
     def forward(self, x):
         return Fn.rmsnorm(x, self.weight, self.eps, self.one_plus, self.scale_in_dtype)

@@ -16,6 +16,9 @@ from ..qwen3.model import Linear
 from .norms import RMSNorm
 
 
+from ...utils.profiling import scoped
+
+
 class Attention(nn.Module):
     def __init__(self, cfg, device=None, dtype=None, tp_size: int = 1):
         super().__init__()
@@ -39,6 +42,7 @@ class Attention(nn.Module):
         self.scale = Kd ** -0.5
         self.qkv_proj.tp_sharded = self.o_proj.tp_sharded = tp_size > 1
 
+    @scoped("attention")
     def forward(self, x, ctx, residual=None):
         tp = tp_lib.current() if self.tp_size > 1 else None
         if tp is not None:

@@ -26,6 +26,9 @@ from ..qwen3.model import Linear
 from .norms import RMSNormGated
 
 
+from ...utils.profiling import scoped
+
+
 def _l2norm(x, eps: float = 1e-6):
     return R.l2norm(x, eps)
 
@@ -92,6 +95,7 @@ class GatedDeltaNet(nn.Module):
             self.dt_bias.fill_(1.0)
             self.A_log.copy_(torch.log(torch.empty(self.nv).uniform_(0, 16).clamp_min(1e-4)))
 
+    @scoped("gated_delta_net")
     def forward(self, x, ctx, residual=None):
         """x [M, D] packed rows of a [B, T] batch; ctx.segment_ids marks real tokens."""
         B, T = ctx.B, ctx.T

@@ -21,6 +21,9 @@ from .norms import RMSNorm
 from .rope import mrope_half_tables
 
 
+from ...utils.profiling import scoped
+
+
 class MLP(_SwiGLU):
     pass
 
@@ -50,6 +53,7 @@ class MoEFeedForward(nn.Module):
             nn.init.normal_(self.experts_gate_up, std=1.0 / math.sqrt(self.experts_gate_up.shape[2]))
             nn.init.normal_(self.experts_down, std=1.0 / math.sqrt(self.experts_down.shape[2]))
 
+    @scoped("moe_ffn")
     def forward(self, x, residual=None):
         probs, w, idx = moe_ops.route(self.router(x), self.k, True)
         if self.ep is not None:
@@ -114,6 +118,7 @@ class TextModel(nn.Module):
         return ForwardCtx(B=B, T=T, sin=sin.reshape(B * T, -1), cos=cos.reshape(B * T, -1), cu_seqlens=cu,
                           segment_ids=segment_ids, k_start=None, positions=position_ids_ZBT)
 
+    @scoped("text_model")
     def forward(self, token_ids, segment_ids, position_ids_ZBT=None, inputs_embeds=None, return_local_rows: bool = False):
         """Under tensor parallelism the rows between the blocks are sequence-parallel (this rank
         carries rows [r*M/tp, (r+1)*M/tp) of the flattened token rows); ``return_local_rows``

@@ -8,6 +8,9 @@ from ...ops import functional as Fn
 from ...ops import reference as R
 
 
+from ...utils.profiling import scoped
+
+
 class RMSNorm(nn.Module):
     """(1 + weight) * x / rms(x), fp32 arithmetic, weight initialised to zero."""
 
@@ -21,6 +24,7 @@ class RMSNorm(nn.Module):
             with torch.no_grad():
                 self.weight.zero_()
 
+    @scoped("rms_norm")
     def forward(self, x):
         return Fn.rmsnorm(x, self.weight, self.eps, one_plus=True)
 
@@ -38,6 +42,7 @@ class RMSNormGated(nn.Module):
             with torch.no_grad():
                 self.weight.fill_(1.0)
 
+    @scoped("rms_norm_gated")
     def forward(self, x, gate):
         return Fn.rmsnorm_gated(x, self.weight, gate, self.eps)
 
@@ -57,5 +62,6 @@ class LayerNorm(nn.Module):
                 self.weight.fill_(1.0)
                 self.bias.zero_()
 
+    @scoped("layer_norm")
     def forward(self, x):
         return Fn.layernorm(x, self.weight, self.bias, self.eps)

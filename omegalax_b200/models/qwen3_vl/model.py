@@ -11,7 +11,7 @@ from torch import nn
 from ...ops import functional as Fn
 from ...ops import reference as R
 from ...parallel import tp as tp_lib
-from ..qwen3.model import DecoderLayer, Embedding, ForwardCtx, Linear, vocab_parallel_head
+from ..qwen3.model import DecoderLayer, Embedding, ForwardCtx, Linear, left_pad_cu_seqlens, vocab_parallel_head
 from ..qwen3.norms import RMSNorm
 from ..qwen3_5.rope import interleave_mrope
 from .config import Qwen3VLConfig
@@ -166,7 +166,7 @@ class Qwen3VL(nn.Module):
         seg = (attention_mask != 0).to(torch.int32)
         first = (seg.cumsum(-1) == 0).sum(-1)
         ctx = ForwardCtx(B=B, T=T, sin=sin.reshape(B * T, -1), cos=cos.reshape(B * T, -1),
-                         cu_seqlens=torch.arange(B + 1, device=dev, dtype=torch.int32) * T, segment_ids=seg,
+                         cu_seqlens=left_pad_cu_seqlens(first, B, T), segment_ids=seg,
                          k_start=first.to(torch.int64), positions=position_ids_ZBT)
         tp = tp_lib.current() if self.tp_size > 1 else None
         if tp is not None:

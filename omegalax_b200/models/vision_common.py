@@ -23,6 +23,9 @@ from .qwen3_5.norms import LayerNorm
 from .qwen3_5.rope import apply_vision_rope
 
 
+from ..utils.profiling import scoped
+
+
 def token_spatial_coords(grid_thw, merge: int, device=None):
     """(row, col, image_id) of every patch token in merge-block order."""
     rows, cols, img = [], [], []
@@ -61,6 +64,7 @@ class VisionMLP(nn.Module):
         self.linear_fc2 = Linear(hidden, dim, bias=True, **kw)
         self.act = act
 
+    @scoped("vision_mlp")
     def forward(self, x):
         h = self.linear_fc1(x)
         h = Fn.gelu_tanh(h) if self.act in ("gelu_pytorch_tanh", "gelu_tanh") else F.gelu(h)
@@ -75,6 +79,7 @@ class VisionAttention(nn.Module):
         self.proj = Linear(dim, dim, bias=True, **kw)
         self.scale = self.Kd ** -0.5
 
+    @scoped("vision_attention")
     def forward(self, x, cos, sin, cu_seqlens, max_seqlen: int):
         N = x.shape[0]
         qkv = self.qkv(x).view(N, 3, self.H, self.Kd)
@@ -110,6 +115,7 @@ class VisionPatchMerger(nn.Module):
         self.linear_fc1 = Linear(self.group, self.group, bias=True, **kw)
         self.linear_fc2 = Linear(self.group, out_dim, bias=True, **kw)
 
+    @scoped("vision_merger")
     def forward(self, x):
         x = self.norm(x.reshape(-1, self.group) if self.postshuffle else x).reshape(-1, self.group)
         return self.linear_fc2(F.gelu(self.linear_fc1(x)))
@@ -176,6 +182,7 @@ class VisionTower(nn.Module):
         emb = torch.cat([rot, rot], dim=-1)
         return emb.cos(), emb.sin()
 
+    @scoped("vision_model")
     def forward(self, pixel_values, grid_thw, cu_seqlens=None):
         grid = _grid_list(grid_thw)
         dev = pixel_values.device

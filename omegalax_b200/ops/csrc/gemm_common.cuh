@@ -36,6 +36,12 @@ struct GemmArgs {
   long long ag_chunk_bytes;
   uint32_t* ag_flags;              // [world] counters, only ever incremented
   uint32_t ag_target;              // value a chunk's counter has when the chunk is complete
+  // CTA-pair kernel only.  raster_gm: tile rows that share one sweep over the tile columns.
+  // l2_prefetch: distance (in k-blocks) of the TMA prefetch into L2 that runs ahead of the loads
+  // (0 = none).  k_splits > 1 (reducing output modes only): the reduction is cut into k_splits
+  // slices of k_per_split elements; every (tile, slice) is one unit of work and its partial result
+  // is added to C with vector reductions.
+  int raster_gm, l2_prefetch, k_splits, k_per_split;
   int* status;
 };
 
@@ -127,7 +133,20 @@ __device__ __forceinline__ void gemm_store_slice(const GemmArgs& p, long long c_
             } else {
               float* cp = (float*)p.C + c_off + grow * p.ldc + col0;
               const bool accum = p.out_mode == 2;
-              if (ncols == 32 && ((((uintptr_t)cp) & 15) == 0)) {
+              if (accum && p.k_splits > 1) {
+                // several units add into the same tile: fire-and-forget vector reductions
+                if (ncols == 32 && ((((uintptr_t)cp) & 15) == 0)) {
+  #pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + i * 4),
+                                 "f"(__uint_as_float(v[i * 4 + 0])), "f"(__uint_as_float(v[i * 4 + 1])),
+                                 "f"(__uint_as_float(v[i * 4 + 2])), "f"(__uint_as_float(v[i * 4 + 3]))
+                                 : "memory");
+                  }
+                } else {
+                  for (int i = 0; i < ncols; ++i) atomicAdd(cp + i, __uint_as_float(v[i]));
+                }
+              } else if (ncols == 32 && ((((uintptr_t)cp) & 15) == 0)) {
   #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                   float4 q = make_float4(__uint_as_float(v[i * 4 + 0]), __uint_as_float(v[i * 4 + 1]),

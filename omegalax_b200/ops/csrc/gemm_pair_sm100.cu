@@ -38,8 +38,8 @@ struct PairTile {
 };
 
 __device__ __forceinline__ PairTile pair_tile(const GemmArgs& p, int t, int rank) {
-  // 4 tile rows (1024 output rows) share a sweep over the tile columns for L2 reuse
-  const int GM = 4;
+  // GM tile rows (GM * 256 output rows) share a sweep over the tile columns for L2 reuse
+  const int GM = p.raster_gm;
   const int per_group = GM * p.num_n_blocks;
   const int g = t / per_group;
   const int first_m = g * GM;
@@ -97,6 +97,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
   const int pair0 = (int)((blockIdx.x - ncopy) >> 1);
   const int pair_step = (int)((gridDim.x - ncopy) >> 1);
+  const int total_units = p.total_tiles * p.k_splits;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kPairStages; ++i) {
@@ -129,7 +130,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       uint32_t phase = 0;
       uint32_t ag_seen = 0;
       bool ok = true;
-      for (int t = pair0; t < p.total_tiles && ok; t += pair_step) {
+      const int pf_dist = p.l2_prefetch * BK;
+      for (int u = pair0; u < total_units && ok; u += pair_step) {
+        const int ks = u / p.total_tiles;        // slice-major: a wave of units shares operand panels
+        const int t = u - ks * p.total_tiles;
+        const int k_begin = ks * p.k_per_split;
+        const int k_end = min(p.K, k_begin + p.k_per_split);
         const PairTile ti = pair_tile(p, t, rank);
         bool ag_local = false;   // tile of this GPU's own chunk: read it where it already is
         int ag_row = 0;
@@ -148,7 +154,22 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             ag_seen |= 1u << ch;
           }
         }
-        for (int k0 = 0; k0 < p.K; k0 += BK) {
+        for (int k0 = k_begin; k0 < k_end; k0 += BK) {
+          if (pf_dist > 0 && !ag_local) {   // warm L2 for the k-block pf_dist ahead of the one loaded now
+            const int kp = k0 + pf_dist;
+            if (kp < k_end) {
+              if (!A_MN) tma_prefetch_l2_2d(&tmA, kp, ti.row0);
+              else {
+#pragma unroll
+                for (int j = 0; j < BM / 64; ++j) tma_prefetch_l2_2d(&tmA, ti.row0 + j * 64, kp);
+              }
+              if (!B_MN) tma_prefetch_l2_2d(&tmB, kp, ti.b_row0);
+              else {
+#pragma unroll
+                for (int j = 0; j < kPairBNL / 64; ++j) tma_prefetch_l2_2d(&tmB, ti.b_row0 + j * 64, kp);
+              }
+            }
+          }
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_EMPTY);
           if (!ok) break;
           uint8_t* sa = smem + stage * L::kStageBytes;
@@ -186,13 +207,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = pair0; t < p.total_tiles && ok; t += pair_step) {
+      for (int u = pair0; u < total_units && ok; u += pair_step) {
+        const int ks = u / p.total_tiles;
+        const int k_begin = ks * p.k_per_split;
+        const int k_end = min(p.K, k_begin + p.k_per_split);
         ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kPairBN;
         uint32_t accumulate = 0;
-        for (int k0 = 0; k0 < p.K; k0 += BK) {
+        for (int k0 = k_begin; k0 < k_end; k0 += BK) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, OB_ERR_WAIT_FULL);
           if (!ok) break;
           tc_fence_after();
@@ -228,7 +252,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int t = pair0; t < p.total_tiles && ok; t += pair_step) {
+    for (int u = pair0; u < total_units && ok; u += pair_step) {
+      const int t = u % p.total_tiles;
       const PairTile ti = pair_tile(p, t, rank);
       ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL);
       if (!ok) break;
@@ -275,9 +300,47 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
 }
 
+// Process-wide tuning knobs (ob_gemm_pair_tune): -1 = decide per launch.
+static int g_tune_gm = -1, g_tune_prefetch = -1, g_tune_splitk = -1;
+
+// Tile rows per raster group: as many as keep the group's A panels (GM x 256 rows x K) within
+// about 24 MB of L2 while the B panels stream past, between 2 and 16.
+static int pick_gm(int K) {
+  if (g_tune_gm > 0) return g_tune_gm;
+  const long long panel = 256ll * (K > 0 ? K : 1) * 2;
+  int gm = 2;
+  while (gm < 16 && (long long)(2 * gm) * panel <= (24ll << 20)) gm *= 2;
+  return gm;
+}
+
+// Slices of the reduction for the reducing output modes: the fewest that fill the last wave of
+// the `pairs` resident clusters to 95 % (every slice at least 1024 deep), at most 8.
+static void pick_splits(GemmArgs& g, int pairs) {
+  g.k_splits = 1;
+  g.k_per_split = g.K > 0 ? g.K : BK;
+  if (g.out_mode < 2 || g.K < 2048 || g_tune_splitk == 0 || pairs <= 0) return;
+  const int kblocks = (g.K + BK - 1) / BK;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= 8; ++s) {
+    if (g_tune_splitk > 0 && s != g_tune_splitk) continue;
+    const int per = (kblocks + s - 1) / s;
+    if (s > 1 && per * BK < 1024) break;
+    const int s_eff = (kblocks + per - 1) / per;
+    const long long units = (long long)g.total_tiles * s_eff;
+    const double eff = (double)units / (double)(((units + pairs - 1) / pairs) * pairs);
+    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    if (best_eff >= 0.95 && g_tune_splitk <= 0) break;
+  }
+  const int per = (kblocks + best - 1) / best;
+  g.k_per_split = per * BK;
+  g.k_splits = (kblocks + per - 1) / per;
+}
+
 template <bool A_MN, bool B_MN>
-static int launch_pair(const void* A, const void* B, const GemmArgs& args, long long a_rows, long long a_cols,
+static int launch_pair(const void* A, const void* B, const GemmArgs& args_in, long long a_rows, long long a_cols,
                        long long lda, long long b_rows, long long b_cols, long long ldb, cudaStream_t stream) {
+  GemmArgs args = args_in;
   CUtensorMap tmA, tmB;
   int e;
   if (!A_MN) e = make_tmap_2d(&tmA, A, a_rows, a_cols, lda, BM, BK);
@@ -320,7 +383,10 @@ static int launch_pair(const void* A, const void* B, const GemmArgs& args, long 
     copy = args.ag_copy_ctas;
     pairs -= copy / 2;
   }
-  if (pairs > args.total_tiles) pairs = args.total_tiles;
+  args.raster_gm = pick_gm(args.K);
+  args.l2_prefetch = g_tune_prefetch >= 0 ? g_tune_prefetch : 0;
+  pick_splits(args, pairs);
+  if (pairs > args.total_tiles * args.k_splits) pairs = args.total_tiles * args.k_splits;
   if (pairs <= 0) return args.ag_side ? 6006 : 0;
   kern<<<2 * pairs + copy, kGemmThreads, PairSmem::kTotal, stream>>>(tmA, tmB, tmL, args);
   OB_CHECK_LAUNCH();
@@ -332,6 +398,13 @@ static int launch_pair(const void* A, const void* B, const GemmArgs& args, long 
 using namespace ob;
 
 extern "C" {
+
+// Tuning knobs of the CTA-pair kernel for the whole process; -1 restores the per-launch choice.
+// gm: tile rows per raster group; prefetch: L2 prefetch distance in k-blocks (0 off);
+// splitk: 0 never split the reduction, n > 0 always n slices (reducing output modes only).
+void ob_gemm_pair_tune(int gm, int prefetch, int splitk) {
+  g_tune_gm = gm; g_tune_prefetch = prefetch; g_tune_splitk = splitk;
+}
 
 // Same contract as ob_gemm_bf16 (plain mode), computed by CTA pairs on 256 x 256 tiles.
 int ob_gemm_bf16_pair(const void* A, const void* B, void* C, const void* residual, int M, int N, int K, long long lda,

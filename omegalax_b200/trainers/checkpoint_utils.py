@@ -11,7 +11,11 @@ Layout under ``save_dir``::
 
 A step directory is written under a temporary name and renamed when every rank is done, so a
 crash never leaves a half-written checkpoint; only the newest ``max_to_keep`` are kept.  The
-device->host copy happens on the caller's stream; file writing runs on a background thread.
+device->host copy happens on the caller's stream; file writing runs on a background thread at
+any world size: every rank's thread writes its own files and then a ``rankNNNNN.ok`` marker (or
+``.err``), rank 0's thread waits for all markers and only then renames, and the next
+``wait_until_finished`` agrees on the outcome over the process group, so a failed write on any
+rank neither produces a "valid" checkpoint nor prunes an older good one.
 Restore reshards: a checkpoint written with W ranks can be read with any other shard count.
 (The reference keeps the same items -- train state incl. optimizer moments and step counters,
 rng, input iterator -- through orbax: omegalax/trainers/text.py:94-155,
@@ -23,6 +27,8 @@ import json
 import os
 import shutil
 import threading
+import time
+import warnings
 from pathlib import Path
 from typing import Any, Protocol
 
@@ -48,6 +54,16 @@ def _world():
     return dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
 
 
+def _all_ranks_ok(ok: bool) -> bool:
+    """Minimum of a success flag over the default process group."""
+    if _world() == 1:
+        return ok
+    dev = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend() == "nccl" else torch.device("cpu")
+    t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(int(t.item()))
+
+
 class CheckpointManager:
     def __init__(self, save_dir: str | os.PathLike, *, save_interval_steps: int | None = None,
                  max_to_keep: int = 2, async_write: bool = True):
@@ -58,6 +74,8 @@ class CheckpointManager:
         self.async_write = async_write
         self._thread: threading.Thread | None = None
         self._error: BaseException | None = None
+        self._pending = False          # a save whose outcome the ranks have not agreed on yet
+        self.peer_write_timeout_s = 1800.0
         if _rank() == 0:
             self.cleanup_tmp_directories()
         _barrier()
@@ -99,6 +117,7 @@ class CheckpointManager:
                     "tp_world": int(getattr(engine, "TP", 1)),
                     "optimizer_step": int(engine.step_count), "params": params, "extra": extra or {}}
         iter_state = input_iter.get_state() if input_iter is not None else None
+        manifest["has_iter_state"] = iter_state is not None
         rng_state = {"cpu": torch.get_rng_state()}
         tmp = self.dir / f"{step:06d}.tmp"
         final = self.step_dir(step)
@@ -116,22 +135,45 @@ class CheckpointManager:
                 torch.save(rng_state, tmp / f"rng_{r:05d}.pt")
                 if r == 0:
                     (tmp / "manifest.json").write_text(json.dumps(manifest))
+                (tmp / f"rank{r:05d}.ok").write_text("ok")
             except BaseException as e:  # surfaced by wait_until_finished
                 self._error = e
+                try:
+                    (tmp / f"rank{r:05d}.err").write_text(repr(e))
+                except Exception:
+                    pass
 
-        if self.async_write and w == 1:
-            self._thread = threading.Thread(target=lambda: (write(), self._finalize(tmp, final)), daemon=True)
+        def write_and_finish():
+            write()
+            if r != 0:
+                return
+            # rank 0 renames once every rank's marker is there; no collective runs on this thread
+            t0 = time.monotonic()
+            while self._error is None:
+                if any(tmp.glob("rank*.err")):
+                    self._error = RuntimeError("a peer rank failed to write its checkpoint shard")
+                    break
+                if len(list(tmp.glob("rank*.ok"))) >= w:
+                    break
+                if time.monotonic() - t0 > self.peer_write_timeout_s:
+                    self._error = TimeoutError("peer ranks did not finish writing their checkpoint shards")
+                    break
+                time.sleep(0.01)
+            self._finalize(tmp, final)
+
+        self._pending = True
+        if self.async_write:
+            self._thread = threading.Thread(target=write_and_finish, daemon=True)
             self._thread.start()
         else:
-            write()
-            _barrier()
-            if r == 0:
-                self._finalize(tmp, final)
-            _barrier()
+            write_and_finish()
+            self.wait_until_finished()
 
     def _finalize(self, tmp: Path, final: Path) -> None:
         if self._error is not None:
             return
+        for marker in list(tmp.glob("rank*.ok")):
+            marker.unlink(missing_ok=True)
         if final.exists():
             shutil.rmtree(final)
         os.replace(tmp, final)
@@ -140,9 +182,16 @@ class CheckpointManager:
             shutil.rmtree(self.step_dir(s), ignore_errors=True)
 
     def wait_until_finished(self) -> None:
+        """Join the writer thread; with several ranks, agree on the outcome (a collective: every
+        rank calls this at the same point of the loop, as ``save`` / ``restore`` / ``close`` do)."""
         if self._thread is not None:
             self._thread.join()
             self._thread = None
+        if self._pending:
+            self._pending = False
+            everyone_ok = _all_ranks_ok(self._error is None)
+            if self._error is None and not everyone_ok:
+                self._error = RuntimeError("another rank failed to write its checkpoint shard")
         if self._error is not None:
             e, self._error = self._error, None
             raise RuntimeError("checkpoint write failed") from e
@@ -213,6 +262,13 @@ class CheckpointManager:
         engine.sync_compute_from_master()
         if input_iter is not None:
             p = d / f"input_iter_{r:05d}.json"
+            if int(manifest["world_size"]) != _world():
+                warnings.warn(f"checkpoint step {step} was written by {manifest['world_size']} ranks and is read by "
+                              f"{_world()}: per-rank data-iterator states do not carry over, rank {r} "
+                              + ("reuses the state of the same rank index" if p.exists() else "restarts its data iterator"),
+                              RuntimeWarning, stacklevel=2)
+            elif not p.exists() and manifest.get("has_iter_state", False):
+                raise RuntimeError(f"checkpoint step {step} has no data-iterator state for rank {r} ({p.name})")
             if p.exists():
                 input_iter.set_state(json.loads(p.read_text()))
         p = d / f"rng_{r:05d}.pt"

@@ -162,6 +162,21 @@ def make_sft_eval_step(cfg, pad_id: int = 0):
     return sft_eval_step
 
 
+def _device_health_check(optimizer, use_cuda: bool) -> None:
+    """Raise if any kernel gave up on a bounded wait, or if an expert-parallel receive buffer
+    overflowed, since the last check.  Called wherever the loop already synchronises (metric
+    read-out, checkpoint write) and always *before* a checkpoint is written, so that a step
+    computed from partial kernel output can never replace a good checkpoint."""
+    if not use_cuda:
+        return
+    from ..ops import lib
+
+    lib.check_status()
+    ep = getattr(optimizer, "_ep", None)
+    if ep is not None:
+        ep.check()
+
+
 def _write_checkpoint_config(save_dir: Path, cfg) -> None:
     if is_primary():
         save_hf_config(export_lib.model_config_to_hf_dict(cfg), save_dir)
@@ -247,6 +262,7 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
                                      peak_tflops=peak_tflops, wandb_run=wandb_run, jsonl_file=jsonl)
         if res is not None:
             last_metrics = res
+            _device_health_check(optimizer, use_cuda)   # the metric read-out above synchronised already
             if is_primary():
                 print(" ".join(f"{k}={v:.6g}" if isinstance(v, float) else f"{k}={v}" for k, v in res.items()), flush=True)
 
@@ -292,6 +308,7 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
             watchdog.beat(step)
             watchdog.pause()      # checkpoint writes and evaluation are not steps
         if manager is not None and save_every and step % save_every == 0:
+            _device_health_check(optimizer, use_cuda)
             manager.save(step, optimizer, data_iter)
         if eval_step is not None and val_every and step % val_every == 0:
             tot = sup = 0.0
@@ -308,23 +325,25 @@ def run_sft(model_id_or_cfg, train_cfg: TrainConfig, data_iter, *, save_dir=None
             watchdog.resume()
     if watchdog is not None:
         watchdog.stop()
-    if hb is not None:
-        hb.leave()
-        hb.stop()
     if prof is not None:
         _stop_profiler(prof, profile_dir)
     log_prev(force=True)
+    _device_health_check(optimizer, use_cuda)
     if manager is not None:
         if last_metrics and (not save_every or last_metrics["step"] % save_every != 0):
             manager.save(int(last_metrics["step"]), optimizer, data_iter)
         manager.wait_until_finished()
         manager.close()
+    if hb is not None:
+        # "left" is published only once this rank is past its last step and its last checkpoint
+        # barrier: the step loop has no host synchronisation, so a peer may still be one step behind
+        # and must not read "left" before its own last hb.check().
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.barrier()
+        hb.leave()
+        hb.stop()
     if jsonl is not None:
         jsonl.close()
-    if use_cuda:
-        from ..ops import lib
-
-        lib.check_status()
     return optimizer, last_metrics
 
 
@@ -341,6 +360,9 @@ _TEXT_FAMILY = _Family(text_api, make_sft_train_step, make_sft_eval_step)
 def _start_profiler(profile_dir):
     """Kineto trace + allocator history for the profile window; also opens the CUDA
     profiler range so an external profiler attached with capture-range can follow it."""
+    from ..utils import profiling
+
+    profiling.enable_scopes(True)     # NVTX ranges named after the modules, for this window only
     Path(profile_dir).mkdir(parents=True, exist_ok=True)
     acts = [torch.profiler.ProfilerActivity.CPU]
     if torch.cuda.is_available():
@@ -363,6 +385,9 @@ def _stop_profiler(prof, profile_dir):
             torch.cuda.memory._record_memory_history(enabled=None)
         except Exception:
             pass
+    from ..utils import profiling
+
+    profiling.enable_scopes(False)
     prof.__exit__(None, None, None)
     prof.export_chrome_trace(str(Path(profile_dir) / f"trace_rank{mesh_lib.rank()}.json"))
     if is_primary():

@@ -23,6 +23,80 @@ def _rel_err(a, b):
     return float((a - b).abs().max() / (b.abs().max() + 1e-6))
 
 
+def _assert_gemm_close(out, ref, K):
+    """Per-element check with tolerances true to the output type: a bf16 result may differ from the
+    fp32 reference by 2 ulp (2^-7 relative), an fp32 result by 1e-4; the absolute term covers sums
+    that cancel (terms of size ~1, K of them, fp32 accumulation in a different order)."""
+    if out.dtype == bf16:
+        torch.testing.assert_close(out.float(), ref, rtol=2.0 ** -7, atol=2.0 ** -7 * math.sqrt(K) * 0.25)
+    else:
+        torch.testing.assert_close(out, ref, rtol=1e-4, atol=2e-5 * math.sqrt(K))
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (300, 520, 136), (1000, 776, 4160)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("mode", ["bf16", "fp32", "acc"])
+def test_gemm_pair_every_output_mode_per_element(M, N, K, a_mn, b_mn, mode):
+    """CTA-pair kernel on shapes that are not multiples of the 256 x 256 x 64 tile, every output
+    mode, checked element by element against fp32 matmul of the same bf16 inputs."""
+    from omegalax_b200.ops import kernels as Kn, lib
+    torch.manual_seed(10)
+    a = torch.randn(M, K, device=_dev()).to(bf16)
+    b = torch.randn(N, K, device=_dev()).to(bf16)
+    ref = a.float() @ b.float().t()
+    aa = a.t().contiguous() if a_mn else a
+    bb = b.t().contiguous() if b_mn else b
+    if mode == "bf16":
+        out = Kn.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn, pair=True)
+    elif mode == "fp32":
+        out = Kn.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32, pair=True)
+    else:
+        out = torch.full((M, N), 0.5, device=_dev(), dtype=torch.float32)
+        Kn.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=True, pair=True)
+        ref = ref + 0.5
+    _check(lib)
+    _assert_gemm_close(out, ref, K)
+
+
+@pytest.mark.parametrize("splits", [-1, 1, 2, 3, 8])
+def test_gemm_pair_split_reduction(splits):
+    """Weight-gradient layout with a long reduction: the (tile, slice) units of the split reduction
+    add up to the unsplit result; -1 lets the launcher choose (few tiles -> it splits)."""
+    from omegalax_b200.ops import kernels as Kn, lib
+    torch.manual_seed(11)
+    M, N, K = 512, 768, 8192 + 64      # 6 tiles; K not a multiple of the slice length
+    dy = torch.randn(K, M, device=_dev()).to(bf16)
+    x = torch.randn(K, N, device=_dev()).to(bf16)
+    ref = dy.float().t() @ x.float() + 1.0
+    lib.gemm_pair_tune(-1, -1, splits)
+    try:
+        out = torch.ones(M, N, device=_dev(), dtype=torch.float32)
+        Kn.gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True, pair=True)
+        _check(lib)
+    finally:
+        lib.gemm_pair_tune(-1, -1, -1)
+    _assert_gemm_close(out, ref, K)
+
+
+@pytest.mark.parametrize("gm,prefetch", [(2, 0), (16, 0), (8, 4), (4, 12)])
+def test_gemm_pair_raster_and_prefetch_knobs(gm, prefetch):
+    from omegalax_b200.ops import kernels as Kn, lib
+    torch.manual_seed(12)
+    M, N, K = 2304, 1280, 1024 + 64
+    a = torch.randn(M, K, device=_dev()).to(bf16)
+    b = torch.randn(N, K, device=_dev()).to(bf16)
+    ref = a.float() @ b.float().t()
+    lib.gemm_pair_tune(gm, prefetch, -1)
+    try:
+        out = Kn.gemm(a, b, pair=True)
+        out_t = Kn.gemm(a, b.t().contiguous(), b_mn=True, pair=True)
+        _check(lib)
+    finally:
+        lib.gemm_pair_tune(-1, -1, -1)
+    _assert_gemm_close(out, ref, K)
+    _assert_gemm_close(out_t, ref, K)
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 512, 384), (300, 200, 136), (1024, 1024, 1024), (128, 4096, 64), (4096, 1536, 2048)])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
 def test_gemm_layouts(M, N, K, a_mn, b_mn):

@@ -122,6 +122,40 @@ def test_kernels_match_reference_ops(name, monkeypatch):
     assert not bad, bad[:8]
 
 
+def test_left_padded_batch_kernels_match_reference_ops():
+    """Left-padded rows: the kernel path (pads and real tokens as separate causal sequences) and
+    the PyTorch path (k_start mask) agree on every real position; pad positions are not compared."""
+    from omegalax_b200.ops import lib
+    from omegalax_b200.text import api as text_api
+
+    dev = _dev()
+    cfg = _configs()["qwen3-dense"]
+    torch.manual_seed(3)
+    model, cfg = text_api.init_model(cfg, 0, tp_size=1, fsdp_size=1, dp_size=1)
+    model = model.to(dev).to(bf16)
+    T = 200
+    tok = torch.randint(1, cfg.vocab_size, (3, T), device=dev, dtype=torch.int32)
+    pads = [0, 37, 150]
+    for b, n in enumerate(pads):
+        tok[b, :n] = 0
+    outs = []
+    for reference in (False, True):
+        if reference:
+            os.environ["OMEGALAX_B200_REFERENCE_OPS"] = "1"
+        else:
+            os.environ.pop("OMEGALAX_B200_REFERENCE_OPS", None)
+        with torch.no_grad():
+            hidden, _ = text_api.forward(model, tok, 0, cfg)
+        outs.append(hidden.float())
+    lib.check_status()
+    real = tok != 0
+    hk, hr = outs[0][real], outs[1][real]
+    assert torch.isfinite(hk).all()
+    err = (hk - hr).abs()
+    assert float(err.max()) < 0.25 * max(1.0, float(hr.abs().max()) / 8), float(err.max())
+    assert float(err.median()) < 0.02
+
+
 @pytest.mark.parametrize("name", ["qwen3-moe", "qwen3.5-hybrid-moe"])
 def test_training_engine_reduces_loss(name):
     from omegalax_b200.ops import lib
