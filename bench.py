@@ -79,20 +79,38 @@ def vlm_batches(cfg, micro: int, T: int, n: int, seed: int):
 
 
 def reference_arm(args) -> int:
-    """The reference is a JAX/Flax program; jax, flax, optax, orbax, grain and the tokamax fork
-    are not installable offline here, so its arm reports itself unavailable."""
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    why = "reference needs jax/flax/optax/orbax/grain/tokamax, none installed and no index access"
-    if os.path.isdir(os.path.join(ref_dir, "omegalax")):
-        try:
-            sys.path.insert(0, ref_dir)
-            import jax  # noqa: F401
-        except Exception as e:  # pragma: no cover - depends on the box
-            why = f"reference sources installed under baseline/_ref but its runtime is missing: {type(e).__name__}: {e}"[:300]
-        else:  # pragma: no cover
-            why = "jax is importable but the reference run harness is not enabled in this build"
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
+    """Run the unmodified reference (baseline/_ref, a JAX program) through its own trainer API on
+    the same synthetic batches; when it cannot run here, say why in one line and exit 0."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as ref
+
+    rank0 = int(os.environ.get("RANK", "0")) == 0
+    model_id, def_T, def_seqs, par = MODELS[args.model]
+    why = ref.availability()
+    if why is None and args.model == "qwen3-vl-2b":
+        why = "the reference harness drives the text trainer only"
+    if why is not None:
+        if rank0:
+            print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    N = max(int(os.environ.get("WORLD_SIZE", "1")), 1)
+    seqs = args.seqs_per_gpu or def_seqs
+    T = args.seq_len or def_T
+    micro = min(args.micro_seqs or (4 if N <= 2 else seqs), seqs)
+    try:
+        res = ref.run(model_id, N, seqs, T, micro, args.steps, args.warmup)
+    except Exception as e:  # pragma: no cover - depends on the box
+        if rank0:
+            print(json.dumps({"impl": "reference", "unavailable": f"reference run failed: {type(e).__name__}: {e}"[:300]}))
+        return 0
+    if rank0:
+        out = {"metric": METRIC, "value": res["value"], "unit": "tokens/s", "n_gpus": N, "steps": args.steps,
+               "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+               "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+               "config": {"model": model_id, "global_batch": seqs * N, "seq_len": T, "parallelism": f"fsdp{N}",
+                          "micro_batch_per_gpu": micro, "grad_accum": max(seqs // micro, 1), "timer": res["timer"]},
+               "e2e": res["e2e"], "gpu_launches": 0, "final_loss": res["final_loss"]}
+        print(json.dumps(out), flush=True)
     return 0
 
 
@@ -149,7 +167,10 @@ def main() -> int:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch_baseline"],
+                    help="ours: this repository's kernels and peer-memory collectives; reference: the unmodified "
+                         "reference package (baseline/_ref); torch_baseline: the same models and engine with every op "
+                         "a PyTorch library call (cuBLAS, flash SDPA, eager elementwise) and NCCL collectives")
     ap.add_argument("--model", default="qwen3-8b", choices=sorted(MODELS))
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncate the layer stack")
     ap.add_argument("--experts", type=int, default=None, help="debug only: shrink the expert count")
@@ -162,6 +183,8 @@ def main() -> int:
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.impl == "torch_baseline":   # read by ops.functional / parallel.engine at call time
+        os.environ["OMEGALAX_B200_OPS"] = "library"
 
     import dataclasses
 
@@ -249,8 +272,10 @@ def main() -> int:
             loss, _ = step_fn(opt, to_dev(pool[(i * accum + a) % len(pool)]))
         return float(loss.item())  # device -> host read of the step's loss
 
+    loss_step0 = None
     for i in range(args.warmup):
-        one_step_e2e(i)
+        l = one_step_e2e(i)
+        loss_step0 = l if loss_step0 is None else loss_step0
     barrier()
     lib.check_status()
 
@@ -312,7 +337,7 @@ def main() -> int:
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": N, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": args.impl,
             "config": {"model": model_id if args.layers is None and args.experts is None
                        else f"{model_id}[layers={args.layers or 'all'}, experts={args.experts or 'all'}]",
                        "global_batch": args.seqs_per_gpu * N, "seq_len": T,
@@ -325,7 +350,7 @@ def main() -> int:
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": launches, "final_loss": last_loss,
+            "gpu_launches": launches, "loss_step0": loss_step0, "final_loss": last_loss,
             "peak_mem_gb": torch.cuda.max_memory_allocated(device) / 1e9,
         }
         print(json.dumps(out), flush=True)

@@ -115,7 +115,7 @@ class Attention(nn.Module):
                                      self.H, self.G, self.Kd, eps=self.eps)
         B, T = ctx.B, ctx.T
         if cache is None:
-            if Fn.use_kernels(q):
+            if Fn.use_kernels(q) or (Fn.library_mode() and q.is_cuda):
                 o = Fn.flash_attention(q, k, v, ctx.cu_seqlens, T, scale=self.scale, causal=True, tag="attn")
             else:
                 ks = None if ctx.k_start is None else ctx.k_start[:, None].expand(B, T)

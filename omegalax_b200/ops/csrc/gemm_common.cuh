@@ -36,12 +36,11 @@ struct GemmArgs {
   long long ag_chunk_bytes;
   uint32_t* ag_flags;              // [world] counters, only ever incremented
   uint32_t ag_target;              // value a chunk's counter has when the chunk is complete
-  // CTA-pair kernel only.  raster_gm: tile rows that share one sweep over the tile columns.
-  // l2_prefetch: distance (in k-blocks) of the TMA prefetch into L2 that runs ahead of the loads
-  // (0 = none).  k_splits > 1 (reducing output modes only): the reduction is cut into k_splits
+  // CTA-pair kernels only.  raster_gm: tile rows that share one sweep over the tile columns.
+  // k_splits > 1 (reducing output modes only): the reduction is cut into k_splits
   // slices of k_per_split elements; every (tile, slice) is one unit of work and its partial result
   // is added to C with vector reductions.
-  int raster_gm, l2_prefetch, k_splits, k_per_split;
+  int raster_gm, k_splits, k_per_split;
   int* status;
 };
 

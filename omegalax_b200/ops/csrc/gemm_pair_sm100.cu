@@ -130,7 +130,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       uint32_t phase = 0;
       uint32_t ag_seen = 0;
       bool ok = true;
-      const int pf_dist = p.l2_prefetch * BK;
       for (int u = pair0; u < total_units && ok; u += pair_step) {
         const int ks = u / p.total_tiles;        // slice-major: a wave of units shares operand panels
         const int t = u - ks * p.total_tiles;
@@ -155,21 +154,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           }
         }
         for (int k0 = k_begin; k0 < k_end; k0 += BK) {
-          if (pf_dist > 0 && !ag_local) {   // warm L2 for the k-block pf_dist ahead of the one loaded now
-            const int kp = k0 + pf_dist;
-            if (kp < k_end) {
-              if (!A_MN) tma_prefetch_l2_2d(&tmA, kp, ti.row0);
-              else {
-#pragma unroll
-                for (int j = 0; j < BM / 64; ++j) tma_prefetch_l2_2d(&tmA, ti.row0 + j * 64, kp);
-              }
-              if (!B_MN) tma_prefetch_l2_2d(&tmB, kp, ti.b_row0);
-              else {
-#pragma unroll
-                for (int j = 0; j < kPairBNL / 64; ++j) tma_prefetch_l2_2d(&tmB, ti.b_row0 + j * 64, kp);
-              }
-            }
-          }
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_EMPTY);
           if (!ok) break;
           uint8_t* sa = smem + stage * L::kStageBytes;
@@ -301,7 +285,22 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 }
 
 // Process-wide tuning knobs (ob_gemm_pair_tune): -1 = decide per launch.
-static int g_tune_gm = -1, g_tune_prefetch = -1, g_tune_splitk = -1;
+static int g_tune_gm = -1, g_tune_wide = -1, g_tune_splitk = -1;
+
+// gemm_pair_wide_sm100.cu
+int launch_pair_wide(const void* A, const void* B, const GemmArgs& g, long long lda, long long ldb, int a_mn, int b_mn,
+                     int gm, int forced_splits, cudaStream_t stream);
+
+// The 512 x 256 tile kernel serves plain GEMMs without a fused residual whose tile count fills
+// the SM pairs at least twice over (or whose reduction can be split to that effect).
+static bool want_wide(const GemmArgs& g) {
+  if (g_tune_wide == 0) return false;
+  if (g.residual != nullptr || g.ag_side != 0 || g.mode != 0) return false;
+  if (g_tune_wide == 1) return true;
+  const long long tiles = (long long)((g.M + 511) / 512) * ((g.N + 255) / 256);
+  if (g.out_mode >= 2) return tiles * (g.K / 1024 > 0 ? g.K / 1024 : 1) >= 148;
+  return tiles >= 296;
+}
 
 // Tile rows per raster group: as many as keep the group's A panels (GM x 256 rows x K) within
 // about 24 MB of L2 while the B panels stream past, between 2 and 16.
@@ -384,7 +383,6 @@ static int launch_pair(const void* A, const void* B, const GemmArgs& args_in, lo
     pairs -= copy / 2;
   }
   args.raster_gm = pick_gm(args.K);
-  args.l2_prefetch = g_tune_prefetch >= 0 ? g_tune_prefetch : 0;
   pick_splits(args, pairs);
   if (pairs > args.total_tiles * args.k_splits) pairs = args.total_tiles * args.k_splits;
   if (pairs <= 0) return args.ag_side ? 6006 : 0;
@@ -400,10 +398,10 @@ using namespace ob;
 extern "C" {
 
 // Tuning knobs of the CTA-pair kernel for the whole process; -1 restores the per-launch choice.
-// gm: tile rows per raster group; prefetch: L2 prefetch distance in k-blocks (0 off);
-// splitk: 0 never split the reduction, n > 0 always n slices (reducing output modes only).
-void ob_gemm_pair_tune(int gm, int prefetch, int splitk) {
-  g_tune_gm = gm; g_tune_prefetch = prefetch; g_tune_splitk = splitk;
+// gm: tile rows per raster group; wide: 0 never / 1 always use the 512 x 256 tile kernel where it
+// applies; splitk: 0 never split the reduction, n > 0 always n slices (reducing output modes only).
+void ob_gemm_pair_tune(int gm, int wide, int splitk) {
+  g_tune_gm = gm; g_tune_wide = wide; g_tune_splitk = splitk;
 }
 
 // Same contract as ob_gemm_bf16 (plain mode), computed by CTA pairs on 256 x 256 tiles.
@@ -422,6 +420,7 @@ int ob_gemm_bf16_pair(const void* A, const void* B, void* C, const void* residua
   g.C = C; g.ldc = ldc; g.out_mode = out_mode;
   g.residual = (const bf16*)residual; g.ldr = ldr;
   g.status = status;
+  if (want_wide(g)) return launch_pair_wide(A, B, g, lda, ldb, a_mn, b_mn, pick_gm(2 * K), g_tune_splitk, stream);
   const long long a_rows = a_mn ? K : M, a_cols = a_mn ? M : K;
   const long long b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;
   if (!a_mn && !b_mn) return launch_pair<false, false>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
@@ -446,6 +445,7 @@ int ob_gemm_bf16_pair_peer_reduce(const void* A, const void* B, void* const* pee
   for (int i = 0; i < world; ++i) g.peer_ptr[i] = (float*)peer_ptrs[i];
   g.rows_per_peer = rows_per_peer;
   g.status = status;
+  if (want_wide(g)) return launch_pair_wide(A, B, g, lda, ldb, a_mn, b_mn, pick_gm(2 * K), g_tune_splitk, stream);
   const long long a_rows = a_mn ? K : M, a_cols = a_mn ? M : K;
   const long long b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;
   if (!a_mn && !b_mn) return launch_pair<false, false>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);

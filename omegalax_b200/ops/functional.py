@@ -84,8 +84,38 @@ def _stash_store(key, value):
         st.items[key] = value
 
 
+def library_mode() -> bool:
+    """``OMEGALAX_B200_OPS=library``: the stand-in baseline.  No kernel of this repository runs;
+    every op is the PyTorch library call a plain PyTorch program would make (cuBLAS through
+    ``F.linear``, flash SDPA, eager elementwise ops, a row-chunked checkpointed cross-entropy) and
+    the engine moves parameters and gradients with NCCL collectives."""
+    return os.environ.get("OMEGALAX_B200_OPS") == "library"
+
+
 def use_kernels(t: torch.Tensor) -> bool:
-    return t.is_cuda and t.dtype == bf16 and os.environ.get("OMEGALAX_B200_REFERENCE_OPS") != "1"
+    return (t.is_cuda and t.dtype == bf16 and os.environ.get("OMEGALAX_B200_REFERENCE_OPS") != "1"
+            and not library_mode())
+
+
+def _sdpa_packed(q, k, v, cu_seqlens, max_seqlen: int, scale: float, causal: bool):
+    """Library attention on packed rows: one flash SDPA call when every sequence has max_seqlen rows
+    (the training batches), else one call per sequence."""
+    N, H, Kd = q.shape
+    G = k.shape[1]
+    B = cu_seqlens.numel() - 1
+    sdpa = torch.nn.functional.scaled_dot_product_attention
+    if N == B * max_seqlen:
+        o = sdpa(q.view(B, max_seqlen, H, Kd).transpose(1, 2), k.reshape(B, max_seqlen, G, Kd).transpose(1, 2),
+                 v.reshape(B, max_seqlen, G, Kd).transpose(1, 2), is_causal=bool(causal), scale=scale, enable_gqa=True)
+        return o.transpose(1, 2).reshape(N, H, Kd)
+    outs = []
+    cu = cu_seqlens.tolist()
+    for a, b in zip(cu[:-1], cu[1:]):
+        if b > a:
+            o = sdpa(q[a:b].transpose(0, 1)[None], k[a:b].transpose(0, 1)[None], v[a:b].transpose(0, 1)[None],
+                     is_causal=bool(causal), scale=scale, enable_gqa=True)
+            outs.append(o[0].transpose(0, 1))
+    return torch.cat(outs, dim=0) if outs else q.new_zeros(q.shape)
 
 
 def _acc_main_grad(w, fn_into, fn_new):
@@ -502,6 +532,8 @@ def flash_attention(q, k, v, cu_seqlens, max_seqlen: int, *, scale: float, causa
         o, lse = _FlashAttnFn.apply(q, k, v, cu_seqlens, int(max_seqlen), float(scale), bool(causal), pre)
         _stash_store(key, (o, lse))
         return o
+    if library_mode() and q.is_cuda:
+        return _sdpa_packed(q, k, v, cu_seqlens, int(max_seqlen), float(scale), bool(causal))
     return R.attention_varlen(q, k, v, cu_seqlens, causal=causal, scale=scale)
 
 
@@ -661,9 +693,16 @@ def linear_cross_entropy(h, w, targets, mask, scale, chunk: int = 4096):
     if use_kernels(h) and w.dtype == bf16 and w.shape[0] % 8 == 0:
         return _LinearCEFn.apply(h.contiguous(), w, targets, mask, scale, chunk)
     total = h.new_zeros((), dtype=torch.float32)
+    ckpt = library_mode() and torch.is_grad_enabled() and (h.requires_grad or w.requires_grad)
     for r0 in range(0, h.shape[0], chunk):
         r1 = min(h.shape[0], r0 + chunk)
-        total = total + R.cross_entropy_sum(h[r0:r1], w, targets[r0:r1], mask[r0:r1])
+        if ckpt:   # the usual memory-saving recipe: the chunk's logits are recomputed in the backward
+            from torch.utils.checkpoint import checkpoint
+
+            total = total + checkpoint(R.cross_entropy_sum, h[r0:r1], w, targets[r0:r1], mask[r0:r1],
+                                       use_reentrant=False)
+        else:
+            total = total + R.cross_entropy_sum(h[r0:r1], w, targets[r0:r1], mask[r0:r1])
     return total * scale.squeeze(0)
 
 

@@ -106,7 +106,8 @@ def gemm(a, b, *, a_mn: bool = False, b_mn: bool = False, out=None, out_dtype=bf
     return out
 
 
-def gemm_peer_reduce(a, b, peer_ptrs, rows_per_peer: int, ldc: int, *, a_mn=False, b_mn=False, bf16_out=False):
+def gemm_peer_reduce(a, b, peer_ptrs, rows_per_peer: int, ldc: int, *, a_mn=False, b_mn=False, bf16_out=False,
+                     pair: bool | None = None):
     """GEMM whose result rows are added into buffers owned by other GPUs (``peer_ptrs[r]`` holds
     rows [r*rows_per_peer, (r+1)*rows_per_peer)): fp32 buffers by default (gradient shards), bf16
     buffers with ``bf16_out`` (activations: half the NVLink bytes, bf16 accumulation)."""
@@ -118,7 +119,9 @@ def gemm_peer_reduce(a, b, peer_ptrs, rows_per_peer: int, ldc: int, *, a_mn=Fals
     N = b.shape[1] if b_mn else b.shape[0]
     arr = (ctypes.c_void_p * len(peer_ptrs))(*peer_ptrs)
     st = lib.status_tensor(a.device)
-    name = "ob_gemm_bf16_pair_peer_reduce" if _use_pair(M, N, K, wgrad=a_mn and b_mn) else "ob_gemm_bf16_peer_reduce"
+    if pair is None:
+        pair = _use_pair(M, N, K, wgrad=a_mn and b_mn)
+    name = "ob_gemm_bf16_pair_peer_reduce" if pair else "ob_gemm_bf16_peer_reduce"
     _call(name, a.data_ptr(), b.data_ptr(), ctypes.cast(arr, ctypes.c_void_p),
           len(peer_ptrs), rows_per_peer, M, N, K, a.stride(0), b.stride(0), ldc, int(a_mn),
           int(b_mn), int(bf16_out), st.data_ptr(), lib.stream_ptr())

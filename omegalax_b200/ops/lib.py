@@ -111,16 +111,17 @@ def load():
     if hasattr(lib, "ob_gemm_pair_tune"):
         lib.ob_gemm_pair_tune.argtypes = [c_int, c_int, c_int]
         lib.ob_gemm_pair_tune.restype = None
-        tune = os.environ.get("OMEGALAX_B200_GEMM_TUNE")     # "gm,prefetch,splitk" (-1 = automatic)
+        tune = os.environ.get("OMEGALAX_B200_GEMM_TUNE")     # "gm,wide,splitk" (-1 = automatic)
         if tune:
             lib.ob_gemm_pair_tune(*[int(v) for v in tune.split(",")])
     return lib
 
 
-def gemm_pair_tune(gm: int = -1, prefetch: int = -1, splitk: int = -1) -> None:
-    """Process-wide knobs of the CTA-pair GEMM (raster group height, L2 prefetch distance in
-    k-blocks, forced number of reduction slices); -1 leaves the per-launch choice in place."""
-    load().ob_gemm_pair_tune(int(gm), int(prefetch), int(splitk))
+def gemm_pair_tune(gm: int = -1, wide: int = -1, splitk: int = -1) -> None:
+    """Process-wide knobs of the CTA-pair GEMMs: raster group height, use of the 512 x 256 tile
+    kernel (0 never, 1 wherever it applies), forced number of reduction slices; -1 leaves the
+    per-launch choice in place."""
+    load().ob_gemm_pair_tune(int(gm), int(wide), int(splitk))
 
 
 def register(name: str, sig) -> None:

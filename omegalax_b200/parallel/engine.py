@@ -136,10 +136,10 @@ class TrainEngine:
             for mod in model.modules():
                 if hasattr(mod, "aux_group"):
                     mod.aux_group = aux_group
-        self.use_cuda_kernels = self.device.type == "cuda"
+        self.use_cuda_kernels = self.device.type == "cuda" and not Fn.library_mode()
         self.compute_dtype = bf16 if self.device.type == "cuda" else torch.float32
         if comm == "auto":
-            comm = "p2p" if (self.device.type == "cuda" and self.W > 1) else "nccl"
+            comm = "p2p" if (self.use_cuda_kernels and self.W > 1) else "nccl"
         self.comm_kind = comm if self.W > 1 else "none"
         self.expert_parallel = bool(expert_parallel) and self.comm_kind == "p2p"
         # The weight of a layer's first projection is gathered inside that projection's GEMM launch

@@ -412,3 +412,42 @@ def tp_decode(rank, world, port, out_path, moe=False):
     dist.barrier()
     tp_lib.set_current(None)
     dist.destroy_process_group()
+
+
+def checkpoint_write_failure(rank, world, port, ckpt_dir, out_path):
+    """Two saves with the background writer: the first succeeds, during the second rank 1's file
+    write raises.  Every rank must learn of it, the failed step must not become a checkpoint, and
+    the first checkpoint must survive (max_to_keep=1 would otherwise prune it)."""
+    _init(rank, world, port)
+    from omegalax_b200.parallel import mesh as mesh_lib
+    from omegalax_b200.trainers import checkpoint_utils
+    from omegalax_b200.trainers import text as trainer
+
+    mesh_lib.set_default_mesh(None)
+    mesh_lib.ensure_mesh(tp_size=1, fsdp_size=world, dp_size=1)
+    tcfg = trainer.TrainConfig(seed=0, batch_size=4, seq_len=16, num_steps=10, learning_rate=1e-2)
+    model, cfg = trainer.init_model("qwen3-smoke-tiny", 0, tp_size=1, fsdp_size=world, dp_size=1, meta=True)
+    opt = trainer.build_optimizer(model, tcfg, device=torch.device("cpu"))
+    mgr = checkpoint_utils.CheckpointManager(ckpt_dir, max_to_keep=1, async_write=True)
+    mgr.save(1, opt)
+    mgr.wait_until_finished()
+    ok_first = mgr.latest_step() == 1
+    import safetensors.torch as st
+
+    orig = st.save_file
+    if rank == 1:
+        def boom(*a, **k):
+            raise OSError("disk full (injected)")
+        st.save_file = boom
+    mgr.save(2, opt)
+    raised = False
+    try:
+        mgr.wait_until_finished()
+    except RuntimeError:
+        raised = True
+    st.save_file = orig
+    dist.barrier()
+    res = {"ok_first": ok_first, "raised": raised, "steps": mgr.all_steps()}
+    torch.save(res, f"{out_path}.{rank}")
+    dist.barrier()
+    dist.destroy_process_group()

@@ -65,6 +65,17 @@ def test_checkpoint_resharding_4_to_2(tmp_path):
         torch.testing.assert_close(b["params"][k], c["params"][k], rtol=2e-3, atol=2e-4)
 
 
+def test_checkpoint_write_failure_on_one_rank_is_seen_by_all(tmp_path):
+    """Asynchronous multi-rank save: a shard that fails to write on rank 1 makes every rank raise,
+    leaves no directory for that step and keeps the previous checkpoint."""
+    out = str(tmp_path / "res.pt")
+    mp.spawn(W.checkpoint_write_failure, args=(2, _port(), str(tmp_path / "ckpt"), out), nprocs=2, join=True)
+    for r in range(2):
+        res = torch.load(f"{out}.{r}")
+        assert res["ok_first"] and res["raised"], res
+        assert res["steps"] == [1], res
+
+
 def test_tensor_parallel_matches_single_rank(tmp_path):
     """tp=2 (sequence-parallel activations, column/row-parallel projections) and tp=2 x fsdp=2
     reproduce the tp=1 loss curve from the same weights and batch."""

@@ -33,14 +33,17 @@ def _assert_gemm_close(out, ref, K):
         torch.testing.assert_close(out, ref, rtol=1e-4, atol=2e-5 * math.sqrt(K))
 
 
-@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (300, 520, 136), (1000, 776, 4160)])
+@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (304, 520, 136), (1000, 776, 4160)])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
 @pytest.mark.parametrize("mode", ["bf16", "fp32", "acc"])
-def test_gemm_pair_every_output_mode_per_element(M, N, K, a_mn, b_mn, mode):
-    """CTA-pair kernel on shapes that are not multiples of the 256 x 256 x 64 tile, every output
-    mode, checked element by element against fp32 matmul of the same bf16 inputs."""
+@pytest.mark.parametrize("wide", [0, 1])
+def test_gemm_pair_every_output_mode_per_element(M, N, K, a_mn, b_mn, mode, wide):
+    """CTA-pair kernels (256 x 256 tile, and the 512 x 256 tile one with its TMA-store epilogue) on
+    shapes that are not multiples of the tile, every output mode, checked element by element
+    against fp32 matmul of the same bf16 inputs."""
     from omegalax_b200.ops import kernels as Kn, lib
     torch.manual_seed(10)
+    lib.gemm_pair_tune(-1, wide, -1)
     a = torch.randn(M, K, device=_dev()).to(bf16)
     b = torch.randn(N, K, device=_dev()).to(bf16)
     ref = a.float() @ b.float().t()
@@ -54,12 +57,14 @@ def test_gemm_pair_every_output_mode_per_element(M, N, K, a_mn, b_mn, mode):
         out = torch.full((M, N), 0.5, device=_dev(), dtype=torch.float32)
         Kn.gemm(aa, bb, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=True, pair=True)
         ref = ref + 0.5
+    lib.gemm_pair_tune(-1, -1, -1)
     _check(lib)
     _assert_gemm_close(out, ref, K)
 
 
+@pytest.mark.parametrize("wide", [0, 1])
 @pytest.mark.parametrize("splits", [-1, 1, 2, 3, 8])
-def test_gemm_pair_split_reduction(splits):
+def test_gemm_pair_split_reduction(splits, wide):
     """Weight-gradient layout with a long reduction: the (tile, slice) units of the split reduction
     add up to the unsplit result; -1 lets the launcher choose (few tiles -> it splits)."""
     from omegalax_b200.ops import kernels as Kn, lib
@@ -68,7 +73,7 @@ def test_gemm_pair_split_reduction(splits):
     dy = torch.randn(K, M, device=_dev()).to(bf16)
     x = torch.randn(K, N, device=_dev()).to(bf16)
     ref = dy.float().t() @ x.float() + 1.0
-    lib.gemm_pair_tune(-1, -1, splits)
+    lib.gemm_pair_tune(-1, wide, splits)
     try:
         out = torch.ones(M, N, device=_dev(), dtype=torch.float32)
         Kn.gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True, pair=True)
@@ -78,15 +83,45 @@ def test_gemm_pair_split_reduction(splits):
     _assert_gemm_close(out, ref, K)
 
 
-@pytest.mark.parametrize("gm,prefetch", [(2, 0), (16, 0), (8, 4), (4, 12)])
-def test_gemm_pair_raster_and_prefetch_knobs(gm, prefetch):
+@pytest.mark.parametrize("wide", [0, 1])
+def test_gemm_pair_unaligned_output_pitch_and_local_peer_reduce(wide):
+    """Outputs the TMA unit cannot address (row pitch not a multiple of 16 bytes) take the
+    register -> global path; the peer-reduction epilogue is exercised with both "peers" being
+    buffers of this GPU (row blocks of the result land in two separate allocations)."""
+    from omegalax_b200.ops import kernels as Kn, lib
+    torch.manual_seed(13)
+    M, N, K = 1024, 520, 2048 + 64
+    a = torch.randn(M, K, device=_dev()).to(bf16)
+    b = torch.randn(N, K, device=_dev()).to(bf16)
+    ref = a.float() @ b.float().t()
+    big = torch.zeros(M, N + 4, device=_dev(), dtype=bf16)
+    big32 = torch.full((M, N + 1), 2.0, device=_dev(), dtype=torch.float32)
+    lib.gemm_pair_tune(-1, wide, -1)
+    try:
+        Kn.gemm(a, b, out=big[:, :N], pair=True)
+        Kn.gemm(a, b, out=big32[:, :N], accumulate=True, pair=True)
+        halves = [torch.zeros(M // 2, N, device=_dev(), dtype=torch.float32) for _ in range(2)]
+        Kn.gemm_peer_reduce(a, b, [h.data_ptr() for h in halves], M // 2, N, pair=True)
+        Kn.gemm_peer_reduce(a, b, [h.data_ptr() for h in halves], M // 2, N, pair=True)
+        _check(lib)
+    finally:
+        lib.gemm_pair_tune(-1, -1, -1)
+    _assert_gemm_close(big[:, :N], ref, K)
+    assert float(big[:, N:].abs().max()) == 0.0          # nothing written beyond the view
+    _assert_gemm_close(big32[:, :N].contiguous(), ref + 2.0, K)
+    assert float((big32[:, N:] - 2.0).abs().max()) == 0.0
+    _assert_gemm_close(torch.cat(halves, 0), 2 * ref, K)
+
+
+@pytest.mark.parametrize("gm,wide", [(2, 0), (16, 0), (3, 1), (16, 1)])
+def test_gemm_pair_raster_knob(gm, wide):
     from omegalax_b200.ops import kernels as Kn, lib
     torch.manual_seed(12)
     M, N, K = 2304, 1280, 1024 + 64
     a = torch.randn(M, K, device=_dev()).to(bf16)
     b = torch.randn(N, K, device=_dev()).to(bf16)
     ref = a.float() @ b.float().t()
-    lib.gemm_pair_tune(gm, prefetch, -1)
+    lib.gemm_pair_tune(gm, wide, -1)
     try:
         out = Kn.gemm(a, b, pair=True)
         out_t = Kn.gemm(a, b.t().contiguous(), b_mn=True, pair=True)
