@@ -68,6 +68,8 @@ def left_pad_cu_seqlens(k_start, B: int, T: int) -> torch.Tensor:
     causal sequences, its pads and its real tokens, so a real query never sees a pad key (what the
     ``k_start`` mask of the PyTorch path does) while the kernels keep plain causal sequences.  Pad
     positions attend among themselves; nothing downstream reads them.  Built on the device."""
+    if Fn.library_mode():   # the library baseline runs plain causal rows, as the reference does
+        return torch.arange(B + 1, device=k_start.device, dtype=torch.int32) * T
     base = torch.arange(B, device=k_start.device, dtype=torch.int64) * T
     cu = torch.stack([base, base + k_start.to(torch.int64).clamp(0, T)], dim=1).reshape(-1)
     end = torch.full((1,), B * T, device=k_start.device, dtype=torch.int64)

@@ -19,6 +19,10 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 BUILD = HERE / "build"
 LIB = HERE / "libomegalax_b200.so"
+DEBUG_LIB = HERE / "libomegalax_b200_debug.so"
+# debug build: GEMM epilogues check every store against the output's extent and record status 8;
+# bounded waits give up after ~0.2 s so a protocol error surfaces quickly
+DEBUG_FLAGS = ["-DOB_DEBUG_BOUNDS", "-DOB_WAIT_CYCLES=400000000ll"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -48,20 +52,24 @@ def sources():
     return sorted(CSRC.glob("*.cu"))
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile (if stale) and return the path of the shared library."""
+def build(force: bool = False, verbose: bool = False, debug: bool = False) -> Path:
+    """Compile (if stale) and return the path of the shared library (``debug``: the variant with
+    in-kernel store checks and short wait budgets, ``libomegalax_b200_debug.so``)."""
     srcs = sources()
     headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
-    stamp = BUILD / "stamp.txt"
-    want = _digest(srcs + headers)
-    if not force and LIB.exists() and stamp.exists() and stamp.read_text() == want:
-        return LIB
-    BUILD.mkdir(exist_ok=True)
+    out_lib = DEBUG_LIB if debug else LIB
+    build_dir = BUILD / "debug" if debug else BUILD
+    extra = DEBUG_FLAGS if debug else []
+    stamp = build_dir / "stamp.txt"
+    want = _digest(srcs + headers) + ("-debug" if debug else "")
+    if not force and out_lib.exists() and stamp.exists() and stamp.read_text() == want:
+        return out_lib
+    build_dir.mkdir(parents=True, exist_ok=True)
     nvcc = _nvcc()
 
     def compile_one(src: Path) -> Path:
-        obj = BUILD / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        obj = build_dir / (src.stem + ".o")
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         res = subprocess.run(cmd, capture_output=True, text=True)
@@ -73,13 +81,13 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(compile_one, srcs))
-    cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs)]
+    cmd = [nvcc, "-shared", "-o", str(out_lib), *map(str, objs)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
     stamp.write_text(want)
-    return LIB
+    return out_lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, debug="--debug" in sys.argv))

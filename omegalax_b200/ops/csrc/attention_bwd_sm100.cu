@@ -13,9 +13,12 @@
 //   B1  dV  += P^T  dO         (A from TMEM, B = dO as MN-major tile)
 //   B2  dK  += dS^T Q          (A from TMEM, B = Q  as MN-major tile)
 //   B3  dQ^T = K^T dS          (A = K as MN-major tile, B = dS^T tile in shared memory)
-//   D   threads add dQ^T into the fp32 dQ buffer
+//   D   dQ^T goes through a transposing shared-memory tile into the fp32 dQ buffer (TMA reduce-add)
 // S^T/dP^T are double buffered so A(i+1) runs while the threads are in E(i); dQ^T(i)
 // reuses the S^T buffer of step i.  Q/dO tiles come through a 3-stage TMA ring.
+// E runs on eight warps (two per TMEM lane quadrant, 32 query columns each), D on four warps of
+// its own (one per quadrant, 64 columns), so draining dQ^T of step i-1 overlaps E of step i and
+// the S^T buffer is handed back to the tensor core without waiting for the softmax warps.
 //
 // Scratch (allocated by the caller): delta [H, rows] fp32 = rowsum(dO * O) from the
 // preprocess kernel, and dq_acc [rows, H, 128] fp32, zeroed before launch and converted to
@@ -25,8 +28,7 @@
 
 namespace ob {
 
-constexpr int kBwdThreads = 320;     // producer warp, MMA warp, 8 compute warps
-constexpr int kBwdCompute = 256;
+constexpr int kBwdThreads = 448;     // producer warp, MMA warp, 8 softmax/dS warps, 4 dQ warps
 constexpr int kHD = 128;
 constexpr int kQT = 64;        // queries per step
 constexpr int kQStages = 3;
@@ -102,11 +104,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(&sp_full[i], 1);
       mbar_init(&ds_ready[i], 8);
       mbar_init(&dq_full[i], 1);
-      mbar_init(&dq_read[i], 8);
+      mbar_init(&dq_read[i], 4);
     }
     mbar_init(dkv_full, 1);
     mbar_init(dqs_free, 1);
-    mbar_init(dqs_full, 8);
+    mbar_init(dqs_full, 4);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -244,52 +246,66 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       if (ok) umma_commit(dkv_full);
     }
-  } else {
-    // ------------------------------------------------------------ compute warps (2..9)
-    // Two warps share each TMEM lane quadrant and split the 64 query columns of a step.
+  } else if (warp >= 10) {
+    // ------------------------------------------------------------ dQ warps (10..13)
+    // D(it): move dQ^T of step `it` from TMEM through a transposing shared-memory tile into the
+    // fp32 dQ buffer with one TMA reduce-add (no per-element atomics).  One warp per TMEM lane
+    // quadrant; thread r holds head-dim index r of all 64 queries of the step.
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;          // which 32 query columns
-    const int r = quad * 32 + lane;            // key row (E) / head-dim index (D)
+    const int r = quad * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-    const int kpos = k0 + r;
-    const bool key_ok = kpos < seqlen;
-    bool ok = true;
-    const bool issuer = (threadIdx.x == 64);
+    const bool issuer = (warp == 10 && lane == 0);
     float* dq_s = reinterpret_cast<float*>(smem + L::kDQOff);
-    // D(it): move dQ^T of step `it` from TMEM through a transposing shared-memory tile into
-    // the fp32 dQ buffer with one TMA reduce-add (no per-element atomics).
-    auto do_D = [&](int it) -> bool {
+    bool ok = true;
+    for (int it = 0; it < n && ok; ++it) {
       const int bb = it & 1;
-      if (!mbar_wait(&dq_full[bb], (it >> 1) & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL))
-        return false;
+      ok = mbar_wait(&dq_full[bb], (it >> 1) & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL);
       __syncwarp();
+      if (!ok) break;
       tc_fence_after();
-      uint32_t v0[32];
-      tmem_ld32(T_S(bb) + lane_addr + half * 32, v0);
+      uint32_t v0[32], v1[32];
+      tmem_ld32(T_S(bb) + lane_addr, v0);
+      tmem_ld32(T_S(bb) + lane_addr + 32, v1);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&dq_read[bb]);
+      if (lane == 0) mbar_arrive(&dq_read[bb]);   // the tensor core may overwrite this S^T buffer
       // the staging tile is free once the previous reduce-add has read it
       if (issuer) {
         tma_store_wait_read<0>();
         mbar_arrive(dqs_free);
       }
-      if (!mbar_wait(dqs_free, it & 1, abort_flag, p.status, OB_ERR_WAIT_MISC)) return false;
+      ok = mbar_wait(dqs_free, it & 1, abort_flag, p.status, OB_ERR_WAIT_MISC);
+      if (!ok) break;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) dq_s[(half * 32 + i) * kHD + r] = __uint_as_float(v0[i]);
+      for (int i = 0; i < 32; ++i) {
+        dq_s[i * kHD + r] = __uint_as_float(v0[i]);
+        dq_s[(32 + i) * kHD + r] = __uint_as_float(v1[i]);
+      }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(dqs_full);
       if (issuer) {
-        if (!mbar_wait(dqs_full, it & 1, abort_flag, p.status, OB_ERR_WAIT_MISC)) return false;
-        const int h = g * R + it / nqt;
-        const int q0 = (i_first + it % nqt) * kQT;
-        tma_reduce_add_2d(&tmDQ, dq_s, h * kHD, seq_start + q0);
-        tma_store_commit();
+        ok = mbar_wait(dqs_full, it & 1, abort_flag, p.status, OB_ERR_WAIT_MISC);
+        if (ok) {
+          const int h = g * R + it / nqt;
+          const int q0 = (i_first + it % nqt) * kQT;
+          tma_reduce_add_2d(&tmDQ, dq_s, h * kHD, seq_start + q0);
+          tma_store_commit();
+        }
       }
-      return true;
-    };
+    }
+    if (issuer) tma_store_wait_all<0>();
+  } else {
+    // ------------------------------------------------------------ softmax / dS warps (2..9)
+    // Two warps share each TMEM lane quadrant and split the 64 query columns of a step.
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;          // which 32 query columns
+    const int r = quad * 32 + lane;            // key row
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    const int kpos = k0 + r;
+    const bool key_ok = kpos < seqlen;
+    bool ok = true;
     for (int it = 0; it < n && ok; ++it) {
       const int bb = it & 1;
       const int s = it % kQStages;
@@ -346,10 +362,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_ready[bb]);
-      if (it >= 1) ok = do_D(it - 1);
     }
-    if (ok && n >= 1) ok = do_D(n - 1);
-    if (issuer) tma_store_wait_all<0>();
     if (ok) ok = mbar_wait(dkv_full, 0, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL);
     if (ok) {
       tc_fence_after();
@@ -461,12 +474,15 @@ int ob_attn_bwd(const void* q, const void* k, const void* v, const void* out, co
   if (e) return 3000 + e;
   e = make_tmap_3d(&tmV, v, HD, G, total_rows, (uint64_t)HD * 2, (uint64_t)v_row_stride * 2, 64, 1, 128);
   if (e) return 3500 + e;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {};   // the attribute is per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!attr_set[dev]) {
     cudaError_t ce = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           AttnBwdSmem::kTotal);
     if (ce != cudaSuccess) return 4000 + (int)ce;
-    attr_set = true;
+    attr_set[dev] = true;
   }
   AttnBwdArgs a = {};
   a.cu_seqlens = cu_seqlens;

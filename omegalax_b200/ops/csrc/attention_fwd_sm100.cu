@@ -340,13 +340,7 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, const At
                    1, 128);
   if (e) return 3500 + e;
   auto kern = attn_fwd_kernel<HD>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          AttnFwdSmem<HD>::kTotal);
-    if (ce != cudaSuccess) return 4000 + (int)ce;
-    attr_set = true;
-  }
+  OB_ENSURE_DYN_SMEM(kern, AttnFwdSmem<HD>::kTotal);
   dim3 grid((max_seqlen + 255) / 256, a.H, B);
   kern<<<grid, kAttnThreads, AttnFwdSmem<HD>::kTotal, stream>>>(tmQ, tmK, tmV, a);
   OB_CHECK_LAUNCH();

@@ -532,6 +532,36 @@ __global__ void ce_fwd_bwd_kernel(bf16* __restrict__ logits, long long ld, int V
   }
 }
 
+// Log-sum-exp and loss of a logits chunk from the per-tile statistics that the logits GEMM wrote
+// in its epilogue (fp32 maximum and sum of exponentials per row and 256-column tile, fp32 target
+// logit per row): one warp per row.  lse_out feeds the gradient pass over the bf16 logits.
+__global__ void ce_finish_kernel(const float2* __restrict__ stats, int n_tiles, const float* __restrict__ tgt_logit,
+                                 const float* __restrict__ mask, float* __restrict__ loss_sum,
+                                 float* __restrict__ lse_out, long long R) {
+  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= R) return;
+  const float2* sp = stats + row * n_tiles;
+  float mx = -INFINITY, sm = 0.f;
+  for (int i = lane; i < n_tiles; i += 32) {
+    const float2 t = sp[i];
+    if (t.x > mx) {
+      sm *= __expf(mx - t.x);
+      mx = t.x;
+    }
+    if (t.x != -INFINITY) sm += t.y * __expf(t.x - mx);
+  }
+  const float gmx = warp_max(mx);
+  sm *= (mx == -INFINITY) ? 0.f : __expf(mx - gmx);
+  const float gsum = warp_sum(sm);
+  if (lane == 0) {
+    const float lse = gmx + logf(gsum);
+    lse_out[row] = lse;
+    const float mk = mask ? mask[row] : 1.f;
+    if (mk != 0.f) atomicAdd(loss_sum, (lse - tgt_logit[row]) * mk);
+  }
+}
+
 // Vocabulary-parallel variant, two passes around an all-reduce of the row statistics.  This GPU
 // holds the logits of vocabulary ids [v0, v0 + V).  Pass 1: row maximum, sum of exp(x - max) and
 // the target's logit (zero when another GPU owns the target).  Pass 2 (after the caller has
@@ -885,6 +915,15 @@ int ob_ce_fwd_bwd(void* logits, long long ld, long long R, int V, const int* tar
   if (R <= 0) return 0;
   ce_fwd_bwd_kernel<<<(unsigned)R, 512, 0, s>>>((bf16*)logits, ld, V, targets, mask, grad_scale,
                                                 loss_sum, lse_out, write_grad);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_ce_finish(const void* stats, int n_tiles, const float* tgt_logit, const float* mask, float* loss_sum,
+                 float* lse_out, long long R, cudaStream_t s) {
+  if (R <= 0) return 0;
+  ce_finish_kernel<<<grid_for(R * 32, 256), 256, 0, s>>>((const float2*)stats, n_tiles, tgt_logit, mask, loss_sum,
+                                                         lse_out, R);
   OB_CHECK_LAUNCH();
   return 0;
 }

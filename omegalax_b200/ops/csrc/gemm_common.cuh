@@ -25,6 +25,14 @@ struct GemmArgs {
   int out_mode;              // 0 bf16, 1 fp32 store, 2 fp32 accumulate, 3 fp32 peer red.add
   const bf16* residual;
   long long ldr;
+  const bf16* bias;          // optional [N]: added to every row before the store (bf16 / fp32 store modes)
+  // Cross-entropy statistics (512 x 256 tile kernel, bf16 output): for every row and every
+  // 256-column tile the maximum of the fp32 logits and the sum of exp(logit - maximum) go to
+  // ce_stats[row * num_n_blocks + tile] and the fp32 logit of the row's target column to
+  // ce_tgt[row], all taken from the accumulator before it is rounded to bf16.
+  const int* ce_targets;
+  float2* ce_stats;
+  float* ce_tgt;
   // out_mode 3: rows [r*rows_per_peer, (r+1)*rows_per_peer) live on peer r at peer_ptr[r]
   float* peer_ptr[kMaxPeers];
   int rows_per_peer;
@@ -60,6 +68,13 @@ struct TileInfo {
 // Store 32 (or fewer) consecutive columns of output row `grow`, held as fp32 bit patterns in v.
 __device__ __forceinline__ void gemm_store_slice(const GemmArgs& p, long long c_off, long long grow, int col0,
                                                  int ncols, uint32_t (&v)[32]) {
+            // debug build: the slice must lie inside the output (plain modes) / inside the owner's block
+            if (!OB_DEBUG_CHECK(grow >= 0 && grow < p.M && col0 >= 0 && col0 + ncols <= p.N && ncols <= 32, p.status))
+              return;
+            if (p.bias) {
+              for (int i = 0; i < ncols; ++i)
+                v[i] = __float_as_uint(__uint_as_float(v[i]) + __bfloat162float(__ldg(p.bias + col0 + i)));
+            }
             if (p.residual) {
               const bf16* rp = p.residual + grow * p.ldr + col0;
               if (ncols == 32 && ((((uintptr_t)rp) & 15) == 0)) {

@@ -296,6 +296,7 @@ int launch_pair_wide(const void* A, const void* B, const GemmArgs& g, long long 
 static bool want_wide(const GemmArgs& g) {
   if (g_tune_wide == 0) return false;
   if (g.residual != nullptr || g.ag_side != 0 || g.mode != 0) return false;
+  if (g.bias != nullptr && g.out_mode != 0) return false;   // its fp32 TMA epilogue adds no bias
   if (g_tune_wide == 1) return true;
   const long long tiles = (long long)((g.M + 511) / 512) * ((g.N + 255) / 256);
   if (g.out_mode >= 2) return tiles * (g.K / 1024 > 0 ? g.K / 1024 : 1) >= 148;
@@ -355,12 +356,7 @@ static int launch_pair(const void* A, const void* B, const GemmArgs& args_in, lo
     if (e) return 3500 + e;
   }
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kTotal);
-    if (ce != cudaSuccess) return 4000 + (int)ce;
-    attr_set = true;
-  }
+  OB_ENSURE_DYN_SMEM(kern, PairSmem::kTotal);
   static int max_pairs = 0;   // clusters of two that can be resident at once (one CTA per SM)
   if (max_pairs == 0) {
     cudaLaunchConfig_t cfg = {};
@@ -405,9 +401,11 @@ void ob_gemm_pair_tune(int gm, int wide, int splitk) {
 }
 
 // Same contract as ob_gemm_bf16 (plain mode), computed by CTA pairs on 256 x 256 tiles.
+// bias (optional, bf16 [N]) is added before the store; ce_targets / ce_stats / ce_tgt (optional, bf16
+// output only) request the cross-entropy statistics epilogue of the 512 x 256 tile kernel.
 int ob_gemm_bf16_pair(const void* A, const void* B, void* C, const void* residual, int M, int N, int K, long long lda,
-                      long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int out_mode, int* status,
-                      cudaStream_t stream) {
+                      long long ldb, long long ldc, long long ldr, int a_mn, int b_mn, int out_mode, const void* bias,
+                      const int* ce_targets, void* ce_stats, float* ce_tgt, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((lda & 7) || (ldb & 7)) return 6001;
   if ((((uintptr_t)A) & 15) || (((uintptr_t)B) & 15)) return 6002;
@@ -419,7 +417,13 @@ int ob_gemm_bf16_pair(const void* A, const void* B, void* C, const void* residua
   g.total_tiles = g.num_m_blocks * g.num_n_blocks;
   g.C = C; g.ldc = ldc; g.out_mode = out_mode;
   g.residual = (const bf16*)residual; g.ldr = ldr;
+  g.bias = (const bf16*)bias;
+  g.ce_targets = ce_targets; g.ce_stats = (float2*)ce_stats; g.ce_tgt = ce_tgt;
   g.status = status;
+  if (ce_stats != nullptr) {
+    if (out_mode != 0 || residual != nullptr) return 6008;
+    return launch_pair_wide(A, B, g, lda, ldb, a_mn, b_mn, pick_gm(2 * K), 0, stream);
+  }
   if (want_wide(g)) return launch_pair_wide(A, B, g, lda, ldb, a_mn, b_mn, pick_gm(2 * K), g_tune_splitk, stream);
   const long long a_rows = a_mn ? K : M, a_cols = a_mn ? M : K;
   const long long b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;

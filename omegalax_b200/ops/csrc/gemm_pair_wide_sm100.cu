@@ -231,6 +231,10 @@ gemm_bf16_pair_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + h * kWideBN;
         if (tma_out && p.out_mode == 0) {
           // bf16: 64 columns (128 bytes per row) per bulk tensor store
+          const long long my_grow = (long long)slab_row0 + lane;
+          const bool do_ce = p.ce_stats != nullptr && my_grow < p.M;
+          const int tgt = do_ce ? __ldg(p.ce_targets + my_grow) : -1;
+          float ce_m = -INFINITY, ce_s = 0.f;
 #pragma unroll 1
           for (int cc = 0; cc < kWideBN / 64; ++cc) {
             uint32_t v0[32], v1[32];
@@ -241,6 +245,53 @@ gemm_bf16_pair_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
             } else {
 #pragma unroll
               for (int i = 0; i < 32; ++i) v0[i] = v1[i] = 0;
+            }
+            if (p.bias) {
+              const int cb = ti.c_col0 + cc * 64;
+              if (cb + 64 <= p.N) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  v0[i] = __float_as_uint(__uint_as_float(v0[i]) + __bfloat162float(__ldg(p.bias + cb + i)));
+                  v1[i] = __float_as_uint(__uint_as_float(v1[i]) + __bfloat162float(__ldg(p.bias + cb + 32 + i)));
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  if (cb + i < p.N) v0[i] = __float_as_uint(__uint_as_float(v0[i]) + __bfloat162float(__ldg(p.bias + cb + i)));
+                  if (cb + 32 + i < p.N)
+                    v1[i] = __float_as_uint(__uint_as_float(v1[i]) + __bfloat162float(__ldg(p.bias + cb + 32 + i)));
+                }
+              }
+            }
+            if (do_ce) {   // online maximum / sum of exponentials over this row's columns of the tile (fp32)
+              const int cb = ti.c_col0 + cc * 64;
+              const int nval = min(64, p.N - cb);
+              if (nval > 0) {
+                float mx = ce_m;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  if (i < nval) mx = fmaxf(mx, __uint_as_float(v0[i]));
+                  if (32 + i < nval) mx = fmaxf(mx, __uint_as_float(v1[i]));
+                }
+                float acc = ce_s * fast_exp2((ce_m - mx) * 1.4426950408889634f);
+                const float mb = mx * 1.4426950408889634f;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  if (i < nval) acc += fast_exp2(__uint_as_float(v0[i]) * 1.4426950408889634f - mb);
+                  if (32 + i < nval) acc += fast_exp2(__uint_as_float(v1[i]) * 1.4426950408889634f - mb);
+                }
+                ce_m = mx;
+                ce_s = acc;
+                if (tgt >= cb && tgt < cb + 64) {
+                  float tl = 0.f;
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) {
+                    if (cb + i == tgt) tl = __uint_as_float(v0[i]);
+                    if (cb + 32 + i == tgt) tl = __uint_as_float(v1[i]);
+                  }
+                  p.ce_tgt[my_grow] = tl;
+                }
+              }
             }
             if (lane == 0) tma_store_wait_read<1>();   // the slab written two stores ago has been read
             __syncwarp();
@@ -269,6 +320,7 @@ gemm_bf16_pair_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
             }
             buf ^= 1;
           }
+          if (do_ce) p.ce_stats[my_grow * p.num_n_blocks + (ti.c_col0 / kWideBN)] = make_float2(ce_m, ce_s);
         } else if (tma_out) {
           // fp32 store / accumulate: 32 columns (128 bytes per row) per bulk tensor store / reduce-add
 #pragma unroll 1
@@ -415,6 +467,7 @@ static int launch_wide(const void* A, const void* B, GemmArgs args, long long a_
   }
   if (pairs > args.total_tiles * args.k_splits) pairs = args.total_tiles * args.k_splits;
   if (pairs <= 0) return 0;
+  if (args.ce_stats != nullptr && !(tma_out && args.out_mode == 0)) return 6008;   // statistics live in the TMA bf16 epilogue
   kern<<<2 * pairs, kGemmThreads, WideSmem::kTotal, stream>>>(tmA, tmB, tmC, args, tma_out);
   OB_CHECK_LAUNCH();
   return 0;

@@ -369,13 +369,7 @@ static int launch_gemm(const void* A, const void* B, const GemmArgs& args, long 
     if (e) return 3500 + e;
   }
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          GemmSmem<BN>::kTotal);
-    if (ce != cudaSuccess) return 4000 + (int)ce;
-    attr_set = true;
-  }
+  OB_ENSURE_DYN_SMEM(kern, GemmSmem<BN>::kTotal);
   int grid = args.total_tiles < num_sms() ? args.total_tiles : num_sms();
   if (grid <= 0) return 0;
   if (args.ag_side) {  // copy CTAs come first in the grid; every CTA is resident from the start
@@ -429,7 +423,7 @@ extern "C" {
 // residual (optional, bf16 [M,N] with pitch ldr) is added before the store.
 int ob_gemm_bf16(const void* A, const void* B, void* C, const void* residual, int M, int N, int K,
                  long long lda, long long ldb, long long ldc, long long ldr, int a_mn, int b_mn,
-                 int out_mode, int bn_override, int* status, cudaStream_t stream) {
+                 int out_mode, int bn_override, const void* bias, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((lda & 7) || (ldb & 7)) return 6001;  // TMA needs 16-byte row pitches
   if ((((uintptr_t)A) & 15) || (((uintptr_t)B) & 15)) return 6002;
@@ -441,6 +435,7 @@ int ob_gemm_bf16(const void* A, const void* B, void* C, const void* residual, in
   g.total_tiles = g.num_m_blocks * g.num_n_blocks;
   g.C = C; g.ldc = ldc; g.out_mode = out_mode;
   g.residual = (const bf16*)residual; g.ldr = ldr;
+  g.bias = (const bf16*)bias;
   g.status = status;
   long long a_rows = a_mn ? K : M, a_cols = a_mn ? M : K;
   long long b_rows = b_mn ? K : N, b_cols = b_mn ? N : K;

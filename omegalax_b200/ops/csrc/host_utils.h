@@ -13,7 +13,20 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// cuTensorMapEncodeTiled is a driver call and needs the device's primary context current in the
+// calling thread.  A thread that has made no runtime call yet (an autograd worker entering its
+// first backward through a GEMM) has none: bind it once per thread through the runtime.
+inline void ensure_thread_context() {
+  static thread_local bool ready = false;
+  if (!ready) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+    ready = true;
+  }
+}
+
 inline EncodeTiledFn get_encode_fn() {
+  ensure_thread_context();
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;
@@ -71,6 +84,21 @@ inline int num_sms() {
   if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
   return n[dev];
 }
+
+// Raise a kernel's dynamic shared-memory limit once per device (the attribute is per device, and
+// one process may drive several).
+#define OB_ENSURE_DYN_SMEM(kern, bytes)                                                               \
+  do {                                                                                                \
+    static bool done__[64] = {};                                                                      \
+    int dev__ = 0;                                                                                    \
+    cudaGetDevice(&dev__);                                                                            \
+    if (dev__ < 0 || dev__ >= 64) dev__ = 0;                                                          \
+    if (!done__[dev__]) {                                                                             \
+      cudaError_t ce__ = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); \
+      if (ce__ != cudaSuccess) return 4000 + (int)ce__;                                               \
+      done__[dev__] = true;                                                                           \
+    }                                                                                                 \
+  } while (0)
 
 #define OB_CHECK_LAUNCH()                                  \
   do {                                                     \

@@ -24,7 +24,17 @@ enum : int {
   OB_ERR_WAIT_FLAG = 5,       // a global-memory flag (peer or staging) never came
   OB_ERR_BAD_ARG = 6,
   OB_ERR_WAIT_MISC = 7,
+  OB_ERR_BAD_STORE = 8,       // debug build: a store fell outside the output it belongs to
 };
+
+// Debug build (-DOB_DEBUG_BOUNDS): OB_DEBUG_CHECK(cond, status) records OB_ERR_BAD_STORE and makes
+// the enclosing statement skip the access when cond is false; a no-op that is always true otherwise.
+#ifdef OB_DEBUG_BOUNDS
+#define OB_DEBUG_CHECK(cond, status) \
+  ((cond) ? true : ((status) ? (atomicCAS((status), 0, OB_ERR_BAD_STORE | (blockIdx.x << 8)), false) : false))
+#else
+#define OB_DEBUG_CHECK(cond, status) (true)
+#endif
 
 // Spin budget for one wait, in SM clock cycles (about 2 s at 2 GHz).
 #ifndef OB_WAIT_CYCLES

@@ -130,18 +130,19 @@ def _acc_main_grad(w, fn_into, fn_new):
 # ----------------------------------------------------------------------------- linear
 class _LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, residual, y_pre=None):
+    def forward(ctx, x, w, residual, y_pre=None, bias=None):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
         y = y_pre
         ag = getattr(w, "ag_spec", None)
-        if y is None and ag is not None:   # sharded weight that is gathered inside this GEMM's launch
+        if y is None and ag is not None and bias is None:   # sharded weight gathered inside this GEMM's launch
             y = ag.run(x2.contiguous(), w, residual)
         if y is None:
-            y = K.gemm(x2, w, residual=residual)
+            y = K.gemm(x2, w, residual=residual, bias=bias)   # bias and residual are added in the GEMM epilogue
         ctx.save_for_backward(x2, w)
         ctx.shp = shp
         ctx.has_res = residual is not None
+        ctx.has_bias = bias is not None
         ctx.w_ref = w
         return y.view(*shp[:-1], w.shape[0])
 
@@ -165,7 +166,8 @@ class _LinearFn(torch.autograd.Function):
                 lambda mg: K.gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=True),
                 lambda: K.gemm(dy2, x2, a_mn=True, b_mn=True),
             )
-        return dx, dw, (dy if ctx.has_res else None), None
+        db = dy2.sum(0) if (ctx.has_bias and ctx.needs_input_grad[4]) else None
+        return dx, dw, (dy if ctx.has_res else None), None, db
 
 
 def linear(x, w, residual=None, bias=None, tag=None):
@@ -181,10 +183,11 @@ def linear(x, w, residual=None, bias=None, tag=None):
         key, pre = _stash_lookup(tag if bias is None else None)
         if pre is _SKIP:
             pre = torch.empty(x.numel() // x.shape[-1], w.shape[0], dtype=x.dtype, device=x.device)
-        y = _LinearFn.apply(x, w, residual if bias is None else None,
-                            None if pre is None else pre.view(-1, w.shape[0]))
+        fused_bias = bias is not None and bias.dtype == bf16 and bias.is_contiguous()
+        y = _LinearFn.apply(x, w, residual if (bias is None or fused_bias) else None,
+                            None if pre is None else pre.view(-1, w.shape[0]), bias if fused_bias else None)
         _stash_store(key, y)
-        if bias is not None:
+        if bias is not None and not fused_bias:
             y = y + bias
             if residual is not None:
                 y = y + residual
@@ -541,9 +544,14 @@ def flash_attention(q, k, v, cu_seqlens, max_seqlen: int, *, scale: float, causa
 class _LinearCEFn(torch.autograd.Function):
     """loss = grad-ready fused  sum_rows mask * nll(h W^T) * scale.
 
-    The logits exist only one row-chunk at a time (bf16, chunk x V).  The gradients with
-    respect to h and W are produced in the same sweep (three GEMMs per chunk), so the
-    backward only rescales; dW goes straight into ``w.main_grad`` when it exists.
+    Per row chunk: the logits GEMM keeps the fp32 accumulator's softmax statistics (maximum and sum
+    of exponentials per 256-column tile, the target's logit) in its epilogue, so the loss and the
+    log-sum-exp are those of fp32 logits, as in the reference (omegalax/trainers/loss.py:24-35); the
+    bf16 copy of the chunk's logits that it also writes is turned into dlogits in place and feeds
+    the dH and dW GEMMs of the same sweep.  No [B,T,V] tensor exists and the backward only
+    rescales; dW goes straight into ``w.main_grad`` when it exists.  (Keeping dlogits out of
+    memory altogether would need the [chunk, D] dH accumulator in TMEM, 4096 columns against the
+    512 there are, or a third pass of the logits GEMM, which costs more than the traffic saved.)
     """
 
     @staticmethod
@@ -562,12 +570,24 @@ class _LinearCEFn(torch.autograd.Function):
         t32 = targets.to(torch.int32).contiguous()
         mk = mask.to(torch.float32).contiguous()
         logits = torch.empty(min(chunk, M), V, dtype=bf16, device=dev)
+        n_tiles = -(-V // 256)
+        stats = torch.empty(min(chunk, M), n_tiles, 2, dtype=torch.float32, device=dev)
+        tgt_logit = torch.zeros(min(chunk, M), dtype=torch.float32, device=dev)
+        lse = torch.empty(min(chunk, M), dtype=torch.float32, device=dev)
+        fp32_stats = os.environ.get("OMEGALAX_B200_CE_STATS", "1") == "1" and h.shape[1] % 8 == 0
         for r0 in range(0, M, chunk):
             r1 = min(M, r0 + chunk)
             lg = logits[: r1 - r0]
             hc = h[r0:r1]
-            K.gemm(hc, w, out=lg)
-            K.ce_fwd_bwd(lg, t32[r0:r1], mk[r0:r1], scale_t, loss_sum, write_grad=need_grad)
+            if fp32_stats:
+                n = r1 - r0
+                K.gemm(hc, w, out=lg, ce=(t32[r0:r1], stats[:n], tgt_logit[:n]))
+                K.ce_finish(stats[:n], tgt_logit[:n], mk[r0:r1], loss_sum, lse[:n])
+                if need_grad:
+                    K.ce_vp_grad_(lg, t32[r0:r1], 0, lse[:n], mk[r0:r1], scale_t)
+            else:
+                K.gemm(hc, w, out=lg)
+                K.ce_fwd_bwd(lg, t32[r0:r1], mk[r0:r1], scale_t, loss_sum, write_grad=need_grad)
             if need_grad:
                 K.gemm(lg, w, b_mn=True, out=dh[r0:r1])
                 if pg is not None:

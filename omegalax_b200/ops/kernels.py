@@ -62,11 +62,15 @@ def _use_pair(M: int, N: int, K: int, wgrad: bool = False) -> bool:
 
 
 def gemm(a, b, *, a_mn: bool = False, b_mn: bool = False, out=None, out_dtype=bf16,
-         accumulate: bool = False, residual=None, bn: int = 0, pair: bool | None = None):
+         accumulate: bool = False, residual=None, bn: int = 0, pair: bool | None = None, bias=None,
+         ce=None):
     """C = op(A) op(B)^T on the tcgen05 kernel.
 
     a: [M,K] (a_mn False) or [K,M] (a_mn True); b: [N,K] (b_mn False) or [K,N] (b_mn True).
     out: optional preallocated [M,N] (bf16 or fp32); ``accumulate`` adds into an fp32 out.
+    ``bias`` (bf16 [N]) and ``residual`` (bf16 [M,N]) are added in the epilogue.  ``ce`` =
+    (targets int32 [M], stats fp32 [M, ceil(N/256), 2], target_logit fp32 [M]) asks the 512 x 256
+    tile kernel for the cross-entropy statistics of the fp32 accumulator (bf16 output only).
     """
     a = _row_major_2d(a)
     b = _row_major_2d(b)
@@ -93,15 +97,23 @@ def gemm(a, b, *, a_mn: bool = False, b_mn: bool = False, out=None, out_dtype=bf
             residual = residual.contiguous()
         res_ptr, ldr = residual.data_ptr(), residual.stride(0)
     st = lib.status_tensor(a.device)
+    if bias is not None and (bias.dtype != bf16 or bias.numel() != N or not bias.is_contiguous()):
+        raise ValueError("bias must be a contiguous bf16 vector of N elements")
     if pair is None:
         pair = bn == 0 and _use_pair(M, N, K, wgrad=a_mn and b_mn)
+    if ce is not None:
+        tg, stats, tl = ce
+        if mode != 0 or residual is not None or tuple(stats.shape) != (M, -(-N // 256), 2) or tl.numel() != M:
+            raise ValueError("cross-entropy statistics need a bf16 output, no residual and [M, ceil(N/256), 2] stats")
+        pair = True
     if pair:
+        ce_ptrs = (None, None, None) if ce is None else (ce[0].data_ptr(), ce[1].data_ptr(), ce[2].data_ptr())
         _call("ob_gemm_bf16_pair", a.data_ptr(), b.data_ptr(), out.data_ptr(), res_ptr, M, N, K,
-              a.stride(0), b.stride(0), out.stride(0), ldr, int(a_mn), int(b_mn), mode, st.data_ptr(),
-              lib.stream_ptr())
+              a.stride(0), b.stride(0), out.stride(0), ldr, int(a_mn), int(b_mn), mode, lib.ptr(bias), *ce_ptrs,
+              st.data_ptr(), lib.stream_ptr())
         return out
     _call("ob_gemm_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), res_ptr, M, N, K,
-          a.stride(0), b.stride(0), out.stride(0), ldr, int(a_mn), int(b_mn), mode, bn,
+          a.stride(0), b.stride(0), out.stride(0), ldr, int(a_mn), int(b_mn), mode, bn, lib.ptr(bias),
           st.data_ptr(), lib.stream_ptr())
     return out
 
@@ -175,6 +187,7 @@ def gemm_grouped(a, b, group_offsets, *, b_mn: bool = False, out=None, out_dtype
     R, K = a.shape
     N = b.shape[2] if b_mn else b.shape[1]
     b2 = b.reshape(-1, b.shape[-1])
+    lib.check_index("gemm_grouped group_offsets", group_offsets, R + 1)
     if out is None:
         out = torch.empty(R, N, dtype=out_dtype, device=a.device)
     mode = 0 if out.dtype == bf16 else 1
@@ -190,6 +203,7 @@ def gemm_grouped_wgrad(dy, x, group_offsets, out, accumulate: bool = True):
     dy = _row_major_2d(dy)
     x = _row_major_2d(x)
     G, N, K = out.shape
+    lib.check_index("gemm_grouped_wgrad group_offsets", group_offsets, dy.shape[0] + 1)
     mode = (2 if accumulate else 1) if out.dtype == torch.float32 else 0
     st = lib.status_tensor(dy.device)
     _call("ob_gemm_bf16_grouped_wgrad", dy.data_ptr(), x.data_ptr(), out.data_ptr(),
@@ -295,8 +309,8 @@ def attn_bwd(q, k, v, o, lse, do, cu_seqlens, max_seqlen, scale, causal, dk_out=
     scratch = _attn_scratch.get(key)
     if scratch is None:
         _attn_scratch.clear()
-        scratch = (torch.empty(N * H * Kd, dtype=torch.float32, device=q.device),
-                   torch.empty(H * N, dtype=torch.float32, device=q.device))
+        scratch = (lib.scratch("attn_bwd dq_acc", N * H * Kd, torch.float32, q.device),
+                   lib.scratch("attn_bwd delta", H * N, torch.float32, q.device))
         _attn_scratch[key] = scratch
     dq_acc, delta = scratch
     st = lib.status_tensor(q.device)
@@ -315,8 +329,16 @@ def ce_fwd_bwd(logits, targets, mask, grad_scale, loss_sum, write_grad=True, lse
           int(write_grad), lib.stream_ptr())
 
 
+def ce_finish(stats, tgt_logit, mask, loss_sum, lse_out):
+    """Row log-sum-exp and masked loss from the statistics the logits GEMM wrote (``gemm(..., ce=)``)."""
+    R, n_tiles = stats.shape[0], stats.shape[1]
+    _call("ob_ce_finish", stats.data_ptr(), n_tiles, tgt_logit.data_ptr(), lib.ptr(mask), loss_sum.data_ptr(),
+          lse_out.data_ptr(), R, lib.stream_ptr())
+
+
 def embedding_fwd(ids, table):
     ids32 = ids.reshape(-1).to(torch.int32)
+    lib.check_index("embedding_fwd ids", ids32, table.shape[0])
     out = torch.empty(ids32.numel(), table.shape[1], dtype=table.dtype, device=table.device)
     _call("ob_embedding_fwd", ids32.data_ptr(), table.data_ptr(), out.data_ptr(), ids32.numel(),
           table.shape[1], lib.stream_ptr())
@@ -329,6 +351,7 @@ def embedding_bwd(ids, dy, dtable_f32, row_lo=0, row_hi=None):
     if not d2.is_contiguous():
         d2 = d2.contiguous()
     hi = dtable_f32.shape[0] + row_lo if row_hi is None else row_hi
+    lib.check_index("embedding_bwd ids", ids32, 2 ** 31 - 1)      # rows outside [row_lo, hi) are skipped, negatives are not expected
     _call("ob_embedding_bwd", ids32.data_ptr(), d2.data_ptr(), dtable_f32.data_ptr(),
           ids32.numel(), d2.shape[1], row_lo, hi, lib.stream_ptr())
 
@@ -524,6 +547,7 @@ def scatter_rows_(dst, idx32, src, replace: bool):
 
 def gather4_fwd(table, idx32_N4, w_N4):
     n = idx32_N4.shape[0]
+    lib.check_index("gather4 idx", idx32_N4, table.shape[0])
     out = torch.empty(n, table.shape[1], dtype=table.dtype, device=table.device)
     _call("ob_gather4_fwd", table.data_ptr(), idx32_N4.data_ptr(), w_N4.data_ptr(), out.data_ptr(), n, table.shape[1],
           lib.stream_ptr())
@@ -531,6 +555,7 @@ def gather4_fwd(table, idx32_N4, w_N4):
 
 
 def gather4_bwd(dout, idx32_N4, w_N4, dtable_f32):
+    lib.check_index("gather4 idx", idx32_N4, dtable_f32.shape[0])
     _call("ob_gather4_bwd", dout.data_ptr(), idx32_N4.data_ptr(), w_N4.data_ptr(), dtable_f32.data_ptr(), idx32_N4.shape[0],
           dout.shape[1], lib.stream_ptr())
 

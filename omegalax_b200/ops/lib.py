@@ -14,7 +14,8 @@ from pathlib import Path
 import torch
 
 _HERE = Path(__file__).resolve().parent
-LIB_PATH = _HERE / "libomegalax_b200.so"
+_DEBUG_LIB = os.environ.get("OMEGALAX_B200_DEBUG", "0") == "1" and os.environ.get("OMEGALAX_B200_DEBUG_LIB", "1") == "1"
+LIB_PATH = _HERE / ("libomegalax_b200_debug.so" if _DEBUG_LIB else "libomegalax_b200.so")
 
 _lib = None
 _status = {}
@@ -27,9 +28,9 @@ L = c_longlong
 F = c_float
 
 _SIGS = {
-    "ob_gemm_bf16": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P, P],
+    "ob_gemm_bf16": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P, P, P],
     "ob_gemm_bf16_pair_peer_reduce": [P, P, P, I, I, I, I, I, L, L, L, I, I, I, P, P],
-    "ob_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, P, P],
+    "ob_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, P, P, P, P, P, P],
     "ob_gemm_bf16_pair_ag": [P, P, P, P, P, I, I, I, L, L, I, I, I, I, I, P, c_uint, I, P, P],
     "ob_gemm_bf16_ag": [P, P, P, P, P, I, I, I, L, L, I, I, I, I, I, P, c_uint, I, P, P],
     "ob_gemm_bf16_peer_reduce": [P, P, P, I, I, I, I, I, L, L, L, I, I, I, P, P],
@@ -53,6 +54,7 @@ _SIGS = {
     "ob_gather4_bwd": [P, P, P, P, L, I, P],
     "ob_gelu_tanh_fwd": [P, P, L, P],
     "ob_gelu_tanh_bwd": [P, P, P, L, P],
+    "ob_ce_finish": [P, I, P, P, P, P, L, P],
     "ob_ce_vp_stats": [P, L, I, L, I, P, P, P, P, P],
     "ob_ce_vp_grad": [P, L, I, L, I, P, P, P, P, P],
     "ob_moe_count": [P, P, L, I, P],
@@ -96,7 +98,7 @@ def load():
         if os.environ.get("OMEGALAX_B200_NO_BUILD") != "1":
             from . import build as _build
 
-            _build.build()
+            _build.build(debug=_DEBUG_LIB)
     if not LIB_PATH.exists():
         raise KernelError(
             f"{LIB_PATH} is missing: run `python -m omegalax_b200.ops.build` (needs nvcc) first"
@@ -150,6 +152,8 @@ def status_tensor(device) -> torch.Tensor:
 
 def check_status(device=None) -> None:
     """Synchronise and raise if any kernel recorded a wait timeout since the last check."""
+    if debug_enabled():
+        check_canaries()
     for key, t in list(_status.items()):
         if device is not None and torch.device(device).index not in (None, key):
             continue
@@ -158,8 +162,71 @@ def check_status(device=None) -> None:
             t.zero_()
             raise KernelError(
                 f"kernel reported status code {v & 0xFF} from block {v >> 8} on cuda:{key} "
-                "(1 stage-full wait, 2 stage-empty wait, 3/4 accumulator waits, 5 flag wait)"
+                "(1 stage-full wait, 2 stage-empty wait, 3/4 accumulator waits, 5 flag wait, "
+                "8 store outside the output in a debug build)"
             )
+
+
+# ---------------------------------------------------------------------------- debug aids
+# OMEGALAX_B200_DEBUG=1 switches on three checks that cost host synchronisations and are therefore
+# off in normal runs:
+#   * every index tensor handed to a kernel that dereferences it (token ids, row maps, expert ids,
+#     routing plans, block tables) is range-checked on the host before the launch, so a bad index
+#     raises IndexError with its position instead of faulting the GPU;
+#   * scratch buffers obtained through ``scratch()`` carry guard bands on both sides, filled with a
+#     fixed pattern that ``check_status()`` verifies: a kernel that writes outside its scratch is
+#     reported by name;
+#   * ``load()`` picks the library built with -DOB_DEBUG_BOUNDS (``build.build(debug=True)``), whose
+#     GEMM epilogues verify every row / column they store against M and N and whose waits give up
+#     after 0.2 s instead of 2 s.
+_CANARY_ELEMS = 1024
+_CANARY_BYTE = 0xC7
+_guards: list = []
+
+
+def debug_enabled() -> bool:
+    return os.environ.get("OMEGALAX_B200_DEBUG", "0") == "1"
+
+
+def check_index(what: str, idx: torch.Tensor, upper: int, lower: int = 0) -> None:
+    """Debug mode only: raise IndexError unless lower <= idx < upper everywhere."""
+    if not debug_enabled() or idx is None or idx.numel() == 0:
+        return
+    lo, hi = int(idx.min()), int(idx.max())
+    if lo < lower or hi >= upper:
+        bad = ((idx < lower) | (idx >= upper)).reshape(-1).nonzero()[0]
+        raise IndexError(f"{what}: value {int(idx.reshape(-1)[bad])} at flat position {int(bad)} is outside "
+                         f"[{lower}, {upper})")
+
+
+def scratch(name: str, shape, dtype, device) -> torch.Tensor:
+    """Uninitialised work buffer for a kernel.  In debug mode it sits between two guard bands."""
+    if not debug_enabled():
+        return torch.empty(shape, dtype=dtype, device=device)
+    n = 1
+    for d in (shape if isinstance(shape, (tuple, list, torch.Size)) else (shape,)):
+        n *= int(d)
+    esz = torch.empty(0, dtype=dtype).element_size()
+    pad = _CANARY_ELEMS * 16 // esz            # 16 KB on each side, keeps 16-byte alignment of the payload
+    raw = torch.empty(n + 2 * pad, dtype=dtype, device=device)
+    raw_bytes = raw.view(torch.uint8)
+    raw_bytes[: pad * esz].fill_(_CANARY_BYTE)
+    raw_bytes[(pad + n) * esz:].fill_(_CANARY_BYTE)
+    _guards.append((name, raw_bytes, pad * esz, (pad + n) * esz))
+    return raw[pad:pad + n].view(shape)
+
+
+def check_canaries() -> None:
+    """Raise if any guard band around a ``scratch()`` buffer was overwritten; drops buffers that
+    nobody references any more."""
+    alive = []
+    for name, raw_bytes, head, tail in _guards:
+        if not (bool((raw_bytes[:head] == _CANARY_BYTE).all()) and bool((raw_bytes[tail:] == _CANARY_BYTE).all())):
+            side = "before" if not bool((raw_bytes[:head] == _CANARY_BYTE).all()) else "after"
+            raise KernelError(f"scratch buffer '{name}': bytes {side} the buffer were overwritten")
+        if raw_bytes._use_count() > 1 if hasattr(raw_bytes, "_use_count") else True:
+            alive.append((name, raw_bytes, head, tail))
+    _guards[:] = alive[-256:]
 
 
 def call(name: str, *args) -> None:

@@ -34,6 +34,7 @@ from ..ops import functional as Fn
 from ..ops import kernels as K
 
 bf16 = torch.bfloat16
+_TORCH_CHUNK = 1 << 26      # elements per slice of the PyTorch optimizer path (bounds its temporaries)
 
 
 # OMEGALAX_B200_POISON=1 fills every gathered-layer buffer with NaN before it is (re)filled, so a read
@@ -494,7 +495,10 @@ class TrainEngine:
         if self.use_cuda_kernels:
             K.sumsq(self.grad, self.norm_sq)
         else:
-            self.norm_sq += (self.grad.double() ** 2).sum().float()
+            acc = torch.zeros((), dtype=torch.float64, device=self.device)
+            for off in range(0, self.grad.numel(), _TORCH_CHUNK):   # bounded temporaries on large shards
+                acc += (self.grad[off:off + _TORCH_CHUNK].double() ** 2).sum()
+            self.norm_sq += acc.float()
         if self.W > 1:
             self._dedup_replicated_norm()
             dist.all_reduce(self.norm_sq, group=self.group)
@@ -525,15 +529,19 @@ class TrainEngine:
                     eps=self.eps, wd=self.wd, step=self.step_count, grad_mul=gmul, norm_sq=nsq,
                     max_norm=self.max_grad_norm, zero_grad=True)
         else:
-            g = self.grad * gmul
+            mul = torch.full((), gmul, dtype=torch.float32, device=self.device)
             if self.max_grad_norm > 0:
                 nrm = torch.sqrt(nsq) * gmul
-                g = g * torch.clamp(self.max_grad_norm / (nrm + 1e-6), max=1.0)
-            self.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
-            self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
-            mh = self.exp_avg / (1 - b1 ** self.step_count)
-            vh = self.exp_avg_sq / (1 - b2 ** self.step_count)
-            self.master.sub_(lr * (mh / (vh.sqrt() + self.eps) + self.wd * self.master))
+                mul = mul * torch.clamp(self.max_grad_norm / (nrm + 1e-6), max=1.0).reshape(())
+            bc1, bc2 = 1 - b1 ** self.step_count, 1 - b2 ** self.step_count
+            for off in range(0, self.grad.numel(), _TORCH_CHUNK):   # in place, chunk-sized temporaries only
+                sl = slice(off, off + _TORCH_CHUNK)
+                g = self.grad[sl] * mul
+                m, v, pm = self.exp_avg[sl], self.exp_avg_sq[sl], self.master[sl]
+                m.mul_(b1).add_(g, alpha=1 - b1)
+                v.mul_(b2).addcmul_(g, g, value=1 - b2)
+                upd = (m / bc1).div_((v / bc2).sqrt_().add_(self.eps))
+                pm.sub_(lr * (upd + self.wd * pm))
             self.grad.zero_()
             self._refresh_compute_shard()
         if self.W > 1:

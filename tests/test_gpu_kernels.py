@@ -152,6 +152,72 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn):
     assert _rel_err(out, ref) < 2e-2
 
 
+@pytest.mark.parametrize("kernel", ["single", "pair", "wide"])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_gemm_bias_epilogue(kernel, with_res):
+    """y = x W^T + bias (+ residual) in the GEMM epilogue, on every GEMM kernel, per element."""
+    from omegalax_b200.ops import kernels as Kn, lib
+    torch.manual_seed(14)
+    M, N, K = 776, 328, 192
+    a = torch.randn(M, K, device=_dev()).to(bf16)
+    b = torch.randn(N, K, device=_dev()).to(bf16)
+    bias = torch.randn(N, device=_dev()).to(bf16)
+    res = torch.randn(M, N, device=_dev()).to(bf16) if with_res else None
+    ref = a.float() @ b.float().t() + bias.float() + (res.float() if with_res else 0.0)
+    lib.gemm_pair_tune(-1, 1 if kernel == "wide" else 0, -1)
+    try:
+        out = Kn.gemm(a, b, bias=bias, residual=res, pair=kernel != "single")
+        _check(lib)
+    finally:
+        lib.gemm_pair_tune(-1, -1, -1)
+    _assert_gemm_close(out, ref, K)
+
+
+def test_linear_with_bias_gradients():
+    from omegalax_b200.ops import functional as Fn, lib
+    torch.manual_seed(15)
+    x = torch.randn(3, 100, 256, device=_dev()).to(bf16).requires_grad_(True)
+    w = (torch.randn(384, 256, device=_dev()) * 0.05).to(bf16).requires_grad_(True)
+    b = torch.randn(384, device=_dev()).to(bf16).requires_grad_(True)
+    r = torch.randn(3, 100, 384, device=_dev()).to(bf16).requires_grad_(True)
+    y = Fn.linear(x, w, residual=r, bias=b)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    _check(lib)
+    xr, wr, br, rr = (t.detach().float().requires_grad_(True) for t in (x, w, b, r))
+    yr = torch.nn.functional.linear(xr, wr, br) + rr
+    yr.backward(dy.float())
+    torch.testing.assert_close(y.float(), yr, rtol=2.0 ** -7, atol=0.05)
+    for got, want in ((x.grad, xr.grad), (w.grad, wr.grad), (b.grad, br.grad), (r.grad, rr.grad)):
+        assert _rel_err(got, want) < 1e-2
+
+
+@pytest.mark.parametrize("V", [1024, 151936 // 8 + 8, 5000 - 8])
+def test_linear_cross_entropy_loss_is_that_of_fp32_logits(V):
+    """The loss comes from the fp32 accumulator of the logits GEMM (statistics epilogue), not from
+    bf16-rounded logits: it equals the fp32 PyTorch value to 1e-5 relative; the gradients, which
+    go through bf16 dlogits, to bf16 accuracy."""
+    from omegalax_b200.ops import functional as Fn, lib
+    torch.manual_seed(16)
+    M, D = 600, 256
+    h = torch.randn(M, D, device=_dev()).to(bf16).requires_grad_(True)
+    w = (torch.randn(V, D, device=_dev()) * 0.1).to(bf16).requires_grad_(True)
+    y = torch.randint(0, V, (M,), device=_dev(), dtype=torch.int32)
+    mask = (torch.rand(M, device=_dev()) > 0.3).float()
+    loss = Fn.linear_cross_entropy(h, w, y, mask, 1.0 / M, chunk=256)
+    loss.backward()
+    _check(lib)
+    hr, wr = h.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    logits = hr @ wr.t()
+    nll = torch.nn.functional.cross_entropy(logits, y.long(), reduction="none")
+    ref = (nll * mask).sum() / M
+    ref.backward()
+    assert abs(float(loss) - float(ref)) <= 1e-5 * abs(float(ref)) + 1e-6, (float(loss), float(ref))
+    # the gradients go through the bf16 copy of the logits (off by up to 2^-9 relative)
+    assert _rel_err(h.grad, hr.grad) < 3e-2
+    assert _rel_err(w.grad, wr.grad) < 3e-2
+
+
 @pytest.mark.parametrize("bn", [128, 256])
 def test_gemm_epilogues(bn):
     from omegalax_b200.ops import kernels as Kn, lib
