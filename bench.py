@@ -178,6 +178,8 @@ def main() -> int:
     ap.add_argument("--micro-seqs", type=int, default=None, help="sequences per GPU per micro-batch")
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--remat", default=None, help="full | selective | save:<tags> (default depends on N)")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (sequence-parallel Megatron layout); "
+                                                      "the remaining N / tp ranks form the FSDP / expert-parallel group")
     ap.add_argument("--kernel-table", default=None,
                     help="after the timed regions, trace one more step and write its per-kernel device times here")
     args = ap.parse_args()
@@ -235,26 +237,32 @@ def main() -> int:
     tcfg = trainer.TrainConfig(seed=0, batch_size=micro * N, seq_len=T, num_steps=10_000, learning_rate=1e-5,
                                weight_decay=0.01, warmup_steps=0, lr_schedule="linear", max_grad_norm=1.0,
                                grad_accum_steps=accum, remat_policy=remat)
-    mesh = mesh_lib.ensure_mesh(tp_size=1, fsdp_size=N, dp_size=1)
+    TP = max(args.tp, 1)
+    if N % TP:
+        raise SystemExit(f"--tp {TP} does not divide {N} GPUs")
+    FS = N // TP
+    mesh = mesh_lib.ensure_mesh(tp_size=TP, fsdp_size=FS, dp_size=1)
     if is_vlm:
         from omegalax_b200.trainers import vlm as vlm_trainer
 
-        model, cfg = vlm_trainer.init_model(cfg, 0, tp_size=1, fsdp_size=N, dp_size=1, meta=True)
+        model, cfg = vlm_trainer.init_model(cfg, 0, tp_size=TP, fsdp_size=FS, dp_size=1, meta=True)
         opt = trainer.build_optimizer(model, tcfg, device=device)
         step_fn = vlm_trainer.make_sft_train_step(cfg, pad_id=0)
     else:
-        model, cfg = trainer.init_model(cfg, 0, tp_size=1, fsdp_size=N, dp_size=1, meta=True)
+        model, cfg = trainer.init_model(cfg, 0, tp_size=TP, fsdp_size=FS, dp_size=1, meta=True)
         opt = trainer.build_optimizer(model, tcfg, device=device)
         step_fn = trainer.make_sft_train_step(cfg, pad_id=0)
 
     # synthetic data in pinned host memory: a pool of distinct micro-batches
-    g = torch.Generator().manual_seed(1234 + rank)
-    pool = vlm_batches(cfg, micro, T, 4, 1234 + rank) if is_vlm else []
+    # the ranks of one tensor-parallel group work on the same rows: micro * TP sequences per data rank
+    drank, mrows = rank // TP, micro * TP
+    g = torch.Generator().manual_seed(1234 + drank)
+    pool = vlm_batches(cfg, mrows, T, 4, 1234 + drank) if is_vlm else []
     for _ in range(0 if is_vlm else 4):
-        tok = torch.randint(1, cfg.vocab_size, (micro, T), generator=g, dtype=torch.int32).pin_memory()
-        lm = torch.zeros(micro, T, dtype=torch.int32)
+        tok = torch.randint(1, cfg.vocab_size, (mrows, T), generator=g, dtype=torch.int32).pin_memory()
+        lm = torch.zeros(mrows, T, dtype=torch.int32)
         lm[:, T // 2:] = 1
-        pool.append({"token_ids_BT": tok, "attention_mask_BT": torch.ones(micro, T, dtype=torch.int32).pin_memory(),
+        pool.append({"token_ids_BT": tok, "attention_mask_BT": torch.ones(mrows, T, dtype=torch.int32).pin_memory(),
                      "loss_mask_BT": lm.pin_memory()})
     h2d_bytes = sum(v.numel() * v.element_size() for v in pool[0].values()) * accum
 
@@ -341,7 +349,7 @@ def main() -> int:
             "config": {"model": model_id if args.layers is None and args.experts is None
                        else f"{model_id}[layers={args.layers or 'all'}, experts={args.experts or 'all'}]",
                        "global_batch": args.seqs_per_gpu * N, "seq_len": T,
-                       "parallelism": f"fsdp{N}" if par == "fsdp" else f"ep{N}+fsdp{N}",
+                       "parallelism": (f"fsdp{FS}" if par == "fsdp" else f"ep{FS}+fsdp{FS}") + (f"+tp{TP}" if TP > 1 else ""),
                        "micro_batch_per_gpu": micro, "grad_accum": accum, "optimizer": "AdamW fp32 master",
                        "remat": remat, "l2": "inputs larger than L2 (weights and activations of one step far exceed 126 MB)"},
             "tokens_per_sec_per_gpu": value / N, "tflops_per_gpu": tflops_per_gpu,

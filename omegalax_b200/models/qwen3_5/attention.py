@@ -53,13 +53,9 @@ class Attention(nn.Module):
         q, k, v, gate = Fn.qk_norm_rope(qkv, self.q_norm.weight, self.k_norm.weight, ctx.sin, ctx.cos,
                                         self.H, self.G, self.Kd, rot=self.rot, eps=self.eps, one_plus=True,
                                         q_stride_heads=2)
-        if Fn.use_kernels(q) and self.Kd in (64, 128):
+        if Fn.use_kernels(q) or (Fn.library_mode() and q.is_cuda):
+            # own flash-attention kernels for 64-, 128- and 256-wide heads (the published configs use 256)
             o = Fn.flash_attention(q, k, v, ctx.cu_seqlens, T, scale=self.scale, causal=True)
-        elif q.is_cuda:
-            o = torch.nn.functional.scaled_dot_product_attention(
-                q.view(B, T, self.H, self.Kd).transpose(1, 2), k.reshape(B, T, self.G, self.Kd).transpose(1, 2),
-                v.reshape(B, T, self.G, self.Kd).transpose(1, 2), is_causal=True, scale=self.scale,
-                enable_gqa=True).transpose(1, 2).reshape(M, self.H, self.Kd)
         else:
             ks = None if ctx.k_start is None else ctx.k_start[:, None].expand(B, T)
             o = R.attention(q.reshape(B, T, self.H, self.Kd), k.reshape(B, T, self.G, self.Kd),

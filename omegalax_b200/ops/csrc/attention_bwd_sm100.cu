@@ -20,6 +20,13 @@
 // its own (one per quadrant, 64 columns), so draining dQ^T of step i-1 overlaps E of step i and
 // the S^T buffer is handed back to the tensor core without waiting for the softmax warps.
 //
+// Heads of 256 (template HD = 256): dK and dV of a 128-key tile would need all 512 TMEM columns, so
+// the kernel runs twice, once per 128-wide half `dh` of the head dimension.  Each pass computes
+// S^T and dP^T over all 256 dimensions (they need the full dot products) and the three gradient
+// products for its half only (dV[:, half], dK[:, half], dQ[:, half]).  The K and V tiles take
+// 128 KB of shared memory there, which leaves room for a single Q/dO stage and no dQ staging tile:
+// the dQ warps add their dQ^T rows to the fp32 buffer with coalesced red.global.add instead.
+//
 // Scratch (allocated by the caller): delta [H, rows] fp32 = rowsum(dO * O) from the
 // preprocess kernel, and dq_acc [rows, H, 128] fp32, zeroed before launch and converted to
 // bf16 by the postprocess kernel.
@@ -29,9 +36,8 @@
 namespace ob {
 
 constexpr int kBwdThreads = 448;     // producer warp, MMA warp, 8 softmax/dS warps, 4 dQ warps
-constexpr int kHD = 128;
+constexpr int kHD = 128;       // width of the head-dim slice one pass produces gradients for
 constexpr int kQT = 64;        // queries per step
-constexpr int kQStages = 3;
 
 struct AttnBwdArgs {
   const int* cu_seqlens;
@@ -44,29 +50,36 @@ struct AttnBwdArgs {
   long long total_rows;
   int H, G;
   int causal;
+  int dh;                // which 128-wide half of the head dimension this pass differentiates (HD 256)
   float scale, scale_log2;
   int* status;
 };
 
+template <int HD>
 struct AttnBwdSmem {
-  static constexpr int kKOff = 0;                       // 32 KB
-  static constexpr int kVOff = 32768;                   // 32 KB
-  static constexpr int kQOff = 65536;                   // 3 x 16 KB
-  static constexpr int kDOOff = kQOff + kQStages * 16384;
-  static constexpr int kDSOff = kDOOff + kQStages * 16384;  // 2 x 16 KB
-  static constexpr int kDQOff = kDSOff + 2 * 16384;         // 32 KB fp32 [64 q][128 d] staging
-  static constexpr int kStatOff = kDQOff + 32768;           // 3 x (64 lse*log2e + 64 delta) fp32
-  static constexpr int kBarOff = kStatOff + kQStages * 512;
+  static constexpr int kStages = HD == 128 ? 3 : 1;     // Q/dO ring depth
+  static constexpr int kKVTile = 128 * HD * 2;          // 32 KB (HD 128) / 64 KB (HD 256)
+  static constexpr int kQTile = kQT * HD * 2;           // 16 KB / 32 KB
+  static constexpr int kKOff = 0;
+  static constexpr int kVOff = kKVTile;
+  static constexpr int kQOff = 2 * kKVTile;
+  static constexpr int kDOOff = kQOff + kStages * kQTile;
+  static constexpr int kDSOff = kDOOff + kStages * kQTile;  // 2 x 16 KB
+  static constexpr int kDQOff = kDSOff + 2 * 16384;         // 32 KB fp32 [64 q][128 d] staging (HD 128 only)
+  static constexpr int kStatOff = kDQOff + (HD == 128 ? 32768 : 0);   // per stage 64 lse*log2e + 64 delta, fp32
+  static constexpr int kBarOff = kStatOff + kStages * 512;
   static constexpr int kTotal = kBarOff + 256 + 1024;
 };
 
+template <int HD>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                 const __grid_constant__ CUtensorMap tmDQ, const AttnBwdArgs p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  using L = AttnBwdSmem;
+  using L = AttnBwdSmem<HD>;
+  constexpr int kQStages = L::kStages;
   uint64_t* kv_full = (uint64_t*)(smem + L::kBarOff);  // [1]
   uint64_t* qdo_full = kv_full + 1;                    // [3]
   uint64_t* qdo_empty = qdo_full + kQStages;           // [3]
@@ -134,8 +147,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
       tma_prefetch_desc(&tmDO);
-      mbar_expect_tx(kv_full, 65536);
-      for (int kb = 0; kb < 2; ++kb) {
+      mbar_expect_tx(kv_full, 2 * L::kKVTile);
+      for (int kb = 0; kb < HD / 64; ++kb) {
         tma_load_3d(smem + L::kKOff + kb * 16384, &tmK, kv_full, kb * 64, g, seq_start + k0);
         tma_load_3d(smem + L::kVOff + kb * 16384, &tmV, kv_full, kb * 64, g, seq_start + k0);
       }
@@ -150,11 +163,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int h = g * R + it / nqt;
       const int q0 = (i_first + it % nqt) * kQT;
       if (lane == 0) {
-        mbar_expect_tx(&qdo_full[s], 32768);
-        for (int kb = 0; kb < 2; ++kb) {
-          tma_load_3d(smem + L::kQOff + s * 16384 + kb * 8192, &tmQ, &qdo_full[s], kb * 64, h,
+        mbar_expect_tx(&qdo_full[s], 2 * L::kQTile);
+        for (int kb = 0; kb < HD / 64; ++kb) {
+          tma_load_3d(smem + L::kQOff + s * L::kQTile + kb * 8192, &tmQ, &qdo_full[s], kb * 64, h,
                       seq_start + q0);
-          tma_load_3d(smem + L::kDOOff + s * 16384 + kb * 8192, &tmDO, &qdo_full[s], kb * 64, h,
+          tma_load_3d(smem + L::kDOOff + s * L::kQTile + kb * 8192, &tmDO, &qdo_full[s], kb * 64, h,
                       seq_start + q0);
         }
       }
@@ -180,17 +193,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t ka = smem_u32(smem + L::kKOff), va = smem_u32(smem + L::kVOff);
       auto issue_A = [&](int it) {
         const int s = it % kQStages, bb = it & 1;
-        const uint32_t qa = smem_u32(smem + L::kQOff + s * 16384);
-        const uint32_t da = smem_u32(smem + L::kDOOff + s * 16384);
+        const uint32_t qa = smem_u32(smem + L::kQOff + s * L::kQTile);
+        const uint32_t da = smem_u32(smem + L::kDOOff + s * L::kQTile);
 #pragma unroll
-        for (int k = 0; k < kHD / 16; ++k) {
+        for (int k = 0; k < HD / 16; ++k) {
           const uint32_t offA = (k >> 2) * 16384 + (k & 3) * 32;
           const uint32_t offB = (k >> 2) * 8192 + (k & 3) * 32;
           umma_ss(T_S(bb), make_smem_desc(ka + offA, 16, 1024), make_smem_desc(qa + offB, 16, 1024),
                   idesc_a, k > 0 ? 1u : 0u);
         }
 #pragma unroll
-        for (int k = 0; k < kHD / 16; ++k) {
+        for (int k = 0; k < HD / 16; ++k) {
           const uint32_t offA = (k >> 2) * 16384 + (k & 3) * 32;
           const uint32_t offB = (k >> 2) * 8192 + (k & 3) * 32;
           umma_ss(T_DP(bb), make_smem_desc(va + offA, 16, 1024), make_smem_desc(da + offB, 16, 1024),
@@ -224,8 +237,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!ok) break;
         tc_fence_after();
         const int s = it % kQStages;
-        const uint32_t qa = smem_u32(smem + L::kQOff + s * 16384);
-        const uint32_t da = smem_u32(smem + L::kDOOff + s * 16384);
+        // the 128-wide head-dim slice of this pass: two 64-column blocks of every tile
+        const uint32_t qa = smem_u32(smem + L::kQOff + s * L::kQTile) + p.dh * 16384;
+        const uint32_t da = smem_u32(smem + L::kDOOff + s * L::kQTile) + p.dh * 16384;
+        const uint32_t kah = ka + p.dh * 32768;
         const uint32_t dsa = smem_u32(smem + L::kDSOff + bb * 16384);
         // dV += P^T dO ; dK += dS^T Q : reduce over the 64 queries (4 steps of 16)
 #pragma unroll
@@ -239,7 +254,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // dQ^T = K^T dS : reduce over the 128 keys (8 steps of 16)
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ss(T_S(bb), make_smem_desc(ka + k * 2048, 16384, 1024),
+          umma_ss(T_S(bb), make_smem_desc(kah + k * 2048, 16384, 1024),
                   make_smem_desc(dsa + k * 2048, 16384, 1024), idesc_q, k > 0 ? 1u : 0u);
         umma_commit(&dq_full[bb]);
         umma_commit(&qdo_empty[s]);
@@ -270,6 +285,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&dq_read[bb]);   // the tensor core may overwrite this S^T buffer
+      if constexpr (HD != 128) {
+        // no staging tile: thread r adds head-dim element r of every query row (a warp covers 128
+        // consecutive bytes of one row per instruction)
+        const int h = g * R + it / nqt;
+        const int q0 = (i_first + it % nqt) * kQT;
+        const int qvalid = min(kQT, seqlen - q0);
+        float* dst = p.dq_acc + ((long long)(seq_start + q0) * p.H + h) * HD + p.dh * kHD + r;
+        const long long rs = (long long)p.H * HD;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (i < qvalid) atomicAdd(dst + i * rs, __uint_as_float(v0[i]));
+          if (32 + i < qvalid) atomicAdd(dst + (32 + i) * rs, __uint_as_float(v1[i]));
+        }
+        continue;
+      }
       // the staging tile is free once the previous reduce-add has read it
       if (issuer) {
         tma_store_wait_read<0>();
@@ -368,8 +398,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       // every lane runs the aligned TMEM loads; only the stores are predicated
       const long long grow = (long long)seq_start + (key_ok ? kpos : 0);
-      bf16* dkp = p.dk + grow * p.dk_row_stride + (long long)g * kHD;
-      bf16* dvp = p.dv + grow * p.dv_row_stride + (long long)g * kHD;
+      bf16* dkp = p.dk + grow * p.dk_row_stride + (long long)g * HD + p.dh * kHD;
+      bf16* dvp = p.dv + grow * p.dv_row_stride + (long long)g * HD + p.dh * kHD;
 #pragma unroll 1
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
@@ -450,7 +480,7 @@ int ob_attn_bwd(const void* q, const void* k, const void* v, const void* out, co
                 long long dv_row_stride, float scale, int causal, int* status,
                 cudaStream_t stream) {
   if (B <= 0 || total_rows <= 0) return 0;
-  if (HD != 128) return 6005;
+  if (HD != 128 && HD != 256) return 6005;
   if ((q_row_stride | k_row_stride | v_row_stride | do_row_stride | dk_row_stride | dv_row_stride) & 7)
     return 6001;
   {
@@ -464,9 +494,7 @@ int ob_attn_bwd(const void* q, const void* k, const void* v, const void* out, co
   cudaError_t me = cudaMemsetAsync(dq_acc, 0, (size_t)total_rows * H * HD * sizeof(float), stream);
   if (me != cudaSuccess) return 4100 + (int)me;
   CUtensorMap tmQ, tmK, tmV, tmDO, tmDQ;
-  int e = make_tmap_2d(&tmDQ, dq_acc, total_rows, (uint64_t)H * HD, (uint64_t)H * HD, kQT, kHD, 4, false);
-  if (e) return 1900 + e;
-  e = make_tmap_3d(&tmQ, q, HD, H, total_rows, (uint64_t)HD * 2, (uint64_t)q_row_stride * 2, 64, 1, kQT);
+  int e = make_tmap_3d(&tmQ, q, HD, H, total_rows, (uint64_t)HD * 2, (uint64_t)q_row_stride * 2, 64, 1, kQT);
   if (e) return 2000 + e;
   e = make_tmap_3d(&tmDO, dout, HD, H, total_rows, (uint64_t)HD * 2, (uint64_t)do_row_stride * 2, 64, 1, kQT);
   if (e) return 2500 + e;
@@ -474,15 +502,10 @@ int ob_attn_bwd(const void* q, const void* k, const void* v, const void* out, co
   if (e) return 3000 + e;
   e = make_tmap_3d(&tmV, v, HD, G, total_rows, (uint64_t)HD * 2, (uint64_t)v_row_stride * 2, 64, 1, 128);
   if (e) return 3500 + e;
-  static bool attr_set[64] = {};   // the attribute is per device
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (!attr_set[dev]) {
-    cudaError_t ce = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          AttnBwdSmem::kTotal);
-    if (ce != cudaSuccess) return 4000 + (int)ce;
-    attr_set[dev] = true;
+  tmDQ = tmQ;   // only the 128-wide kernel adds dQ through a tensor map
+  if (HD == 128) {
+    e = make_tmap_2d(&tmDQ, dq_acc, total_rows, (uint64_t)H * HD, (uint64_t)H * HD, kQT, kHD, 4, false);
+    if (e) return 1900 + e;
   }
   AttnBwdArgs a = {};
   a.cu_seqlens = cu_seqlens;
@@ -493,8 +516,18 @@ int ob_attn_bwd(const void* q, const void* k, const void* v, const void* out, co
   a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
   dim3 grid((max_seqlen + 127) / 128, G, B);
-  attn_bwd_kernel<<<grid, kBwdThreads, AttnBwdSmem::kTotal, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, a);
-  OB_CHECK_LAUNCH();
+  if (HD == 128) {
+    OB_ENSURE_DYN_SMEM(attn_bwd_kernel<128>, AttnBwdSmem<128>::kTotal);
+    attn_bwd_kernel<128><<<grid, kBwdThreads, AttnBwdSmem<128>::kTotal, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, a);
+    OB_CHECK_LAUNCH();
+  } else {
+    OB_ENSURE_DYN_SMEM(attn_bwd_kernel<256>, AttnBwdSmem<256>::kTotal);
+    for (int dh = 0; dh < 2; ++dh) {   // one pass per 128-wide half of the head dimension
+      a.dh = dh;
+      attn_bwd_kernel<256><<<grid, kBwdThreads, AttnBwdSmem<256>::kTotal, stream>>>(tmQ, tmK, tmV, tmDO, tmDQ, a);
+      OB_CHECK_LAUNCH();
+    }
+  }
   // fp32 accumulation buffer -> bf16 dq
   extern int ob_cast_f32_bf16(const float*, void*, long long, cudaStream_t);
   return ob_cast_f32_bf16(dq_acc, dq, total_rows * H * HD, stream);
@@ -543,6 +576,7 @@ extern "C" int ob_attn_bwd_noalloc(const void* q, const void* k, const void* v, 
                                    long long dv_row_stride, float scale, int causal, int* status,
                                    cudaStream_t stream) {
   if (B <= 0 || total_rows <= 0) return 0;
+  if (HD != 128) return 6005;   // the built-in scratch is laid out for 128-wide heads
   if (total_rows * (long long)H > OB_ATTN_NOALLOC_MAX_ROW_HEADS) return 6100;  // beyond the built-in scratch
   int err = 0;
   unsigned char* base = noalloc_scratch_for_current_device(&err);

@@ -347,6 +347,12 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, const At
   return 0;
 }
 
+// attention_fwd256_sm100.cu
+int launch_attn_fwd256(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_seqlens, int B,
+                       int max_seqlen, long long total_rows, int H, int G, long long q_row_stride,
+                       long long k_row_stride, long long v_row_stride, long long o_row_stride, float scale, int causal,
+                       int* status, cudaStream_t stream);
+
 }  // namespace ob
 
 using namespace ob;
@@ -379,6 +385,9 @@ int ob_attn_fwd(const void* q, const void* k, const void* v, void* out, float* l
   if (HD == 64)
     return launch_attn_fwd<64>(q, k, v, a, q_row_stride, k_row_stride, v_row_stride, B, max_seqlen,
                                stream);
+  if (HD == 256)
+    return launch_attn_fwd256(q, k, v, out, lse, cu_seqlens, B, max_seqlen, total_rows, H, G, q_row_stride,
+                              k_row_stride, v_row_stride, o_row_stride, scale, causal, status, stream);
   return 6005;
 }
 

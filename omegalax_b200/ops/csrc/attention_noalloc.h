@@ -23,9 +23,11 @@
 //   * The first call on each device looks up the device address of the array (with that device
 //     current) and caches it; make that first call outside of any stream capture.
 //
-// Arguments are those of ob_attn_bwd without the two scratch pointers; head_dim must be 128.
-// Returns 0 on success, 6100 if the problem exceeds the built-in scratch, 6101 if the address
-// lookup failed, otherwise the code of ob_attn_bwd.
+// Arguments are those of ob_attn_bwd without the two scratch pointers; head_dim must be 128 (the
+// scratch is laid out for that width; other widths return 6005 and launch nothing).  One process
+// may call it on several devices: the address cache and the kernel's shared-memory attribute are
+// kept per device.  Returns 0 on success, 6100 if the problem exceeds the built-in scratch, 6101 if
+// the address lookup failed, otherwise the code of ob_attn_bwd.
 #pragma once
 #include <cuda_runtime.h>
 

@@ -88,11 +88,58 @@ __global__ void reduce_scatter_pull_kernel(PeerPtrs full, float* __restrict__ ou
   }
 }
 
+// ---------------------------------------------------------------- slab sum (two-phase reduce-scatter)
+// out[i] = sum over the `slots` slabs of staging[s * slab_elems + i] (+ residual[i]); bf16 in and out,
+// fp32 accumulation.  Second phase of the GEMM -> reduce-scatter whose first phase stored every
+// sender's partial tile into its own slab of this GPU's staging buffer.
+__global__ void slab_sum_kernel(const bf16* __restrict__ staging, int slots, long long slab_elems,
+                                const bf16* __restrict__ residual, bf16* __restrict__ out) {
+  const long long nv = slab_elems >> 3;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (residual) {
+      const uint4 q = reinterpret_cast<const uint4*>(residual)[i];
+      const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16(u[j]);
+        acc[2 * j] = f.x; acc[2 * j + 1] = f.y;
+      }
+    }
+    for (int s = 0; s < slots; ++s) {
+      const uint4 q = reinterpret_cast<const uint4*>(staging + (long long)s * slab_elems)[i];
+      const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16(u[j]);
+        acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
 }  // namespace ob
 
 using namespace ob;
 
 extern "C" {
+
+int ob_slab_sum(const void* staging, int slots, long long slab_elems, const void* residual, void* out,
+                cudaStream_t stream) {
+  if (slab_elems <= 0) return 0;
+  if (slab_elems % 8) return 6001;
+  if (((uintptr_t)staging | (uintptr_t)out | (uintptr_t)residual) & 15) return 6002;
+  long long blocks = (slab_elems / 8 + 255) / 256;
+  const long long cap = (long long)num_sms() * 8;
+  slab_sum_kernel<<<(unsigned)(blocks > cap ? cap : blocks), 256, 0, stream>>>((const bf16*)staging, slots, slab_elems,
+                                                                             (const bf16*)residual, (bf16*)out);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
 
 // ---- allocation / IPC (host side)
 int ob_symm_alloc(void** out, long long bytes) {
@@ -171,6 +218,16 @@ int ob_reduce_scatter_pull(void* const* full_ptrs, int world, int rank, float* o
 //       with an upstream gradient (gradient of the routing weights).
 // One warp per pair (push) or per token (pull); rows are moved as 16-byte vectors.
 namespace ob {
+
+// Every rank writes its per-expert pair counts into row `rank` of every peer's count table
+// (W x E ints on each GPU): after the next device barrier all ranks hold the same table and derive
+// the same routing plan from it, without a host-launched collective.
+__global__ void ep_publish_counts_kernel(PeerPtrs tbl, const int* __restrict__ mine, int E, int world, int rank) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= world * E) return;
+  const int peer = t / E, e = t - peer * E;
+  reinterpret_cast<int*>(tbl.p[peer])[rank * E + e] = mine[e];
+}
 
 __global__ void ep_push_kernel(PeerPtrs dst, const bf16* __restrict__ src, const int* __restrict__ src_row,
                                const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
@@ -254,6 +311,17 @@ __global__ void ep_pull_kernel(PeerPtrs src, bf16* __restrict__ out, const int* 
 }  // namespace ob
 
 extern "C" {
+
+int ob_ep_publish_counts(void* const* tbl_ptrs, int world, int rank, const int* mine, int E, cudaStream_t stream) {
+  if (world > kMaxRanks) return 6003;
+  if (E <= 0) return 0;
+  PeerPtrs t = {};
+  for (int i = 0; i < world; ++i) t.p[i] = tbl_ptrs[i];
+  const int n = world * E;
+  ep_publish_counts_kernel<<<(n + 255) / 256, 256, 0, stream>>>(t, mine, E, world, rank);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
 
 int ob_ep_push(void* const* dst_ptrs, int world, const void* src, const int* src_row, const int* dst_rank,
                const int* dst_row, const float* scale, long long P, int D, cudaStream_t stream) {

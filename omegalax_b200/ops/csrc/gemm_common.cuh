@@ -22,7 +22,8 @@ struct GemmArgs {
   void* C;
   long long ldc;
   long long c_group_stride;  // mode 2: elements between consecutive groups' outputs
-  int out_mode;              // 0 bf16, 1 fp32 store, 2 fp32 accumulate, 3 fp32 peer red.add
+  int out_mode;              // 0 bf16, 1 fp32 store, 2 fp32 accumulate, 3 fp32 peer red.add, 4 bf16 peer red.add,
+                             // 5 bf16 peer store into the sender's slot of the owner's staging buffer
   const bf16* residual;
   long long ldr;
   const bf16* bias;          // optional [N]: added to every row before the store (bf16 / fp32 store modes)
@@ -36,6 +37,10 @@ struct GemmArgs {
   // out_mode 3: rows [r*rows_per_peer, (r+1)*rows_per_peer) live on peer r at peer_ptr[r]
   float* peer_ptr[kMaxPeers];
   int rows_per_peer;
+  // out_mode 5: the owner's staging buffer holds one [rows_per_peer, ldc] slab per sender; this
+  // GEMM writes slab `peer_slot` (plain 16-byte stores over NVLink, no atomics); the owner sums
+  // the slabs afterwards (two-phase reduce-scatter).
+  int peer_slot;
   // gather mode: ag_side 1 = rows of A, 2 = rows of B are assembled inside this launch
   int ag_side, ag_world, ag_rank, ag_copy_ctas;
   int ag_rows_per_rank;            // multiple of the tile extent on that side
@@ -128,6 +133,23 @@ __device__ __forceinline__ void gemm_store_slice(const GemmArgs& p, long long c_
       }
     } else {
       for (int i = 0; i < ncols; ++i) atomicAdd(reinterpret_cast<__nv_bfloat16*>(cp + i), __float2bfloat16(__uint_as_float(v[i])));
+    }
+  } else if (p.out_mode == 5) {
+    const int owner = (int)(grow / p.rows_per_peer);
+    const long long lrow = grow - (long long)owner * p.rows_per_peer + (long long)p.peer_slot * p.rows_per_peer;
+    bf16* cp = reinterpret_cast<bf16*>(p.peer_ptr[owner]) + lrow * p.ldc + col0;
+    if (ncols == 32 && ((((uintptr_t)cp) & 15) == 0)) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 q;
+        q.x = pack_bf16(__uint_as_float(v[i * 8 + 0]), __uint_as_float(v[i * 8 + 1]));
+        q.y = pack_bf16(__uint_as_float(v[i * 8 + 2]), __uint_as_float(v[i * 8 + 3]));
+        q.z = pack_bf16(__uint_as_float(v[i * 8 + 4]), __uint_as_float(v[i * 8 + 5]));
+        q.w = pack_bf16(__uint_as_float(v[i * 8 + 6]), __uint_as_float(v[i * 8 + 7]));
+        *reinterpret_cast<uint4*>(cp + i * 8) = q;
+      }
+    } else {
+      for (int i = 0; i < ncols; ++i) cp[i] = __float2bfloat16(__uint_as_float(v[i]));
     }
   } else if (p.out_mode == 3) {
               const int owner = (int)(grow / p.rows_per_peer);

@@ -299,7 +299,7 @@ static bool want_wide(const GemmArgs& g) {
   if (g.bias != nullptr && g.out_mode != 0) return false;   // its fp32 TMA epilogue adds no bias
   if (g_tune_wide == 1) return true;
   const long long tiles = (long long)((g.M + 511) / 512) * ((g.N + 255) / 256);
-  if (g.out_mode >= 2) return tiles * (g.K / 1024 > 0 ? g.K / 1024 : 1) >= 148;
+  if (g.out_mode >= 2 && g.out_mode <= 4) return tiles * (g.K / 1024 > 0 ? g.K / 1024 : 1) >= 148;
   return tiles >= 296;
 }
 
@@ -318,7 +318,7 @@ static int pick_gm(int K) {
 static void pick_splits(GemmArgs& g, int pairs) {
   g.k_splits = 1;
   g.k_per_split = g.K > 0 ? g.K : BK;
-  if (g.out_mode < 2 || g.K < 2048 || g_tune_splitk == 0 || pairs <= 0) return;
+  if (g.out_mode < 2 || g.out_mode > 4 || g.K < 2048 || g_tune_splitk == 0 || pairs <= 0) return;
   const int kblocks = (g.K + BK - 1) / BK;
   int best = 1;
   double best_eff = 0.0;
@@ -435,6 +435,8 @@ int ob_gemm_bf16_pair(const void* A, const void* B, void* C, const void* residua
 
 // Same contract as ob_gemm_bf16_peer_reduce (fp32 result rows added into the owning GPUs' buffers
 // with vector reductions over NVLink), computed by CTA pairs.
+// bf16_out: 0 fp32 reduction, 1 bf16 reduction, 2 + s = bf16 store into slab s of the owner's staging
+// buffer (first phase of the two-phase reduce-scatter; the owner sums the slabs afterwards).
 int ob_gemm_bf16_pair_peer_reduce(const void* A, const void* B, void* const* peer_ptrs, int world, int rows_per_peer,
                                   int M, int N, int K, long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
                                   int bf16_out, int* status, cudaStream_t stream) {
@@ -445,7 +447,8 @@ int ob_gemm_bf16_pair_peer_reduce(const void* A, const void* B, void* const* pee
   g.num_m_blocks = (M + 255) / 256;
   g.num_n_blocks = (N + kPairBN - 1) / kPairBN;
   g.total_tiles = g.num_m_blocks * g.num_n_blocks;
-  g.C = nullptr; g.ldc = ldc; g.out_mode = bf16_out ? 4 : 3;
+  g.C = nullptr; g.ldc = ldc; g.out_mode = bf16_out >= 2 ? 5 : bf16_out ? 4 : 3;
+  g.peer_slot = bf16_out >= 2 ? bf16_out - 2 : 0;
   for (int i = 0; i < world; ++i) g.peer_ptr[i] = (float*)peer_ptrs[i];
   g.rows_per_peer = rows_per_peer;
   g.status = status;

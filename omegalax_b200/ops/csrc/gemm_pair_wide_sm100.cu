@@ -447,7 +447,7 @@ static int launch_wide(const void* A, const void* B, GemmArgs args, long long a_
   // reduction slices (reducing output modes only): fewest that fill the last wave to 95 %
   args.k_splits = 1;
   args.k_per_split = args.K > 0 ? ((args.K + BK - 1) / BK) * BK : BK;
-  if (args.out_mode >= 2 && args.K >= 2048 && forced_splits != 0) {
+  if (args.out_mode >= 2 && args.out_mode <= 4 && args.K >= 2048 && forced_splits != 0) {
     const int kblocks = (args.K + BK - 1) / BK;
     int best = 1;
     double best_eff = 0.0;

@@ -457,7 +457,8 @@ int ob_gemm_bf16_peer_reduce(const void* A, const void* B, void* const* peer_ptr
   g.num_m_blocks = (M + BM - 1) / BM;
   g.num_n_blocks = (N + bn - 1) / bn;
   g.total_tiles = g.num_m_blocks * g.num_n_blocks;
-  g.C = nullptr; g.ldc = ldc; g.out_mode = bf16_out ? 4 : 3;
+  g.C = nullptr; g.ldc = ldc; g.out_mode = bf16_out >= 2 ? 5 : bf16_out ? 4 : 3;   // 2 + s: store into slab s
+  g.peer_slot = bf16_out >= 2 ? bf16_out - 2 : 0;
   for (int i = 0; i < world; ++i) g.peer_ptr[i] = (float*)peer_ptrs[i];
   g.rows_per_peer = rows_per_peer;
   g.status = status;

@@ -481,7 +481,7 @@ _ATTN_BWD_IMPL = {"impl": None}
 
 def _attn_bwd_dispatch(q, k, v, o, lse, do, cu_seqlens, max_seqlen, scale, causal):
     """dq, dk, dv of packed-row attention."""
-    if q.shape[-1] == 128 and os.environ.get("OMEGALAX_B200_ATTN_BWD", "sm100") == "sm100":
+    if q.shape[-1] in (128, 256) and os.environ.get("OMEGALAX_B200_ATTN_BWD", "sm100") == "sm100":
         return K.attn_bwd(q, k, v, o, lse, do, cu_seqlens, max_seqlen, scale, causal)
     if q.shape[-1] == 64 and os.environ.get("OMEGALAX_B200_ATTN_BWD", "sm100") == "sm100":
         # 64-wide heads (vision tower): run the 128-wide kernel on zero-padded heads.  The padding
@@ -530,7 +530,7 @@ class _FlashAttnFn(torch.autograd.Function):
 
 def flash_attention(q, k, v, cu_seqlens, max_seqlen: int, *, scale: float, causal: bool, tag=None):
     """Packed-row attention.  q [N,H,Kd]; k, v [N,G,Kd]; cu_seqlens int32 [B+1]."""
-    if use_kernels(q) and q.shape[-1] in (64, 128):
+    if use_kernels(q) and q.shape[-1] in (64, 128, 256):
         key, pre = _stash_lookup(tag)
         o, lse = _FlashAttnFn.apply(q, k, v, cu_seqlens, int(max_seqlen), float(scale), bool(causal), pre)
         _stash_store(key, (o, lse))

@@ -119,10 +119,12 @@ def gemm(a, b, *, a_mn: bool = False, b_mn: bool = False, out=None, out_dtype=bf
 
 
 def gemm_peer_reduce(a, b, peer_ptrs, rows_per_peer: int, ldc: int, *, a_mn=False, b_mn=False, bf16_out=False,
-                     pair: bool | None = None):
+                     pair: bool | None = None, slot: int | None = None):
     """GEMM whose result rows are added into buffers owned by other GPUs (``peer_ptrs[r]`` holds
     rows [r*rows_per_peer, (r+1)*rows_per_peer)): fp32 buffers by default (gradient shards), bf16
-    buffers with ``bf16_out`` (activations: half the NVLink bytes, bf16 accumulation)."""
+    buffers with ``bf16_out`` (activations: half the NVLink bytes, bf16 accumulation).  With
+    ``slot`` nothing is reduced: the bf16 rows are stored into slab ``slot`` of the owner's staging
+    buffer ([senders, rows_per_peer, ldc]) and the owner sums the slabs with ``slab_sum``."""
     import ctypes
 
     a = _row_major_2d(a)
@@ -136,7 +138,14 @@ def gemm_peer_reduce(a, b, peer_ptrs, rows_per_peer: int, ldc: int, *, a_mn=Fals
     name = "ob_gemm_bf16_pair_peer_reduce" if pair else "ob_gemm_bf16_peer_reduce"
     _call(name, a.data_ptr(), b.data_ptr(), ctypes.cast(arr, ctypes.c_void_p),
           len(peer_ptrs), rows_per_peer, M, N, K, a.stride(0), b.stride(0), ldc, int(a_mn),
-          int(b_mn), int(bf16_out), st.data_ptr(), lib.stream_ptr())
+          int(b_mn), (2 + int(slot)) if slot is not None else int(bf16_out), st.data_ptr(), lib.stream_ptr())
+
+
+def slab_sum(staging, slots: int, out, residual=None):
+    """out = sum of the ``slots`` equal slabs of ``staging`` (+ residual): bf16, fp32 accumulation."""
+    _call("ob_slab_sum", staging.data_ptr(), int(slots), out.numel(), lib.ptr(residual), out.data_ptr(),
+          lib.stream_ptr())
+    return out
 
 
 def ag_copy_ctas(M: int, N: int, Kd: int, total_bytes: float) -> int:

@@ -40,6 +40,7 @@ _SIGS = {
     "ob_attn_bwd": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, L, I, I, I, L, L, L, L, L, L, L, F, I, P, P],
     "ob_decode_append": [P, P, P, P, P, P, P, I, I, P, P, P, L, I, I, I, I, F, F, I, P],
     "ob_decode_attn": [P, P, P, P, P, I, I, I, I, I, I, I, F, P, P, P, P],
+    "ob_slab_sum": [P, I, L, P, P, P],
     "ob_ep_push": [P, I, P, P, P, P, P, L, I, P],
     "ob_ep_pull": [P, I, P, P, P, P, P, P, L, I, I, P],
     "ob_gated_rmsnorm_fwd": [P, P, P, P, P, L, I, F, P],
@@ -94,7 +95,7 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
+    if (not LIB_PATH.exists() or _DEBUG_LIB):     # the debug variant is re-checked against the sources every time
         if os.environ.get("OMEGALAX_B200_NO_BUILD") != "1":
             from . import build as _build
 
@@ -203,6 +204,8 @@ def scratch(name: str, shape, dtype, device) -> torch.Tensor:
     """Uninitialised work buffer for a kernel.  In debug mode it sits between two guard bands."""
     if not debug_enabled():
         return torch.empty(shape, dtype=dtype, device=device)
+    import weakref
+
     n = 1
     for d in (shape if isinstance(shape, (tuple, list, torch.Size)) else (shape,)):
         n *= int(d)
@@ -212,21 +215,32 @@ def scratch(name: str, shape, dtype, device) -> torch.Tensor:
     raw_bytes = raw.view(torch.uint8)
     raw_bytes[: pad * esz].fill_(_CANARY_BYTE)
     raw_bytes[(pad + n) * esz:].fill_(_CANARY_BYTE)
-    _guards.append((name, raw_bytes, pad * esz, (pad + n) * esz))
-    return raw[pad:pad + n].view(shape)
+    payload = raw[pad:pad + n].view(shape)
+    # the registry must not keep the buffer alive: it remembers the payload weakly and finds the
+    # guard bands again through the payload's storage
+    _guards.append((name, weakref.ref(payload), pad * esz, (pad + n) * esz))
+    return payload
+
+
+def _guard_bytes(payload: torch.Tensor) -> torch.Tensor:
+    return torch.empty(0, dtype=torch.uint8, device=payload.device).set_(payload.untyped_storage())
 
 
 def check_canaries() -> None:
-    """Raise if any guard band around a ``scratch()`` buffer was overwritten; drops buffers that
-    nobody references any more."""
+    """Raise if any guard band around a live ``scratch()`` buffer was overwritten."""
     alive = []
-    for name, raw_bytes, head, tail in _guards:
-        if not (bool((raw_bytes[:head] == _CANARY_BYTE).all()) and bool((raw_bytes[tail:] == _CANARY_BYTE).all())):
-            side = "before" if not bool((raw_bytes[:head] == _CANARY_BYTE).all()) else "after"
-            raise KernelError(f"scratch buffer '{name}': bytes {side} the buffer were overwritten")
-        if raw_bytes._use_count() > 1 if hasattr(raw_bytes, "_use_count") else True:
-            alive.append((name, raw_bytes, head, tail))
-    _guards[:] = alive[-256:]
+    for name, ref, head, tail in _guards:
+        payload = ref()
+        if payload is None:
+            continue
+        raw_bytes = _guard_bytes(payload)
+        before_ok = bool((raw_bytes[:head] == _CANARY_BYTE).all())
+        after_ok = bool((raw_bytes[tail:] == _CANARY_BYTE).all())
+        if not (before_ok and after_ok):
+            raise KernelError(f"scratch buffer '{name}': bytes {'after' if before_ok else 'before'} the buffer "
+                              "were overwritten")
+        alive.append((name, ref, head, tail))
+    _guards[:] = alive
 
 
 def call(name: str, *args) -> None:

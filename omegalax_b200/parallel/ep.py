@@ -34,6 +34,7 @@ def _register():
     P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
     lib.register("ob_ep_push", [P, I, P, P, P, P, P, L, I, P])
     lib.register("ob_ep_pull", [P, I, P, P, P, P, P, P, L, I, I, P])
+    lib.register("ob_ep_publish_counts", [P, I, I, P, I, P])
 
 
 _register()
@@ -84,18 +85,28 @@ def build_plan(idx, E: int, W: int, rank: int, group, capacity: int) -> Plan:
     return p
 
 
-def build_plan_device(idx, E: int, W: int, rank: int, group, capacity: int, overflow_flag, src_tok) -> Plan:
-    """Same plan as ``build_plan`` from three kernel launches and one count all-gather.  Rows of
-    one sender inside an expert segment are assigned by an atomic cursor, so their order (not
-    their set) can differ from run to run."""
+def build_plan_device(idx, E: int, W: int, rank: int, group, capacity: int, overflow_flag, src_tok, ep=None) -> Plan:
+    """Same plan as ``build_plan`` from kernel launches only.  With ``ep`` (an ``ExpertParallel``)
+    every rank stores its counts into all peers' count tables and the device barrier that follows
+    doubles as the "previous contents consumed" barrier of the dispatch; without it the counts are
+    all-gathered by the process group.  Rows of one sender inside an expert segment are assigned by
+    an atomic cursor, so their order (not their set) can differ from run to run."""
     M, k = idx.shape
     dev = idx.device
     idx32 = idx.reshape(-1).to(torch.int32)
-    allc = torch.empty(W, E, dtype=torch.int32, device=dev)
-    mine = allc[rank]
-    lib.call("ob_moe_count", idx32.data_ptr(), mine.data_ptr(), idx32.numel(), E, lib.stream_ptr())
-    if W > 1:
-        dist.all_gather_into_tensor(allc.view(-1), mine.clone(), group=group)
+    lib.check_index("expert ids", idx32, E)
+    if ep is not None and W > 1:
+        allc = ep.count_table
+        mine = ep.my_counts
+        lib.call("ob_moe_count", idx32.data_ptr(), mine.data_ptr(), idx32.numel(), E, lib.stream_ptr())
+        lib.call("ob_ep_publish_counts", ep.count_buf.ptr_table(), W, rank, mine.data_ptr(), E, lib.stream_ptr())
+        ep.barrier()      # counts of every rank have landed; every rank is done with the previous exchange
+    else:
+        allc = torch.empty(W, E, dtype=torch.int32, device=dev)
+        mine = allc[rank]
+        lib.call("ob_moe_count", idx32.data_ptr(), mine.data_ptr(), idx32.numel(), E, lib.stream_ptr())
+        if W > 1:
+            dist.all_gather_into_tensor(allc.view(-1), mine.clone(), group=group)
     p = Plan()
     scratch = torch.empty(2 * E, dtype=torch.int32, device=dev)
     p.offsets_local = torch.empty(E // W + 1, dtype=torch.int32, device=dev)
@@ -128,6 +139,10 @@ class ExpertParallel:
         self.buf_gout = symm.SymmetricBuffer(nbytes, group)
         self.buf_gin = symm.SymmetricBuffer(nbytes, group)
         self.barrier = symm.DeviceBarrier(group)
+        # per-expert pair counts of every rank, written by the peers themselves (no host collective)
+        self.count_buf = symm.SymmetricBuffer(max(self.W * self.E * 4, 256), group)
+        self.count_table = self.count_buf.view(torch.int32, self.W * self.E).view(self.W, self.E)
+        self.my_counts = torch.zeros(self.E, dtype=torch.int32, device="cuda")
         self.dtype = dtype
         self.overflow_flag = torch.zeros(1, dtype=torch.int32, device="cuda")
         self._src_tok = {}
@@ -168,7 +183,10 @@ class ExpertParallel:
         if st is None:
             st = torch.arange(idx.shape[0], device=idx.device, dtype=torch.int32).repeat_interleave(idx.shape[1])
             self._src_tok[key] = st
-        plan = build_plan_device(idx, self.E, self.W, self.rank, self.group, self.capacity, self.overflow_flag, st)
+        if not self.reuse_buffers:
+            self.local(self.buf_in).zero_()       # padding rows start from zero (before the barrier inside the plan)
+        plan = build_plan_device(idx, self.E, self.W, self.rank, self.group, self.capacity, self.overflow_flag, st,
+                                 ep=self)
         xp = _Dispatch.apply(x.contiguous(), self, plan)
         out = self.local(self.buf_out) if self.reuse_buffers else None
         yp = moe_ops.expert_mlp_permuted(xp, w_gate_up_local, w_down_local, plan.offsets_local, out)
@@ -178,9 +196,8 @@ class ExpertParallel:
 class _Dispatch(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, ep: ExpertParallel, plan: Plan):
-        if not ep.reuse_buffers:
-            ep.local(ep.buf_in).zero_()       # padding rows start from zero
-        ep.barrier()                          # every rank is done with the previous contents
+        if ep.W == 1:
+            ep.barrier()                      # (with peers the plan's count exchange has already synchronised)
         ep.push(ep.buf_in, x, plan)
         ep.barrier()                          # all rows have landed
         ctx.ep, ctx.plan = ep, plan

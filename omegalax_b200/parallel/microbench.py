@@ -5,7 +5,10 @@
 
 For each fused path the device time (CUDA events, max over ranks, after warm-up) is reported
 next to its unfused counterpart (own pull / NCCL collective + GEMM) and to its roofline: the
-slower of FLOPs / measured GEMM peak and bytes that must cross NVLink / 770 GB/s per direction.
+slower of FLOPs / measured GEMM peak and bytes that must cross NVLink / measured link rate.  The
+GEMM peak is read from ``MEASURED_PEAKS.json`` at the repository root (``bf16_tflops``; 1590 if the
+file is absent) and the link rate is measured at start-up with a peer copy of 256 MB from the next
+rank (``--link-gbs`` overrides it).
 """
 from __future__ import annotations
 
@@ -21,8 +24,35 @@ from ..ops import lib
 from . import symm
 
 bf16 = torch.bfloat16
-GEMM_PEAK_TFLOPS = 1613.6     # measured cuBLAS bf16 burst on this pool
-LINK_GBS = 770.0              # measured peer copy bandwidth per direction
+GEMM_PEAK_TFLOPS = 1590.0     # replaced by MEASURED_PEAKS.json when present (see _load_peaks)
+LINK_GBS = 900.0              # nominal NVLink 5 per direction; replaced by the start-up measurement
+
+
+def _load_peaks():
+    global GEMM_PEAK_TFLOPS
+    here = os.path.dirname(os.path.abspath(__file__))
+    path = os.path.join(os.path.dirname(os.path.dirname(here)), "MEASURED_PEAKS.json")
+    try:
+        GEMM_PEAK_TFLOPS = float(json.load(open(path)).get("bf16_tflops", GEMM_PEAK_TFLOPS))
+        return "measured"
+    except Exception:
+        return "fallback"
+
+
+def _measure_link(rank, world, dev, nbytes=256 << 20, iters=5):
+    """Per-direction peer bandwidth: every rank pulls ``nbytes`` from its right neighbour with the
+    pull all-gather kernel (all links busy at once, as in the collectives timed below)."""
+    global LINK_GBS
+    if world < 2:
+        return LINK_GBS
+    src = symm.SymmetricBuffer(nbytes)
+    src.view(torch.uint8, nbytes).fill_(1)
+    dst = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    tab = symm.make_copy_segments([((rank + 1) % world, 0, 0, nbytes)], dev)
+    ms = _time(lambda: symm.allgather_pull(src, dst, tab), iters, 2, world)
+    LINK_GBS = nbytes / ms / 1e6
+    return LINK_GBS
+
 
 
 def _time(fn, iters, warmup, world):
@@ -61,6 +91,7 @@ def main():
     ap.add_argument("--ffn", type=int, default=24576, help="full output width of the gathered projections")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--link-gbs", type=float, default=None, help="link rate for the rooflines instead of measuring it")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     W = int(os.environ.get("WORLD_SIZE", "1"))
@@ -70,6 +101,16 @@ def main():
     if W > 1:
         dist.init_process_group("nccl", device_id=dev)
     bar = symm.DeviceBarrier() if W > 1 else (lambda: None)
+    which = _load_peaks()
+    global LINK_GBS
+    if a.link_gbs:
+        LINK_GBS = a.link_gbs
+    else:
+        _measure_link(rank, W, dev)
+    if rank == 0:
+        print(json.dumps({"gemm_peak_tflops": GEMM_PEAK_TFLOPS, "gemm_peak_source": which,
+                          "link_gbs_per_direction": round(LINK_GBS, 1),
+                          "link_source": "--link-gbs" if a.link_gbs else ("measured" if W > 1 else "nominal")}), flush=True)
     M, D, Fw = a.tokens, a.hidden, a.ffn
     m, f = M // W, Fw // W
     torch.manual_seed(rank)

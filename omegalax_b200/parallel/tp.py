@@ -17,6 +17,8 @@ has no sequence parallelism.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -172,21 +174,48 @@ def reduce_scatter_rows(y, tp: TPContext | None):
 
 
 # ----------------------------------------------------------------------------- fused row-parallel
+def _rs_mode(tp: "TPContext") -> str:
+    """How a GEMM's result rows reach their owners.  "atomic": the epilogue adds every tile into the
+    owner's rows with vector bf16 reductions (one pass, best for two ranks); "staged": the epilogue
+    stores the tile into the sender's slab of the owner's staging buffer with plain 16-byte stores
+    and the owner sums the slabs (wider groups, where the reduction rate of the atomics, not the
+    link, was the bound: 0.09 of the NVLink roofline at eight ranks)."""
+    forced = os.environ.get("OMEGALAX_B200_TP_RS")
+    if forced in ("atomic", "staged"):
+        return forced
+    return "atomic" if tp.size <= 2 else "staged"
+
+
+def _gemm_reduce_scatter(x, w, tp: "TPContext", *, b_mn: bool, residual=None):
+    """rows [r*m, (r+1)*m) of x @ op(w), summed over the tensor-parallel ranks, land on rank r
+    (+ residual): GEMM and reduce-scatter over NVLink peer memory, no library collective."""
+    M = x.shape[0]
+    N = w.shape[1] if b_mn else w.shape[0]
+    m = M // tp.size
+    if _rs_mode(tp) == "atomic":
+        buf = tp.rs_buffer(m, N)
+        acc = buf.view(torch.bfloat16, m * N)
+        acc.zero_()
+        tp._barrier()                                   # every owner has cleared its rows
+        K.gemm_peer_reduce(x, w, buf.peer_ptr_list(0), m, N, b_mn=b_mn, bf16_out=True)
+        tp._barrier()                                   # all contributions have landed
+        return acc.view(m, N) + residual if residual is not None else acc.view(m, N).clone()
+    buf = tp.rs_buffer(m * tp.size, N)                  # one [m, N] slab per sender
+    tp._barrier()                                       # every owner has summed the previous call's slabs
+    K.gemm_peer_reduce(x, w, buf.peer_ptr_list(0), m, N, b_mn=b_mn, slot=tp.rank)
+    tp._barrier()                                       # all slabs have landed
+    out = torch.empty(m, N, dtype=torch.bfloat16, device=x.device)
+    res = residual.contiguous() if residual is not None else None
+    return K.slab_sum(buf.view(torch.bfloat16, tp.size * m * N), tp.size, out, res)
+
+
 class _RowParallelLinearFn(torch.autograd.Function):
     """y[M/tp, N] = reduce_scatter_rows(x[M, K/tp] @ w[N, K/tp]^T) (+ residual), with the
     reduce-scatter performed by the GEMM epilogue over NVLink peer memory."""
 
     @staticmethod
     def forward(ctx, x, w, residual, tp: TPContext):
-        M, N = x.shape[0], w.shape[0]
-        m = M // tp.size
-        buf = tp.rs_buffer(m, N)
-        acc = buf.view(torch.bfloat16, m * N)
-        acc.zero_()
-        tp._barrier()                                   # every owner has cleared its rows
-        K.gemm_peer_reduce(x, w, buf.peer_ptr_list(0), m, N, bf16_out=True)
-        tp._barrier()                                   # all contributions have landed
-        y = acc.view(m, N) + residual if residual is not None else acc.view(m, N).clone()
+        y = _gemm_reduce_scatter(x, w, tp, b_mn=False, residual=residual)
         ctx.save_for_backward(x, w)
         ctx.tp, ctx.w_ref, ctx.has_res = tp, w, residual is not None
         return y
@@ -236,16 +265,7 @@ class _ColumnParallelLinearFn(torch.autograd.Function):
         dy = dy.contiguous()
         M, Kd = full.shape
         m = M // tp.size
-        if tp.size <= 2:
-            buf = tp.rs_buffer(m, Kd)
-            acc = buf.view(torch.bfloat16, m * Kd)
-            acc.zero_()
-            tp._barrier()
-            K.gemm_peer_reduce(dy, w, buf.peer_ptr_list(0), m, Kd, b_mn=True, bf16_out=True)   # dx rows land on their owners
-            tp._barrier()
-            dx = acc.view(m, Kd).clone()
-        else:
-            dx = _rs_rows(K.gemm(dy, w, b_mn=True), tp)
+        dx = _gemm_reduce_scatter(dy, w, tp, b_mn=True)     # dx rows land on their owners
         mg = getattr(ctx.w_ref, "main_grad", None)
         pg = getattr(ctx.w_ref, "peer_grad", None)
         dw = None
@@ -277,10 +297,10 @@ def row_parallel_linear(x_cols, w_local, residual_local, tp: TPContext | None):
         y = Fn.linear(x_cols, w_local).contiguous()
         dist.all_reduce(y, group=tp.group)
         return y if residual_local is None else y + residual_local
-    # The epilogue reduction uses vector atomics over NVLink: measured 0.9x the time of GEMM + NCCL
-    # reduce-scatter at tp = 2, but several times slower at tp = 8 (atomic rate, not link rate),
-    # so wider groups take the unfused path.
-    if tp.transport == "p2p" and tp.size <= 2 and Fn.use_kernels(x_cols) and w_local.dtype == torch.bfloat16:
+    # GEMM and reduce-scatter over peer memory at every group size: vector atomics in the epilogue for
+    # two ranks, per-sender slabs summed by the owner for wider groups (see _rs_mode).
+    if tp.transport == "p2p" and Fn.use_kernels(x_cols) and w_local.dtype == torch.bfloat16 \
+            and w_local.shape[0] % 8 == 0 and os.environ.get("OMEGALAX_B200_TP_RS") != "nccl":
         return _RowParallelLinearFn.apply(x_cols.contiguous(), w_local, residual_local, tp)
     y = reduce_scatter_rows(Fn.linear(x_cols, w_local), tp)
     return y if residual_local is None else y + residual_local

@@ -58,6 +58,9 @@ class TrainConfig:
     grad_accum_steps: int = 1
     print_every: int = 1
     remat_policy: str = "full"
+    ep_size: int = 0             # expert parallelism: 0 automatic (over the shard group when experts and peer
+                                 # memory exist), 1 off (experts travel like any sharded parameter), else the
+                                 # shard-group size it must equal
 
 
 def init_model(cfg_or_model_id, rng: int = 0, *, tp_size=None, fsdp_size=None, dp_size=None, **kw):
@@ -80,11 +83,15 @@ def build_optimizer(model, train_cfg: TrainConfig, *, device=None, init_from_mod
         tp_lib.set_current(tp_lib.TPContext(tp_group))
     if init_from_model is None:
         init_from_model = not any(p.device.type == "meta" for p in model.parameters())
+    shard_world = dist.get_world_size(group) if group is not None else 1
+    if train_cfg.ep_size not in (0, 1, shard_world):
+        raise ValueError(f"ep_size={train_cfg.ep_size}: experts are sharded over the shard group "
+                         f"({shard_world} ranks here); use 0 (automatic), 1 (off) or {shard_world}")
     return MixedPrecisionOptimizer(
         model, device=device, shard_group=group, lr=train_cfg.learning_rate, weight_decay=train_cfg.weight_decay,
         max_grad_norm=train_cfg.max_grad_norm, remat=train_cfg.remat_policy, seed=train_cfg.seed,
         init_from_model=init_from_model, lr_schedule=sched, grad_accum_steps=train_cfg.grad_accum_steps,
-        tp_group=tp_group)
+        tp_group=tp_group, expert_parallel=train_cfg.ep_size != 1)
 
 
 def tp_rows_loss(model, rows, tok, mask, count):

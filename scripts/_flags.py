@@ -52,7 +52,8 @@ def common_train_flags(p: Flags, *, batch_size: int, workers: int, worker_buffer
     p.define("tp_size", 1)
     p.define("fsdp_size", 1)
     p.define("dp_size", 1)
-    p.define("ep_size", 1, "expert-parallel size (experts sharded over the data ranks)")
+    p.define("ep_size", 0, "expert parallelism: 0 automatic (experts sharded over the fsdp ranks when peer memory is "
+                           "available), 1 off, or the fsdp size")
     p.define("remat_policy", "full", "full | selective | save:<tag,tag> (tags: qkv, attn, gate_up) | none")
     p.define("save_dir", None, type=str)
     p.define("jax_cache_dir", None, "accepted for command-line compatibility; unused", type=str)

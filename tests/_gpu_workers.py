@@ -68,7 +68,7 @@ def symm_primitives(rank, world, port, out_path):
     dist.destroy_process_group()
 
 
-def fsdp_train_gpu(rank, world, port, comm, steps, out_path):
+def fsdp_train_gpu(rank, world, port, comm, steps, out_path, gbatch=4):
     _init(rank, world, port)
     import dataclasses
 
@@ -82,15 +82,15 @@ def fsdp_train_gpu(rank, world, port, comm, steps, out_path):
     mesh = mesh_lib.ensure_mesh(tp_size=1, fsdp_size=world, dp_size=1)
     cfg = dataclasses.replace(text_api.resolve_config("Qwen/Qwen3-8B"), num_layers=3, emb_dim=512, mlp_dim=1024,
                               num_heads=4, num_kv_heads=2, vocab_size=4096)
-    tcfg = trainer.TrainConfig(seed=0, batch_size=4, seq_len=256, num_steps=100, learning_rate=1e-3, max_grad_norm=1.0)
+    tcfg = trainer.TrainConfig(seed=0, batch_size=gbatch, seq_len=256, num_steps=100, learning_rate=1e-3, max_grad_norm=1.0)
     model, cfg = trainer.init_model(cfg, 0, tp_size=1, fsdp_size=world, dp_size=1, meta=True)
     group = mesh.group("shard")
     opt = MixedPrecisionOptimizer(model, device=torch.device("cuda", rank), shard_group=group, lr=1e-3,
                                   weight_decay=0.01, max_grad_norm=1.0, seed=0, comm=comm)
     step = trainer.make_sft_train_step(cfg)
     g = torch.Generator().manual_seed(0)
-    tok = torch.randint(1, cfg.vocab_size, (4, 256), generator=g, dtype=torch.int32)
-    per = 4 // world
+    tok = torch.randint(1, cfg.vocab_size, (gbatch, 256), generator=g, dtype=torch.int32)
+    per = gbatch // world
     sl = slice(rank * per, (rank + 1) * per)
     batch = {"token_ids_BT": tok[sl].cuda(), "attention_mask_BT": torch.ones(per, 256, dtype=torch.int32).cuda(),
              "loss_mask_BT": torch.ones(per, 256, dtype=torch.int32).cuda()}
@@ -105,7 +105,7 @@ def fsdp_train_gpu(rank, world, port, comm, steps, out_path):
     dist.destroy_process_group()
 
 
-def ep_train_gpu(rank, world, port, steps, out_path):
+def ep_train_gpu(rank, world, port, steps, out_path, gbatch=4):
     """Qwen3-MoE with experts sharded over the ranks (expert parallel) vs the same run on one GPU."""
     _init(rank, world, port)
     import dataclasses
@@ -126,8 +126,8 @@ def ep_train_gpu(rank, world, port, steps, out_path):
                                   weight_decay=0.01, max_grad_norm=1.0, seed=0)
     step = trainer.make_sft_train_step(cfg)
     g = torch.Generator().manual_seed(0)
-    tok = torch.randint(1, cfg.vocab_size, (4, 256), generator=g, dtype=torch.int32)
-    per = 4 // world
+    tok = torch.randint(1, cfg.vocab_size, (gbatch, 256), generator=g, dtype=torch.int32)
+    per = gbatch // world
     sl = slice(rank * per, (rank + 1) * per)
     batch = {"token_ids_BT": tok[sl].cuda(), "attention_mask_BT": torch.ones(per, 256, dtype=torch.int32).cuda(),
              "loss_mask_BT": torch.ones(per, 256, dtype=torch.int32).cuda()}
@@ -143,9 +143,11 @@ def ep_train_gpu(rank, world, port, steps, out_path):
     dist.destroy_process_group()
 
 
-def tp_train_gpu(rank, world, port, tp, steps, out_path):
+def tp_train_gpu(rank, world, port, tp, steps, out_path, rs_mode=None):
     """Tensor parallel (sequence-parallel activations, peer-memory transport) vs one GPU, same weights."""
     _init(rank, world, port)
+    if rs_mode:
+        os.environ["OMEGALAX_B200_TP_RS"] = rs_mode
     import dataclasses
 
     from omegalax_b200.models.qwen3.model import Qwen3

@@ -113,6 +113,34 @@ def test_gemm_pair_unaligned_output_pitch_and_local_peer_reduce(wide):
     _assert_gemm_close(torch.cat(halves, 0), 2 * ref, K)
 
 
+@pytest.mark.parametrize("kernel", ["single", "pair", "wide"])
+def test_gemm_two_phase_reduce_scatter_on_local_slabs(kernel):
+    """First phase: two "senders" (two GEMMs with different operands) store their bf16 result rows
+    into their own slab of each owner's staging buffer; second phase: every owner sums its slabs
+    and adds the residual.  Both owners are buffers of this GPU."""
+    from omegalax_b200.ops import kernels as Kn, lib
+    torch.manual_seed(18)
+    M, N, K, W = 1024, 520, 320, 2
+    m = M // W
+    xs = [torch.randn(M, K, device=_dev()).to(bf16) for _ in range(W)]
+    ws = [torch.randn(N, K, device=_dev()).to(bf16) for _ in range(W)]
+    res = torch.randn(M, N, device=_dev()).to(bf16)
+    stage = [torch.full((W, m, N), float("nan"), device=_dev(), dtype=bf16) for _ in range(W)]   # per owner
+    lib.gemm_pair_tune(-1, 1 if kernel == "wide" else 0, -1)
+    try:
+        for sender in range(W):
+            Kn.gemm_peer_reduce(xs[sender], ws[sender], [t.data_ptr() for t in stage], m, N, slot=sender,
+                                pair=kernel != "single")
+        outs = [Kn.slab_sum(stage[o], W, torch.empty(m, N, device=_dev(), dtype=bf16), res[o * m:(o + 1) * m].contiguous())
+                for o in range(W)]
+        _check(lib)
+    finally:
+        lib.gemm_pair_tune(-1, -1, -1)
+    parts = [(xs[s].float() @ ws[s].float().t()).to(bf16).float() for s in range(W)]    # each slab is rounded to bf16
+    ref = parts[0] + parts[1] + res.float()
+    torch.testing.assert_close(torch.cat(outs, 0).float(), ref, rtol=2.0 ** -7, atol=0.15)
+
+
 @pytest.mark.parametrize("gm,wide", [(2, 0), (16, 0), (3, 1), (16, 1)])
 def test_gemm_pair_raster_knob(gm, wide):
     from omegalax_b200.ops import kernels as Kn, lib
@@ -761,6 +789,33 @@ def test_gather_scatter_gelu_kernels():
     _check(lib)
 
 
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("lens", [[512], [200, 456, 77], [128, 1]])
+def test_attention_head_dim_256_forward_backward(causal, lens):
+    """256-wide heads (Qwen3.5 gated attention, 16 query heads per kv head): forward (two warpgroups
+    share the output by head-dim halves) and backward (one pass per head-dim half) on packed
+    sequences of uneven length, per element against fp32 PyTorch."""
+    from omegalax_b200.ops import functional as Fn, reference as R, lib
+    torch.manual_seed(17)
+    dev = _dev()
+    H, G, HD = 4, 2, 256
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=dev, dtype=torch.int32)
+    N = sum(lens)
+    q = torch.randn(N, H, HD, device=dev).to(bf16).requires_grad_(True)
+    k = torch.randn(N, G, HD, device=dev).to(bf16).requires_grad_(True)
+    v = torch.randn(N, G, HD, device=dev).to(bf16).requires_grad_(True)
+    o = Fn.flash_attention(q, k, v, cu, max(lens), scale=HD ** -0.5, causal=causal)
+    do = torch.randn_like(o)
+    o.backward(do)
+    _check(lib)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = R.attention_varlen(qr, kr, vr, cu, causal=causal, scale=HD ** -0.5)
+    ref.backward(do.float())
+    torch.testing.assert_close(o.float(), ref, rtol=2.0 ** -6, atol=2e-2)
+    for got, want in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
+        torch.testing.assert_close(got.float(), want, rtol=2.0 ** -5, atol=3e-2 * float(want.abs().max()))
+
+
 def test_attention_backward_head_dim_64_varlen():
     """64-wide heads (vision tower): non-causal packed sequences of different lengths."""
     from omegalax_b200.ops import functional as Fn, reference as R, lib
@@ -812,3 +867,47 @@ def test_gemm_cta_pair_epilogues():
     Kn.gemm(a, b, out=acc, accumulate=True, pair=True)
     assert _rel_err(acc, ref + 1.0) < 1e-2
     _check(lib)
+
+
+_DEBUG_SCRIPT = r"""
+import torch
+from omegalax_b200.ops import kernels as K, lib
+assert lib.debug_enabled() and str(lib.LIB_PATH).endswith("_debug.so")
+dev = torch.device("cuda", 0)
+table = torch.randn(64, 32, device=dev).to(torch.bfloat16)
+try:
+    K.embedding_fwd(torch.tensor([1, 64], device=dev), table)
+    raise SystemExit("bad id was not caught")
+except IndexError as e:
+    assert "value 64 at flat position 1" in str(e), e
+a = torch.randn(300, 136, device=dev).to(torch.bfloat16)
+b = torch.randn(520, 136, device=dev).to(torch.bfloat16)
+for pair in (False, True):
+    out = K.gemm(a, b, pair=pair)
+    torch.testing.assert_close(out.float(), a.float() @ b.float().t(), rtol=2 ** -7, atol=0.1)
+N, H, G, Kd = 256, 2, 1, 128
+q = torch.randn(N, H, Kd, device=dev).to(torch.bfloat16)
+k = torch.randn(N, G, Kd, device=dev).to(torch.bfloat16)
+v = torch.randn(N, G, Kd, device=dev).to(torch.bfloat16)
+cu = torch.tensor([0, N], device=dev, dtype=torch.int32)
+o, lse = K.attn_fwd(q, k, v, cu, N, Kd ** -0.5, True)
+K.attn_bwd(q, k, v, o, lse, torch.randn_like(o), cu, N, Kd ** -0.5, True)
+torch.cuda.synchronize()
+lib.check_status()          # guard bands around the attention scratch intact, no store outside an output
+print("debug ok")
+"""
+
+
+def test_debug_mode_catches_bad_indices_on_the_host_and_keeps_kernels_correct():
+    """OMEGALAX_B200_DEBUG=1 in a fresh process: the debug library is built and loaded, an
+    out-of-range token id raises on the host before any launch, kernels still agree with PyTorch
+    and the scratch guard bands stay intact."""
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, OMEGALAX_B200_DEBUG="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-c", _DEBUG_SCRIPT], env=env, cwd=root, capture_output=True, text=True,
+                         timeout=600)
+    assert res.returncode == 0 and "debug ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]

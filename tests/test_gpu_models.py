@@ -44,7 +44,9 @@ def _configs():
                                  linear_num_key_heads=2, linear_num_value_heads=4, num_experts=32,
                                  num_experts_per_tok=4, moe_intermediate_size=128,
                                  shared_expert_intermediate_size=128, mrope_section=(8, 4, 4))
-    return {"qwen3-dense": dense, "qwen3-moe": moe, "qwen3.5-hybrid-moe": hybrid}
+    # the published Qwen3.5 configs use 256-wide attention heads (two-pass backward, split-output forward)
+    hybrid256 = dataclasses.replace(hybrid, head_dim=256, mrope_section=(16, 8, 8))
+    return {"qwen3-dense": dense, "qwen3-moe": moe, "qwen3.5-hybrid-moe": hybrid, "qwen3.5-hybrid-moe-hd256": hybrid256}
 
 
 def _run(model, cfg, tok, reference: bool):
@@ -66,7 +68,7 @@ def _run(model, cfg, tok, reference: bool):
     return logits.detach().float(), grads
 
 
-@pytest.mark.parametrize("name", ["qwen3-dense", "qwen3-moe", "qwen3.5-hybrid-moe"])
+@pytest.mark.parametrize("name", ["qwen3-dense", "qwen3-moe", "qwen3.5-hybrid-moe", "qwen3.5-hybrid-moe-hd256"])
 def test_kernels_match_reference_ops(name, monkeypatch):
     from omegalax_b200.ops import lib
     from omegalax_b200.text import api as text_api

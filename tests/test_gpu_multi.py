@@ -84,11 +84,14 @@ def test_expert_parallel_two_gpus_matches_one(tmp_path):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_tensor_parallel_two_gpus_matches_one(tmp_path):
+@pytest.mark.parametrize("rs_mode", ["atomic", "staged"])
+def test_tensor_parallel_two_gpus_matches_one(tmp_path, rs_mode):
+    """rs_mode: how the row-parallel GEMMs reduce-scatter over peer memory -- vector atomics in the
+    epilogue (the choice for two ranks) or per-sender slabs summed by the owner (wider groups)."""
     from tests import _gpu_workers as W
 
     mp.spawn(W.tp_train_gpu, args=(1, _port(), 1, 4, str(tmp_path / "one.pt")), nprocs=1, join=True)
-    mp.spawn(W.tp_train_gpu, args=(2, _port(), 2, 4, str(tmp_path / "two.pt")), nprocs=2, join=True)
+    mp.spawn(W.tp_train_gpu, args=(2, _port(), 2, 4, str(tmp_path / "two.pt"), rs_mode), nprocs=2, join=True)
     a, b = torch.load(tmp_path / "one.pt"), torch.load(tmp_path / "two.pt")
     assert b["transport"] == "p2p"
     assert b["vocab_parallel"]          # untied head: split over the vocabulary, CE statistics combined over tp
@@ -112,3 +115,50 @@ def test_tensor_parallel_other_families_two_gpus_match_one(tmp_path, family):
     assert all(l == l for l in b["losses"]), b["losses"]
     assert b["losses"][-1] < b["losses"][0]
     assert a["losses"] == pytest.approx(b["losses"], rel=4e-2, abs=4e-2)
+
+
+def _many():
+    """Largest tested world: every GPU of the box up to 8 (4 at least, else the 2-GPU tests above cover it)."""
+    n = min(8, _ngpu())
+    return n if n >= 4 else 0
+
+
+@pytest.mark.skipif(_many() == 0, reason="needs 4 or more GPUs")
+def test_fsdp_all_gpus_matches_one(tmp_path):
+    """FSDP over every GPU of the box (peer-memory gathers, weight-gradient GEMMs reducing into the
+    owners' shards over NVLink) follows the single-GPU loss curve on the same global batch."""
+    from tests import _gpu_workers as W
+
+    n = _many()
+    mp.spawn(W.fsdp_train_gpu, args=(1, _port(), "auto", 4, str(tmp_path / "one.pt"), 8), nprocs=1, join=True)
+    mp.spawn(W.fsdp_train_gpu, args=(n, _port(), "p2p", 4, str(tmp_path / "all.pt"), 8), nprocs=n, join=True)
+    a, b = torch.load(tmp_path / "one.pt"), torch.load(tmp_path / "all.pt")
+    assert b["losses"][-1] < b["losses"][0]
+    assert a["losses"] == pytest.approx(b["losses"], rel=3e-2, abs=3e-2)
+    assert a["grad_norm"] == pytest.approx(b["grad_norm"], rel=5e-2)
+
+
+@pytest.mark.skipif(_many() == 0, reason="needs 4 or more GPUs")
+def test_expert_parallel_all_gpus_matches_one(tmp_path):
+    from tests import _gpu_workers as W
+
+    n = _many()
+    mp.spawn(W.ep_train_gpu, args=(1, _port(), 4, str(tmp_path / "one.pt"), 8), nprocs=1, join=True)
+    mp.spawn(W.ep_train_gpu, args=(n, _port(), 4, str(tmp_path / "all.pt"), 8), nprocs=n, join=True)
+    a, b = torch.load(tmp_path / "one.pt"), torch.load(tmp_path / "all.pt")
+    assert b["used_ep"] and not a["used_ep"]
+    assert b["losses"][-1] < b["losses"][0]
+    assert a["losses"] == pytest.approx(b["losses"], rel=3e-2, abs=3e-2)
+
+
+@pytest.mark.skipif(_many() == 0, reason="needs 4 or more GPUs")
+def test_tensor_parallel_times_fsdp_all_gpus_matches_one(tmp_path):
+    """tp 2 x fsdp (n/2): sequence-parallel tensor parallelism inside FSDP groups against one GPU."""
+    from tests import _gpu_workers as W
+
+    n = _many()
+    mp.spawn(W.tp_train_gpu, args=(1, _port(), 1, 4, str(tmp_path / "one.pt")), nprocs=1, join=True)
+    mp.spawn(W.tp_train_gpu, args=(n, _port(), 2, 4, str(tmp_path / "all.pt")), nprocs=n, join=True)
+    a, b = torch.load(tmp_path / "one.pt"), torch.load(tmp_path / "all.pt")
+    assert b["losses"][-1] < b["losses"][0]
+    assert a["losses"] == pytest.approx(b["losses"], rel=3e-2, abs=3e-2)

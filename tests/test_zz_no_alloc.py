@@ -45,17 +45,43 @@ def test_noalloc_matches_regular_entry_point_twice():
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated(dev)
+        # memory_allocated only sees PyTorch's caching allocator; the driver's free-byte count would
+        # also move if the entry point called cudaMalloc / cudaFree itself (checked from the second
+        # call on: the first call on a device may load the kernel image)
+        free_before = torch.cuda.mem_get_info(dev)[0]
         rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(), dq.data_ptr(),
                 dk.data_ptr(), dv.data_ptr(), cu.data_ptr(), B, T, N, H, G, HD, q.stride(0), k.stride(0), v.stride(0),
                 o.stride(0), do.stride(0), dk.stride(0), dv.stride(0), scale, 1, st.data_ptr(),
                 torch.cuda.current_stream().cuda_stream)
         assert rc == 0
         torch.cuda.synchronize()
+        free_after = torch.cuda.mem_get_info(dev)[0]
         lib.check_status()
         assert torch.cuda.memory_allocated(dev) == before
+        if trial > 0:
+            assert free_after == free_before
         for got, want in ((dq, ref_dq), (dk, ref_dk), (dv, ref_dv)):
             err = float((got.float() - want.float()).abs().max() / (want.float().abs().max() + 1e-6))
             assert err < 3e-2, err
+        # and against the fp32 PyTorch definition of the same gradients
+        from omegalax_b200.ops import reference as R
+
+        qr, kr, vr = (t.float().view(B, T, -1, HD).requires_grad_(True) for t in (q, k, v))
+        R.attention(qr, kr, vr, causal=True, scale=scale).backward(do.float().view(B, T, H, HD))
+        for got, want in ((dq, qr.grad.reshape(N, H, HD)), (dk, kr.grad.reshape(N, G, HD)), (dv, vr.grad.reshape(N, G, HD))):
+            err = float((got.float() - want).abs().max() / (want.abs().max() + 1e-6))
+            assert err < 3e-2, err
+
+
+def test_noalloc_rejects_other_head_widths():
+    from omegalax_b200.ops import lib
+
+    fn = lib.load().ob_attn_bwd_noalloc
+    _sig(fn, 10)
+    # the built-in scratch is laid out for 128-wide heads: 256 is refused before anything is launched
+    rc = fn(None, None, None, None, None, None, None, None, None, None, 1, 128, 128, 2, 1, 256, 512, 256, 256,
+            512, 512, 256, 256, 0.1, 1, None, None)
+    assert rc == 6005
 
 
 def test_noalloc_rejects_problems_beyond_its_scratch():
