@@ -61,7 +61,7 @@ class Attention(nn.Module):
             o = R.attention(q.reshape(B, T, self.H, self.Kd), k.reshape(B, T, self.G, self.Kd),
                             v.reshape(B, T, self.G, self.Kd), causal=True, scale=self.scale,
                             k_start=ks).reshape(M, self.H, self.Kd)
-        o = o * torch.sigmoid(gate.to(o.dtype))
+        o = Fn.sigmoid_gate(o, gate)
         if tp is not None:
             return tp_lib.row_parallel_linear(o.reshape(M, self.H * self.Kd), self.o_proj.weight, residual, tp)
         return self.o_proj(o.reshape(M, self.H * self.Kd), residual=residual)

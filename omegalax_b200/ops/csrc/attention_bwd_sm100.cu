@@ -217,21 +217,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         issue_A(0);
         umma_commit(&sp_full[0]);
       }
+      // A(it+1): S^T / dP^T of the next step.  With a Q/dO ring it is issued ahead of B(it) so that it
+      // runs while the threads are in E(it); with a single stage (256-wide heads) its operands can
+      // only be loaded once B(it) has released the stage, so it follows B(it).
+      auto issue_next = [&](int it) -> bool {
+        if (it + 1 >= n) return true;
+        const int nx = it + 1;
+        if (nx >= 2) {  // the S^T buffer of step nx still holds dQ^T of step nx-2
+          if (!mbar_wait(&dq_read[nx & 1], ((nx - 2) >> 1) & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY))
+            return false;
+        }
+        if (!mbar_wait(&qdo_full[nx % kQStages], (nx / kQStages) & 1, abort_flag, p.status, OB_ERR_WAIT_FULL))
+          return false;
+        tc_fence_after();
+        issue_A(nx);
+        umma_commit(&sp_full[nx & 1]);
+        return true;
+      };
       for (int it = 0; it < n && ok; ++it) {
         const int bb = it & 1;
-        if (it + 1 < n) {
-          const int nx = it + 1;
-          if (nx >= 2) {  // the S^T buffer of step nx still holds dQ^T of step nx-2
-            ok = mbar_wait(&dq_read[nx & 1], ((nx - 2) >> 1) & 1, abort_flag, p.status,
-                           OB_ERR_WAIT_TMEM_EMPTY);
-            if (!ok) break;
-          }
-          ok = mbar_wait(&qdo_full[nx % kQStages], (nx / kQStages) & 1, abort_flag, p.status,
-                         OB_ERR_WAIT_FULL);
+        if (kQStages > 1) {
+          ok = issue_next(it);
           if (!ok) break;
-          tc_fence_after();
-          issue_A(nx);
-          umma_commit(&sp_full[nx & 1]);
         }
         ok = mbar_wait(&ds_ready[bb], (it >> 1) & 1, abort_flag, p.status, OB_ERR_WAIT_MISC);
         if (!ok) break;
@@ -258,6 +265,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                   make_smem_desc(dsa + k * 2048, 16384, 1024), idesc_q, k > 0 ? 1u : 0u);
         umma_commit(&dq_full[bb]);
         umma_commit(&qdo_empty[s]);
+        if (kQStages == 1) ok = issue_next(it);
       }
       if (ok) umma_commit(dkv_full);
     }

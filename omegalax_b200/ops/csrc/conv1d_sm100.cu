@@ -71,80 +71,83 @@ __global__ void conv1d_silu_fwd_kernel(const bf16* __restrict__ x, const bf16* _
 }
 
 // dpre[t] = dy[t] * silu'(pre[t]);  dx[t] = sum_j w[j] * dpre[t + KW-1-j];  dw[j] += dpre[t] * x[t-KW+1+j]
+// One thread walks a run of kRun time steps of two channels with sliding windows: x[t-3 .. t+3] and
+// dpre[t .. t+3] live in registers, so a step costs one x load, one dy load, one sigmoid and one
+// store (the first version re-derived every dpre four times: 24 loads and 4 sigmoids per step).
+// A warp covers 64 consecutive channels (128 bytes) per access.
 template <int KW>
 __global__ void conv1d_silu_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                        const bf16* __restrict__ dy, bf16* __restrict__ dx,
                                        float* __restrict__ dw, int B, int T, int C) {
-  const int cv = C >> 3;
+  static_assert(KW == 4, "window arithmetic below is written for four taps");
+  constexpr int CPT = 2;
+  const int cv = C / CPT;
   const int runs = (T + kRun - 1) / kRun;
   const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (idx >= (long long)B * runs * cv) return;
-  const int c8 = (int)(idx % cv);
+  const int cg = (int)(idx % cv);
   const int run = (int)((idx / cv) % runs);
   const int b = (int)(idx / ((long long)cv * runs));
-  const int c0 = c8 * 8;
-  float wv[8][KW], dwv[8][KW];
+  const int c0 = cg * CPT;
+  float wv[CPT][KW], dwv[CPT][KW];
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < CPT; ++i)
 #pragma unroll
     for (int j = 0; j < KW; ++j) { wv[i][j] = __bfloat162float(w[(c0 + i) * KW + j]); dwv[i][j] = 0.f; }
   const int t0 = run * kRun, t1 = min(T, t0 + kRun);
-  auto xat = [&](int t, float* f) {
-    if (t >= 0 && t < T) load8(x + ((long long)b * T + t) * C + c0, f);
-    else
-#pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = 0.f;
-  };
-  // dpre at time t (zero outside [0,T)); recomputes the pre-activation from x
-  auto dpre_at = [&](int t, float* f) {
-    if (t < 0 || t >= T) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = 0.f;
-      return;
-    }
-    float g[8];
-    load8(dy + ((long long)b * T + t) * C + c0, g);
-    float pre[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) pre[i] = 0.f;
-#pragma unroll
-    for (int j = 0; j < KW; ++j) {
-      float xv[8];
-      xat(t - KW + 1 + j, xv);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) pre[i] += wv[i][j] * xv[i];
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float s = 1.f / (1.f + __expf(-pre[i]));
-      f[i] = g[i] * s * (1.f + pre[i] * (1.f - s));
+  const bf16* xb = x + (long long)b * T * C + c0;
+  const bf16* gb = dy + (long long)b * T * C + c0;
+  auto ld2 = [&](const bf16* base, int t, float* f) {   // two channels of time step t, zero outside [0, T)
+    if (t >= 0 && t < T) {
+      const float2 v = unpack_bf16(*reinterpret_cast<const uint32_t*>(base + (long long)t * C));
+      f[0] = v.x; f[1] = v.y;
+    } else {
+      f[0] = f[1] = 0.f;
     }
   };
+  float xw[7][CPT];   // x[t-3 .. t+3]
+  float dp[4][CPT];   // dpre[t .. t+3]
+#pragma unroll
+  for (int o = 0; o < 6; ++o) ld2(xb, t0 - 3 + o, xw[o]);
+  auto dpre_from = [&](const float (*xs)[CPT], int t, float* out) {   // xs[0..3] = x[t-3 .. t]
+    float g[CPT];
+    ld2(gb, t, g);
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) {
+      float pre = 0.f;
+#pragma unroll
+      for (int j = 0; j < KW; ++j) pre += wv[i][j] * xs[j][i];
+      const float sg = 1.f / (1.f + __expf(-pre));
+      out[i] = (t < T) ? g[i] * sg * (1.f + pre * (1.f - sg)) : 0.f;
+    }
+  };
+#pragma unroll
+  for (int o = 0; o < 3; ++o) dpre_from(&xw[o], t0 + o, dp[o]);
   for (int t = t0; t < t1; ++t) {
-    float acc[8];
+    ld2(xb, t + 3, xw[6]);
+    dpre_from(&xw[3], t + 3, dp[3]);
+    float acc[CPT];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int i = 0; i < CPT; ++i) {
+      acc[i] = 0.f;
 #pragma unroll
-    for (int j = 0; j < KW; ++j) {
-      float d[8];
-      dpre_at(t + KW - 1 - j, d);
+      for (int j = 0; j < KW; ++j) acc[i] += wv[i][j] * dp[KW - 1 - j][i];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += wv[i][j] * d[i];
-      if (j == KW - 1) {  // d is dpre[t]: weight gradient contributions of this time step
-#pragma unroll
-        for (int jj = 0; jj < KW; ++jj) {
-          float xv[8];
-          xat(t - KW + 1 + jj, xv);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) dwv[i][jj] += d[i] * xv[i];
-        }
-      }
+      for (int jj = 0; jj < KW; ++jj) dwv[i][jj] += dp[0][i] * xw[jj][i];   // x[t-3+jj]
     }
-    store8(dx + ((long long)b * T + t) * C + c0, acc);
+    *reinterpret_cast<uint32_t*>(dx + ((long long)b * T + t) * C + c0) = pack_bf16(acc[0], acc[1]);
+#pragma unroll
+    for (int o = 0; o < 6; ++o)
+#pragma unroll
+      for (int i = 0; i < CPT; ++i) xw[o][i] = xw[o + 1][i];
+#pragma unroll
+    for (int o = 0; o < 3; ++o)
+#pragma unroll
+      for (int i = 0; i < CPT; ++i) dp[o][i] = dp[o + 1][i];
   }
   if (dw) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < CPT; ++i)
 #pragma unroll
       for (int j = 0; j < KW; ++j) atomicAdd(dw + (c0 + i) * KW + j, dwv[i][j]);
   }
@@ -170,7 +173,7 @@ int ob_conv1d_silu_bwd(const void* x, const void* w, const void* dy, void* dx, f
                        int KW, cudaStream_t s) {
   if (C % 8) return 6001;
   if (KW != 4) return 6005;
-  long long n = (long long)B * ((T + kRun - 1) / kRun) * (C / 8);
+  long long n = (long long)B * ((T + kRun - 1) / kRun) * (C / 2);
   if (n <= 0) return 0;
   conv1d_silu_bwd_kernel<4><<<(unsigned)((n + 127) / 128), 128, 0, s>>>((const bf16*)x, (const bf16*)w, (const bf16*)dy,
                                                                         (bf16*)dx, dw, B, T, C);

@@ -110,39 +110,52 @@ decode_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
 #pragma unroll
     for (int c = 0; c < C; ++c) o[r][c] = 0.f;
   }
-  for (int s0 = k_lo; s0 < k_hi; s0 += NW) {   // uniform trip count: the shuffles below need all lanes
-    const int s = s0 + sub;
-    const bool ok = s < k_hi;
-    float kv[C], vv[C];
+  // Four key rows per half-warp and iteration: the block-table lookups and the eight 16-byte row
+  // loads of an iteration are issued back to back before any arithmetic, so a thread keeps 128
+  // bytes in flight (the kernel is latency bound otherwise: one K and one V row per round trip).
+  constexpr int U = 4;
+  for (int s0 = k_lo; s0 < k_hi; s0 += NW * U) {   // uniform trip count: the shuffles below need all lanes
+    uint4 ku[U], vu[U];
+    bool okv[U];
 #pragma unroll
-    for (int c = 0; c < C; ++c) { kv[c] = 0.f; vv[c] = 0.f; }
-    if (ok) {
-      const int page = block_table[(long long)b * max_blocks + s / page_size];
-      const long long row = (((long long)page * page_size + s % page_size) * G + g) * HD + hl * C;
-      const uint4 ku = *reinterpret_cast<const uint4*>(k_pages + row);
-      const uint4 vu = *reinterpret_cast<const uint4*>(v_pages + row);
-      const uint32_t kw[4] = {ku.x, ku.y, ku.z, ku.w}, vw[4] = {vu.x, vu.y, vu.z, vu.w};
+    for (int u = 0; u < U; ++u) {
+      const int s = s0 + u * NW + sub;
+      okv[u] = s < k_hi;
+      ku[u] = make_uint4(0, 0, 0, 0);
+      vu[u] = make_uint4(0, 0, 0, 0);
+      if (okv[u]) {
+        const int page = __ldg(block_table + (long long)b * max_blocks + s / page_size);
+        const long long row = (((long long)page * page_size + s % page_size) * G + g) * HD + hl * C;
+        ku[u] = *reinterpret_cast<const uint4*>(k_pages + row);
+        vu[u] = *reinterpret_cast<const uint4*>(v_pages + row);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const bool ok = okv[u];
+      float kv[C], vv[C];
+      const uint32_t kw[4] = {ku[u].x, ku[u].y, ku[u].z, ku[u].w}, vw[4] = {vu[u].x, vu[u].y, vu[u].z, vu[u].w};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const float2 a = unpack_bf16(kw[c]), d = unpack_bf16(vw[c]);
         kv[2 * c] = a.x; kv[2 * c + 1] = a.y;
         vv[2 * c] = d.x; vv[2 * c + 1] = d.y;
       }
-    }
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      float d = 0.f;
+      for (int r = 0; r < R; ++r) {
+        float d = 0.f;
 #pragma unroll
-      for (int c = 0; c < C; ++c) d = fmaf(qv[r][c], kv[c], d);
+        for (int c = 0; c < C; ++c) d = fmaf(qv[r][c], kv[c], d);
 #pragma unroll
-      for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
-      if (ok) {
-        const float mn = fmaxf(m[r], d);
-        const float a = __expf(m[r] - mn), p = __expf(d - mn);
-        l[r] = l[r] * a + p;
+        for (int x = 8; x > 0; x >>= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
+        if (ok) {
+          const float mn = fmaxf(m[r], d);
+          const float a = __expf(m[r] - mn), p = __expf(d - mn);
+          l[r] = l[r] * a + p;
 #pragma unroll
-        for (int c = 0; c < C; ++c) o[r][c] = o[r][c] * a + p * vv[c];
-        m[r] = mn;
+          for (int c = 0; c < C; ++c) o[r][c] = o[r][c] * a + p * vv[c];
+          m[r] = mn;
+        }
       }
     }
   }

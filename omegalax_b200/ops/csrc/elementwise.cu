@@ -468,6 +468,59 @@ __global__ void qknorm_rope_bwd128_kernel(const bf16* __restrict__ qkv, const bf
   }
 }
 
+// ------------------------------------------------------------------ sigmoid output gate
+// out[m,h,:] = o[m,h,:] * sigmoid(gate[m,h,:]) (gated attention of Qwen3.5: every query head of the
+// fused projection is followed by a gate head, so the gate is a strided view of that buffer).
+// o / out / dout / d_o / d_gate are dense [M, H, Kd]; the gate has its own row and head strides.
+__global__ void sigmoid_gate_fwd_kernel(const bf16* __restrict__ o, const bf16* __restrict__ gate, bf16* __restrict__ out,
+                                        long long M, int H, int Kd, long long g_row, long long g_head) {
+  const int kv = Kd >> 3;
+  const long long total = M * H * kv;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(t % kv);
+    const long long mh = t / kv;
+    const int h = (int)(mh % H);
+    const long long m = mh / H;
+    const uint4 a = reinterpret_cast<const uint4*>(o)[t];
+    const uint4 gq = *reinterpret_cast<const uint4*>(gate + m * g_row + h * g_head + c * 8);
+    const uint32_t au[4] = {a.x, a.y, a.z, a.w}, gu[4] = {gq.x, gq.y, gq.z, gq.w};
+    uint32_t r[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = unpack_bf16(au[j]), g = unpack_bf16(gu[j]);
+      r[j] = pack_bf16(x.x / (1.f + __expf(-g.x)), x.y / (1.f + __expf(-g.y)));
+    }
+    reinterpret_cast<uint4*>(out)[t] = make_uint4(r[0], r[1], r[2], r[3]);
+  }
+}
+
+__global__ void sigmoid_gate_bwd_kernel(const bf16* __restrict__ o, const bf16* __restrict__ gate,
+                                        const bf16* __restrict__ dout, bf16* __restrict__ d_o, bf16* __restrict__ d_gate,
+                                        long long M, int H, int Kd, long long g_row, long long g_head) {
+  const int kv = Kd >> 3;
+  const long long total = M * H * kv;
+  for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(t % kv);
+    const long long mh = t / kv;
+    const int h = (int)(mh % H);
+    const long long m = mh / H;
+    const uint4 a = reinterpret_cast<const uint4*>(o)[t];
+    const uint4 d = reinterpret_cast<const uint4*>(dout)[t];
+    const uint4 gq = *reinterpret_cast<const uint4*>(gate + m * g_row + h * g_head + c * 8);
+    const uint32_t au[4] = {a.x, a.y, a.z, a.w}, du[4] = {d.x, d.y, d.z, d.w}, gu[4] = {gq.x, gq.y, gq.z, gq.w};
+    uint32_t ro[4], rg[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = unpack_bf16(au[j]), dy = unpack_bf16(du[j]), g = unpack_bf16(gu[j]);
+      const float s0 = 1.f / (1.f + __expf(-g.x)), s1 = 1.f / (1.f + __expf(-g.y));
+      ro[j] = pack_bf16(dy.x * s0, dy.y * s1);
+      rg[j] = pack_bf16(dy.x * x.x * s0 * (1.f - s0), dy.y * x.y * s1 * (1.f - s1));
+    }
+    reinterpret_cast<uint4*>(d_o)[t] = make_uint4(ro[0], ro[1], ro[2], ro[3]);
+    reinterpret_cast<uint4*>(d_gate)[t] = make_uint4(rg[0], rg[1], rg[2], rg[3]);
+  }
+}
+
 // ------------------------------------------------------------------ softmax cross-entropy
 // One CTA per row of a bf16 logits chunk [R, V] (pitch ld).  Adds mask*nll to loss_sum and
 // overwrites the row with dlogits = (softmax - onehot) * mask * (*grad_scale).
@@ -915,6 +968,26 @@ int ob_ce_fwd_bwd(void* logits, long long ld, long long R, int V, const int* tar
   if (R <= 0) return 0;
   ce_fwd_bwd_kernel<<<(unsigned)R, 512, 0, s>>>((bf16*)logits, ld, V, targets, mask, grad_scale,
                                                 loss_sum, lse_out, write_grad);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_sigmoid_gate_fwd(const void* o, const void* gate, void* out, long long M, int H, int Kd, long long g_row,
+                        long long g_head, cudaStream_t s) {
+  if (Kd % 8 || g_row % 8 || g_head % 8 || (((uintptr_t)gate | (uintptr_t)o | (uintptr_t)out) & 15)) return 6001;
+  if (M <= 0) return 0;
+  sigmoid_gate_fwd_kernel<<<grid_for(M * H * (Kd / 8), 256), 256, 0, s>>>((const bf16*)o, (const bf16*)gate, (bf16*)out,
+                                                                          M, H, Kd, g_row, g_head);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_sigmoid_gate_bwd(const void* o, const void* gate, const void* dout, void* d_o, void* d_gate, long long M, int H,
+                        int Kd, long long g_row, long long g_head, cudaStream_t s) {
+  if (Kd % 8 || g_row % 8 || g_head % 8 || (((uintptr_t)gate | (uintptr_t)o | (uintptr_t)dout) & 15)) return 6001;
+  if (M <= 0) return 0;
+  sigmoid_gate_bwd_kernel<<<grid_for(M * H * (Kd / 8), 256), 256, 0, s>>>(
+      (const bf16*)o, (const bf16*)gate, (const bf16*)dout, (bf16*)d_o, (bf16*)d_gate, M, H, Kd, g_row, g_head);
   OB_CHECK_LAUNCH();
   return 0;
 }

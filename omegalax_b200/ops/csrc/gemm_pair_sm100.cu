@@ -291,13 +291,18 @@ static int g_tune_gm = -1, g_tune_wide = -1, g_tune_splitk = -1;
 int launch_pair_wide(const void* A, const void* B, const GemmArgs& g, long long lda, long long ldb, int a_mn, int b_mn,
                      int gm, int forced_splits, cudaStream_t stream);
 
-// The 512 x 256 tile kernel serves plain GEMMs without a fused residual whose tile count fills
-// the SM pairs at least twice over (or whose reduction can be split to that effect).
+// The 512 x 256 tile kernel serves plain GEMMs into this GPU's memory without a fused residual whose
+// tile count fills the SM pairs at least twice over (or whose reduction can be split to that
+// effect).  Outputs that travel over NVLink from the epilogue (peer reductions / peer stores) stay on
+// the 256 x 256 kernel: a CTA's fair share of the link is a few GB/s, so draining a tile takes tens
+// of microseconds, which the double-buffered accumulators of that kernel hide behind the next tile's
+// main loop and the single accumulator set of the wide kernel would not.
 static bool want_wide(const GemmArgs& g) {
   if (g_tune_wide == 0) return false;
   if (g.residual != nullptr || g.ag_side != 0 || g.mode != 0) return false;
   if (g.bias != nullptr && g.out_mode != 0) return false;   // its fp32 TMA epilogue adds no bias
   if (g_tune_wide == 1) return true;
+  if (g.out_mode >= 3) return false;
   const long long tiles = (long long)((g.M + 511) / 512) * ((g.N + 255) / 256);
   if (g.out_mode >= 2 && g.out_mode <= 4) return tiles * (g.K / 1024 > 0 ? g.K / 1024 : 1) >= 148;
   return tiles >= 296;

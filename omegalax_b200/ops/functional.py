@@ -475,6 +475,28 @@ def qk_norm_rope(qkv, qw, kw, sin, cos, H: int, G: int, Kd: int, rot: int | None
     return q, k, v, gate
 
 
+# ----------------------------------------------------------------------------- sigmoid output gate
+class _SigmoidGateFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, o, gate):
+        ctx.save_for_backward(o, gate)
+        return K.sigmoid_gate_fwd(o, gate)
+
+    @staticmethod
+    def backward(ctx, dout):
+        o, gate = ctx.saved_tensors
+        return K.sigmoid_gate_bwd(o, gate, dout.contiguous())
+
+
+def sigmoid_gate(o, gate):
+    """o * sigmoid(gate) (output gate of the Qwen3.5 attention, reference
+    omegalax/models/qwen3_5/attention.py:122); ``gate`` may be a strided view of the fused projection."""
+    if use_kernels(o) and o.dim() == 3 and o.is_contiguous() and gate.dtype == bf16 and gate.stride(2) == 1 \
+            and o.shape[2] % 8 == 0 and gate.stride(0) % 8 == 0 and gate.stride(1) % 8 == 0:
+        return _SigmoidGateFn.apply(o, gate)
+    return o * torch.sigmoid(gate.to(o.dtype))
+
+
 # ----------------------------------------------------------------------------- attention
 _ATTN_BWD_IMPL = {"impl": None}
 

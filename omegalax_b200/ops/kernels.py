@@ -338,6 +338,23 @@ def ce_fwd_bwd(logits, targets, mask, grad_scale, loss_sum, write_grad=True, lse
           int(write_grad), lib.stream_ptr())
 
 
+def sigmoid_gate_fwd(o, gate):
+    """o [M,H,Kd] dense, gate [M,H,Kd] (any row / head stride, unit inner stride): o * sigmoid(gate)."""
+    M, H, Kd = o.shape
+    out = torch.empty_like(o)
+    _call("ob_sigmoid_gate_fwd", o.data_ptr(), gate.data_ptr(), out.data_ptr(), M, H, Kd, gate.stride(0), gate.stride(1),
+          lib.stream_ptr())
+    return out
+
+
+def sigmoid_gate_bwd(o, gate, dout):
+    M, H, Kd = o.shape
+    d_o, d_gate = torch.empty_like(o), torch.empty_like(o)
+    _call("ob_sigmoid_gate_bwd", o.data_ptr(), gate.data_ptr(), dout.data_ptr(), d_o.data_ptr(), d_gate.data_ptr(), M, H,
+          Kd, gate.stride(0), gate.stride(1), lib.stream_ptr())
+    return d_o, d_gate
+
+
 def ce_finish(stats, tgt_logit, mask, loss_sum, lse_out):
     """Row log-sum-exp and masked loss from the statistics the logits GEMM wrote (``gemm(..., ce=)``)."""
     R, n_tiles = stats.shape[0], stats.shape[1]

@@ -55,6 +55,8 @@ _SIGS = {
     "ob_gather4_bwd": [P, P, P, P, L, I, P],
     "ob_gelu_tanh_fwd": [P, P, L, P],
     "ob_gelu_tanh_bwd": [P, P, P, L, P],
+    "ob_sigmoid_gate_fwd": [P, P, P, L, I, I, L, L, P],
+    "ob_sigmoid_gate_bwd": [P, P, P, P, P, L, I, I, L, L, P],
     "ob_ce_finish": [P, I, P, P, P, P, L, P],
     "ob_ce_vp_stats": [P, L, I, L, I, P, P, P, P, P],
     "ob_ce_vp_grad": [P, L, I, L, I, P, P, P, P, P],

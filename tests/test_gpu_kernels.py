@@ -816,6 +816,25 @@ def test_attention_head_dim_256_forward_backward(causal, lens):
         torch.testing.assert_close(got.float(), want, rtol=2.0 ** -5, atol=3e-2 * float(want.abs().max()))
 
 
+def test_sigmoid_gate_on_a_strided_gate_view():
+    from omegalax_b200.ops import functional as Fn, lib
+    torch.manual_seed(19)
+    M, H, Kd = 300, 4, 256
+    fused = torch.randn(M, H * 2 * Kd + 64, device=_dev()).to(bf16).requires_grad_(True)   # [q | gate] per head, then more
+    o = torch.randn(M, H, Kd, device=_dev()).to(bf16).requires_grad_(True)
+    gate = fused[:, : H * 2 * Kd].view(M, H, 2, Kd)[:, :, 1]
+    y = Fn.sigmoid_gate(o, gate)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    _check(lib)
+    fr, orf = fused.detach().float().requires_grad_(True), o.detach().float().requires_grad_(True)
+    yr = orf * torch.sigmoid(fr[:, : H * 2 * Kd].view(M, H, 2, Kd)[:, :, 1])
+    yr.backward(dy.float())
+    torch.testing.assert_close(y.float(), yr, rtol=2.0 ** -7, atol=1e-2)
+    torch.testing.assert_close(o.grad.float(), orf.grad, rtol=2.0 ** -6, atol=1e-2)
+    torch.testing.assert_close(fused.grad.float(), fr.grad, rtol=2.0 ** -6, atol=1e-2)
+
+
 def test_attention_backward_head_dim_64_varlen():
     """64-wide heads (vision tower): non-causal packed sequences of different lengths."""
     from omegalax_b200.ops import functional as Fn, reference as R, lib
