@@ -8,11 +8,13 @@
 //   warps 8-11  softmax warpgroup 1
 // Per KV tile j and warpgroup w:  S_w = Q_w K_j^T lands in TMEM; the warpgroup reads its
 // row, applies scale / mask / online softmax and writes P_w as packed bf16 back into the
-// first half of the S_w columns; the issuing thread then runs O_w = P_w V_j with P_w as
-// the TMEM A operand and V_j as an MN-major shared-memory B operand into a scratch
-// accumulator, which the warpgroup folds into its fp32 register accumulator with the
-// online-softmax rescale.  While warpgroup 0 does softmax, the tensor core works for
-// warpgroup 1 and vice versa.
+// first half of the S_w columns; the issuing thread then runs O_w += P_w V_j with P_w as
+// the TMEM A operand and V_j as an MN-major shared-memory B operand.  O_w stays in TMEM for
+// the whole walk: the exponentials are taken against a reference maximum that is only moved
+// (and O_w rescaled, a TMEM load / multiply / store by the warp that owns the rows) when a
+// row's running maximum has grown by more than 2^8 since the reference was set, so in the
+// common case a KV tile costs the warpgroup no accumulator traffic at all and it never waits
+// for P V.  While warpgroup 0 does softmax, the tensor core works for warpgroup 1 and vice versa.
 //
 // Sequences are packed: row r of sequence b is global row cu_seqlens[b] + r.  Q/O are
 // [rows, H, HD]; K/V are [rows, G, HD] with arbitrary row pitch (they may be slices of a
@@ -160,13 +162,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                   make_smem_desc(ka + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int w, int s) {
+      auto issue_pv = [&](int w, int s, bool first) {
         const uint32_t va = smem_u32(smem + L::kVOff + s * L::kTile);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           // 16 keys per step: A = 8 packed TMEM columns, B advances 16 rows of 128 bytes
           umma_ts(tmem_base + 256 + w * 128, tmem_base + w * 128 + k * 8,
-                  make_smem_desc(va + k * 2048, 16384, 1024), idesc_o, k > 0 ? 1u : 0u);
+                  make_smem_desc(va + k * 2048, 16384, 1024), idesc_o, (!first || k > 0) ? 1u : 0u);
         }
       };
       bool ok = mbar_wait(&k_full[0], 0, abort_flag, p.status, OB_ERR_WAIT_FULL);
@@ -190,7 +192,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           ok = mbar_wait(&p_ready[w], j & 1, abort_flag, p.status, OB_ERR_WAIT_MISC);
           if (!ok) break;
           tc_fence_after();
-          issue_pv(w, s);
+          issue_pv(w, s, j == 0);
           umma_commit(&o_full[w]);
           if (j + 1 < n_w[w]) {
             if (!k_next_ready) {
@@ -219,10 +221,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_addr + w * 128;
     const uint32_t o_addr = tmem_base + lane_addr + 256 + w * 128;
-    float o_acc[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    // m_ref: the maximum the exponentials (and O in TMEM) are currently taken against; m_run: the true
+    // running maximum.  They differ by at most kRescaleLog2 between rescales.
+    constexpr float kRescaleLog2 = 8.f;
+    float m_ref = -INFINITY, m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     const int nj = n_w[w];
     for (int j = 0; j < nj && ok; ++j) {
@@ -248,10 +250,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
         }
       }
-      const float m_new = fmaxf(m_run, mx * p.scale_log2);
-      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = fast_exp2(m_run - m_safe);
-      m_run = m_new;
+      m_run = fmaxf(m_run, mx * p.scale_log2);
+      // move the reference (and rescale O) only when some row of this warp needs it; the TMEM
+      // accesses below are warp-wide, so the decision is too
+      const bool mine = (m_run > m_ref + kRescaleLog2) || (m_ref == -INFINITY && m_run != -INFINITY);
+      if (__any_sync(0xffffffffu, mine)) {
+        const float m_new = mine ? m_run : m_ref;
+        const float alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);   // 1 for rows that keep their reference
+        if (j > 0) {   // O holds the products of the previous tiles: wait for the last of them, then rescale
+          ok = mbar_wait(&o_full[w], (j - 1) & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld32(o_addr + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st32(o_addr + c * 32, v);
+          }
+          tmem_st_wait();
+        }
+        l_run *= alpha;
+        m_ref = m_new;
+      }
+      const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
       float lsum = 0.f;
       // pass 2: probabilities, packed bf16 into the first 64 columns of S
 #pragma unroll 1
@@ -274,24 +298,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_st16(s_addr + c * 16, pk);
       }
       tmem_st_wait();
-      l_run = l_run * alpha + lsum;
+      l_run += lsum;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[w]);
-      // fold P V into the register accumulator
-      ok = mbar_wait(&o_full[w], j & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL);
-      if (!ok) break;
-      tc_fence_after();
+    }
+    // the accumulator of the last tile
+    float o_acc[HD];
+    if (ok && nj > 0) {
+      ok = mbar_wait(&o_full[w], (nj - 1) & 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL);
+      if (ok) {
+        tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(o_addr + c * 32, v);
-        tmem_ld_wait();
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(o_addr + c * 32, v);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(v[i]);
+          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = __uint_as_float(v[i]);
+        }
+        tc_fence_before();
       }
-      tc_fence_before();
     }
     if (ok && nj > 0 && qpos < seqlen) {
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -306,9 +333,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         q.w = pack_bf16(o_acc[i * 8 + 6] * inv_l, o_acc[i * 8 + 7] * inv_l);
         *reinterpret_cast<uint4*>(op + i * 8) = q;
       }
-      if (p.lse)
+      if (p.lse)   // l_run is relative to the reference maximum
         p.lse[(long long)h * p.total_rows + grow] =
-            m_run * 0.6931471805599453f + logf(fmaxf(l_run, 1e-30f));
+            m_ref * 0.6931471805599453f + logf(fmaxf(l_run, 1e-30f));
     }
   }
 

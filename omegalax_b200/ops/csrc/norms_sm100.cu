@@ -251,17 +251,28 @@ __global__ void layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __
       }
     }
   }
+  // per-column sums: first over the 8 warps of the CTA in shared memory (one 256-column slice at a
+  // time), then one atomic per column and CTA (the earlier version issued one per column and warp:
+  // 2 x D x 8 x CTAs atomics on 2 x D addresses, which dominated the kernel on short inputs)
+  __shared__ float red_w[8][256], red_b[8][256];
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const int c = 8 * lane + 256 * i;
-    if (c < D)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        atomicAdd(dw + c + e, dwv[i][e]);
-        atomicAdd(db + c + e, dbv[i][e]);
-      }
+    for (int e = 0; e < 8; ++e) {
+      red_w[warp][8 * lane + e] = dwv[i][e];
+      red_b[warp][8 * lane + e] = dbv[i][e];
+    }
+    __syncthreads();
+    const int c = 256 * i + threadIdx.x;      // blockDim.x == 256
+    if (c < D) {
+      float sw = 0.f, sb = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) { sw += red_w[q][threadIdx.x]; sb += red_b[q][threadIdx.x]; }
+      atomicAdd(dw + c, sw);
+      atomicAdd(db + c, sb);
+    }
+    __syncthreads();
   }
-  (void)warp;
 }
 
 }  // namespace ob
@@ -312,7 +323,7 @@ int ob_layernorm_bwd(const void* dy, const void* x, const void* w, const float* 
   if (M <= 0) return 0;
   if (D % 8 || D > 2048) return 6001;
   long long want = (M + 7) / 8;
-  const unsigned blocks = (unsigned)(want < (long long)num_sms() * 2 ? want : (long long)num_sms() * 2);
+  const unsigned blocks = (unsigned)(want < (long long)num_sms() ? want : (long long)num_sms());
 #define OB_LN_BWD(NV) layernorm_bwd_kernel<NV><<<blocks, 256, 0, s>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, mean, rstd, (bf16*)dx, dw, db, M, D)
   if (D <= 1024) OB_LN_BWD(4);
   else if (D <= 1536) OB_LN_BWD(6);

@@ -101,7 +101,7 @@ def bench_attn(a, dev, flush):
     fl = 4.0 * B * T * T * H * HD / 2
     _report("attention fwd (causal, GQA)", timeit(lambda: K.attn_fwd(q, k, v, cu, T, sc, True), a.iters, a.warmup, flush),
             fl, None, batch=B, seq=T, heads=H, kv_heads=G, head_dim=HD)
-    if HD == 128:
+    if HD in (128, 256):
         _report("attention bwd (causal, GQA)",
                 timeit(lambda: K.attn_bwd(q, k, v, o, lse, do, cu, T, sc, True), a.iters, a.warmup, flush), 2.5 * fl, None)
     if a.baseline:
