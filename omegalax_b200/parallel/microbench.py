@@ -194,6 +194,15 @@ def main():
 
     y_full = torch.empty(M, D, dtype=bf16, device=dev)
     y_loc = torch.empty(m, D, dtype=bf16, device=dev)
+    slabs = symm.SymmetricBuffer(W * m * D * 2)          # one [m, D] slab per sender on every owner
+    slab_ptrs = slabs.peer_ptr_list(0)
+    slab_view = slabs.view(bf16, W * m * D)
+
+    def staged_rs():
+        bar()                                            # the owner has summed the previous call's slabs
+        K.gemm_peer_reduce(h, w_row, slab_ptrs, m, D, slot=rank)
+        bar()
+        K.slab_sum(slab_view, W, y_loc)
 
     def gemm_then_nccl():
         K.gemm(h, w_row, out=y_full)
@@ -204,6 +213,8 @@ def main():
     link3 = (W - 1) * m * D * 2.0
     _report(rank, "TP row: GEMM -> reduce-scatter in the epilogue (bf16 adds over NVLink, incl. clear + 2 barriers)",
             _time(fused_rs, a.iters, a.warmup, W), fl3, link3, M=M, N=D, K=h.shape[1], world=W)
+    _report(rank, "TP row: GEMM -> per-sender slabs on the owner (plain stores over NVLink) -> slab sum (incl. 2 barriers)",
+            _time(staged_rs, a.iters, a.warmup, W), fl3, link3, M=M, N=D, K=h.shape[1], world=W)
     _report(rank, "  GEMM, then NCCL reduce_scatter (bf16)", _time(gemm_then_nccl, a.iters, a.warmup, W), fl3,
             (W - 1) * m * D * 2.0, M=M, N=D, K=h.shape[1], world=W)
 
