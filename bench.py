@@ -96,7 +96,7 @@ def reference_arm(args) -> int:
     N = max(int(os.environ.get("WORLD_SIZE", "1")), 1)
     seqs = args.seqs_per_gpu or def_seqs
     T = args.seq_len or def_T
-    micro = min(args.micro_seqs or (4 if N <= 2 else seqs), seqs)
+    micro = min(args.micro_seqs or (4 if N == 1 else seqs), seqs)
     try:
         res = ref.run(model_id, N, seqs, T, micro, args.steps, args.warmup)
     except Exception as e:  # pragma: no cover - depends on the box
@@ -223,7 +223,10 @@ def main() -> int:
             cfg = dataclasses.replace(cfg, num_hidden_layers=args.layers, layer_types=cfg.layer_types[:args.layers])
     if args.experts is not None:
         cfg = dataclasses.replace(cfg, num_experts=args.experts)
-    micro = args.micro_seqs or (4 if N <= 2 else args.seqs_per_gpu)  # keeps the kept activations inside 180 GB
+    # N >= 2 run the same settings (8 sequences in one micro-batch, `selective` remat) so that the scaling
+    # figures compare like with like; a single GPU holds all 148 GB of fp32 state and has to run two
+    # micro-batches of 4 with fewer stashed activations, which is reported in `config`.
+    micro = args.micro_seqs or (4 if N == 1 else args.seqs_per_gpu)
     micro = min(micro, args.seqs_per_gpu)
     accum = args.seqs_per_gpu // micro
     T = args.seq_len

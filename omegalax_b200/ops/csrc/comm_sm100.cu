@@ -88,6 +88,38 @@ __global__ void reduce_scatter_pull_kernel(PeerPtrs full, float* __restrict__ ou
   }
 }
 
+// ---------------------------------------------------------------- scatter-add of small gradients
+// Gradients of the parameters that do not go through a GEMM epilogue (norm weights, biases, router
+// tables): every rank holds a full fp32 gradient of the unit's parameters and adds each element
+// into the owning rank's gradient shard with an fp32 reduction over NVLink (into every rank's copy
+// for replicated parameters), then clears its local buffer.  No rank waits for another here: the
+// reductions are ordered by the same end-of-backward barrier as the weight-gradient epilogues, so
+// a layer's backward has no cross-rank synchronisation point at all.
+struct ScatSeg {
+  long long src_off, dst_off;   // elements: into the local full buffer / into every rank's shard buffer
+  int numel, shard_numel;       // shard_numel == numel for replicated parameters
+  int sharded, pad;
+};
+
+__global__ void peer_scatter_add_kernel(float* __restrict__ src, PeerPtrs dst, const ScatSeg* __restrict__ segs,
+                                        int nsegs, int world) {
+  for (int s = blockIdx.y; s < nsegs; s += gridDim.y) {
+    const ScatSeg sg = segs[s];
+    float* sp = src + sg.src_off;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < sg.numel; i += gridDim.x * blockDim.x) {
+      const float v = sp[i];
+      sp[i] = 0.f;
+      if (v == 0.f) continue;
+      if (sg.sharded) {
+        const int owner = i / sg.shard_numel;
+        atomicAdd(reinterpret_cast<float*>(dst.p[owner]) + sg.dst_off + (i - owner * sg.shard_numel), v);
+      } else {
+        for (int r = 0; r < world; ++r) atomicAdd(reinterpret_cast<float*>(dst.p[r]) + sg.dst_off + i, v);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- slab sum (two-phase reduce-scatter)
 // out[i] = sum over the `slots` slabs of staging[s * slab_elems + i] (+ residual[i]); bf16 in and out,
 // fp32 accumulation.  Second phase of the GEMM -> reduce-scatter whose first phase stored every
@@ -127,6 +159,21 @@ __global__ void slab_sum_kernel(const bf16* __restrict__ staging, int slots, lon
 using namespace ob;
 
 extern "C" {
+
+int ob_peer_scatter_add(float* src, void* const* dst_ptrs, int world, const void* segs, int nsegs, int max_numel,
+                        cudaStream_t stream) {
+  if (world > kMaxRanks) return 6003;
+  if (nsegs <= 0) return 0;
+  PeerPtrs d = {};
+  for (int i = 0; i < world; ++i) d.p[i] = dst_ptrs[i];
+  int bx = (max_numel + 255) / 256;
+  if (bx > 64) bx = 64;
+  if (bx < 1) bx = 1;
+  dim3 grid(bx, nsegs < 64 ? nsegs : 64);
+  peer_scatter_add_kernel<<<grid, 256, 0, stream>>>(src, d, (const ScatSeg*)segs, nsegs, world);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
 
 int ob_slab_sum(const void* staging, int slots, long long slab_elems, const void* residual, void* out,
                 cudaStream_t stream) {

@@ -35,9 +35,57 @@ struct PairTile {
   int b_row0;      // first B row (= output column) this CTA stages
   int c_col0;      // first output column of the tile
   int rows_valid, cols_valid;
+  int b_k_off;     // grouped rows with an MN-major B: row offset of the group's matrix
+  int k_begin, k_end;   // grouped reduction: the group's rows
+  long long c_off; // grouped reduction: element offset of the group's output
+  bool valid;
 };
 
+__device__ __forceinline__ int pair_find_group(const int* offs, int G, int row) {
+  int lo = 0, hi = G;  // invariant: offs[lo] <= row < offs[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(offs + mid) <= row) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
 __device__ __forceinline__ PairTile pair_tile(const GemmArgs& p, int t, int rank) {
+  if (p.mode == 1) {
+    // rows of A and C are ragged per group; every group boundary is a multiple of 256, so a pair
+    // tile lies inside one group and reads that group's matrix of B
+    PairTile ti;
+    const int mb = t / p.num_n_blocks, nb = t - mb * p.num_n_blocks;
+    const int row0 = mb * 256;
+    ti.valid = row0 < __ldg(p.group_offsets + p.num_groups);
+    const int g = ti.valid ? pair_find_group(p.group_offsets, p.num_groups, row0) : 0;
+    ti.row0 = row0 + rank * 128;
+    ti.rows_valid = 128;
+    if (p.b_mn) { ti.b_row0 = nb * kPairBN + rank * kPairBNL; ti.b_k_off = g * p.b_group_rows; }
+    else { ti.b_row0 = g * p.b_group_rows + nb * kPairBN + rank * kPairBNL; ti.b_k_off = 0; }
+    ti.c_col0 = nb * kPairBN;
+    ti.cols_valid = min(kPairBN, p.N - ti.c_col0);
+    ti.k_begin = 0; ti.k_end = p.K; ti.c_off = 0;
+    return ti;
+  }
+  if (p.mode == 2) {
+    // per-group weight gradient: the reduction runs over the group's rows
+    PairTile ti;
+    const int per_group = p.num_m_blocks * p.num_n_blocks;
+    const int g = t / per_group, r = t - g * per_group;
+    const int mb = r / p.num_n_blocks, nb = r - mb * p.num_n_blocks;
+    ti.valid = true;
+    ti.row0 = mb * 256 + rank * 128;
+    ti.b_row0 = nb * kPairBN + rank * kPairBNL;
+    ti.b_k_off = 0;
+    ti.c_col0 = nb * kPairBN;
+    ti.rows_valid = min(128, p.M - ti.row0);
+    ti.cols_valid = min(kPairBN, p.N - ti.c_col0);
+    ti.k_begin = __ldg(p.group_offsets + g);
+    ti.k_end = __ldg(p.group_offsets + g + 1);
+    ti.c_off = (long long)g * p.c_group_stride;
+    return ti;
+  }
   // GM tile rows (GM * 256 output rows) share a sweep over the tile columns for L2 reuse
   const int GM = p.raster_gm;
   const int per_group = GM * p.num_n_blocks;
@@ -67,6 +115,7 @@ __device__ __forceinline__ PairTile pair_tile(const GemmArgs& p, int t, int rank
   ti.c_col0 = nb * kPairBN;
   ti.rows_valid = min(128, p.M - ti.row0);
   ti.cols_valid = min(kPairBN, p.N - ti.c_col0);
+  ti.b_k_off = 0; ti.k_begin = 0; ti.k_end = p.K; ti.c_off = 0; ti.valid = true;
   return ti;
 }
 
@@ -133,9 +182,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (int u = pair0; u < total_units && ok; u += pair_step) {
         const int ks = u / p.total_tiles;        // slice-major: a wave of units shares operand panels
         const int t = u - ks * p.total_tiles;
-        const int k_begin = ks * p.k_per_split;
-        const int k_end = min(p.K, k_begin + p.k_per_split);
         const PairTile ti = pair_tile(p, t, rank);
+        if (!ti.valid) continue;
+        const int k_begin = p.mode ? ti.k_begin : ks * p.k_per_split;
+        const int k_end = p.mode ? ti.k_end : min(p.K, k_begin + p.k_per_split);
         bool ag_local = false;   // tile of this GPU's own chunk: read it where it already is
         int ag_row = 0;
         if (p.ag_side) {  // the chunk this CTA's part of the tile reads must have arrived
@@ -173,7 +223,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           } else {
 #pragma unroll
             for (int j = 0; j < kPairBNL / 64; ++j)
-              tma_load_2d_pair(sb + j * (BK * 128), &tmB, fb, ti.b_row0 + j * 64, k0);
+              tma_load_2d_pair(sb + j * (BK * 128), &tmB, fb, ti.b_row0 + j * 64, ti.b_k_off + k0);
           }
           if (++stage == kPairStages) {
             stage = 0;
@@ -193,8 +243,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       bool ok = true;
       for (int u = pair0; u < total_units && ok; u += pair_step) {
         const int ks = u / p.total_tiles;
-        const int k_begin = ks * p.k_per_split;
-        const int k_end = min(p.K, k_begin + p.k_per_split);
+        int k_begin = ks * p.k_per_split;
+        int k_end = min(p.K, k_begin + p.k_per_split);
+        if (p.mode) {
+          const PairTile ti = pair_tile(p, u - ks * p.total_tiles, 0);
+          if (!ti.valid) continue;
+          k_begin = ti.k_begin; k_end = ti.k_end;
+        }
         ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1, abort_flag, p.status, OB_ERR_WAIT_TMEM_EMPTY);
         if (!ok) break;
         tc_fence_after();
@@ -239,6 +294,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     for (int u = pair0; u < total_units && ok; u += pair_step) {
       const int t = u % p.total_tiles;
       const PairTile ti = pair_tile(p, t, rank);
+      if (!ti.valid) continue;
+      const bool empty_k = p.mode ? (ti.k_end <= ti.k_begin) : (p.K <= 0);
       ok = mbar_wait(&tfull_bar[acc], acc_phase, abort_flag, p.status, OB_ERR_WAIT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
@@ -248,7 +305,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 #pragma unroll 1
       for (int c = 0; c < kPairBN / 32; ++c) {
         uint32_t v[32];
-        if (p.K > 0) {
+        if (!empty_k) {
           tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * kPairBN + c * 32, v);
           tmem_ld_wait();
         } else {
@@ -257,7 +314,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         }
         const int col0 = ti.c_col0 + c * 32;
         const int ncols = min(32, ti.cols_valid - c * 32);
-        if (row_ok && ncols > 0) gemm_store_slice(p, 0, grow, col0, ncols, v);
+        if (row_ok && ncols > 0) gemm_store_slice(p, ti.c_off, grow, col0, ncols, v);
       }
       tc_fence_before();
       __syncwarp();
@@ -323,7 +380,7 @@ static int pick_gm(int K) {
 static void pick_splits(GemmArgs& g, int pairs) {
   g.k_splits = 1;
   g.k_per_split = g.K > 0 ? g.K : BK;
-  if (g.out_mode < 2 || g.out_mode > 4 || g.K < 2048 || g_tune_splitk == 0 || pairs <= 0) return;
+  if (g.mode != 0 || g.out_mode < 2 || g.out_mode > 4 || g.K < 2048 || g_tune_splitk == 0 || pairs <= 0) return;
   const int kblocks = (g.K + BK - 1) / BK;
   int best = 1;
   double best_eff = 0.0;
@@ -464,6 +521,45 @@ int ob_gemm_bf16_pair_peer_reduce(const void* A, const void* B, void* const* pee
   if (!a_mn && b_mn) return launch_pair<false, true>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
   if (a_mn && b_mn) return launch_pair<true, true>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
   return launch_pair<true, false>(A, B, g, a_rows, a_cols, lda, b_rows, b_cols, ldb, stream);
+}
+
+// Grouped GEMM over ragged row groups on CTA pairs (mixture-of-experts forward and input gradient):
+// same contract as ob_gemm_bf16_grouped, but every entry of group_offsets and max_rows must be a
+// multiple of 256 (a 256-row pair tile must not straddle two groups).
+int ob_gemm_bf16_pair_grouped(const void* A, const void* B, void* C, const int* group_offsets, int G, int max_rows,
+                              int N, int K, long long lda, long long ldc, int b_mn, int out_mode, int* status,
+                              cudaStream_t stream) {
+  if (max_rows <= 0) return 0;
+  if ((lda & 7) || (max_rows % 256)) return 6001;
+  GemmArgs g = {};
+  g.M = max_rows; g.N = N; g.K = K; g.mode = 1;
+  g.num_groups = G; g.group_offsets = group_offsets;
+  g.b_group_rows = b_mn ? K : N;
+  g.b_mn = b_mn;
+  g.num_m_blocks = max_rows / 256;
+  g.num_n_blocks = (N + kPairBN - 1) / kPairBN;
+  g.total_tiles = g.num_m_blocks * g.num_n_blocks;
+  g.C = C; g.ldc = ldc; g.out_mode = out_mode;
+  g.status = status;
+  const long long b_rows = (long long)G * (b_mn ? K : N), b_cols = b_mn ? N : K;
+  if (b_mn) return launch_pair<false, true>(A, B, g, max_rows, K, lda, b_rows, b_cols, b_cols, stream);
+  return launch_pair<false, false>(A, B, g, max_rows, K, lda, b_rows, b_cols, b_cols, stream);
+}
+
+// Grouped weight gradient on CTA pairs: same contract as ob_gemm_bf16_grouped_wgrad.
+int ob_gemm_bf16_pair_grouped_wgrad(const void* A, const void* B, void* C, const int* group_offsets, int G,
+                                    int max_rows, int N, int K, long long lda, long long ldb, int out_mode, int* status,
+                                    cudaStream_t stream) {
+  if ((lda & 7) || (ldb & 7)) return 6001;
+  GemmArgs g = {};
+  g.M = N; g.N = K; g.K = max_rows; g.mode = 2;
+  g.num_groups = G; g.group_offsets = group_offsets;
+  g.num_m_blocks = (N + 255) / 256;
+  g.num_n_blocks = (K + kPairBN - 1) / kPairBN;
+  g.total_tiles = G * g.num_m_blocks * g.num_n_blocks;
+  g.C = C; g.ldc = K; g.c_group_stride = (long long)N * K; g.out_mode = out_mode;
+  g.status = status;
+  return launch_pair<true, true>(A, B, g, max_rows, N, lda, max_rows, K, ldb, stream);
 }
 
 // Same contract as ob_gemm_bf16_ag (all-gather -> GEMM in one launch), computed by CTA pairs.  The

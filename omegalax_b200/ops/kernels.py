@@ -188,9 +188,10 @@ def gemm_ag(other, full, src_ptrs, *, side: int, rank: int, rows_per_rank: int, 
     return out
 
 
-def gemm_grouped(a, b, group_offsets, *, b_mn: bool = False, out=None, out_dtype=bf16):
+def gemm_grouped(a, b, group_offsets, *, b_mn: bool = False, out=None, out_dtype=bf16, pair: bool = False):
     """Ragged-row grouped GEMM.  a: [R,K] rows grouped by ``group_offsets`` (int32 [G+1],
-    multiples of 128, R % 128 == 0); b: [G,N,K] (or [G,K,N] when b_mn)."""
+    multiples of 128, R % 128 == 0); b: [G,N,K] (or [G,K,N] when b_mn).  ``pair``: run on CTA pairs
+    (256 x 256 tiles); the caller guarantees that every group offset and R are multiples of 256."""
     a = _row_major_2d(a)
     G = b.shape[0]
     R, K = a.shape
@@ -201,21 +202,23 @@ def gemm_grouped(a, b, group_offsets, *, b_mn: bool = False, out=None, out_dtype
         out = torch.empty(R, N, dtype=out_dtype, device=a.device)
     mode = 0 if out.dtype == bf16 else 1
     st = lib.status_tensor(a.device)
-    _call("ob_gemm_bf16_grouped", a.data_ptr(), b2.data_ptr(), out.data_ptr(),
+    pair = pair and R % 256 == 0
+    _call("ob_gemm_bf16_pair_grouped" if pair else "ob_gemm_bf16_grouped", a.data_ptr(), b2.data_ptr(), out.data_ptr(),
           group_offsets.data_ptr(), G, R, N, K, a.stride(0), out.stride(0), int(b_mn), mode,
           st.data_ptr(), lib.stream_ptr())
     return out
 
 
-def gemm_grouped_wgrad(dy, x, group_offsets, out, accumulate: bool = True):
-    """out[g] (+)= dy[rows of g]^T x[rows of g]; dy [R,N], x [R,K], out fp32 [G,N,K]."""
+def gemm_grouped_wgrad(dy, x, group_offsets, out, accumulate: bool = True, pair: bool = False):
+    """out[g] (+)= dy[rows of g]^T x[rows of g]; dy [R,N], x [R,K], out fp32 [G,N,K].  ``pair`` as in
+    ``gemm_grouped``."""
     dy = _row_major_2d(dy)
     x = _row_major_2d(x)
     G, N, K = out.shape
     lib.check_index("gemm_grouped_wgrad group_offsets", group_offsets, dy.shape[0] + 1)
     mode = (2 if accumulate else 1) if out.dtype == torch.float32 else 0
     st = lib.status_tensor(dy.device)
-    _call("ob_gemm_bf16_grouped_wgrad", dy.data_ptr(), x.data_ptr(), out.data_ptr(),
+    _call("ob_gemm_bf16_pair_grouped_wgrad" if pair else "ob_gemm_bf16_grouped_wgrad", dy.data_ptr(), x.data_ptr(), out.data_ptr(),
           group_offsets.data_ptr(), G, dy.shape[0], N, K, dy.stride(0), x.stride(0), mode,
           st.data_ptr(), lib.stream_ptr())
     return out

@@ -36,10 +36,13 @@ _SIGS = {
     "ob_gemm_bf16_peer_reduce": [P, P, P, I, I, I, I, I, L, L, L, I, I, I, P, P],
     "ob_gemm_bf16_grouped": [P, P, P, P, I, I, I, I, L, L, I, I, P, P],
     "ob_gemm_bf16_grouped_wgrad": [P, P, P, P, I, I, I, I, L, L, I, P, P],
+    "ob_gemm_bf16_pair_grouped": [P, P, P, P, I, I, I, I, L, L, I, I, P, P],
+    "ob_gemm_bf16_pair_grouped_wgrad": [P, P, P, P, I, I, I, I, L, L, I, P, P],
     "ob_attn_fwd": [P, P, P, P, P, P, I, I, L, I, I, I, L, L, L, L, F, I, P, P],
     "ob_attn_bwd": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, L, I, I, I, L, L, L, L, L, L, L, F, I, P, P],
     "ob_decode_append": [P, P, P, P, P, P, P, I, I, P, P, P, L, I, I, I, I, F, F, I, P],
     "ob_decode_attn": [P, P, P, P, P, I, I, I, I, I, I, I, F, P, P, P, P],
+    "ob_peer_scatter_add": [P, P, I, P, I, I, P],
     "ob_slab_sum": [P, I, L, P, P, P],
     "ob_ep_push": [P, I, P, P, P, P, P, L, I, P],
     "ob_ep_pull": [P, I, P, P, P, P, P, P, L, I, I, P],

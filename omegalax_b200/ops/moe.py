@@ -14,7 +14,13 @@ from . import kernels as K
 from . import reference as R
 
 bf16 = torch.bfloat16
-PAD = 128
+# Expert segments are padded to multiples of PAD rows.  256 lets the grouped GEMMs run on CTA pairs
+# (a 256-row pair tile must lie inside one expert's segment); OMEGALAX_B200_MOE_PAD=128 selects the
+# single-CTA grouped kernel and its smaller padding.
+import os as _os
+
+PAD = int(_os.environ.get("OMEGALAX_B200_MOE_PAD", "256"))
+_PAIR = PAD % 256 == 0
 
 
 class _RouteFn(torch.autograd.Function):
@@ -124,7 +130,7 @@ class _GroupedLinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w, offsets, out=None):
-        y = K.gemm_grouped(x, w, offsets, out=out)
+        y = K.gemm_grouped(x, w, offsets, out=out, pair=_PAIR)
         ctx.save_for_backward(x, w, offsets)
         ctx.w_ref = w
         return y
@@ -133,15 +139,15 @@ class _GroupedLinearFn(torch.autograd.Function):
     def backward(ctx, dy):
         x, w, offsets = ctx.saved_tensors
         dy = dy.contiguous()
-        dx = K.gemm_grouped(dy, w, offsets, b_mn=True) if ctx.needs_input_grad[0] else None
+        dx = K.gemm_grouped(dy, w, offsets, b_mn=True, pair=_PAIR) if ctx.needs_input_grad[0] else None
         dw = None
         if ctx.needs_input_grad[1]:
             mg = getattr(ctx.w_ref, "main_grad", None)
             if mg is not None:
-                K.gemm_grouped_wgrad(dy, x, offsets, mg, accumulate=True)
+                K.gemm_grouped_wgrad(dy, x, offsets, mg, accumulate=True, pair=_PAIR)
             else:
                 dwf = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
-                K.gemm_grouped_wgrad(dy, x, offsets, dwf, accumulate=False)
+                K.gemm_grouped_wgrad(dy, x, offsets, dwf, accumulate=False, pair=_PAIR)
                 dw = dwf.to(w.dtype)
         return dx, dw, None, None
 

@@ -27,7 +27,7 @@ from ..ops import lib
 from ..ops import moe as moe_ops
 from . import symm
 
-PAD = 128
+PAD = moe_ops.PAD    # expert segments are padded to this many rows (256: grouped GEMMs on CTA pairs)
 
 
 def _register():

@@ -268,38 +268,44 @@ def test_gemm_epilogues(bn):
     assert _rel_err(o32, ref) < 1e-2
 
 
-def test_gemm_grouped_and_wgrad():
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_grouped_and_wgrad(pair):
+    """Grouped expert GEMMs (forward, input gradient, weight gradient) on the single-CTA kernel
+    (segments padded to 128 rows) and on CTA pairs (segments padded to 256 rows; one expert is left
+    empty), per expert against fp32 matmul."""
     from omegalax_b200.ops import kernels as Kn, lib
     from omegalax_b200.ops import moe
     torch.manual_seed(2)
-    E, D, F, M, k = 4, 256, 384, 500, 2
-    idx = torch.randint(0, E, (M, k), device=_dev())
-    dest, offsets, cap = moe.build_permutation(idx, E)
+    E, D, F, M, k = 5, 256, 384, 700, 2
+    idx = torch.randint(0, E - 1, (M, k), device=_dev())      # expert E-1 receives nothing
+    dest, offsets, cap = moe.build_permutation(idx, E, pad=256 if pair else 128)
     x = torch.randn(M, D, device=_dev()).to(bf16)
     xp = torch.zeros(cap, D, device=_dev(), dtype=bf16)
     tok = torch.arange(M, device=_dev()).repeat_interleave(k)
     xp.index_copy_(0, dest, x[tok])
     w = torch.randn(E, F, D, device=_dev()).to(bf16) * 0.05
-    y = Kn.gemm_grouped(xp, w, offsets)
+    y = Kn.gemm_grouped(xp, w, offsets, pair=pair)
     _check(lib)
     offs = offsets.tolist()
+    if pair:
+        assert all(o % 256 == 0 for o in offs) and cap % 256 == 0
     for e in range(E):
         a, b = offs[e], offs[e + 1]
         if b > a:
-            assert _rel_err(y[a:b], xp[a:b].float() @ w[e].float().t()) < 2e-2
+            _assert_gemm_close(y[a:b], xp[a:b].float() @ w[e].float().t(), D)
     # dgrad layout: B given as [E, K, N]
     wt = w.transpose(1, 2).contiguous()
-    y2 = Kn.gemm_grouped(xp, wt, offsets, b_mn=True)
+    y2 = Kn.gemm_grouped(xp, wt, offsets, b_mn=True, pair=pair)
     _check(lib)
-    assert _rel_err(y2[: offs[-1]], y[: offs[-1]]) < 2e-2
+    torch.testing.assert_close(y2[: offs[-1]].float(), y[: offs[-1]].float(), rtol=2.0 ** -7, atol=2e-2)
     dy = torch.randn(cap, F, device=_dev()).to(bf16)
-    dw = torch.zeros(E, F, D, device=_dev(), dtype=torch.float32)
-    Kn.gemm_grouped_wgrad(dy, xp, offsets, dw, accumulate=True)
+    dw = torch.full((E, F, D), 0.25, device=_dev(), dtype=torch.float32)
+    Kn.gemm_grouped_wgrad(dy, xp, offsets, dw, accumulate=True, pair=pair)
     _check(lib)
     for e in range(E):
         a, b = offs[e], offs[e + 1]
-        ref = dy[a:b].float().t() @ xp[a:b].float()
-        assert _rel_err(dw[e], ref) < 2e-2
+        ref = dy[a:b].float().t() @ xp[a:b].float() + 0.25
+        _assert_gemm_close(dw[e], ref, max(b - a, 1))
 
 
 @pytest.mark.parametrize("D", [64, 1024, 4096])
