@@ -834,6 +834,28 @@ static inline int grid_for(long long work, int threads) {
   return (int)(b < 1 ? 1 : (b > cap ? cap : b));
 }
 
+// Embedding gradient with the table's rows spread over the GPUs (rows_per_rank consecutive rows on
+// each): every token's gradient row is added into the owner's fp32 shard over NVLink.  A warp
+// covers 64 consecutive columns of one token (256 contiguous bytes) per step.
+struct EmbPeerPtrs {
+  float* p[8];
+};
+__global__ void embedding_bwd_peer_kernel(const int* __restrict__ ids, const bf16* __restrict__ dy, EmbPeerPtrs dst,
+                                          long long M, int D, int rows_per_rank, int world) {
+  const int dv = D >> 1;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < M * dv;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long m = idx / dv;
+    const int c = (int)(idx - m * dv);
+    const int id = ids[m];
+    const int owner = id / rows_per_rank;
+    if (id < 0 || owner >= world) continue;
+    const float2 f = unpack_bf16(reinterpret_cast<const uint32_t*>(dy + m * D)[c]);
+    float* d = dst.p[owner] + (long long)(id - owner * rows_per_rank) * D + 2 * c;
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(d), "f"(f.x), "f"(f.y) : "memory");
+  }
+}
+
 }  // namespace ob
 
 using namespace ob;
@@ -1035,6 +1057,18 @@ int ob_embedding_bwd(const int* ids, const void* dy, float* dtable, long long M,
   if (M <= 0) return 0;
   embedding_bwd_kernel<<<grid_for(M * (D / 2), 256), 256, 0, s>>>(ids, (const bf16*)dy, dtable, M,
                                                                   D, row_lo, row_hi);
+  OB_CHECK_LAUNCH();
+  return 0;
+}
+
+int ob_embedding_bwd_peer(const int* ids, const void* dy, void* const* dst_ptrs, int world, int rows_per_rank,
+                          long long M, int D, cudaStream_t s) {
+  if (D % 2 || world > 8 || rows_per_rank <= 0) return 6001;
+  if (M <= 0) return 0;
+  EmbPeerPtrs d = {};
+  for (int i = 0; i < world; ++i) d.p[i] = (float*)dst_ptrs[i];
+  embedding_bwd_peer_kernel<<<grid_for(M * (D / 2), 256), 256, 0, s>>>(ids, (const bf16*)dy, d, M, D, rows_per_rank,
+                                                                       world);
   OB_CHECK_LAUNCH();
   return 0;
 }

@@ -26,7 +26,8 @@ struct PairSmem {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = kPairBNL * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOff = kPairStages * kStageBytes;
+  static constexpr int kStagingOff = kPairStages * kStageBytes;   // 4 epilogue warps x 4 KB (coalesced peer output)
+  static constexpr int kBarOff = kStagingOff + 4 * 4096;
   static constexpr int kTotal = kBarOff + 256 + 1024;
 };
 
@@ -141,7 +142,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   // cluster is either all copy or all compute)
   const int ncopy = p.ag_side ? p.ag_copy_ctas : 0;
   if ((int)blockIdx.x < ncopy) {
-    if (threadIdx.x == 0) ag_copy_role<(L::kBarOff / 32768 < 6 ? L::kBarOff / 32768 : 6)>(p, smem, full_bar, abort_flag);
+    if (threadIdx.x == 0) ag_copy_role<(L::kStagingOff / 32768 < 6 ? L::kStagingOff / 32768 : 6)>(p, smem, full_bar, abort_flag);
     return;
   }
   const int pair0 = (int)((blockIdx.x - ncopy) >> 1);
@@ -291,6 +292,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    // peer output modes with 16-byte aligned row segments go through the coalescing slab
+    const bool peer_coalesced = p.out_mode >= 3 && p.mode == 0 &&
+                                ((p.ldc * (p.out_mode == 3 ? 4 : 2)) & 15) == 0 &&
+                                ((reinterpret_cast<uintptr_t>(p.peer_ptr[0]) & 15) == 0);
     for (int u = pair0; u < total_units && ok; u += pair_step) {
       const int t = u % p.total_tiles;
       const PairTile ti = pair_tile(p, t, rank);
@@ -314,7 +319,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         }
         const int col0 = ti.c_col0 + c * 32;
         const int ncols = min(32, ti.cols_valid - c * 32);
-        if (row_ok && ncols > 0) gemm_store_slice(p, ti.c_off, grow, col0, ncols, v);
+        if (peer_coalesced && ncols == 32) {   // warp-uniform: rows owned by other GPUs leave as whole row segments
+          peer_chunk_out(p, smem + L::kStagingOff + quad * 4096, lane, (long long)ti.row0 + quad * 32, col0, v);
+        } else if (row_ok && ncols > 0) {
+          gemm_store_slice(p, ti.c_off, grow, col0, ncols, v);
+        }
       }
       tc_fence_before();
       __syncwarp();

@@ -392,6 +392,10 @@ class _EmbeddingFn(torch.autograd.Function):
     def backward(ctx, dy):
         (ids,) = ctx.saved_tensors
         t = ctx.t_ref
+        pg = getattr(t, "peer_embed_grad", None)
+        if pg is not None:      # table rows sharded over the GPUs: rows go to their owners over NVLink
+            K.embedding_bwd_peer(ids, dy, pg[0], pg[1])
+            return None, None
         mg = getattr(t, "main_grad", None)
         if mg is not None:
             K.embedding_bwd(ids, dy, mg)

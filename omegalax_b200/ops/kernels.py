@@ -385,6 +385,21 @@ def embedding_bwd(ids, dy, dtable_f32, row_lo=0, row_hi=None):
           ids32.numel(), d2.shape[1], row_lo, hi, lib.stream_ptr())
 
 
+def embedding_bwd_peer(ids, dy, peer_ptrs, rows_per_rank: int):
+    """Embedding gradient rows added into the owners' fp32 shards over NVLink (``peer_ptrs[r]`` holds
+    table rows [r*rows_per_rank, (r+1)*rows_per_rank))."""
+    import ctypes
+
+    ids32 = ids.reshape(-1).to(torch.int32)
+    d2 = dy.reshape(-1, dy.shape[-1])
+    if not d2.is_contiguous():
+        d2 = d2.contiguous()
+    lib.check_index("embedding_bwd_peer ids", ids32, rows_per_rank * len(peer_ptrs))
+    arr = (ctypes.c_void_p * len(peer_ptrs))(*peer_ptrs)
+    _call("ob_embedding_bwd_peer", ids32.data_ptr(), d2.data_ptr(), ctypes.cast(arr, ctypes.c_void_p), len(peer_ptrs),
+          int(rows_per_rank), ids32.numel(), d2.shape[1], lib.stream_ptr())
+
+
 def sumsq(g, out):
     _call("ob_sumsq", g.data_ptr(), g.numel(), out.data_ptr(), lib.stream_ptr())
 

@@ -79,6 +79,7 @@ _SIGS = {
     "ob_ce_fwd_bwd": [P, L, L, I, P, P, P, P, P, I, P],
     "ob_embedding_fwd": [P, P, P, L, I, P],
     "ob_embedding_bwd": [P, P, P, L, I, I, I, P],
+    "ob_embedding_bwd_peer": [P, P, P, I, I, L, I, P],
     "ob_sumsq": [P, L, P, P],
     "ob_adamw": [P, P, P, P, P, L, F, F, F, F, F, F, F, F, P, F, I, P],
     "ob_cast_f32_bf16": [P, P, L, P],

@@ -327,6 +327,15 @@ class TrainEngine:
             if not (s.sharded and len(s.shape) == 2 and s.pname.endswith("weight") and s.shape[0] % 8 == 0):
                 continue
             owner = s.module.get_submodule(s.pname.rsplit(".", 1)[0]) if "." in s.pname else s.module
+            if type(owner).__name__ == "Embedding" and self.compute_dtype == bf16 and s.shape[1] % 2 == 0:
+                # token-embedding table: gradient rows are added into the owners' shards by the embedding
+                # backward itself (no full fp32 table gradient, no 2.5 GB reduce-scatter per step)
+                s.peer = True
+                off_bytes = (u.shard_base + s.shard_off) * 4
+                s.param.peer_embed_grad = (self._grad_buf.peer_ptr_list(off_bytes), s.shape[0] // self.W)
+                # a head tied to this table reaches the same shards through its weight-gradient GEMM
+                s.param.peer_grad = (self._grad_buf.peer_ptr_list(off_bytes), s.shape[0] // self.W, s.shape[1])
+                continue
             if type(owner).__name__ != "Linear":
                 continue
             s.peer = True

@@ -441,6 +441,11 @@ def test_embedding_and_optimizer_kernels():
     ref = torch.zeros(V, D, device=_dev()).index_add_(0, ids, dy.float())
     _check(lib)
     assert _rel_err(dt, ref) < 1e-5
+    # the same gradient with the table's rows split over four owners (here four buffers of one GPU)
+    shards = [torch.zeros(V // 4, D, device=_dev()) for _ in range(4)]
+    Kn.embedding_bwd_peer(ids, dy, [t.data_ptr() for t in shards], V // 4)
+    _check(lib)
+    assert _rel_err(torch.cat(shards), ref) < 1e-5
     n = 100003
     p = torch.randn(n, device=_dev()); m = torch.zeros(n, device=_dev()); v = torch.zeros(n, device=_dev())
     g = torch.randn(n, device=_dev()); p16 = torch.empty(n, device=_dev(), dtype=bf16)
