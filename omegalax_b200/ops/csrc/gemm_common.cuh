@@ -41,6 +41,10 @@ struct GemmArgs {
   // GEMM writes slab `peer_slot` (plain 16-byte stores over NVLink, no atomics); the owner sums
   // the slabs afterwards (two-phase reduce-scatter).
   int peer_slot;
+  // peer output modes: the tile rows are walked starting m_rot blocks further on (wrapping), so that
+  // the GPUs of a group, which run the same GEMM at the same time, each write to a different owner
+  // at any moment instead of all converging on owner 0, then owner 1, ...
+  int m_rot;
   // gather mode: ag_side 1 = rows of A, 2 = rows of B are assembled inside this launch
   int ag_side, ag_world, ag_rank, ag_copy_ctas;
   int ag_rows_per_rank;            // multiple of the tile extent on that side

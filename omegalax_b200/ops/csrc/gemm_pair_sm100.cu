@@ -109,6 +109,9 @@ __device__ __forceinline__ PairTile pair_tile(const GemmArgs& p, int t, int rank
   } else if (p.ag_side == 1) {  // own chunk of A first, then the chunks in arrival order
     mb += p.ag_rank * (p.ag_rows_per_rank / 256);
     if (mb >= p.num_m_blocks) mb -= p.num_m_blocks;
+  } else if (p.m_rot) {
+    mb += p.m_rot;
+    if (mb >= p.num_m_blocks) mb -= p.num_m_blocks;
   }
   PairTile ti;
   ti.row0 = mb * 256 + rank * 128;
@@ -510,12 +513,14 @@ int ob_gemm_bf16_pair(const void* A, const void* B, void* C, const void* residua
 // buffer (first phase of the two-phase reduce-scatter; the owner sums the slabs afterwards).
 int ob_gemm_bf16_pair_peer_reduce(const void* A, const void* B, void* const* peer_ptrs, int world, int rows_per_peer,
                                   int M, int N, int K, long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
-                                  int bf16_out, int* status, cudaStream_t stream) {
+                                  int bf16_out, int first_owner, int* status, cudaStream_t stream) {
   if (world > kMaxPeers) return 6003;
   if ((lda & 7) || (ldb & 7)) return 6001;
   GemmArgs g = {};
   g.M = M; g.N = N; g.K = K; g.mode = 0;
   g.num_m_blocks = (M + 255) / 256;
+  if (first_owner > 0 && first_owner < world)
+    g.m_rot = (int)(((long long)first_owner * rows_per_peer / 256) % g.num_m_blocks);
   g.num_n_blocks = (N + kPairBN - 1) / kPairBN;
   g.total_tiles = g.num_m_blocks * g.num_n_blocks;
   g.C = nullptr; g.ldc = ldc; g.out_mode = bf16_out >= 2 ? 5 : bf16_out ? 4 : 3;

@@ -67,6 +67,9 @@ __device__ __forceinline__ TileInfo get_tile(const GemmArgs& p, int t) {
       if (p.ag_side == 1) {  // own chunk of A first, then the chunks in arrival order
         mb += p.ag_rank * (p.ag_rows_per_rank / BM);
         if (mb >= p.num_m_blocks) mb -= p.num_m_blocks;
+      } else if (p.m_rot) {
+        mb += p.m_rot;
+        if (mb >= p.num_m_blocks) mb -= p.num_m_blocks;
       }
     } else {  // B is gathered: sweep the row blocks for 8 column blocks of one chunk at a time
       int per_group = GM * p.num_m_blocks;
@@ -448,13 +451,16 @@ int ob_gemm_bf16(const void* A, const void* B, void* C, const void* residual, in
 // sum) before any rank launches; completion is published by the caller's barrier.
 int ob_gemm_bf16_peer_reduce(const void* A, const void* B, void* const* peer_ptrs, int world,
                              int rows_per_peer, int M, int N, int K, long long lda, long long ldb,
-                             long long ldc, int a_mn, int b_mn, int bf16_out, int* status, cudaStream_t stream) {
+                             long long ldc, int a_mn, int b_mn, int bf16_out, int first_owner, int* status,
+                             cudaStream_t stream) {
   if (world > kMaxPeers) return 6003;
   if ((lda & 7) || (ldb & 7)) return 6001;
   int bn = pick_bn(M, N);
   GemmArgs g = {};
   g.M = M; g.N = N; g.K = K; g.mode = 0;
   g.num_m_blocks = (M + BM - 1) / BM;
+  if (first_owner > 0 && first_owner < world)
+    g.m_rot = (int)(((long long)first_owner * rows_per_peer / BM) % g.num_m_blocks);
   g.num_n_blocks = (N + bn - 1) / bn;
   g.total_tiles = g.num_m_blocks * g.num_n_blocks;
   g.C = nullptr; g.ldc = ldc; g.out_mode = bf16_out >= 2 ? 5 : bf16_out ? 4 : 3;   // 2 + s: store into slab s

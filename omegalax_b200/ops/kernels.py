@@ -124,7 +124,10 @@ def gemm_peer_reduce(a, b, peer_ptrs, rows_per_peer: int, ldc: int, *, a_mn=Fals
     rows [r*rows_per_peer, (r+1)*rows_per_peer)): fp32 buffers by default (gradient shards), bf16
     buffers with ``bf16_out`` (activations: half the NVLink bytes, bf16 accumulation).  With
     ``slot`` nothing is reduced: the bf16 rows are stored into slab ``slot`` of the owner's staging
-    buffer ([senders, rows_per_peer, ldc]) and the owner sums the slabs with ``slab_sum``."""
+    buffer ([senders, rows_per_peer, ldc]) and the owner sums the slabs with ``slab_sum``.
+    A ``peer_ptrs`` list with a ``rank`` attribute (``SymmetricBuffer.peer_ptr_list``) makes the
+    tiles start with this GPU's own rows and walk the owners from there, so that the GPUs of the
+    group write to distinct owners at any moment."""
     import ctypes
 
     a = _row_major_2d(a)
@@ -138,7 +141,8 @@ def gemm_peer_reduce(a, b, peer_ptrs, rows_per_peer: int, ldc: int, *, a_mn=Fals
     name = "ob_gemm_bf16_pair_peer_reduce" if pair else "ob_gemm_bf16_peer_reduce"
     _call(name, a.data_ptr(), b.data_ptr(), ctypes.cast(arr, ctypes.c_void_p),
           len(peer_ptrs), rows_per_peer, M, N, K, a.stride(0), b.stride(0), ldc, int(a_mn),
-          int(b_mn), (2 + int(slot)) if slot is not None else int(bf16_out), st.data_ptr(), lib.stream_ptr())
+          int(b_mn), (2 + int(slot)) if slot is not None else int(bf16_out), int(getattr(peer_ptrs, "rank", 0)),
+          st.data_ptr(), lib.stream_ptr())
 
 
 def slab_sum(staging, slots: int, out, residual=None):

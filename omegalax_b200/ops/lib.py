@@ -29,11 +29,11 @@ F = c_float
 
 _SIGS = {
     "ob_gemm_bf16": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, I, P, P, P],
-    "ob_gemm_bf16_pair_peer_reduce": [P, P, P, I, I, I, I, I, L, L, L, I, I, I, P, P],
+    "ob_gemm_bf16_pair_peer_reduce": [P, P, P, I, I, I, I, I, L, L, L, I, I, I, I, P, P],
     "ob_gemm_bf16_pair": [P, P, P, P, I, I, I, L, L, L, L, I, I, I, P, P, P, P, P, P],
     "ob_gemm_bf16_pair_ag": [P, P, P, P, P, I, I, I, L, L, I, I, I, I, I, P, c_uint, I, P, P],
     "ob_gemm_bf16_ag": [P, P, P, P, P, I, I, I, L, L, I, I, I, I, I, P, c_uint, I, P, P],
-    "ob_gemm_bf16_peer_reduce": [P, P, P, I, I, I, I, I, L, L, L, I, I, I, P, P],
+    "ob_gemm_bf16_peer_reduce": [P, P, P, I, I, I, I, I, L, L, L, I, I, I, I, P, P],
     "ob_gemm_bf16_grouped": [P, P, P, P, I, I, I, I, L, L, I, I, P, P],
     "ob_gemm_bf16_grouped_wgrad": [P, P, P, P, I, I, I, I, L, L, I, P, P],
     "ob_gemm_bf16_pair_grouped": [P, P, P, P, I, I, I, I, L, L, I, I, P, P],

@@ -43,6 +43,12 @@ class _RawCudaArray:
         self._owner = owner
 
 
+class PeerPtrs(list):
+    """Per-rank device addresses of one symmetric region, plus the index of the local one."""
+
+    rank = 0
+
+
 class SymmetricBuffer:
     def __init__(self, nbytes: int, group=None):
         self.group = group
@@ -87,7 +93,9 @@ class SymmetricBuffer:
         return ctypes.cast(arr, ctypes.c_void_p)
 
     def peer_ptr_list(self, byte_offset: int = 0):
-        return [p + byte_offset for p in self.peer_ptrs]
+        out = PeerPtrs(p + byte_offset for p in self.peer_ptrs)
+        out.rank = self.rank
+        return out
 
     def view(self, dtype, numel: int, byte_offset: int = 0) -> torch.Tensor:
         esz = torch.empty(0, dtype=dtype).element_size()

@@ -113,6 +113,26 @@ def test_gemm_pair_unaligned_output_pitch_and_local_peer_reduce(wide):
     _assert_gemm_close(torch.cat(halves, 0), 2 * ref, K)
 
 
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_peer_reduce_starting_at_another_owner(pair):
+    """The tile rows may be walked starting at any owner's block (each GPU of a group starts at its
+    own): every row block is still produced exactly once."""
+    from omegalax_b200.ops import kernels as Kn, lib
+    from omegalax_b200.parallel.symm import PeerPtrs
+    torch.manual_seed(14)
+    M, N, K, W = 2048 + 256, 384, 512, 4      # 576 rows per owner: not a multiple of the tile height
+    a = torch.randn(K, M, device=_dev()).to(bf16)
+    b = torch.randn(K, N, device=_dev()).to(bf16)
+    ref = a.float().t() @ b.float()
+    for first in range(W):
+        parts = [torch.zeros(M // W, N, device=_dev()) for _ in range(W)]
+        ptrs = PeerPtrs(t.data_ptr() for t in parts)
+        ptrs.rank = first
+        Kn.gemm_peer_reduce(a, b, ptrs, M // W, N, a_mn=True, b_mn=True, pair=pair)
+        _check(lib)
+        _assert_gemm_close(torch.cat(parts, 0), ref, K)
+
+
 @pytest.mark.parametrize("kernel", ["single", "pair", "wide"])
 def test_gemm_two_phase_reduce_scatter_on_local_slabs(kernel):
     """First phase: two "senders" (two GEMMs with different operands) store their bf16 result rows
