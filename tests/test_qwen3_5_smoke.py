@@ -78,3 +78,31 @@ def test_export_roundtrip(mid):
         assert cfg2.text_config.layer_types == cfg.text_config.layer_types
         for (n1, p1), (n2, p2) in zip(model.named_parameters(), back.named_parameters()):
             assert n1 == n2 and torch.equal(p1, p2), n1
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_image_and_text_logits_match_hf(moe):
+    """Pixels through the vision tower (patch embedding, interpolated position table, 2-D rotary
+    attention, merger), spliced into the token sequence at the image placeholders, 3-D rotary
+    positions from the grid: logits against ``Qwen3_5(Moe)ForConditionalGeneration``."""
+    from omegalax_b200.models.qwen3_vl import get_rope_index
+
+    IMG, VID, VSTART, VEND = 1000, 1001, 1002, 1003
+    grid = [(1, 4, 6), (1, 6, 4)]
+    n_merged = [t * (h // 2) * (w // 2) for t, h, w in grid]
+    toks = [7, 8, VSTART] + [IMG] * n_merged[0] + [VEND, 9, 10, VSTART] + [IMG] * n_merged[1] + [VEND, 11, 12, 13]
+    tok = torch.tensor([toks])
+    torch.manual_seed(3)
+    pix = torch.randn(sum(t * h * w for t, h, w in grid), 3 * 2 * 16 * 16)
+    with tempfile.TemporaryDirectory() as tmp:
+        hf = _hf(tmp, moe)
+        ours, cfg = create_qwen3_5_from_safetensors(tmp, tp_size=1, fsdp_size=1, dp_size=1)
+        pos, _ = get_rope_index(tok.numpy(), grid, None, None, 2, IMG, VID, VSTART)
+        hidden, _ = ours(tok, torch.ones_like(tok), pix, grid, torch.from_numpy(pos))
+        with torch.no_grad():
+            ref = hf(input_ids=tok, pixel_values=pix, image_grid_thw=torch.tensor(grid),
+                     mm_token_type_ids=(tok == IMG).int()).logits
+        torch.testing.assert_close(ours.lm_head(hidden), ref, rtol=3e-4, atol=3e-4)
+        # and the image must matter: without pixels the logits at the text tail differ
+        hidden_txt, _ = ours(tok, torch.ones_like(tok))
+        assert (ours.lm_head(hidden_txt)[0, -1] - ref[0, -1]).abs().max() > 1e-3
