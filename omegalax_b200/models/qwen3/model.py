@@ -177,8 +177,8 @@ class MLP(nn.Module):
         # With a residual this call produces the decoder layer's output, whose value nothing in the
         # layer's own backward reads ("down" may then be skipped when the layer is re-run).  Without
         # one (e.g. a shared expert whose output is gated) the value is needed: no tag.
-        return self.down_proj(Fn.swiglu(self.gate_up_proj(x, tag="gate_up")), residual=residual,
-                              tag="down" if residual is not None else None)
+        return Fn.swiglu_linear(self.gate_up_proj(x, tag="gate_up"), self.down_proj.weight, residual,
+                                tag="down" if residual is not None else None)
 
 
 class MoEFeedForward(nn.Module):

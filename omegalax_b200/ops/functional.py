@@ -380,6 +380,61 @@ def swiglu(gu):
     return R.swiglu(gu)
 
 
+class _SwiGLULinearFn(torch.autograd.Function):
+    """y = (silu(gate) * up) @ w.T (+ residual) as one node.  Only [gate | up] is kept for the
+    backward pass: the activation, which the weight gradient needs, comes back out of the SwiGLU
+    backward kernel, which reads gate and up anyway.  When the output is already known (a layer
+    re-run whose result nobody reads) nothing at all is computed in forward."""
+
+    @staticmethod
+    def forward(ctx, gu, w, residual, y_pre=None):
+        shp = gu.shape
+        g2 = gu.reshape(-1, shp[-1])
+        y = y_pre
+        if y is None:
+            y = K.gemm(K.swiglu_fwd(g2), w, residual=residual)
+        ctx.save_for_backward(g2, w)
+        ctx.shp = shp
+        ctx.has_res = residual is not None
+        ctx.w_ref = w
+        return y.view(*shp[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        g2, w = ctx.saved_tensors
+        w_obj = ctx.w_ref
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dact = K.gemm(dy2, w, b_mn=True)
+        dgu, act = K.swiglu_bwd(g2, dact, with_act=True)
+        del dact
+        dw = None
+        pg = getattr(w_obj, "peer_grad", None)
+        if ctx.needs_input_grad[1] and pg is not None:
+            K.gemm_peer_reduce(dy2, act, pg[0], pg[1], pg[2], a_mn=True, b_mn=True)
+        elif ctx.needs_input_grad[1]:
+            dw = _acc_main_grad(
+                w_obj,
+                lambda mg: K.gemm(dy2, act, a_mn=True, b_mn=True, out=mg, accumulate=True),
+                lambda: K.gemm(dy2, act, a_mn=True, b_mn=True),
+            )
+        return dgu.view(ctx.shp), dw, (dy if ctx.has_res else None), None
+
+
+def swiglu_linear(gu, w, residual=None, tag=None):
+    """linear(swiglu(gu), w, residual) -- the second half of a SwiGLU feed-forward block."""
+    if (use_kernels(gu) and w.dtype == bf16 and gu.shape[-1] % 16 == 0 and w.shape[0] % 8 == 0
+            and getattr(w, "ag_spec", None) is None):
+        key, pre = _stash_lookup(tag)
+        if pre is _SKIP:
+            pre = torch.empty(gu.numel() // gu.shape[-1], w.shape[0], dtype=gu.dtype, device=gu.device)
+        y = _SwiGLULinearFn.apply(gu.contiguous(), w, residual, None if pre is None else pre.view(-1, w.shape[0]))
+        _stash_store(key, y)
+        return y
+    return linear(swiglu(gu), w, residual, tag=tag)
+
+
 # ----------------------------------------------------------------------------- embedding
 class _EmbeddingFn(torch.autograd.Function):
     @staticmethod

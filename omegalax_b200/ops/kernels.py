@@ -261,16 +261,19 @@ def swiglu_fwd(gu):
     return act.view(*gu.shape[:-1], F)
 
 
-def swiglu_bwd(gu, dact):
+def swiglu_bwd(gu, dact, with_act: bool = False):
+    """Gradient of silu(gate) * up; ``with_act`` also returns the activation itself, recomputed in
+    the same pass (for a caller that did not keep it)."""
     g2 = gu.reshape(-1, gu.shape[-1])
     F = g2.shape[1] // 2
     d2 = dact.reshape(-1, F)
     if not d2.is_contiguous():
         d2 = d2.contiguous()
     dgu = torch.empty_like(g2)
-    _call("ob_swiglu_bwd", g2.data_ptr(), d2.data_ptr(), dgu.data_ptr(), None, g2.shape[0], F,
+    act = torch.empty(g2.shape[0], F, dtype=gu.dtype, device=gu.device) if with_act else None
+    _call("ob_swiglu_bwd", g2.data_ptr(), d2.data_ptr(), dgu.data_ptr(), lib.ptr(act), g2.shape[0], F,
           lib.stream_ptr())
-    return dgu.view(gu.shape)
+    return (dgu.view(gu.shape), act) if with_act else dgu.view(gu.shape)
 
 
 def qknorm_rope_fwd(qkv, qw, kw, cos, sin, H, G, K, rot, eps, one_plus=False, q_stride_heads=1):
