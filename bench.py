@@ -230,9 +230,11 @@ def main() -> int:
     micro = min(micro, args.seqs_per_gpu)
     accum = args.seqs_per_gpu // micro
     T = args.seq_len
-    # One GPU holds all fp32 state (148 GB): only the small attention-side tensors are kept from the
-    # first forward.  With the state sharded there is room to keep the wide MLP activation too.
-    remat = args.remat or ("save:qkv,attn" if N == 1 else "selective")
+    # One GPU holds all fp32 state (148 GB): the small attention-side tensors are kept from the first
+    # forward, and the memory that is left after one whole step decides how many layers also keep the
+    # attention block's output and the wide MLP activation ("auto").  With the state sharded there is
+    # room to keep them in every layer ("selective").
+    remat = args.remat or ("auto" if N == 1 else "selective")
     if args.model != "qwen3-8b" and args.remat is None:
         # the small-hidden models have room for the stashed attention-side outputs; the Qwen3.5 slice
         # (117 GB of expert state per GPU at 8 GPUs) recomputes whole layers
@@ -354,7 +356,8 @@ def main() -> int:
                        "global_batch": args.seqs_per_gpu * N, "seq_len": T,
                        "parallelism": (f"fsdp{FS}" if par == "fsdp" else f"ep{FS}+fsdp{FS}") + (f"+tp{TP}" if TP > 1 else ""),
                        "micro_batch_per_gpu": micro, "grad_accum": accum, "optimizer": "AdamW fp32 master",
-                       "remat": remat, "l2": "inputs larger than L2 (weights and activations of one step far exceed 126 MB)"},
+                       "remat": remat if getattr(opt, "_auto", None) is None else
+                       f"auto (save:qkv,attn; layers that also keep o / gate_up: {opt._auto.summary()})", "l2": "inputs larger than L2 (weights and activations of one step far exceed 126 MB)"},
             "tokens_per_sec_per_gpu": value / N, "tflops_per_gpu": tflops_per_gpu,
             "mfu_of_measured_burst": tflops_per_gpu / PEAK_TFLOPS["b200_measured_burst"],
             "mfu_of_nominal": tflops_per_gpu / PEAK_TFLOPS["b200"],

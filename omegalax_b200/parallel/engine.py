@@ -122,8 +122,14 @@ class TrainEngine:
             self.remat_tags = tuple(t for t in remat[5:].split(",") if t) + ("down!",)
         elif remat == "full":
             self.remat_tags = ("down!",)
+        elif remat == "auto":
+            # the small attention-side tensors always; after the first optimizer step the memory that
+            # is still free decides how many layers also keep the attention block's output and the
+            # wide MLP activation
+            self.remat_tags = ("qkv", "attn", "down!")
         else:
             self.remat_tags = ()
+        self._auto = _AutoStash(("o", "gate_up")) if remat == "auto" else None
         self.step_count = 0
         self.micro_steps = 0
         self.tp_group = tp_group
@@ -593,6 +599,8 @@ class TrainEngine:
                 if u.resident:
                     self._all_gather(u, u.gathered)
         self.micro_steps = 0
+        if self._auto is not None and self._auto.phase == "measure":
+            self._auto.open_budget(self.device, sum(1 for u in self.units if u.name.startswith("layers.")))
         return torch.sqrt(nsq) * gmul
 
     # ------------------------------------------------------------------ state I/O
@@ -687,15 +695,86 @@ class _LazyEP:
         return eng._ep.moe_mlp(x, w, idx, gate_up_local, down_local)
 
 
+class _AutoStash:
+    """Remat policy "auto": which layers keep which of the larger tagged outputs, decided from the
+    memory the device still has after one complete step (forward, backward, optimizer) has run
+    with the base policy.  The first forward after that records the extra tags layer by layer
+    while the budget lasts; from then on the choice is fixed.  Tags are listed in order of value
+    per byte: every layer gets the first before any layer gets the second."""
+
+    def __init__(self, extra_tags, margin_bytes: int | None = None):
+        self.extra = tuple(extra_tags)
+        self.phase = "measure"          # -> "grow" (one forward) -> "done"
+        self.budget = 0
+        self.n_layers = 0
+        self.plan = None                # tag -> number of layers that may keep it
+        self.per_layer: dict[int, tuple] = {}
+        gb = float(os.environ.get("OMEGALAX_B200_STASH_MARGIN_GB", "6"))
+        self.margin = int(gb * (1 << 30)) if margin_bytes is None else margin_bytes
+
+    def open_budget(self, device, n_layers: int):
+        fixed = os.environ.get("OMEGALAX_B200_STASH_BUDGET_MB")   # an explicit budget instead of "what is free"
+        if fixed is not None:
+            self.budget = int(float(fixed) * (1 << 20))
+        else:
+            free = torch.cuda.mem_get_info(device)[0] if torch.device(device).type == "cuda" else 0
+            self.budget = max(0, free - self.margin)
+        self.n_layers = n_layers
+        self.phase = "grow" if self.budget > 0 and n_layers > 0 else "done"
+
+    def tags_for(self, idx: int, base: tuple) -> tuple:
+        if idx in self.per_layer:
+            return base + self.per_layer[idx]
+        return base + (self.extra if self.phase == "grow" else ())
+
+    def account(self, idx: int, stash):
+        """After layer ``idx`` was recorded with every extra tag: keep what fits, drop the rest."""
+        if self.phase != "grow" or idx in self.per_layer:
+            return
+        size = {t: 0 for t in self.extra}
+        for (tag, _), v in stash.items.items():
+            if tag in size:
+                size[tag] += v.numel() * v.element_size()
+        if self.plan is None:           # layers are alike: share the budget tag by tag
+            left, self.plan = self.budget, {}
+            for t in self.extra:
+                n = self.n_layers if size[t] == 0 else min(self.n_layers, left // size[t])
+                self.plan[t] = n
+                left -= n * size[t]
+        keep = []
+        for t in self.extra:
+            if self.plan[t] > 0 and size[t] <= self.budget:
+                keep.append(t)
+                self.plan[t] -= 1
+                self.budget -= size[t]
+            else:
+                for k in [k for k in stash.items if k[0] == t]:
+                    del stash.items[k]
+        self.per_layer[idx] = tuple(keep)
+
+    def close(self):
+        if self.phase == "grow":
+            self.phase = "done"
+
+    def summary(self) -> dict:
+        return {t: sum(1 for v in self.per_layer.values() if t in v) for t in self.extra}
+
+
 class _RematLayerFn(torch.autograd.Function):
     """Run a decoder layer without keeping its activations; recompute them in backward."""
 
     @staticmethod
     def forward(ctx, x, engine: TrainEngine, unit: Unit, layer, fctx):
         engine._acquire(unit, +1)
-        stash = Fn._Stash(engine.remat_tags) if engine.remat_tags else None
+        tags, auto = engine.remat_tags, engine._auto
+        if auto is not None and unit.name.startswith("layers."):
+            idx = int(unit.name.split(".")[1])
+            tags = auto.tags_for(idx, tags)
+        stash = Fn._Stash(tags) if tags else None
         with torch.no_grad(), Fn.stash_scope(stash, "record"):
             y, aux = layer(x, fctx)
+        if auto is not None and stash is not None and unit.name.startswith("layers."):
+            auto.account(idx, stash)
         ctx.stash = stash
         ctx.save_for_backward(x)
         ctx.engine, ctx.unit, ctx.layer, ctx.fctx = engine, unit, layer, fctx
@@ -705,6 +784,8 @@ class _RematLayerFn(torch.autograd.Function):
     def backward(ctx, dy, daux):
         (x,) = ctx.saved_tensors
         engine, unit, layer, fctx = ctx.engine, ctx.unit, ctx.layer, ctx.fctx
+        if engine._auto is not None:
+            engine._auto.close()
         engine._acquire(unit, -1)
         with torch.enable_grad(), Fn.stash_scope(ctx.stash, "replay"):
             xin = x.detach().requires_grad_(True)

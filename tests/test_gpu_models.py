@@ -177,6 +177,42 @@ def test_training_engine_reduces_loss(name):
     assert losses[-1] < losses[0] - 0.05, losses
 
 
+def test_remat_policies_follow_the_same_loss_curve(monkeypatch):
+    """full / selective / auto rematerialisation compute the same step: the stashed or replayed
+    tensors are the ones a full re-run would produce.  "auto" gets a budget that lets every layer
+    keep the attention block's output and only one layer the wide MLP activation."""
+    from omegalax_b200.ops import lib
+    from omegalax_b200.trainers import text as trainer
+
+    dev = _dev()
+    cfg0 = dataclasses.replace(_configs()["qwen3-dense"], num_layers=3)
+    B, T = 2, 256
+    per_layer_o, per_layer_gu = B * T * cfg0.emb_dim * 2, B * T * 2 * cfg0.mlp_dim * 2
+    monkeypatch.setenv("OMEGALAX_B200_STASH_BUDGET_MB", str((3 * per_layer_o + per_layer_gu + 1024) / (1 << 20)))
+    curves = {}
+    for policy in ("full", "selective", "auto"):
+        from omegalax_b200.parallel import mesh as mesh_lib
+
+        mesh_lib.set_default_mesh(None)
+        tcfg = trainer.TrainConfig(batch_size=B, seq_len=T, num_steps=8, learning_rate=1e-3, max_grad_norm=1.0,
+                                   remat_policy=policy, grad_accum_steps=2)
+        model, cfg = trainer.init_model(cfg0, 0, tp_size=1, fsdp_size=1, dp_size=1, meta=True)
+        opt = trainer.build_optimizer(model, tcfg, device=dev)
+        step = trainer.make_sft_train_step(cfg)
+        g = torch.Generator().manual_seed(5)
+        tok = torch.randint(1, cfg.vocab_size, (B, T), generator=g, dtype=torch.int32).to(dev)
+        batch = {"token_ids_BT": tok, "attention_mask_BT": torch.ones_like(tok), "loss_mask_BT": torch.ones_like(tok)}
+        curves[policy] = [float(step(opt, batch)[0]) for _ in range(8)]
+        lib.check_status()
+        if policy == "auto":
+            auto = opt._auto
+            assert auto.phase == "done" and auto.summary() == {"o": 3, "gate_up": 1}, auto.summary()
+    for policy in ("selective", "auto"):
+        for a, b in zip(curves[policy], curves["full"]):
+            assert abs(a - b) < 2e-2 * max(1.0, abs(b)), curves
+    assert curves["full"][-1] < curves["full"][0]
+
+
 def test_qwen3_vl_kernels_match_reference_ops():
     """Qwen3-VL with an image: vision tower (LayerNorm, tanh-GELU, non-causal varlen attention,
     interpolated position table), feature scatter, DeepStack adds and the 3-D MRoPE decoder."""

@@ -136,6 +136,32 @@ def test_stash_records_replays_and_skips():
     assert Fn._stash_lookup("qkv") == (None, None)           # no active stash outside the scopes
 
 
+def test_auto_stash_shares_the_budget_by_value_per_byte():
+    """Remat policy "auto": every layer gets the first extra tag before any layer gets the second;
+    what does not fit is dropped from the recorded stash and is recomputed in the re-run."""
+    import torch
+
+    from omegalax_b200.ops import functional as Fn
+    from omegalax_b200.parallel.engine import _AutoStash
+
+    auto = _AutoStash(("o", "gate_up"), margin_bytes=0)
+    assert auto.tags_for(0, ("qkv",)) == ("qkv",)             # nothing extra before a budget exists
+    auto.budget, auto.n_layers, auto.phase = 4 * 40 + 2 * 400 + 100, 4, "grow"
+    kept = []
+    for idx in range(4):
+        st = Fn._Stash(auto.tags_for(idx, ("qkv", "down!")))
+        assert "o" in st.tags and "gate_up" in st.tags and "down" in st.skip
+        st.items = {("qkv", 0): torch.zeros(5), ("o", 0): torch.zeros(10), ("gate_up", 0): torch.zeros(100)}
+        auto.account(idx, st)
+        kept.append(sorted(k[0] for k in st.items))
+    assert kept == [["gate_up", "o", "qkv"]] * 2 + [["o", "qkv"]] * 2
+    assert auto.summary() == {"o": 4, "gate_up": 2}
+    auto.close()
+    assert auto.phase == "done"
+    assert auto.tags_for(1, ("qkv",)) == ("qkv", "o", "gate_up") and auto.tags_for(3, ("qkv",)) == ("qkv", "o")
+    assert auto.tags_for(7, ("qkv",)) == ("qkv",)             # a layer that was never recorded
+
+
 def test_gemm_dispatch_heuristics():
     """Host-side choices of the GEMM wrappers: CTA-pair kernel for GEMMs that fill every SM pair,
     an even number of copy CTAs that grows with the bytes to gather per unit of GEMM time."""
