@@ -116,6 +116,8 @@ class PeerHeartbeat:
         self.store, self.rank, self.world = store, int(rank), int(world)
         self.interval_s, self.max_age_s, self.prefix = interval_s, max_age_s, prefix
         self._stop = threading.Event()
+        self._lock = threading.Lock()
+        self._left = False
         self._seen: dict[int, tuple[int, float]] = {}
         self._count = 0
         self._thread = threading.Thread(target=self._run, name="peer-heartbeat", daemon=True)
@@ -131,8 +133,11 @@ class PeerHeartbeat:
         return self
 
     def _publish(self):
-        self._count += 1
-        self.store.set(self._key(self.rank), str(self._count))
+        with self._lock:
+            if self._left:       # "left" stays the last word of this rank
+                return
+            self._count += 1
+            self.store.set(self._key(self.rank), str(self._count))
 
     def _run(self):
         while not self._stop.wait(self.interval_s):
@@ -144,10 +149,12 @@ class PeerHeartbeat:
     def leave(self):
         """Announce an orderly exit (between steps, nothing in flight), then stop beating."""
         self._stop.set()
-        try:
-            self.store.set(self._key(self.rank), "left")
-        except Exception:
-            pass
+        with self._lock:         # a beat that is being written finishes first and none follows
+            self._left = True
+            try:
+                self.store.set(self._key(self.rank), "left")
+            except Exception:
+                pass
 
     def stop(self):
         self._stop.set()
