@@ -230,11 +230,11 @@ def main() -> int:
     micro = min(micro, args.seqs_per_gpu)
     accum = args.seqs_per_gpu // micro
     T = args.seq_len
-    # One GPU holds all fp32 state (148 GB): the small attention-side tensors are kept from the first
-    # forward, and the memory that is left after one whole step decides how many layers also keep the
-    # attention block's output and the wide MLP activation ("auto").  With the state sharded there is
-    # room to keep them in every layer ("selective").
-    remat = args.remat or ("auto" if N == 1 else "selective")
+    # "auto": the small attention-side tensors are kept from the first forward, and the memory that is
+    # left after one whole step decides how many layers also keep the attention block's output and the
+    # wide MLP activation.  One GPU holds all fp32 state (148 GB) and has room for about 15 layers; from
+    # 4 GPUs on every layer keeps them (the same as "selective").
+    remat = args.remat or "auto"
     if args.model != "qwen3-8b" and args.remat is None:
         # the small-hidden models have room for the stashed attention-side outputs; the Qwen3.5 slice
         # (117 GB of expert state per GPU at 8 GPUs) recomputes whole layers

@@ -178,9 +178,10 @@ __global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict_
 }
 
 // dgu = [dact * up * dsilu(gate) | dact * silu(gate)]; optionally also re-emits act.
-__global__ void swiglu_bwd_kernel(const bf16* __restrict__ gu, const bf16* __restrict__ dact,
-                                  bf16* __restrict__ dgu, bf16* __restrict__ act_out, long long M,
-                                  int F) {
+// dgu may be gu itself (no __restrict__ on the two): every thread reads its eight gate and up
+// values before it writes the gradients to the same places, and no other thread touches them.
+__global__ void swiglu_bwd_kernel(const bf16* gu, const bf16* __restrict__ dact, bf16* dgu,
+                                  bf16* __restrict__ act_out, long long M, int F) {
   const int fv = F >> 3;
   const long long total = M * fv;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;

@@ -384,7 +384,9 @@ class _SwiGLULinearFn(torch.autograd.Function):
     """y = (silu(gate) * up) @ w.T (+ residual) as one node.  Only [gate | up] is kept for the
     backward pass: the activation, which the weight gradient needs, comes back out of the SwiGLU
     backward kernel, which reads gate and up anyway.  When the output is already known (a layer
-    re-run whose result nobody reads) nothing at all is computed in forward."""
+    re-run whose result nobody reads) nothing at all is computed in forward.  The backward pass is
+    the last reader of [gate | up] and writes its gradient over it (a non-leaf input only; a graph
+    kept for a second backward pass would find it overwritten)."""
 
     @staticmethod
     def forward(ctx, gu, w, residual, y_pre=None):
@@ -397,6 +399,7 @@ class _SwiGLULinearFn(torch.autograd.Function):
         ctx.shp = shp
         ctx.has_res = residual is not None
         ctx.w_ref = w
+        ctx.inplace = bool(gu.requires_grad and not gu.is_leaf and g2.is_contiguous())
         return y.view(*shp[:-1], w.shape[0])
 
     @staticmethod
@@ -407,7 +410,7 @@ class _SwiGLULinearFn(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dact = K.gemm(dy2, w, b_mn=True)
-        dgu, act = K.swiglu_bwd(g2, dact, with_act=True)
+        dgu, act = K.swiglu_bwd(g2, dact, with_act=True, inplace=ctx.inplace)
         del dact
         dw = None
         pg = getattr(w_obj, "peer_grad", None)

@@ -261,15 +261,18 @@ def swiglu_fwd(gu):
     return act.view(*gu.shape[:-1], F)
 
 
-def swiglu_bwd(gu, dact, with_act: bool = False):
+def swiglu_bwd(gu, dact, with_act: bool = False, inplace: bool = False):
     """Gradient of silu(gate) * up; ``with_act`` also returns the activation itself, recomputed in
-    the same pass (for a caller that did not keep it)."""
+    the same pass (for a caller that did not keep it); ``inplace`` writes the gradient over
+    ``gu`` (contiguous), for a caller that is the last reader of it."""
     g2 = gu.reshape(-1, gu.shape[-1])
     F = g2.shape[1] // 2
     d2 = dact.reshape(-1, F)
     if not d2.is_contiguous():
         d2 = d2.contiguous()
-    dgu = torch.empty_like(g2)
+    if inplace and not g2.is_contiguous():
+        raise ValueError("swiglu_bwd(inplace=True) needs a contiguous [gate | up] tensor")
+    dgu = g2 if inplace else torch.empty_like(g2)
     act = torch.empty(g2.shape[0], F, dtype=gu.dtype, device=gu.device) if with_act else None
     _call("ob_swiglu_bwd", g2.data_ptr(), d2.data_ptr(), dgu.data_ptr(), lib.ptr(act), g2.shape[0], F,
           lib.stream_ptr())

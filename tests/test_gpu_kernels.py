@@ -363,21 +363,24 @@ def test_swiglu():
     assert _rel_err(gu.grad, gr.grad) < 2e-2
 
 
-@pytest.mark.parametrize("with_res", [False, True])
-def test_swiglu_linear_keeps_only_gate_up(with_res):
+@pytest.mark.parametrize("with_res,leaf", [(False, True), (True, True), (True, False)])
+def test_swiglu_linear_keeps_only_gate_up(with_res, leaf):
     """silu(gate) * up followed by the down projection as one autograd node: the activation is not
-    kept, its copy for the weight gradient comes out of the SwiGLU backward kernel."""
+    kept, its copy for the weight gradient comes out of the SwiGLU backward kernel.  A non-leaf
+    [gate | up] (the usual case: a projection's output) receives its gradient in place."""
     from omegalax_b200.ops import functional as Fn, lib
     torch.manual_seed(41)
     M, Fh, D = 300, 256, 136
-    gu = (0.7 * torch.randn(M, 2 * Fh, device=_dev())).to(bf16).requires_grad_(True)
+    gu0 = (0.7 * torch.randn(M, 2 * Fh, device=_dev())).to(bf16).requires_grad_(True)
+    gu = gu0 if leaf else gu0 * 1.0
+    ptr = gu.data_ptr()
     w = (torch.randn(D, Fh, device=_dev()) / 16).to(bf16).requires_grad_(True)
     res = torch.randn(M, D, device=_dev()).to(bf16).requires_grad_(True) if with_res else None
     y = Fn.swiglu_linear(gu, w, res)
     dy = torch.randn_like(y)
     y.backward(dy)
     _check(lib)
-    gr, wr = gu.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    gr, wr = gu0.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
     act = torch.nn.functional.silu(gr[:, :Fh]) * gr[:, Fh:]
     yr = act.to(bf16).float() @ wr.t()          # the kernel path rounds the activation to bf16 too
     if with_res:
@@ -385,10 +388,12 @@ def test_swiglu_linear_keeps_only_gate_up(with_res):
         yr = yr + rr
     yr.backward(dy.float())
     torch.testing.assert_close(y.float(), yr, rtol=2.0 ** -7, atol=2e-2)
-    torch.testing.assert_close(gu.grad.float(), gr.grad, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(gu0.grad.float(), gr.grad, rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(w.grad.float(), wr.grad, rtol=2e-2, atol=6e-2)
     if with_res:
         assert torch.equal(res.grad, dy)
+    if not leaf:      # the gradient was written over the (dead) input, not into a new buffer
+        assert torch.equal(gu.detach().view(-1)[:64], gu0.grad.view(-1)[:64]) and gu.data_ptr() == ptr
 
 
 @pytest.mark.parametrize("Kd,rot,qs", [(128, 128, 1), (64, 64, 1), (256, 64, 2)])
