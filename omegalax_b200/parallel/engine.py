@@ -766,14 +766,17 @@ class _RematLayerFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, engine: TrainEngine, unit: Unit, layer, fctx):
         engine._acquire(unit, +1)
-        tags, auto = engine.remat_tags, engine._auto
-        if auto is not None and unit.name.startswith("layers."):
+        # a forward pass that no backward pass follows (evaluation) keeps nothing and decides nothing
+        training = bool(ctx.needs_input_grad[0])
+        tags, auto = (engine.remat_tags if training else ()), engine._auto
+        is_layer = unit.name.startswith("layers.")
+        if auto is not None and is_layer and training:
             idx = int(unit.name.split(".")[1])
             tags = auto.tags_for(idx, tags)
         stash = Fn._Stash(tags) if tags else None
         with torch.no_grad(), Fn.stash_scope(stash, "record"):
             y, aux = layer(x, fctx)
-        if auto is not None and stash is not None and unit.name.startswith("layers."):
+        if auto is not None and stash is not None and is_layer and training:
             auto.account(idx, stash)
         ctx.stash = stash
         ctx.save_for_backward(x)
