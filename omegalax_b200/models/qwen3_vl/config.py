@@ -45,6 +45,7 @@ class Qwen3VLConfig:
     image_token_id: int
     video_token_id: int
     vision_start_token_id: int
+    vision_end_token_id: int | None = None   # carried through from a loaded HF config; not used by the model
     moe_intermediate_size: int = 0
     num_experts: int = 0
     num_experts_per_tok: int = 0
@@ -189,5 +190,6 @@ def make_vl_config_from_hf(hf_cfg: dict[str, Any]) -> Qwen3VLConfig:
         decoder_sparse_step=txt.get("decoder_sparse_step", 1) if moe else 1,
         norm_topk_prob=txt.get("norm_topk_prob", True) if moe else True,
         image_token_id=_req(hf_cfg, "image_token_id", "hf_cfg"), video_token_id=_req(hf_cfg, "video_token_id", "hf_cfg"),
-        vision_start_token_id=_req(hf_cfg, "vision_start_token_id", "hf_cfg"), dtype=tdt,
+        vision_start_token_id=_req(hf_cfg, "vision_start_token_id", "hf_cfg"),
+        vision_end_token_id=hf_cfg.get("vision_end_token_id"), dtype=tdt,
         vision=Qwen3VLVisionConfig(deepstack_visual_indexes=tuple(_req(vis, "deepstack_visual_indexes", V)), dtype=vdt, **vkw))

@@ -31,11 +31,13 @@ def qwen3_vl_to_hf_config_dict(cfg: Qwen3VLConfig) -> dict:
            "spatial_merge_size": v.spatial_merge_size, "out_hidden_size": v.out_hidden_size, "depth": v.depth,
            "hidden_act": v.hidden_act, "num_position_embeddings": v.num_position_embeddings,
            "deepstack_visual_indexes": list(v.deepstack_visual_indexes), "dtype": torch_dtype_to_hf(v.dtype)}
-    return {"architectures": ["Qwen3VLMoeForConditionalGeneration" if cfg.is_moe else "Qwen3VLForConditionalGeneration"],
-            "model_type": "qwen3_vl_moe" if cfg.is_moe else "qwen3_vl", "text_config": txt, "vision_config": vis,
-            "tie_word_embeddings": cfg.tie_word_embeddings, "image_token_id": cfg.image_token_id,
-            "video_token_id": cfg.video_token_id, "vision_start_token_id": cfg.vision_start_token_id,
-            "vision_end_token_id": cfg.vision_start_token_id + 1}
+    out = {"architectures": ["Qwen3VLMoeForConditionalGeneration" if cfg.is_moe else "Qwen3VLForConditionalGeneration"],
+           "model_type": "qwen3_vl_moe" if cfg.is_moe else "qwen3_vl", "text_config": txt, "vision_config": vis,
+           "tie_word_embeddings": cfg.tie_word_embeddings, "image_token_id": cfg.image_token_id,
+           "video_token_id": cfg.video_token_id, "vision_start_token_id": cfg.vision_start_token_id}
+    if cfg.vision_end_token_id is not None:   # only what a loaded config said; never guessed
+        out["vision_end_token_id"] = cfg.vision_end_token_id
+    return out
 
 
 def export_qwen3_vl_to_safetensors(model, cfg: Qwen3VLConfig, out_dir) -> Path:
