@@ -79,11 +79,27 @@ def iter_payload_blocks(jsonl_path, messages_per_record: int):
                        "message_end": end, "session_meta": meta, "messages": msgs[start:end]}
 
 
+def _prepare_output_dir(out: Path, overwrite: bool) -> None:
+    """A non-empty output directory is refused unless ``overwrite``, which empties it first
+    (reference: omegalax/data/grain_pipeline.py:28-40)."""
+    import shutil
+
+    if out.exists() and any(out.iterdir()):
+        if not overwrite:
+            raise ValueError(f"Refusing to overwrite non-empty output directory: {out}")
+        for child in out.iterdir():
+            if child.is_dir() and not child.is_symlink():
+                shutil.rmtree(child)
+            else:
+                child.unlink()
+    out.mkdir(parents=True, exist_ok=True)
+
+
 def compile_jsonl_to_records(jsonl_path, out_dir, *, messages_per_record: int = 64,
-                             records_per_shard: int = 4096) -> dict:
+                             records_per_shard: int = 4096, overwrite: bool = False) -> dict:
     """Stage 1.  Returns the metadata dict that was written."""
     out = Path(out_dir)
-    out.mkdir(parents=True, exist_ok=True)
+    _prepare_output_dir(out, overwrite)
     w = _ShardedWriter(out, records_per_shard)
     sessions = set()
     for block in iter_payload_blocks(jsonl_path, messages_per_record):
@@ -138,7 +154,7 @@ def _token_stats(lengths: list[int], max_length: int) -> dict:
 
 def build_chunk_index(payload_dir, out_dir, length_fn: Callable[[dict], Any], *, max_length: int,
                       num_workers: int = 0, records_per_shard: int = 65536, profile_metadata: dict | None = None,
-                      write_token_stats: bool = True) -> dict:
+                      write_token_stats: bool = True, overwrite: bool = False) -> dict:
     """Stage 2.  ``length_fn(message)`` returns a token count or a dict with ``length`` and
     optional ``vision_tokens`` / ``vision_patches`` / ``num_images``."""
     src = open_source(payload_dir)
@@ -152,7 +168,7 @@ def build_chunk_index(payload_dir, out_dir, length_fn: Callable[[dict], Any], *,
         measured = [_measure_block(r) for r in raws]
 
     out = Path(out_dir)
-    out.mkdir(parents=True, exist_ok=True)
+    _prepare_output_dir(out, overwrite)
     w = _ShardedWriter(out, records_per_shard)
     lengths: list[int] = []
     cur = None  # open chunk

@@ -10,10 +10,12 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
 class Flags(argparse.ArgumentParser):
-    def define(self, name: str, default=None, help: str = "", type=None, choices=None):
-        names = [f"--{name}"]
-        if "_" in name:
-            names.append(f"--{name.replace('_', '-')}")
+    def define(self, name: str, default=None, help: str = "", type=None, choices=None, aliases=()):
+        names = []
+        for n in (name, *aliases):
+            names.append(f"--{n}")
+            if "_" in n:
+                names.append(f"--{n.replace('_', '-')}")
         if isinstance(default, bool):
             self.add_argument(*names, dest=name, default=default, help=help,
                               type=lambda s: str(s).lower() in ("1", "true", "yes", "y"), nargs="?", const=True)

@@ -122,3 +122,41 @@ def test_required_epochs():
     assert P.required_epochs_for_batches(100, 8, 10, dp_size=2) == 2
     with pytest.raises(ValueError):
         P.required_epochs_for_batches(3, 8, 1)
+
+
+def test_dataset_scripts_take_the_reference_flags_and_refuse_to_overwrite(tmp_path):
+    """Both build stages through their command lines, with the flag names of the reference's scripts
+    (scripts/compile_sft_dataset.py:11-15, scripts/build_sft_chunk_index.py:16-25); a second run into
+    the same directory is refused without --overwrite."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    jl = tmp_path / "train.jsonl"
+    _write_jsonl(jl, sessions=9)
+    env = dict(os.environ, PYTHONPATH=root)
+
+    def run(script, *args):
+        return subprocess.run([sys.executable, os.path.join(root, "scripts", script), *args], env=env,
+                              capture_output=True, text=True, timeout=300)
+
+    a = run("compile_sft_dataset.py", "--data_path", str(jl), "--out_dir", str(tmp_path / "payload"),
+            "--messages_per_record", "2", "--records_per_shard", "5")
+    assert a.returncode == 0, a.stderr
+    again = run("compile_sft_dataset.py", "--data_path", str(jl), "--out_dir", str(tmp_path / "payload"))
+    assert again.returncode != 0 and "Refusing to overwrite" in again.stderr
+    a = run("compile_sft_dataset.py", "--data_path", str(jl), "--out_dir", str(tmp_path / "payload"), "--overwrite",
+            "--messages_per_record", "2")
+    assert a.returncode == 0, a.stderr
+    b = run("build_sft_chunk_index.py", "--data_path", str(tmp_path / "payload"), "--out_dir", str(tmp_path / "index"),
+            "--model_id", "qwen3-smoke", "--max_length", "96", "--records_per_shard", "4", "--num_workers", "2")
+    assert b.returncode == 0, b.stderr
+    meta = P.load_metadata(tmp_path / "index")
+    assert meta["num_records"] > 0 and meta["num_shards"] > 1
+    assert meta.get("profile", meta).get("model_id", "qwen3-smoke") == "qwen3-smoke"
+    # the older spellings still work
+    c = run("build_sft_chunk_index.py", "--payload_dir", str(tmp_path / "payload"), "--output_dir",
+            str(tmp_path / "index2"), "--tokenizer", "stub", "--max-length", "96", "--num_workers", "0")
+    assert c.returncode == 0, c.stderr
+    assert P.load_metadata(tmp_path / "index2")["num_records"] == meta["num_records"]
