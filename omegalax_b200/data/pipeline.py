@@ -10,12 +10,15 @@ Stage 2  ``build_chunk_index``: every message is measured once (optionally on a 
          an error); chunk descriptors go into their own record files.
 Stage 3  ``make_data_iterator``: global shuffle per epoch (seeded), sharding over the
          data-parallel ranks with the remainder dropped, random access into the payload to
-         resolve each descriptor, batching through a collator, background prefetch, and
-         ``get_state`` / ``set_state`` so that a resumed run continues with the next batch.
+         resolve each descriptor (rows of a batch on a thread pool), batching through a collator
+         on a prefetch thread or on worker processes that build batches in turn, and
+         ``get_state`` / ``set_state`` so that a resumed run continues with the next batch
+         whatever the thread / process counts on either side.
 Functional reference: omegalax/data/grain_pipeline.py (which builds on grain + array_record).
 """
 from __future__ import annotations
 
+import dataclasses
 import json
 import multiprocessing as mp
 import queue
@@ -117,7 +120,33 @@ compile_jsonl_to_arrayrecord = compile_jsonl_to_records  # name used by the refe
 
 
 def load_metadata(path) -> dict:
-    return json.loads((Path(path) / METADATA).read_text())
+    mp_ = Path(path).expanduser() / METADATA
+    if not mp_.exists():
+        raise ValueError(f"compiled dataset metadata does not exist: {mp_}")
+    return json.loads(mp_.read_text())
+
+
+load_compiled_metadata = load_metadata  # name used by the reference (grain_pipeline.py:231)
+
+
+def resolve_record_paths(path) -> list[Path]:
+    """Shard files of a compiled dataset directory (or the one shard file that was named), checked
+    for existence (reference: resolve_arrayrecord_paths, grain_pipeline.py:210-228)."""
+    path = Path(path).expanduser().resolve()
+    if path.is_file():
+        if path.suffix != ".olrf":
+            raise ValueError(f"expected a record shard (.olrf) or a dataset directory, got file: {path}")
+        return [path]
+    shards = [path / rel for rel in load_metadata(path)["shard_paths"]]
+    if not shards:
+        raise ValueError(f"no record shards found under: {path}")
+    missing = [p for p in shards if not p.exists()]
+    if missing:
+        raise ValueError(f"missing record shard(s): {missing}")
+    return shards
+
+
+resolve_arrayrecord_paths = resolve_record_paths
 
 
 def open_source(path) -> ShardedRecordSource:
@@ -260,6 +289,10 @@ class IndexSampler:
         return int(self.epoch_order(epoch)[k])
 
 
+def _identity(d):
+    return d
+
+
 class ChunkResolver:
     """Turns a chunk descriptor into the example dict a collator consumes by random access
     into the payload shards."""
@@ -267,6 +300,9 @@ class ChunkResolver:
     def __init__(self, payload_path):
         self.payload_path = str(payload_path)
         self._src: ShardedRecordSource | None = None
+
+    def __getstate__(self):
+        return {"payload_path": self.payload_path, "_src": None}
 
     def __call__(self, desc: dict) -> dict:
         if self._src is None:
@@ -284,47 +320,168 @@ class ChunkResolver:
         return out
 
 
+@dataclasses.dataclass(frozen=True)
+class ReadOptions:
+    """How the rows of one batch are fetched: ``num_threads`` rows are read and resolved against
+    the payload at the same time (the record files are memory-mapped; the reads and the JSON
+    decoding of large image payloads overlap); ``prefetch_buffer_size`` batches are kept ready
+    ahead of the consumer when no worker processes are used.  (reference: grain.ReadOptions as built by
+    omegalax/data/grain_pipeline.py:587-592)"""
+
+    num_threads: int = 16
+    prefetch_buffer_size: int = 2
+
+
+@dataclasses.dataclass(frozen=True)
+class MultiprocessingOptions:
+    """``num_workers`` processes build batches in turn (worker w builds batches w, w + N, ...), each
+    keeping ``per_worker_buffer_size`` finished batches ready; 0 builds them on a thread of the
+    training process.  (reference: grain.MultiprocessingOptions, grain_pipeline.py:595-605)"""
+
+    num_workers: int = 0
+    per_worker_buffer_size: int = 1
+    # "fork": the collator and tokenizer reach the workers by inheritance (anything works, but the
+    # parent should not hold locks in other threads at that moment); "spawn" / "forkserver": they
+    # are pickled into fresh interpreters (no inherited threads or CUDA state)
+    start_method: str = "fork"
+
+
+def make_grain_read_options(*, num_threads: int = 16, prefetch_buffer_size: int = 500) -> ReadOptions:
+    """The reference's prefetch buffer counts records; here it counts batches and is capped."""
+    return ReadOptions(num_threads=max(int(num_threads), 1), prefetch_buffer_size=max(2, min(int(prefetch_buffer_size), 8)))
+
+
+def make_grain_multiprocessing_options(*, num_workers: int = 0, per_worker_buffer_size: int = 1,
+                                       enable_profiling: bool = False, start_method: str = "fork") -> MultiprocessingOptions:
+    del enable_profiling   # grain's own profiler; nothing to switch on here
+    if start_method not in ("fork", "spawn", "forkserver"):
+        raise ValueError(f"unknown start method {start_method!r}")
+    return MultiprocessingOptions(num_workers=max(int(num_workers), 0),
+                                  per_worker_buffer_size=max(int(per_worker_buffer_size), 1), start_method=start_method)
+
+
+def _worker_process_main(it: "DataIterator", wid: int, nworkers: int, start: int, q, stop):
+    """Body of one loader process (forked, so ``it`` is the parent's iterator object): builds the
+    batches b >= start with b % nworkers == wid, in order, until the data ends or ``stop`` is set."""
+    import pickle
+    import traceback
+
+    b = start + ((wid - start) % nworkers)
+    pool = it._row_pool()
+    try:
+        while not stop.is_set():
+            try:
+                item = it._make_batch(b, pool)
+                payload = ("ok", item)
+                pickle.dumps(payload)     # a batch that cannot cross the process boundary is reported, not lost
+            except BaseException as e:    # delivered to the consumer
+                payload = ("err", f"{type(e).__name__}: {e}\n{traceback.format_exc()}")
+            while not stop.is_set():
+                try:
+                    q.put((b, payload), timeout=0.1)
+                    break
+                except queue.Full:
+                    continue
+            if payload[0] == "err" or payload[1] is None:
+                break
+            b += nworkers
+    finally:
+        if pool is not None:
+            pool.shutdown(wait=False)
+        q.close()
+        q.join_thread()
+
+
+class DataLoaderError(RuntimeError):
+    """A loader process failed; the message carries its traceback."""
+
+
 class DataIterator:
     """Checkpointable batch iterator.  ``state`` is the number of batches handed out; restoring
-    it makes the next ``next()`` return exactly the batch the saved run would have produced."""
+    it makes the next ``next()`` return exactly the batch the saved run would have produced,
+    whatever the number of threads or worker processes on either side."""
 
     def __init__(self, index_source, sampler: IndexSampler, transform: Callable[[dict], dict], batch_size: int,
-                 batch_fn: Callable[[list], Any], *, prefetch: int = 2, read_threads: int = 4):
+                 batch_fn: Callable[[list], Any], *, prefetch: int = 2, read_threads: int = 4, num_workers: int = 0,
+                 worker_buffer: int = 1, start_method: str = "fork"):
         self.src, self.sampler, self.transform = index_source, sampler, transform
         self.batch_size, self.batch_fn = batch_size, batch_fn
-        self.prefetch, self.read_threads = max(int(prefetch), 0), read_threads
+        self.prefetch, self.read_threads = max(int(prefetch), 0), max(int(read_threads), 1)
+        self.num_workers, self.worker_buffer = max(int(num_workers), 0), max(int(worker_buffer), 1)
+        self.start_method = start_method
         self._consumed = 0
         self._q: queue.Queue | None = None
         self._thread: threading.Thread | None = None
         self._stop = threading.Event()
+        self._procs: list = []
+        self._pqs: list = []
+        self._pstop = None
+        self._pool = None
 
-    def _make_batch(self, b: int):
-        rows = []
+    def __getstate__(self):     # what a spawned loader process needs: no queues, threads or children
+        st = dict(self.__dict__)
+        st.update(_q=None, _thread=None, _stop=None, _procs=[], _pqs=[], _pstop=None, _pool=None)
+        return st
+
+    def __setstate__(self, st):
+        self.__dict__.update(st)
+        self._stop = threading.Event()
+
+    def _row_pool(self):
+        if self.read_threads <= 1 or self.batch_size <= 1:
+            return None
+        from concurrent.futures import ThreadPoolExecutor
+
+        return ThreadPoolExecutor(max_workers=min(self.read_threads, self.batch_size), thread_name_prefix="loader-row")
+
+    def _row(self, rec: int):
+        return self.transform(json.loads(self.src[rec]))
+
+    def _make_batch(self, b: int, pool=None):
+        recs = []
         for k in range(self.batch_size):
             rec = self.sampler.record_at(b * self.batch_size + k)
             if rec is None:
                 return None
-            rows.append(self.transform(json.loads(self.src[rec])))
+            recs.append(rec)
+        rows = list(pool.map(self._row, recs)) if pool is not None else [self._row(r) for r in recs]
         return self.batch_fn(rows)
 
     def _worker(self, start: int, q: queue.Queue, stop: threading.Event):
         b = start
-        while not stop.is_set():
-            try:
-                item = self._make_batch(b)
-            except BaseException as e:  # delivered to the consumer
-                item = e
+        pool = self._row_pool()
+        try:
             while not stop.is_set():
                 try:
-                    q.put((b, item), timeout=0.1)
-                    break
-                except queue.Full:
-                    continue
-            if item is None or isinstance(item, BaseException):
-                return
-            b += 1
+                    item = self._make_batch(b, pool)
+                except BaseException as e:  # delivered to the consumer
+                    item = e
+                while not stop.is_set():
+                    try:
+                        q.put((b, item), timeout=0.1)
+                        break
+                    except queue.Full:
+                        continue
+                if item is None or isinstance(item, BaseException):
+                    return
+                b += 1
+        finally:
+            if pool is not None:
+                pool.shutdown(wait=False)
 
     def _ensure_worker(self):
+        if self.num_workers > 0:
+            if self._procs:
+                return
+            ctx = mp.get_context(self.start_method)
+            self._pstop = ctx.Event()
+            self._pqs = [ctx.Queue(maxsize=self.worker_buffer) for _ in range(self.num_workers)]
+            for w in range(self.num_workers):
+                p = ctx.Process(target=_worker_process_main, name=f"loader-{w}", daemon=True,
+                                args=(self, w, self.num_workers, self._consumed, self._pqs[w], self._pstop))
+                p.start()
+                self._procs.append(p)
+            return
         if self.prefetch == 0 or self._thread is not None:
             return
         self._stop = threading.Event()
@@ -337,13 +494,59 @@ class DataIterator:
             self._stop.set()
             self._thread.join(timeout=5)
             self._thread, self._q = None, None
+        if self._procs:
+            self._pstop.set()
+            for q in self._pqs:          # unblock producers that wait on a full queue
+                try:
+                    while True:
+                        q.get_nowait()
+                except Exception:
+                    pass
+            for p in self._procs:
+                p.join(timeout=5)
+                if p.is_alive():
+                    p.terminate()
+                    p.join(timeout=2)
+            for q in self._pqs:
+                q.close()
+                q.cancel_join_thread()
+            self._procs, self._pqs, self._pstop = [], [], None
+        if self._pool is not None:
+            self._pool.shutdown(wait=False)
+            self._pool = None
 
     def __iter__(self):
         return self
 
+    def _next_from_processes(self):
+        w = self._consumed % self.num_workers
+        q, p = self._pqs[w], self._procs[w]
+        while True:
+            try:
+                b, (kind, item) = q.get(timeout=1.0)
+                break
+            except queue.Empty:
+                if not p.is_alive():
+                    try:                 # it may have finished between the time-out and this check
+                        b, (kind, item) = q.get(timeout=0.5)
+                        break
+                    except queue.Empty:
+                        self._shutdown()
+                        raise DataLoaderError(f"loader process {w} exited with code {p.exitcode} without a result") from None
+        assert b == self._consumed, (b, self._consumed)
+        if kind == "err":
+            self._shutdown()
+            raise DataLoaderError(f"loader process {w} failed on batch {b}:\n{item}")
+        return item
+
     def __next__(self):
-        if self.prefetch == 0:
-            item = self._make_batch(self._consumed)
+        if self.num_workers > 0:
+            self._ensure_worker()
+            item = self._next_from_processes()
+        elif self.prefetch == 0:
+            if self._pool is None:
+                self._pool = self._row_pool()
+            item = self._make_batch(self._consumed, self._pool)
         else:
             self._ensure_worker()
             b, item = self._q.get()
@@ -379,12 +582,27 @@ class DataIterator:
             pass
 
 
-def make_data_iterator(index_path, *, batch_size: int, collator: Callable[[list], Any], shuffle: bool = True,
+def make_data_iterator(index_path, *, batch_size: int, collator: Callable[[list], Any] | None = None, shuffle: bool = True,
                        seed: int = 0, num_epochs: int | None = None, dp_index: int | None = None,
                        dp_size: int | None = None, prefetch: int = 2, read_threads: int = 4,
-                       resolve_chunks: bool = True) -> DataIterator:
+                       resolve_chunks: bool = True, read_options: ReadOptions | None = None,
+                       multiprocessing_options: MultiprocessingOptions | None = None, batch_fn=None) -> DataIterator:
     """Stage 3.  ``batch_size`` is per data-parallel rank.  ``dp_index`` / ``dp_size`` default to
-    this process's position in the active mesh (or its torch.distributed rank)."""
+    this process's position in the active mesh (or its torch.distributed rank).  ``read_options`` /
+    ``multiprocessing_options`` (``make_grain_read_options`` / ``make_grain_multiprocessing_options``)
+    take precedence over ``prefetch`` / ``read_threads``; ``batch_fn`` is the reference's name for
+    ``collator``."""
+    collator = collator if batch_fn is None else batch_fn
+    if collator is None:
+        raise TypeError("make_data_iterator needs a collator (batch_fn)")
+    if batch_size <= 0:
+        raise ValueError("batch_size must be > 0")
+    nworkers, wbuf, start = 0, 1, "fork"
+    if read_options is not None:
+        prefetch, read_threads = read_options.prefetch_buffer_size, read_options.num_threads
+    if multiprocessing_options is not None:
+        nworkers, wbuf = multiprocessing_options.num_workers, multiprocessing_options.per_worker_buffer_size
+        start = multiprocessing_options.start_method
     from ..parallel import mesh as mesh_lib
 
     if dp_size is None:
@@ -396,10 +614,11 @@ def make_data_iterator(index_path, *, batch_size: int, collator: Callable[[list]
     if resolve_chunks and meta.get("kind") == "chunk_index":
         transform = ChunkResolver(meta["payload_path"])
     else:
-        transform = lambda d: d  # noqa: E731
+        transform = _identity
     sampler = IndexSampler(len(src), shuffle=shuffle, seed=seed, num_epochs=num_epochs, dp_index=dp_index,
                            dp_size=dp_size)
-    return DataIterator(src, sampler, transform, batch_size, collator, prefetch=prefetch, read_threads=read_threads)
+    return DataIterator(src, sampler, transform, batch_size, collator, prefetch=prefetch, read_threads=read_threads,
+                        num_workers=nworkers, worker_buffer=wbuf, start_method=start)
 
 
 make_grain_iterator = make_data_iterator  # name used by the reference scripts

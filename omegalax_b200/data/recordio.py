@@ -115,6 +115,17 @@ class RecordReader:
     def __init__(self, path, native: bool | None = None, verify: bool = True):
         self.path = str(path)
         self.verify = verify
+        self._native_arg = native
+        self._open(native)
+
+    def __getstate__(self):     # travels to another process as its path and is opened again there
+        return {"path": self.path, "verify": self.verify, "native": self._native_arg}
+
+    def __setstate__(self, st):
+        self.path, self.verify, self._native_arg = st["path"], st["verify"], st["native"]
+        self._open(self._native_arg)
+
+    def _open(self, native):
         L = _native() if native is not False else None
         self._L = L
         if L is not None:

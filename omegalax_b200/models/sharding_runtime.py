@@ -67,6 +67,12 @@ def _to_device(x, device, pinned: bool = True):
     return x.to(dev, non_blocking=True)
 
 
+def batch_partition_spec(shd_cfg):
+    """Layout of a [B, T] batch: the batch dim over the data axes of the activation layout, the
+    sequence dim whole (reference: omegalax/models/sharding_runtime.py:55-56)."""
+    return (shd_cfg.act_btd[0], None)
+
+
 def shard_batch(token_ids_BT, shd_cfg=None, mesh=None, device=None):
     device = device or ("cuda" if torch.cuda.is_available() else "cpu")
     return _to_device(token_ids_BT, device)

@@ -67,7 +67,7 @@ def align_config_to_mesh(cfg, mesh: Mesh):
 
 
 def batch_partition_spec(cfg):
-    return (cfg.shd_cfg.act_btd[0], None)
+    return _rt.batch_partition_spec(cfg.shd_cfg)
 
 
 def shard_batch(token_ids_BT, cfg, mesh: Mesh | None = None, device=None):

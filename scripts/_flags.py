@@ -77,8 +77,8 @@ def common_train_flags(p: Flags, *, batch_size: int, workers: int, worker_buffer
     p.define("val_data_path", None, type=str)
     p.define("val_every", None, type=int)
     p.define("val_steps", 10)
-    p.define("grain_read_threads", 16, "record read threads")
-    p.define("grain_read_buffer_size", 500, "accepted for compatibility")
-    p.define("grain_workers", workers, "prefetch depth of the loader")
-    p.define("grain_worker_buffer_size", worker_buffer, "accepted for compatibility")
+    p.define("grain_read_threads", 16, "threads that read and resolve the rows of a batch")
+    p.define("grain_read_buffer_size", 500, "read-ahead (the reference counts records; here batches, capped at 8)")
+    p.define("grain_workers", workers, "loader processes that build batches in turn (0: a thread of the trainer)")
+    p.define("grain_worker_buffer_size", worker_buffer, "finished batches each loader process keeps ready")
     p.define("log_file", None, "JSONL metrics file", type=str)

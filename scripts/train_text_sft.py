@@ -21,7 +21,8 @@ def main(argv=None):
 
     from omegalax_b200 import registry
     from omegalax_b200.data.collator_qwen3 import TextSFTCollator
-    from omegalax_b200.data.pipeline import load_metadata, make_data_iterator, required_epochs_for_batches
+    from omegalax_b200.data.pipeline import (load_metadata, make_data_iterator, make_grain_multiprocessing_options,
+                                             make_grain_read_options, required_epochs_for_batches)
     from omegalax_b200.parallel import mesh as mesh_lib
     from omegalax_b200.trainers import text as text_trainer
     from omegalax_b200.trainers.perf import resolve_peak_tflops
@@ -38,7 +39,11 @@ def main(argv=None):
         n = load_metadata(path)["num_records"]
         epochs = required_epochs_for_batches(n, per_rank, n_batches, mesh_lib.data_parallel_size())
         return make_data_iterator(path, batch_size=per_rank, collator=collator, shuffle=shuffle, seed=a.seed,
-                                  num_epochs=epochs, prefetch=max(a.grain_workers, 2), read_threads=a.grain_read_threads)
+                                  num_epochs=epochs,
+                                  read_options=make_grain_read_options(num_threads=a.grain_read_threads,
+                                                                       prefetch_buffer_size=a.grain_read_buffer_size),
+                                  multiprocessing_options=make_grain_multiprocessing_options(
+                                      num_workers=a.grain_workers, per_worker_buffer_size=a.grain_worker_buffer_size))
 
     data_iter = make_iter(a.data_path, True, a.num_steps * a.grad_accum_steps)
     val_iter = None

@@ -160,3 +160,65 @@ def test_dataset_scripts_take_the_reference_flags_and_refuse_to_overwrite(tmp_pa
             str(tmp_path / "index2"), "--tokenizer", "stub", "--max-length", "96", "--num_workers", "0")
     assert c.returncode == 0, c.stderr
     assert P.load_metadata(tmp_path / "index2")["num_records"] == meta["num_records"]
+
+
+def test_worker_processes_and_row_threads_yield_the_same_batches(dataset):
+    """Batches come out in the same order with 0, 1 or 3 loader processes and with 1 or many row
+    threads; a checkpoint taken with workers continues without them (and the other way round)."""
+    d, tok = dataset
+    col = TextSFTCollator(tok, max_length=96)
+
+    def mk(**kw):
+        return P.make_data_iterator(d / "index", batch_size=3, collator=col, seed=11, num_epochs=2, dp_index=0,
+                                    dp_size=1, **kw)
+
+    def drain(it, n=None):
+        out = []
+        for b in it:
+            out.append(b["token_ids_BT"].copy())
+            if n is not None and len(out) == n:
+                break
+        return out
+
+    base = drain(mk(prefetch=0, read_threads=1))
+    assert len(base) > 6
+    for kw in (dict(read_options=P.make_grain_read_options(num_threads=8)),
+               dict(multiprocessing_options=P.make_grain_multiprocessing_options(num_workers=1)),
+               dict(multiprocessing_options=P.make_grain_multiprocessing_options(num_workers=3, per_worker_buffer_size=2)),
+               dict(multiprocessing_options=P.make_grain_multiprocessing_options(num_workers=2, start_method="spawn"))):
+        it = mk(**kw)
+        got = drain(it)
+        it.close()
+        assert len(got) == len(base)
+        assert all(np.array_equal(a, b) for a, b in zip(got, base)), kw
+    # stop after 4 batches with three workers, carry the state into an in-process iterator and back
+    it = mk(multiprocessing_options=P.make_grain_multiprocessing_options(num_workers=3))
+    head = drain(it, 4)
+    state = it.get_state()
+    it.close()
+    it2 = mk(prefetch=0)
+    it2.set_state(state)
+    mid = drain(it2, 2)
+    state2 = it2.get_state()
+    it3 = mk(multiprocessing_options=P.make_grain_multiprocessing_options(num_workers=2))
+    it3.set_state(state2)
+    tail = drain(it3)
+    it3.close()
+    joined = head + mid + tail
+    assert len(joined) == len(base) and all(np.array_equal(a, b) for a, b in zip(joined, base))
+
+
+def test_failure_in_a_loader_process_reaches_the_consumer(dataset):
+    d, tok = dataset
+
+    def bad_collator(rows):
+        raise KeyError("no such field")
+
+    it = P.make_data_iterator(d / "index", batch_size=2, collator=bad_collator, seed=1, num_epochs=1, dp_index=0,
+                              dp_size=1, multiprocessing_options=P.make_grain_multiprocessing_options(num_workers=2))
+    with pytest.raises(P.DataLoaderError) as ei:
+        next(it)
+    assert "KeyError" in str(ei.value) and "no such field" in str(ei.value)
+    it.close()
+    assert P.resolve_arrayrecord_paths(d / "index")[0].exists()
+    assert P.load_compiled_metadata(d / "index")["kind"] == "chunk_index"
