@@ -204,6 +204,17 @@ class TrainEngine:
     def _allocate(self):
         dev = self.device
         n = self.total_shard
+        if dev.type == "cuda":
+            # fp32 master, two moments and gradients plus the compute copy: say so before the first of
+            # five allocations fails somewhere in the middle
+            per = 16 + (0 if (self.compute_dtype == torch.float32 and self.W == 1) else
+                        (2 if self.compute_dtype == bf16 else 4))
+            free = torch.cuda.mem_get_info(dev)[0]
+            if n * per > free:
+                raise MemoryError(
+                    f"this rank's parameter shard has {n / 1e9:.2f} G elements and needs {n * per / 1e9:.1f} GB of "
+                    f"optimizer state, the device has {free / 1e9:.1f} GB free: shard over more ranks "
+                    f"(fsdp / expert-parallel size {self.W}, tensor-parallel size {self.TP})")
         self.master = torch.zeros(n, dtype=torch.float32, device=dev)
         self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
