@@ -64,6 +64,10 @@ def _all_ranks_ok(ok: bool) -> bool:
     return bool(int(t.item()))
 
 
+class CheckpointUnreadable(RuntimeError):
+    """A step directory whose manifest or shard files cannot be opened."""
+
+
 class CheckpointManager:
     def __init__(self, save_dir: str | os.PathLike, *, save_interval_steps: int | None = None,
                  max_to_keep: int = 2, async_write: bool = True):
@@ -200,6 +204,26 @@ class CheckpointManager:
         self.wait_until_finished()
 
     # ---------------------------------------------------------------- restore
+    def _open_step(self, step: int):
+        """Manifest and open shard files of one step; ``CheckpointUnreadable`` names the file that
+        is missing, truncated or not a safetensors file (nothing has been loaded at that point)."""
+        from safetensors import safe_open
+
+        d = self.step_dir(step)
+        try:
+            manifest = json.loads((d / "manifest.json").read_text())
+        except (OSError, ValueError) as e:
+            raise CheckpointUnreadable(f"checkpoint step {step}: manifest.json is unreadable ({e})") from e
+        files = []
+        for i in range(manifest["world_size"]):
+            path = d / f"rank{i:05d}.safetensors"
+            try:
+                files.append(safe_open(str(path), framework="pt"))
+            except Exception as e:
+                raise CheckpointUnreadable(f"checkpoint step {step}: shard {path.name} is unreadable "
+                                           f"({type(e).__name__}: {e})") from e
+        return manifest, files
+
     def restore(self, step: int | None, engine, input_iter: CheckpointableIterator | None = None) -> dict:
         """Load master weights and moments into ``engine`` (resharding if needed), the data
         iterator state and the RNG state.  Returns the manifest."""
@@ -207,16 +231,29 @@ class CheckpointManager:
 
         self.wait_until_finished()
         if step is None:
-            step = self.latest_step()
-        if step is None:
-            raise ValueError("No checkpoint found to restore.")
+            # the newest step whose manifest and shard files all open; a damaged newest step (a
+            # truncated or corrupted shard file) is skipped with a warning in favour of the one before
+            candidates = sorted(self.all_steps(), reverse=True)
+            if not candidates:
+                raise ValueError("No checkpoint found to restore.")
+            err = None
+            for cand in candidates:
+                try:
+                    manifest, files = self._open_step(cand)
+                    step = cand
+                    break
+                except CheckpointUnreadable as e:
+                    warnings.warn(f"{e}; trying the step before it")
+                    err = e
+            else:
+                raise err
+        else:
+            manifest, files = self._open_step(step)
         d = self.step_dir(step)
-        manifest = json.loads((d / "manifest.json").read_text())
         saved_w = manifest["shard_world"]
         saved_tp = int(manifest.get("tp_world", manifest["world_size"] // saved_w))
         tp, tp_rank = int(getattr(engine, "TP", 1)), int(getattr(engine, "tp_rank", 0))
         meta = {p["name"]: p for p in manifest["params"]}
-        files = [safe_open(str(d / f"rank{i:05d}.safetensors"), framework="pt") for i in range(manifest["world_size"])]
         # ranks are laid out (shard, tp) with tp fastest: shard rank i, tensor-parallel rank t wrote
         # the file of global rank i * saved_tp + t
         per = saved_tp

@@ -222,3 +222,32 @@ def test_failure_in_a_loader_process_reaches_the_consumer(dataset):
     it.close()
     assert P.resolve_arrayrecord_paths(d / "index")[0].exists()
     assert P.load_compiled_metadata(d / "index")["kind"] == "chunk_index"
+
+
+def test_a_killed_loader_process_is_reported_not_waited_for(dataset):
+    """Failure injected on the host: one of the loader processes dies (here: killed by its exact
+    pid).  The consumer gets a DataLoaderError for the batch that process owed, instead of blocking
+    on its queue; the iterator can be rebuilt from its state."""
+    import os
+    import signal
+
+    d, tok = dataset
+    col = TextSFTCollator(tok, max_length=96)
+    mk = lambda **kw: P.make_data_iterator(d / "index", batch_size=2, collator=col, seed=3, num_epochs=4, dp_index=0,  # noqa: E731
+                                           dp_size=1, **kw)
+    ref = [b["token_ids_BT"].copy() for b in mk(prefetch=0)]
+    it = mk(multiprocessing_options=P.make_grain_multiprocessing_options(num_workers=2))
+    got = [next(it)["token_ids_BT"].copy() for _ in range(3)]
+    victim = it._procs[1]
+    os.kill(victim.pid, signal.SIGKILL)
+    victim.join(timeout=5)
+    with pytest.raises(P.DataLoaderError, match="exited with code"):
+        for _ in range(8):          # batches the dead process had already queued may still arrive
+            got.append(next(it)["token_ids_BT"].copy())
+    state = it.get_state()
+    it.close()
+    again = mk(multiprocessing_options=P.make_grain_multiprocessing_options(num_workers=2))
+    again.set_state(state)
+    got += [b["token_ids_BT"].copy() for b in again]
+    again.close()
+    assert len(got) == len(ref) and all(np.array_equal(a, b) for a, b in zip(got, ref))

@@ -71,6 +71,43 @@ def test_text_sft_trains_and_resumes_identically(tmp_path):
     assert (run / "config.json").exists() and (run / "000006" / "manifest.json").exists()
 
 
+def test_resume_skips_a_damaged_newest_checkpoint(tmp_path):
+    """Failure injected on the host: the newest step's shard file is cut short (a writer that died
+    mid-copy, a full disk).  Resume warns, falls back to the step before it and retrains from
+    there; with every kept step damaged it raises and names the file."""
+    from omegalax_b200.trainers.checkpoint_utils import CheckpointUnreadable
+
+    tok, _ = _dataset(tmp_path)
+    col = TextSFTCollator(tok, 96)
+    mk = lambda: P.make_data_iterator(tmp_path / "index", batch_size=4, collator=col, seed=1, num_epochs=8, dp_index=0, dp_size=1)  # noqa: E731
+    cfg = lambda n: text_trainer.TrainConfig(batch_size=4, seq_len=96, num_steps=n, learning_rate=3e-3, max_grad_norm=1.0)  # noqa: E731
+    run, log = tmp_path / "run", tmp_path / "log.jsonl"
+    text_trainer.run_sft("qwen3-smoke", cfg(4), mk(), tp_size=1, fsdp_size=1, dp_size=1, log_every=1, log_file=log,
+                         device="cpu", save_dir=run, save_every=2)
+    first = [json.loads(l) for l in log.read_text().splitlines()]
+    assert (run / "000002").exists() and (run / "000004").exists()
+    shard = run / "000004" / "rank00000.safetensors"
+    raw = shard.read_bytes()
+    shard.write_bytes(raw[: len(raw) // 2])
+    mesh_lib.set_default_mesh(None)
+    log2 = tmp_path / "log2.jsonl"
+    with pytest.warns(UserWarning, match="rank00000.safetensors is unreadable"):
+        text_trainer.run_sft("qwen3-smoke", cfg(4), mk(), tp_size=1, fsdp_size=1, dp_size=1, log_every=1, log_file=log2,
+                             device="cpu", save_dir=run, save_every=2, resume=True)
+    again = [json.loads(l) for l in log2.read_text().splitlines()]
+    assert [m["step"] for m in again] == [3, 4]                     # restarted after step 2, not after step 4
+    assert [m["loss"] for m in again] == pytest.approx([m["loss"] for m in first[2:]], rel=1e-5, abs=1e-6)
+    # now both kept steps are damaged: nothing to fall back to
+    for step in ("000002", "000004"):
+        f = run / step / "rank00000.safetensors"
+        if f.exists():
+            f.write_bytes(b"not a checkpoint")
+    mesh_lib.set_default_mesh(None)
+    with pytest.warns(UserWarning), pytest.raises(CheckpointUnreadable, match="rank00000.safetensors"):
+        text_trainer.run_sft("qwen3-smoke", cfg(4), mk(), tp_size=1, fsdp_size=1, dp_size=1, device="cpu",
+                             save_dir=run, save_every=2, resume=True)
+
+
 def test_vlm_text_only_and_multimodal_steps(tmp_path):
     tok, ip = _dataset(tmp_path, with_images=True)
     col = VLMSFTCollator(tok, 96, ip)
