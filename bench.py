@@ -180,6 +180,11 @@ def main() -> int:
     ap.add_argument("--remat", default=None, help="full | selective | save:<tags> (default depends on N)")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (sequence-parallel Megatron layout); "
                                                       "the remaining N / tp ranks form the FSDP / expert-parallel group")
+    ap.add_argument("--ep", type=int, default=0,
+                    help="expert-parallel size: 0 = the N / tp ranks of the FSDP group; N with --tp > 1 = experts over "
+                         "every rank while attention stays tensor-parallel (library all-to-all transport)")
+    ap.add_argument("--ep-transport", default="auto", choices=["auto", "a2a"],
+                    help="a2a: token exchange by library all_to_all instead of the peer-memory kernels")
     ap.add_argument("--kernel-table", default=None,
                     help="after the timed regions, trace one more step and write its per-kernel device times here")
     args = ap.parse_args()
@@ -241,7 +246,8 @@ def main() -> int:
         remat = "full" if args.model == "qwen3.5-8l" else "selective"
     tcfg = trainer.TrainConfig(seed=0, batch_size=micro * N, seq_len=T, num_steps=10_000, learning_rate=1e-5,
                                weight_decay=0.01, warmup_steps=0, lr_schedule="linear", max_grad_norm=1.0,
-                               grad_accum_steps=accum, remat_policy=remat)
+                               grad_accum_steps=accum, remat_policy=remat, ep_size=args.ep,
+                               ep_transport=args.ep_transport)
     TP = max(args.tp, 1)
     if N % TP:
         raise SystemExit(f"--tp {TP} does not divide {N} GPUs")
@@ -360,7 +366,9 @@ def main() -> int:
             "config": {"model": model_id if args.layers is None and args.experts is None
                        else f"{model_id}[layers={args.layers or 'all'}, experts={args.experts or 'all'}]",
                        "global_batch": args.seqs_per_gpu * N, "seq_len": T,
-                       "parallelism": (f"fsdp{FS}" if par == "fsdp" else f"ep{FS}+fsdp{FS}") + (f"+tp{TP}" if TP > 1 else ""),
+                       "parallelism": (f"fsdp{FS}" if par == "fsdp" else
+                                       f"ep{args.ep or FS}{'(a2a)' if getattr(opt, 'ep_kind', None) == 'a2a' else ''}+fsdp{FS}")
+                       + (f"+tp{TP}" if TP > 1 else ""),
                        "micro_batch_per_gpu": micro, "grad_accum": accum, "optimizer": "AdamW fp32 master",
                        "remat": remat if getattr(opt, "_auto", None) is None else
                        f"auto (save:qkv,attn; layers that also keep o / gate_up: {opt._auto.summary()})", "l2": "inputs larger than L2 (weights and activations of one step far exceed 126 MB)"},

@@ -59,6 +59,9 @@ class ParamSlot:
     ep: bool = False       # expert-parallel: never gathered, this rank computes with its own slice
     fused_ag: bool = False  # gathered inside its forward GEMM launch, not by the prefetch
     tp_sharded: bool = False   # differs between tensor-parallel ranks (no gradient all-reduce over tp)
+    shard_world: int = 1       # number of ranks the parameter is cut over (1 when replicated) ...
+    shard_rank: int = 0        # ... and which piece this rank holds
+    ep_product: bool = False   # experts cut over shard group x tensor-parallel group (every rank of the job)
 
 
 @dataclasses.dataclass
@@ -103,7 +106,8 @@ class TrainEngine:
                  weight_decay: float = 0.01, betas=(0.9, 0.999), eps: float = 1e-8,
                  max_grad_norm: float | None = 1.0, remat: str = "full", seed: int = 0,
                  init_from_model: bool = False, comm: str = "auto", expert_parallel: bool = True,
-                 ep_capacity_factor: float = 2.0, tp_group=None, fused_gather: bool = True):
+                 ep_capacity_factor: float = 2.0, tp_group=None, fused_gather: bool = True,
+                 ep_over_tp: bool = False):
         self.model = model
         self.device = torch.device(device)
         self.group = shard_group
@@ -149,7 +153,23 @@ class TrainEngine:
         if comm == "auto":
             comm = "p2p" if (self.use_cuda_kernels and self.W > 1) else "nccl"
         self.comm_kind = comm if self.W > 1 else "none"
-        self.expert_parallel = bool(expert_parallel) and self.comm_kind == "p2p"
+        # expert parallelism: the peer-memory exchange kernels when GPUs can map each other's memory;
+        # "a2a" asks for the library all-to-all form on any transport (NCCL baseline, CPU ranks)
+        self.ep_kind = "a2a" if expert_parallel == "a2a" else ("p2p" if (expert_parallel and self.comm_kind == "p2p") else None)
+        # experts over every rank of the job (shard group x tensor-parallel group) instead of the shard
+        # group only: the routed experts see sequence-parallel rows, so each of the W x TP ranks brings
+        # its own tokens and can own its own E / (W x TP) experts.  Library all-to-all transport only.
+        self.ep_over_tp = bool(ep_over_tp) and self.TP > 1 and bool(expert_parallel)
+        if self.ep_over_tp:
+            if dist.get_world_size() != self.W * self.TP:
+                raise ValueError("experts over the tensor-parallel group need shard group x tp group = all ranks")
+            self.ep_kind = "a2a"
+            self.ep_group, self.EPW, self.ep_rank = dist.group.WORLD, self.W * self.TP, self.rank * self.TP + self.tp_rank
+        else:
+            self.ep_group, self.EPW, self.ep_rank = shard_group, self.W, self.rank
+            if self.W == 1:
+                self.ep_kind = None
+        self.expert_parallel = self.ep_kind is not None
         # The weight of a layer's first projection is gathered inside that projection's GEMM launch
         # instead of by the prefetch.  Every backward must re-run the forward GEMM for this to hold
         # the weight when the gradient GEMMs need it, hence only with full rematerialisation.
@@ -182,14 +202,20 @@ class TrainEngine:
                     row_numel = numel // max(rows, 1)
                     sharded = (self.W > 1 and len(shape) >= 1 and rows % self.W == 0
                                and ((rows // self.W) * row_numel) % 8 == 0)
-                    sn = numel // self.W if sharded else numel
+                    is_expert = pname.rsplit(".", 1)[-1] in ("experts_gate_up", "experts_down")
+                    sw, sr = (self.W, self.rank) if sharded else (1, 0)
+                    product = bool(self.ep_over_tp and is_expert and rows % self.EPW == 0
+                                   and ((rows // self.EPW) * row_numel) % 8 == 0)
+                    if product:
+                        sharded, sw, sr = True, self.EPW, self.ep_rank
+                    sn = numel // sw if sharded else numel
                     slot = ParamSlot(f"{uname}.{mi}.{pname}", p, shape, numel, sharded, sn, shard_off, full_off, m, pname)
+                    slot.shard_world, slot.shard_rank, slot.ep_product = sw, sr, product
                     owner = m.get_submodule(pname.rsplit(".", 1)[0]) if "." in pname else m
                     slot.tp_sharded = bool(getattr(owner, "tp_sharded", False))
                     # expert tensors under expert parallelism are never gathered: they take no room
                     # in the gathered-layer buffers
-                    slot.ep = bool(self.expert_parallel and sharded
-                                   and pname.rsplit(".", 1)[-1] in ("experts_gate_up", "experts_down"))
+                    slot.ep = bool(self.expert_parallel and sharded and is_expert)
                     slots.append(slot)
                     shard_off += _align(sn)
                     if not slot.ep:
@@ -275,7 +301,7 @@ class TrainEngine:
             for s in u.slots:
                 src = s.param.data.detach().to(device=self.device, dtype=torch.float32).reshape(-1)
                 if s.sharded:
-                    src = src[self.rank * s.shard_numel:(self.rank + 1) * s.shard_numel]
+                    src = src[s.shard_rank * s.shard_numel:(s.shard_rank + 1) * s.shard_numel]
                 mshard[s.shard_off:s.shard_off + s.shard_numel].copy_(src)
             for s in u.slots:  # drop the transient full-precision copy
                 s.param.data = torch.empty(0, dtype=self.compute_dtype, device=self.device)
@@ -302,11 +328,14 @@ class TrainEngine:
                 cs = self._unit_views(u, self.compute_shard)
                 gs = self._unit_views(u, self.grad)
                 for s in u.slots:
-                    s.param.data = cs[s.shard_off:s.shard_off + s.numel].view(s.shape)
-                    s.param.main_grad = gs[s.shard_off:s.shard_off + s.numel].view(s.shape)
+                    shp = (s.shape[0] // s.shard_world, *s.shape[1:]) if s.ep else s.shape   # local experts only
+                    s.param.data = cs[s.shard_off:s.shard_off + s.shard_numel].view(shp)
+                    s.param.main_grad = gs[s.shard_off:s.shard_off + s.shard_numel].view(shp)
+                if self.expert_parallel:
+                    self._mark_peer_slots(u)
                 u.resident = True
             else:
-                if self.comm_kind == "p2p":
+                if self.comm_kind == "p2p" or self.expert_parallel:
                     self._mark_peer_slots(u)
                 is_layer = u.name.startswith("layers.")
                 if not is_layer:  # embedding / head stay gathered between optimizer steps
@@ -323,7 +352,7 @@ class TrainEngine:
     def _bind(self, u: Unit, full: torch.Tensor, full_grad: torch.Tensor | None):
         for s in u.slots:
             if s.ep:  # this rank's experts only, straight from the shard buffers
-                shp = (s.shape[0] // self.W, *s.shape[1:])
+                shp = (s.shape[0] // s.shard_world, *s.shape[1:])
                 cs, gs = self._unit_views(u, self.compute_shard), self._unit_views(u, self.grad)
                 s.param.data = cs[s.shard_off:s.shard_off + s.shard_numel].view(shp)
                 s.param.main_grad = gs[s.shard_off:s.shard_off + s.shard_numel].view(shp)
@@ -336,10 +365,12 @@ class TrainEngine:
         """Weights of Linear modules take their gradient through the GEMM epilogue that adds
         each row block straight into the owning rank's fp32 gradient shard over NVLink."""
         for s in u.slots:
-            if self.expert_parallel and s.sharded and s.pname.rsplit(".", 1)[-1] in ("experts_gate_up", "experts_down"):
-                s.ep = s.peer = True
+            if s.ep:
+                s.peer = True        # gradients of this rank's experts are complete locally: nothing to reduce
                 owner = s.module.get_submodule(s.pname.rsplit(".", 1)[0]) if "." in s.pname else s.module
                 owner.ep = _LazyEP(self, owner)
+                continue
+            if self.comm_kind != "p2p":
                 continue
             if not (s.sharded and len(s.shape) == 2 and s.pname.endswith("weight") and s.shape[0] % 8 == 0):
                 continue
@@ -394,6 +425,8 @@ class TrainEngine:
         dist.all_gather_into_tensor(stage, cs, group=self.group)
         st = stage.view(self.W, u.shard_numel)
         for s in u.slots:
+            if s.ep:        # this rank's experts stay in the shard buffers, they have no place in `full`
+                continue
             dst = full[s.full_off:s.full_off + s.numel]
             if s.sharded:
                 dst.view(self.W, s.shard_numel).copy_(st[:, s.shard_off:s.shard_off + s.shard_numel])
@@ -500,7 +533,7 @@ class TrainEngine:
         for s in u.slots:
             p = s.param
             if p.grad is not None:
-                p.main_grad.add_(p.grad.to(torch.float32).view(s.shape))
+                p.main_grad.add_(p.grad.to(torch.float32).view(p.main_grad.shape))   # local experts: [E/W, ...]
                 p.grad = None
         if self.W > 1 and not u.resident:
             self._reduce_scatter(u, self._ring_grad)
@@ -527,7 +560,7 @@ class TrainEngine:
         for u in self.units:
             gs = self._unit_views(u, self.grad)
             for s in u.slots:
-                if not s.tp_sharded:
+                if not s.tp_sharded and not s.ep_product:   # an expert that lives on one rank has its whole gradient
                     dist.all_reduce(gs[s.shard_off:s.shard_off + s.shard_numel], group=self.tp_group)
 
     # ------------------------------------------------------------------ optimizer
@@ -544,7 +577,7 @@ class TrainEngine:
                     if not s.sharded and self.W > 1 and self.rank != 0:
                         continue
                     g = gs[s.shard_off:s.shard_off + s.shard_numel]
-                    (shd if s.tp_sharded else rep).add_((g.double() ** 2).sum().float())
+                    (shd if (s.tp_sharded or s.ep_product) else rep).add_((g.double() ** 2).sum().float())
             dist.all_reduce(shd, group=self.tp_group)
             self.norm_sq += rep + shd
             if self.W > 1:
@@ -631,7 +664,7 @@ class TrainEngine:
         ms = self._unit_views(u, self.master)
         flat = value.detach().to(device=self.device, dtype=torch.float32).reshape(-1)
         if slot.sharded:
-            flat = flat[self.rank * slot.shard_numel:(self.rank + 1) * slot.shard_numel]
+            flat = flat[slot.shard_rank * slot.shard_numel:(slot.shard_rank + 1) * slot.shard_numel]
         ms[slot.shard_off:slot.shard_off + slot.shard_numel].copy_(flat)
 
     def sync_compute_from_master(self):
@@ -652,10 +685,10 @@ class TrainEngine:
         """Assemble the full fp32 master value of a parameter (collective when sharded)."""
         u = next(u for u in self.units if slot in u.slots)
         ms = self._unit_views(u, self.master)[slot.shard_off:slot.shard_off + slot.shard_numel]
-        if self.W == 1 or not slot.sharded:
+        if slot.shard_world == 1 or not slot.sharded:
             return ms.clone().view(slot.shape)
-        out = torch.empty(self.W * slot.shard_numel, dtype=torch.float32, device=self.device)
-        dist.all_gather_into_tensor(out, ms.contiguous(), group=self.group)
+        out = torch.empty(slot.shard_world * slot.shard_numel, dtype=torch.float32, device=self.device)
+        dist.all_gather_into_tensor(out, ms.contiguous(), group=self.ep_group if slot.ep_product else self.group)
         return out.view(slot.shape)
 
 
@@ -696,6 +729,12 @@ class _LazyEP:
 
     def moe_mlp(self, x, w, idx, gate_up_local, down_local):
         eng = self.engine
+        if eng.ep_kind == "a2a":
+            if eng._ep is None:
+                from .ep import ExpertParallelA2A
+
+                eng._ep = ExpertParallelA2A(eng.ep_group, self.module.E)
+            return eng._ep.moe_mlp(x, w, idx, gate_up_local, down_local)
         if eng._ep is None or eng._ep.max_tokens < x.shape[0]:
             from .ep import ExpertParallel
 

@@ -242,3 +242,73 @@ class _Combine(torch.autograd.Function):
         ep.barrier()
         # consumed by the expert MLP's backward before any other layer writes this buffer
         return ep.local(ep.buf_gout), dots.view_as(weights), None, None
+
+
+# ----------------------------------------------------------------------------- library path
+class _AllToAllRows(torch.autograd.Function):
+    """``dist.all_to_all_single`` over row blocks; the gradient travels the same way back."""
+
+    @staticmethod
+    def forward(ctx, rows, send_counts, recv_counts, group):
+        ctx.group, ctx.send, ctx.recv = group, send_counts, recv_counts
+        out = rows.new_empty((sum(recv_counts),) + tuple(rows.shape[1:]))
+        dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=recv_counts, input_split_sizes=send_counts,
+                               group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        back = g.new_empty((sum(ctx.send),) + tuple(g.shape[1:]))
+        dist.all_to_all_single(back, g.contiguous(), output_split_sizes=ctx.send, input_split_sizes=ctx.recv,
+                               group=ctx.group)
+        return back, None, None, None
+
+
+class ExpertParallelA2A:
+    """Expert parallelism on library collectives: the same contract as ``ExpertParallel.moe_mlp``
+    (rank r owns experts [r*E/W, (r+1)*E/W); every (token, slot) pair is computed by the rank that
+    owns its expert), moved with two ``all_to_all_single`` calls per direction instead of the
+    peer-memory kernels.  It is the baseline those kernels are measured against, the fallback
+    where GPUs cannot map each other's memory, and the form that runs on CPU ranks (gloo) in the
+    tests.  One host synchronisation per layer (the split sizes are host integers); no capacity
+    limit, nothing is ever dropped."""
+
+    def __init__(self, group, num_experts: int):
+        self.group = group
+        self.W = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        if num_experts % self.W:
+            raise ValueError(f"{num_experts} experts do not divide over {self.W} ranks")
+        self.E, self.El = num_experts, num_experts // self.W
+        self.max_tokens = 1 << 62
+
+    def check(self):          # same surface as the peer-memory exchange; nothing can overflow here
+        return None
+
+    def moe_mlp(self, x, w, idx, gate_up_local, down_local):
+        from ..ops import moe as moe_ops
+
+        M, D = x.shape
+        k = idx.shape[1]
+        pair_e = idx.reshape(-1).long()                               # expert of pair p = token * k + slot
+        order = torch.argsort(pair_e, stable=True)                    # pairs grouped by expert, hence by owner
+        e_sorted = pair_e[order]
+        send = torch.bincount(e_sorted // self.El, minlength=self.W)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)
+        send_l, recv_l = send.tolist(), recv.tolist()
+        rows = x.index_select(0, order // k)                          # differentiable gather of the token rows
+        got = _AllToAllRows.apply(rows, send_l, recv_l, self.group)
+        eid = torch.empty(sum(recv_l), dtype=torch.long, device=x.device)
+        dist.all_to_all_single(eid, e_sorted - 0, output_split_sizes=recv_l, input_split_sizes=send_l, group=self.group)
+        eid = eid - self.rank * self.El                               # local expert index of every received row
+        if got.shape[0]:
+            y = moe_ops.moe_mlp(got, torch.ones(got.shape[0], 1, dtype=torch.float32, device=x.device), eid.view(-1, 1),
+                                gate_up_local, down_local)
+        else:   # keep the local experts in the graph so that every rank runs the same backward collectives
+            y = got + 0.0 * (gate_up_local.sum() + down_local.sum()).to(got.dtype)
+        back = _AllToAllRows.apply(y, recv_l, send_l, self.group)     # expert outputs, in this rank's sorted pair order
+        inv = torch.empty_like(order)
+        inv[order] = torch.arange(order.numel(), device=order.device)
+        per_pair = back.index_select(0, inv).view(M, k, D)
+        return (per_pair.float() * w.float().unsqueeze(-1)).sum(1).to(x.dtype)

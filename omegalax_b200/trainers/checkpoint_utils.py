@@ -116,7 +116,8 @@ class CheckpointManager:
                 tensors[slot.name + suffix] = t.detach().to("cpu", copy=True)
             params.append({"name": slot.name, "shape": list(slot.shape), "sharded": bool(slot.sharded),
                            "shard_numel": int(slot.shard_numel),
-                           "tp_sharded": bool(getattr(slot, "tp_sharded", False))})
+                           "tp_sharded": bool(getattr(slot, "tp_sharded", False)),
+                           "ep_product": bool(getattr(slot, "ep_product", False))})
         manifest = {"step": int(step), "world_size": w, "shard_world": int(engine.W),
                     "tp_world": int(getattr(engine, "TP", 1)),
                     "optimizer_step": int(engine.step_count), "params": params, "extra": extra or {}}
@@ -274,9 +275,19 @@ class CheckpointManager:
             if list(slot.shape) != pm["shape"] and not retile:
                 raise RuntimeError(f"shape mismatch for '{slot.name}': {pm['shape']} vs {list(slot.shape)}")
             t = tp_rank if (saved_tp == tp and pm.get("tp_sharded", False)) else 0
+            # experts cut over every rank of the job (shard group x tensor-parallel group), on either
+            # side: assemble the whole tensor and take this rank's piece under the current layout
+            product = bool(pm.get("ep_product", False) or getattr(slot, "ep_product", False))
+            srank = int(getattr(slot, "shard_rank", engine.rank))
             for suffix, dst in ((".master", master), (".exp_avg", m1), (".exp_avg_sq", m2)):
                 key = slot.name + suffix
-                if retile:
+                if product:
+                    if pm.get("ep_product", False):   # piece j is in the file of global rank j
+                        full = torch.cat([f.get_tensor(key).reshape(-1) for f in files])
+                    else:                             # the other layout keeps experts identical over tp
+                        full = saved_full(key, pm, 0)
+                    src = full[srank * slot.shard_numel:(srank + 1) * slot.shard_numel] if slot.sharded else full
+                elif retile:
                     full = _retile_tp(model_names[id(slot.param)], [saved_full(key, pm, i).view(pm["shape"]) for i in range(saved_tp)],
                                       engine, tp, tp_rank)
                     if list(full.shape) != list(slot.shape):

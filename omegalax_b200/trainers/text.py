@@ -59,8 +59,12 @@ class TrainConfig:
     print_every: int = 1
     remat_policy: str = "full"
     ep_size: int = 0             # expert parallelism: 0 automatic (over the shard group when experts and peer
-                                 # memory exist), 1 off (experts travel like any sharded parameter), else the
-                                 # shard-group size it must equal
+                                 # memory exist), 1 off (experts travel like any sharded parameter), the
+                                 # shard-group size, or shard-group size x tp size (experts over every rank of
+                                 # the job while attention is tensor-parallel; library all-to-all transport)
+    ep_transport: str = "auto"   # "auto": the peer-memory exchange kernels where GPUs can map each other's
+                                 # memory, else experts travel like any sharded parameter; "a2a": library
+                                 # all-to-all on any transport (NCCL baseline, CPU ranks)
 
 
 def init_model(cfg_or_model_id, rng: int = 0, *, tp_size=None, fsdp_size=None, dp_size=None, **kw):
@@ -84,14 +88,19 @@ def build_optimizer(model, train_cfg: TrainConfig, *, device=None, init_from_mod
     if init_from_model is None:
         init_from_model = not any(p.device.type == "meta" for p in model.parameters())
     shard_world = dist.get_world_size(group) if group is not None else 1
-    if train_cfg.ep_size not in (0, 1, shard_world):
-        raise ValueError(f"ep_size={train_cfg.ep_size}: experts are sharded over the shard group "
-                         f"({shard_world} ranks here); use 0 (automatic), 1 (off) or {shard_world}")
+    tp_world = dist.get_world_size(tp_group) if tp_group is not None else 1
+    if train_cfg.ep_size not in (0, 1, shard_world, shard_world * tp_world):
+        raise ValueError(f"ep_size={train_cfg.ep_size}: experts are sharded over the shard group ({shard_world} ranks "
+                         f"here) or over shard group x tensor-parallel group ({shard_world * tp_world}); use 0 "
+                         f"(automatic: the shard group), 1 (off), {shard_world} or {shard_world * tp_world}")
+    ep_over_tp = tp_world > 1 and train_cfg.ep_size == shard_world * tp_world
     return MixedPrecisionOptimizer(
         model, device=device, shard_group=group, lr=train_cfg.learning_rate, weight_decay=train_cfg.weight_decay,
         max_grad_norm=train_cfg.max_grad_norm, remat=train_cfg.remat_policy, seed=train_cfg.seed,
         init_from_model=init_from_model, lr_schedule=sched, grad_accum_steps=train_cfg.grad_accum_steps,
-        tp_group=tp_group, expert_parallel=train_cfg.ep_size != 1)
+        tp_group=tp_group,
+        expert_parallel=False if train_cfg.ep_size == 1 else ("a2a" if (train_cfg.ep_transport == "a2a" or ep_over_tp) else True),
+        ep_over_tp=ep_over_tp)
 
 
 def tp_rows_loss(model, rows, tok, mask, count):

@@ -56,6 +56,8 @@ def common_train_flags(p: Flags, *, batch_size: int, workers: int, worker_buffer
     p.define("dp_size", 1)
     p.define("ep_size", 0, "expert parallelism: 0 automatic (experts sharded over the fsdp ranks when peer memory is "
                            "available), 1 off, or the fsdp size")
+    p.define("ep_transport", "auto", "auto: peer-memory exchange kernels when available | a2a: library all-to-all",
+             choices=["auto", "a2a"])
     p.define("remat_policy", "full", "full | selective | auto (selective on as many layers as the free memory after the first step allows) | save:<tag,tag> (tags: qkv, attn, o, gate_up) | none")
     p.define("save_dir", None, type=str)
     p.define("jax_cache_dir", None, "accepted for command-line compatibility; unused", type=str)

@@ -65,7 +65,7 @@ def main(argv=None):
     data_iter = make_iter(a.data_path, True, a.num_steps * a.grad_accum_steps)
     val_iter = make_iter(a.val_data_path, False, max(1, (a.num_steps // max(a.val_every or a.num_steps, 1)) * a.val_steps)) \
         if a.val_data_path else None
-    cfg = vlm_trainer.TrainConfig(seed=a.seed, ep_size=a.ep_size, batch_size=a.batch_size, seq_len=a.max_length, num_steps=a.num_steps,
+    cfg = vlm_trainer.TrainConfig(seed=a.seed, ep_size=a.ep_size, ep_transport=a.ep_transport, batch_size=a.batch_size, seq_len=a.max_length, num_steps=a.num_steps,
                                   learning_rate=a.learning_rate, weight_decay=a.weight_decay, warmup_steps=a.warmup_steps,
                                   lr_schedule=a.lr_schedule, lr_end_factor=a.lr_end_factor,
                                   lr_stable_fraction=a.lr_stable_fraction, max_grad_norm=a.max_grad_norm,

@@ -10,7 +10,8 @@ def _init(rank, world, port):
     dist.init_process_group("gloo", rank=rank, world_size=world)
 
 
-def fsdp_train(rank, world, port, model_id, steps, out_path, ckpt_dir=None, resume=False, aux_coef=None):
+def fsdp_train(rank, world, port, model_id, steps, out_path, ckpt_dir=None, resume=False, aux_coef=None,
+               ep_transport="auto"):
     """Train `steps` optimizer steps with FSDP over `world` CPU ranks on a fixed global batch;
     rank 0 stores the loss curve and the gathered fp32 parameters."""
     _init(rank, world, port)
@@ -20,7 +21,8 @@ def fsdp_train(rank, world, port, model_id, steps, out_path, ckpt_dir=None, resu
 
     mesh_lib.set_default_mesh(None)
     mesh_lib.ensure_mesh(tp_size=1, fsdp_size=world, dp_size=1)
-    tcfg = trainer.TrainConfig(seed=0, batch_size=4, seq_len=32, num_steps=100, learning_rate=1e-2, max_grad_norm=1.0)
+    tcfg = trainer.TrainConfig(seed=0, batch_size=4, seq_len=32, num_steps=100, learning_rate=1e-2, max_grad_norm=1.0,
+                               ep_transport=ep_transport)
     if aux_coef is not None:   # a router loss large enough to steer the run
         import dataclasses
 
@@ -54,12 +56,14 @@ def fsdp_train(rank, world, port, model_id, steps, out_path, ckpt_dir=None, resu
         for s in u.slots:
             full[names[id(s.param)]] = opt.full_param(s).clone()
     if rank == 0:
-        torch.save({"losses": losses, "params": full, "grad_norm": float(opt.last_grad_norm)}, out_path)
+        torch.save({"losses": losses, "params": full, "grad_norm": float(opt.last_grad_norm),
+                    "ep_kind": getattr(opt, "ep_kind", None)}, out_path)
     dist.barrier()
     dist.destroy_process_group()
 
 
-def tp_train(rank, world, port, tp, steps, out_path, untied=False, ckpt_dir=None, resume=False, moe_aux=None):
+def tp_train(rank, world, port, tp, steps, out_path, untied=False, ckpt_dir=None, resume=False, moe_aux=None,
+             ep_size=0):
     """Same weights, same batch: tensor-parallel (tp) x fsdp (world/tp) run on CPU ranks."""
     _init(rank, world, port)
     import dataclasses
@@ -82,7 +86,7 @@ def tp_train(rank, world, port, tp, steps, out_path, untied=False, ckpt_dir=None
     torch.manual_seed(0)
     full = Qwen3(cfg, dtype=torch.float32)                       # identical on every rank
     tcfg = trainer.TrainConfig(seed=0, batch_size=2 * (world // tp), seq_len=32, num_steps=100, learning_rate=1e-2,
-                               max_grad_norm=1.0)
+                               max_grad_norm=1.0, ep_size=ep_size)
     model, cfg2 = trainer.init_model(cfg, 0, tp_size=tp, fsdp_size=world // tp, dp_size=1, meta=True)
     opt = trainer.build_optimizer(model, tcfg, device=torch.device("cpu"))
     src = dict(full.named_parameters())
@@ -116,7 +120,9 @@ def tp_train(rank, world, port, tp, steps, out_path, untied=False, ckpt_dir=None
         mgr.close()
     if rank == 0:
         torch.save({"losses": losses, "grad_norm": float(opt.last_grad_norm),
-                    "vocab_parallel": bool(getattr(model, "vocab_parallel", False))}, out_path)
+                    "vocab_parallel": bool(getattr(model, "vocab_parallel", False)),
+                    "ep": (opt.ep_kind, bool(opt.ep_over_tp), sum(s.ep_product for u in opt.units for s in u.slots))},
+                   out_path)
     dist.barrier()
     tp_lib.set_current(None)
     dist.destroy_process_group()

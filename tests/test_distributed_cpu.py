@@ -32,6 +32,26 @@ def test_fsdp_matches_single_rank(tmp_path, model_id):
         torch.testing.assert_close(a["params"][k], b["params"][k], rtol=2e-3, atol=2e-4)
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_over_library_all_to_all_matches_single_rank(tmp_path, world):
+    """Experts sharded over the ranks and tokens exchanged with all_to_all_single (the library form
+    of expert parallelism, here on gloo): same loss curve, gradient norm and parameters as one rank
+    that holds every expert, and a checkpoint written that way restores on another rank count."""
+    _run(1, "qwen3-smoke-moe", 3, str(tmp_path / "w1.pt"))
+    _run(world, "qwen3-smoke-moe", 3, str(tmp_path / "wn.pt"), str(tmp_path / "ck"), False, None, "a2a")
+    a, b = torch.load(tmp_path / "w1.pt"), torch.load(tmp_path / "wn.pt")
+    assert b["ep_kind"] == "a2a" and a["ep_kind"] is None
+    assert a["losses"] == pytest.approx(b["losses"], rel=2e-4, abs=2e-4)
+    assert a["grad_norm"] == pytest.approx(b["grad_norm"], rel=1e-3)
+    for k in a["params"]:
+        torch.testing.assert_close(a["params"][k], b["params"][k], rtol=2e-3, atol=2e-4)
+    if world == 4:     # resume the 4-rank expert-parallel checkpoint on 2 ranks without expert parallelism
+        _run(2, "qwen3-smoke-moe", 1, str(tmp_path / "r2.pt"), str(tmp_path / "ck"), True)
+        _run(1, "qwen3-smoke-moe", 4, str(tmp_path / "s4.pt"))
+        r, s4 = torch.load(tmp_path / "r2.pt"), torch.load(tmp_path / "s4.pt")
+        assert r["losses"][0] == pytest.approx(s4["losses"][3], rel=5e-4, abs=5e-4)
+
+
 def test_moe_aux_loss_uses_global_statistics(tmp_path):
     """The router load-balance loss is taken over the tokens of every data rank: value and
     gradient from 2 and 4 token slices equal the single-rank ones, and an FSDP run whose loss is
@@ -102,6 +122,36 @@ def test_moe_tensor_parallel_aux_loss_matches_single_rank(tmp_path):
         got = run(world, tp, "b.pt")
         assert ref["losses"] == pytest.approx(got["losses"], rel=3e-4, abs=3e-4), (world, tp)
         assert ref["grad_norm"] == pytest.approx(got["grad_norm"], rel=2e-3)
+
+
+def test_experts_over_every_rank_with_tensor_parallel_attention(tmp_path):
+    """Experts cut over shard group x tensor-parallel group (ep_size = fsdp x tp) while attention and
+    the dense projections are tensor-parallel: tp 2 (two ranks, one expert pair each) and tp 2 x
+    fsdp 2 (four ranks, one expert each) follow the single-rank loss curve; a checkpoint written in
+    that layout resumes under plain tp 2 x fsdp 1 (experts identical over tp) and the other way."""
+    def run(world, tp, name, ep_size=0, ckpt=None, resume=False, steps=3):
+        mp.spawn(W.tp_train, args=(world, _port(), tp, steps, str(tmp_path / name), False, ckpt, resume, 0.05, ep_size),
+                 nprocs=world, join=True)
+        return torch.load(tmp_path / name)
+
+    one = run(1, 1, "a.pt")
+    two = run(2, 2, "b.pt", ep_size=2)
+    assert two["ep"][:2] == ("a2a", True) and two["ep"][2] > 0
+    assert one["losses"] == pytest.approx(two["losses"], rel=5e-4, abs=5e-4)
+    assert one["grad_norm"] == pytest.approx(two["grad_norm"], rel=3e-3)
+    # four ranks (tp 2 x fsdp 2, one expert each) against two data ranks without tensor parallelism
+    ref = run(2, 1, "r.pt", ep_size=1, steps=4)
+    four = run(4, 2, "c.pt", ep_size=4, ckpt=str(tmp_path / "ck4"))
+    assert four["ep"][:2] == ("a2a", True)
+    assert ref["losses"][:3] == pytest.approx(four["losses"], rel=5e-4, abs=5e-4)
+    # three steps in the product layout, the fourth under tp 2 x fsdp 2 with the experts identical over tp ...
+    resumed = run(4, 2, "e.pt", ep_size=1, ckpt=str(tmp_path / "ck4"), resume=True, steps=1)
+    assert not resumed["ep"][1]
+    assert resumed["losses"][0] == pytest.approx(ref["losses"][3], rel=1e-3, abs=1e-3)
+    # ... and the other way: written without expert parallelism, resumed with one expert per rank
+    run(4, 2, "f.pt", ep_size=1, ckpt=str(tmp_path / "ck2"))
+    back = run(4, 2, "g.pt", ep_size=4, ckpt=str(tmp_path / "ck2"), resume=True, steps=1)
+    assert back["ep"][1] and back["losses"][0] == pytest.approx(ref["losses"][3], rel=1e-3, abs=1e-3)
 
 
 def test_vocab_parallel_head_matches_single_rank(tmp_path):
