@@ -45,6 +45,14 @@ def test_expert_parallel_over_library_all_to_all_matches_single_rank(tmp_path, w
     assert a["grad_norm"] == pytest.approx(b["grad_norm"], rel=1e-3)
     for k in a["params"]:
         torch.testing.assert_close(a["params"][k], b["params"][k], rtol=2e-3, atol=2e-4)
+    if world == 2:     # the Qwen3.5 mixture (shared expert, squared-load loss): one step, before routing flips can amplify
+        _run(1, "qwen3.5-smoke", 1, str(tmp_path / "q1.pt"))
+        _run(2, "qwen3.5-smoke", 1, str(tmp_path / "q2.pt"), None, False, None, "a2a")
+        q1, q2 = torch.load(tmp_path / "q1.pt"), torch.load(tmp_path / "q2.pt")
+        assert q2["ep_kind"] == "a2a" and q1["losses"] == pytest.approx(q2["losses"], rel=1e-5)
+        assert q1["grad_norm"] == pytest.approx(q2["grad_norm"], rel=1e-4)
+        for k in q1["params"]:
+            torch.testing.assert_close(q1["params"][k], q2["params"][k], rtol=0, atol=5e-3)
     if world == 4:     # resume the 4-rank expert-parallel checkpoint on 2 ranks without expert parallelism
         _run(2, "qwen3-smoke-moe", 1, str(tmp_path / "r2.pt"), str(tmp_path / "ck"), True)
         _run(1, "qwen3-smoke-moe", 4, str(tmp_path / "s4.pt"))
