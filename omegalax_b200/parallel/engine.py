@@ -1,7 +1,9 @@
 """Sharded training state: fp32 master weights + AdamW moments sharded over the data ranks
-(ZeRO-3 / FSDP), bf16 compute copies gathered one unit (decoder layer) at a time, full
-rematerialisation of each unit in the backward, gradient reduce-scatter per unit, and a
-fused clip + AdamW + bf16 re-cast over the flat shard.
+(ZeRO-3 / FSDP), bf16 compute copies gathered one unit (decoder layer) at a time,
+rematerialisation of each unit in the backward (whole, or with tagged outputs kept: fixed tag
+lists or as many as the free memory allows), gradient reduce-scatter per unit (inside the
+weight-gradient GEMMs where GPUs map each other's memory), expert tensors that stay with their
+owner under expert parallelism, and a fused clip + AdamW + bf16 re-cast over the flat shard.
 
 One process drives one GPU.  With a single rank every collective degenerates to a no-op
 and the bf16 compute copy is simply the cast of the master buffer.

@@ -2,9 +2,10 @@
 
 Rank r owns experts [r*E/W, (r+1)*E/W).  One MoE layer runs as
 
-    plan      counts per (rank, expert) are all-gathered (E ints per rank); every rank derives
+    plan      every rank stores its per-expert pair counts into all peers' count tables (one small
+              kernel and a device barrier, no host-launched collective); every rank then derives
               the same row layout of every receive buffer: per local expert, the senders'
-              segments in rank order, each expert padded to a multiple of 128 rows
+              segments in rank order, each expert padded to a multiple of PAD rows
     dispatch  each (token, slot) row is written straight into the owner's receive buffer at
               its final row -- router permutation and all-to-all in one kernel (peer stores)
     experts   grouped tcgen05 GEMMs + SwiGLU on the local receive buffer
@@ -15,6 +16,11 @@ The backward uses the same two kernels with the roles swapped (a scaled push for
 a pull for the dispatch, plus a pull that returns the per-pair dot products for the routing
 weight gradient).  Cross-GPU ordering uses the bounded device barrier.  The reference has no
 expert parallelism (it evaluates every expert for every token: omegalax/models/qwen3/model.py:92-104).
+
+``ExpertParallelA2A`` at the end of this file is the same contract on library collectives
+(``all_to_all_single``): the baseline for the kernels above, the fallback without peer memory and
+the form that runs on CPU ranks; it is also the transport when the experts are cut over shard
+group x tensor-parallel group.
 """
 from __future__ import annotations
 
