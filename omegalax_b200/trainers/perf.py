@@ -15,7 +15,9 @@ import torch
 
 TRAINING_FLOP_MULTIPLIER = 3
 
-# Peak dense bf16 TFLOP/s used as the MFU denominator.
+# Peak dense bf16 TFLOP/s used as the MFU denominator.  The two "measured" entries are cuBLAS figures
+# of one particular B200 under its 1000 W cap (best of ten 8192^3 products; four seconds back to
+# back); a ``MEASURED_PEAKS.json`` of the machine at hand replaces them (``measured_peaks()``).
 PEAK_TFLOPS: dict[str, float] = {
     "b200": 2250.0,
     "b200_measured_burst": 1613.6,
@@ -27,6 +29,33 @@ PEAK_TFLOPS: dict[str, float] = {
     "a100_pcie_80": 312.0,
     "a100_pcie_40": 312.0,
 }
+
+
+def measured_peaks(path: str | None = None) -> dict | None:
+    """Peaks measured on this machine, when a ``MEASURED_PEAKS.json`` (keys ``bf16_tflops``,
+    ``bf16_tflops_sustained``, ``hbm_gbs``) is named by ``path`` / ``OMEGALAX_B200_MEASURED_PEAKS`` or
+    sits in the working directory or next to the package; its GEMM figures replace the
+    ``b200_measured_*`` presets."""
+    import json
+    import os
+
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    for cand in (path, os.environ.get("OMEGALAX_B200_MEASURED_PEAKS"), "MEASURED_PEAKS.json",
+                 os.path.join(here, "MEASURED_PEAKS.json")):
+        if cand and os.path.isfile(cand):
+            try:
+                d = json.load(open(cand))
+            except (OSError, ValueError):
+                continue
+            if "bf16_tflops" in d:
+                PEAK_TFLOPS["b200_measured_burst"] = float(d["bf16_tflops"])
+            if "bf16_tflops_sustained" in d:
+                PEAK_TFLOPS["b200_measured_sustained"] = float(d["bf16_tflops_sustained"])
+            return d
+    return None
+
+
+measured_peaks()
 
 
 def resolve_peak_tflops(spec: str | float | None) -> float | None:

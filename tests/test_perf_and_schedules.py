@@ -174,3 +174,21 @@ def test_gemm_dispatch_heuristics():
     small = K.ag_copy_ctas(32768, 6144, 4096, 50e6)
     big = K.ag_copy_ctas(32768, 3072, 4096, 268e6)
     assert small % 2 == 0 and big % 2 == 0 and 2 <= small <= big <= 16
+
+
+def test_measured_peaks_file_replaces_the_presets(tmp_path, monkeypatch):
+    import json
+
+    from omegalax_b200.trainers import perf
+
+    before = dict(perf.PEAK_TFLOPS)
+    f = tmp_path / "peaks.json"
+    f.write_text(json.dumps({"bf16_tflops": 1500.5, "bf16_tflops_sustained": 1300.25, "hbm_gbs": 6000.0}))
+    try:
+        d = perf.measured_peaks(str(f))
+        assert d["hbm_gbs"] == 6000.0
+        assert perf.resolve_peak_tflops("b200_measured_burst") == 1500.5
+        assert perf.resolve_peak_tflops("b200_measured_sustained") == 1300.25
+        assert perf.resolve_peak_tflops("b200") == 2250.0 and perf.resolve_peak_tflops(123.0) == 123.0
+    finally:
+        perf.PEAK_TFLOPS.update(before)
